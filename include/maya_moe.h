@@ -1,0 +1,203 @@
+/*
+ * maya_moe.h - C ABI of the B200 (sm_100a) routed-MoE expert-FFN library.
+ *
+ * One entry point per reference entry point of the path: router -> q8_1 activations -> quantized
+ * GEMV (decode) / grouped GEMM (prefill) over unmodified GGUF expert blocks -> weighted combine ->
+ * cross-GPU sum.  Plain pointers and sizes only.  Unless a function says otherwise:
+ *   - every pointer is a device pointer of the current device; the caller owns all memory, the callee
+ *     allocates nothing, never synchronises and enqueues on `stream` (a cudaStream_t; NULL = default
+ *     stream, still asynchronous);
+ *   - the return value is a status: 0 = enqueued, < 0 = refused (nothing launched), see maya_status;
+ *   - ggml type ids: Q8_0 = 8, Q4_K = 12, IQ3_S = 21, IQ2_S = 22;
+ *   - weights are unmodified row-major GGUF blocks; expert blob = [gate rows | up rows | down rows];
+ *   - blobs, rows and q8_1 buffers must be 16-byte aligned (cudaMalloc gives 256).
+ *
+ * Each declaration cites the reference interface it replaces (path inside the reference tree : line).
+ */
+#ifndef MAYA_MOE_H
+#define MAYA_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MAYA_API __attribute__((visibility("default")))
+
+enum maya_status {
+    MAYA_OK = 0,
+    MAYA_ERR_ARG = -1,         /* bad size / null pointer / misalignment */
+    MAYA_ERR_TYPE = -2,        /* ggml type without a kernel here */
+    MAYA_ERR_LAUNCH = -3,      /* the CUDA launch failed (see maya_last_cuda_error) */
+    MAYA_ERR_LIMIT = -4,       /* beyond a documented maximum (k, tokens, experts, scratch) */
+    MAYA_ERR_DEVICE = -5       /* not an sm_100 device / no CUDA device */
+};
+
+enum maya_ggml_type { MAYA_Q8_0 = 8, MAYA_Q4_K = 12, MAYA_IQ3_S = 21, MAYA_IQ2_S = 22 };
+
+#define MAYA_MAX_K 8            /* plan entries per token (glm_fast.hpp:341) */
+#define MAYA_MAX_WIN_TOKENS 16  /* tokens of a window (glm_fast.hpp:459) */
+#define MAYA_MAX_COLS 8         /* activation columns of maya_mmvq (native_mmvq.cu:783) */
+
+/* Library / device -------------------------------------------------------------------------------- */
+MAYA_API const char* maya_version(void);
+/* cudaError_t of the last failed launch on this thread, as an int (0 = none). */
+MAYA_API int maya_last_cuda_error(void);
+/* Launches refused or failed since load (glmf::launch_errors, glm_fast.cu:5803; mmq::launch_errors, moe_mmq.hpp:99). */
+MAYA_API int maya_launch_errors(void);
+/* 0 when the current device is sm_100; MAYA_ERR_DEVICE otherwise. */
+MAYA_API int maya_device_ok(void);
+
+/* Formats ----------------------------------------------------------------------------------------- */
+/* native_mmvq_supported (native_mmvq.hpp:105) / iq_supported (iq_kernels.hpp:17). */
+MAYA_API int maya_type_supported(int ggml_type);
+/* iq_row_bytes (iq_kernels.hpp:19): bytes of one row of n values; 0 for a bad type or n. */
+MAYA_API size_t maya_row_bytes(int ggml_type, int64_t n);
+/* native_mmvq_weight_bytes (native_mmvq.hpp:106). */
+MAYA_API size_t maya_weight_bytes(int ggml_type, int n_in, int n_out);
+/* native_q8_1_bytes (native_mmvq.hpp:30): 36 bytes per 32 values, no row padding. */
+MAYA_API size_t maya_q8_1_bytes(int n_in, int ncols);
+
+/* NativeExpertLayout / native_expert_layout (iq_kernels.hpp:63-77). */
+typedef struct maya_expert_layout {
+    int gu_type, d_type;
+    int64_t n_embd, n_ff;
+    size_t gu_row, d_row;      /* bytes per row */
+    size_t up_off, down_off;   /* byte offsets inside the blob */
+    size_t bytes;              /* the whole blob */
+    int u_type;                /* the up rows' type (gu_type unless mixed) */
+    size_t u_row;
+} maya_expert_layout;
+MAYA_API int maya_expert_layout_make(int gu_type, int up_type, int d_type, int64_t n_embd, int64_t n_ff,
+                                     maya_expert_layout* out);
+
+/* Router ------------------------------------------------------------------------------------------ */
+/* router_top10 (router_top10.hpp:17): softmax over all experts (exp and sum in double), stable descending
+ * top-k (ties -> lower index), weights renormalised by max(sum, 2^-14).  logits [n_tokens, n_expert] f32;
+ * ids [n_tokens, k] i32; weights [n_tokens, k] f32.  k <= 64, n_expert <= 2048.  n_tokens <= 0: no-op, 0. */
+MAYA_API int maya_router_top10(const float* logits, int n_tokens, int n_expert, int k, int* ids, float* weights,
+                               void* stream);
+/* router_sigmoid (router_sigmoid.hpp:27) / glmb::route (glm_batch.hpp:131): p = sigmoid(logit); selection on
+ * p + bias (bias NULL: none); weights from the unbiased p, divided by max(sum, 2^-14) when norm_w, times w_scale. */
+MAYA_API int maya_router_sigmoid(const float* logits, const float* bias, int n_tokens, int n_expert, int k,
+                                 float w_scale, int norm_w, int* ids, float* weights, void* stream);
+
+/* Activations ------------------------------------------------------------------------------------- */
+/* native_quantize_q8_1 (native_mmvq.hpp:38) / quantize_q8_1_rows (iq_kernels.hpp:21): x [ncols, n_in] f32 ->
+ * ncols * n_in/32 q8_1 blocks {f16 d, f16 sum(x), i8 q[32]}.  n_in % 32 == 0. */
+MAYA_API int maya_quantize_q8_1(const float* x, void* x_q8_1, int n_in, int ncols, void* stream);
+/* The same from bf16 activations (raw bf16 bits); each value is widened to f32 exactly first. */
+MAYA_API int maya_quantize_q8_1_bf16(const uint16_t* x, void* x_q8_1, int n_in, int ncols, void* stream);
+
+/* glmf::swiglu_q8 (glm_fast.hpp:280): h = clamped SwiGLU(gate, up) (limit; INFINITY = plain silu(g) * u), written
+ * as n/32 q8_1 blocks.  n % 32 == 0.  The shared expert's h is made with this. */
+MAYA_API int maya_swiglu_q8_1(const float* gate, const float* up, float limit, int64_t n, void* hq, void* stream);
+
+/* Quantized GEMV ---------------------------------------------------------------------------------- */
+/* native_mmvq (native_mmvq.hpp:109) / iq_mmvq (iq_kernels.hpp:24): y[c * n_out + r] = W_r . x_c, ncols in 1..8;
+ * column c's q8_1 blocks at x_q8_1 + c * n_in/32 blocks.  Every column equals its single-column result bit for bit. */
+MAYA_API int maya_mmvq(int ggml_type, const void* weights, const void* x_q8_1, float* y, int n_in, int n_out,
+                       int ncols, void* stream);
+
+/* Decode experts (plan form) ---------------------------------------------------------------------- */
+/* The part of MoeDev the expert kernels read (glm_fast.hpp:293-300): k blob addresses (0 = entry skipped),
+ * k router weights, optional CPU-lane partial and flag, optional skip flag (non-zero = do nothing). */
+typedef struct maya_moe_plan {
+    const unsigned long long* plan_ptr;  /* [k] device addresses of expert blobs */
+    const float* plan_w;                 /* [k] */
+    const float* cpu_part;               /* [n_embd] or NULL */
+    const int* cpu_flag;                 /* [1] or NULL */
+    const int* skip;                     /* [1] or NULL */
+} maya_moe_plan;
+
+/* glmf::moe_gate_up (glm_fast.hpp:496-498): for each plan entry i < k: rows of gate and up over xq, clamped
+ * SwiGLU (limit; INFINITY = unclamped), q8_1 of h into hq[i * n_ff/32 ..].  When sh_down != NULL the same launch
+ * computes the shared expert's down rows over sh_hq (n_ff_sh values, type sh_type) into sh_out[n_embd]. */
+MAYA_API int maya_moe_gate_up(int gu_type, const maya_moe_plan* plan, int k, int n_embd, int n_ff, float limit,
+                              const void* xq, void* hq, const void* sh_down, int sh_type, const void* sh_hq,
+                              int n_ff_sh, float* sh_out, void* stream);
+/* glmf::moe_down (glm_fast.hpp:499-501): out[r] = sum_i w_i * (down_i[r] . hq_i) in plan order (+ cpu_part[r] when
+ * *cpu_flag) + sh_out[r] (when given).  down_off = byte offset of the down rows inside a blob. */
+MAYA_API int maya_moe_down(int d_type, const maya_moe_plan* plan, int k, int n_embd, int n_ff, size_t down_off,
+                           const void* hq, const float* sh_out, float* out, void* stream);
+
+/* glmf::MoeWin / moe_win_experts (glm_fast.hpp:439-465): T <= 16 tokens, each distinct expert's rows read once for all
+ * the tokens that routed it; every token's output equals maya_moe_gate_up + maya_moe_down for it alone, bit for bit. */
+typedef struct maya_moe_win {
+    const unsigned long long* plan_ptr;  /* [T][8] */
+    const float* plan_w;                 /* [T][8] */
+    const float* cpu_part;               /* [T][n_embd] or NULL */
+    const int* cpu_flag;                 /* [T] or NULL */
+    const void* xq;                      /* the tokens' q8_1 inputs, xq_stride bytes apart */
+    size_t xq_stride;
+    void* hq;                            /* scratch: [T * 8][n_ff / 32] q8_1 */
+    float* part;                         /* scratch: [T * 8][n_embd] */
+    const float* sh_out;                 /* [T][n_embd] or NULL */
+    float* out;                          /* [T][n_embd], out_stride floats apart */
+    size_t out_stride;
+    unsigned long long* grp_ptr;         /* scratch: [T * 8] */
+    int* grp_start;                      /* scratch: [T * 8 + 1] */
+    int* grp_ent;                        /* scratch: [T * 8] */
+    int* n_groups;                       /* scratch: [1] */
+    int T, k, n_embd, n_ff;
+    float limit;
+    size_t down_off;
+} maya_moe_win;
+MAYA_API int maya_moe_win_experts(int gu_type, int d_type, const maya_moe_win* w, void* stream);
+/* glmf::moe_win_group (glm_fast.hpp:468): the grouping alone. */
+MAYA_API int maya_moe_win_group(const maya_moe_win* w, void* stream);
+
+/* Grouped experts (native form) ------------------------------------------------------------------- */
+/* native_expert_scratch_bytes (iq_kernels.hpp:80). */
+MAYA_API size_t maya_expert_scratch_bytes(int64_t cap_entries, int64_t n_ff);
+/* native_expert_grouped (iq_kernels.hpp:89-92): group g's blob at grp_ptr[g]; its entries
+ * [grp_start[g], grp_start[g+1]) read token ent_tok[e]'s q8_1 activation and write row ent_dst[e] of out
+ * (n_embd floats, unweighted).  *n_groups is read on the device. */
+MAYA_API int maya_expert_grouped(const maya_expert_layout* L, const unsigned long long* grp_ptr,
+                                 const int32_t* grp_start, const int32_t* n_groups, const int32_t* ent_dst,
+                                 const int32_t* ent_tok, int64_t cap_groups, int64_t cap_entries, const void* x_q8_1,
+                                 void* scratch, float* out, void* stream, float swiglu_limit);
+
+/* Combine ----------------------------------------------------------------------------------------- */
+/* native_moe_combine[_multi] (native_moe.hpp:16-20) / moe_combine (shared_expert.hpp:98): per token
+ * y = parts[0] * w[0], then fused multiply-adds in expert order, + shared (NULL: none).  parts [n_tok][k][n_embd]. */
+MAYA_API int maya_moe_combine(const float* parts, const float* weights, const float* shared, float* y,
+                              int64_t n_embd, int64_t k, int n_tok, void* stream);
+
+/* Whole decode layer, one call (no single counterpart: the sequence Glm5Model::fast_moe runs,
+ * src/core/glm_fast_path.cu:6917-7100: route -> gate/up -> down + combine, the shared expert alongside). */
+typedef struct maya_moe_layer {
+    int n_embd, n_ff, n_expert, k;
+    int gu_type, d_type;
+    const void* experts;         /* n_expert blobs, expert_stride bytes apart */
+    size_t expert_stride;
+    int n_ff_sh;                 /* 0: no shared expert */
+    int sh_gu_type, sh_d_type;
+    const void* shared;          /* the shared expert's blob [gate | up | down] */
+    float limit;                 /* SwiGLU clamp; INFINITY = none */
+    int expert_lo, expert_hi;    /* this rank's experts [lo, hi); others contribute nothing (expert-parallel) */
+    int shared_here;             /* non-zero: this rank adds the shared expert */
+} maya_moe_layer;
+/* Bytes of scratch maya_moe_layer_decode needs for n_tokens tokens. */
+MAYA_API size_t maya_moe_layer_scratch_bytes(const maya_moe_layer* L, int n_tokens);
+/* logits [n_tokens, n_expert] f32; x [n_tokens, n_embd] f32 (x_is_bf16 == 0) or bf16 bits; out [n_tokens, n_embd] f32;
+ * ids / weights [n_tokens, k] (outputs, may be NULL... then scratch holds them).  n_tokens <= MAYA_MAX_WIN_TOKENS. */
+MAYA_API int maya_moe_layer_decode(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
+                                   int n_tokens, int* ids, float* weights, float* out, void* scratch,
+                                   size_t scratch_bytes, void* stream);
+
+/* Synthetic expert weights (bench / test support; host-callable generators) ------------------------ */
+/* Quantize rows of f32 weights to a GGUF type (own quantizers: nearest-codeword search for the i-quants).
+ * Host memory in, host memory out.  n_cols a multiple of the block size. */
+MAYA_API int maya_quantize_weights_host(int ggml_type, const float* w, int64_t n_rows, int64_t n_cols, void* out);
+/* The same on the device, the weights drawn N(0, sigma) from a counter-based generator keyed by (seed, index):
+ * fills n_rows * n_cols values' worth of blocks at `out` (device). */
+MAYA_API int maya_synth_weights(int ggml_type, uint64_t seed, float sigma, int64_t n_rows, int64_t n_cols, void* out,
+                                void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MAYA_MOE_H */

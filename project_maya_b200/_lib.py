@@ -1,0 +1,95 @@
+"""Loader of the C-ABI library (libmaya_moe.so) and its ctypes signatures.
+
+There is no fallback: if the library has not been built, importing the compute entry points raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "libmaya_moe.so"
+
+c_void_p, c_int, c_float, c_size_t, c_int64, c_uint64 = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_int64, C.c_uint64
+
+
+class ExpertLayout(C.Structure):
+    _fields_ = [("gu_type", c_int), ("d_type", c_int), ("n_embd", c_int64), ("n_ff", c_int64),
+                ("gu_row", c_size_t), ("d_row", c_size_t), ("up_off", c_size_t), ("down_off", c_size_t),
+                ("bytes", c_size_t), ("u_type", c_int), ("u_row", c_size_t)]
+
+
+class MoePlan(C.Structure):
+    _fields_ = [("plan_ptr", c_void_p), ("plan_w", c_void_p), ("cpu_part", c_void_p), ("cpu_flag", c_void_p),
+                ("skip", c_void_p)]
+
+
+class MoeWin(C.Structure):
+    _fields_ = [("plan_ptr", c_void_p), ("plan_w", c_void_p), ("cpu_part", c_void_p), ("cpu_flag", c_void_p),
+                ("xq", c_void_p), ("xq_stride", c_size_t), ("hq", c_void_p), ("part", c_void_p), ("sh_out", c_void_p),
+                ("out", c_void_p), ("out_stride", c_size_t), ("grp_ptr", c_void_p), ("grp_start", c_void_p),
+                ("grp_ent", c_void_p), ("n_groups", c_void_p), ("T", c_int), ("k", c_int), ("n_embd", c_int),
+                ("n_ff", c_int), ("limit", c_float), ("down_off", c_size_t)]
+
+
+class MoeLayerDesc(C.Structure):
+    _fields_ = [("n_embd", c_int), ("n_ff", c_int), ("n_expert", c_int), ("k", c_int), ("gu_type", c_int),
+                ("d_type", c_int), ("experts", c_void_p), ("expert_stride", c_size_t), ("n_ff_sh", c_int),
+                ("sh_gu_type", c_int), ("sh_d_type", c_int), ("shared", c_void_p), ("limit", c_float),
+                ("expert_lo", c_int), ("expert_hi", c_int), ("shared_here", c_int)]
+
+
+_SIGNATURES = {
+    "maya_version": (C.c_char_p, []),
+    "maya_last_cuda_error": (c_int, []),
+    "maya_launch_errors": (c_int, []),
+    "maya_device_ok": (c_int, []),
+    "maya_type_supported": (c_int, [c_int]),
+    "maya_row_bytes": (c_size_t, [c_int, c_int64]),
+    "maya_weight_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "maya_q8_1_bytes": (c_size_t, [c_int, c_int]),
+    "maya_expert_layout_make": (c_int, [c_int, c_int, c_int, c_int64, c_int64, C.POINTER(ExpertLayout)]),
+    "maya_router_top10": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "maya_router_sigmoid": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]),
+    "maya_quantize_q8_1": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "maya_quantize_q8_1_bf16": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "maya_swiglu_q8_1": (c_int, [c_void_p, c_void_p, c_float, c_int64, c_void_p, c_void_p]),
+    "maya_mmvq": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "maya_moe_gate_up": (c_int, [c_int, C.POINTER(MoePlan), c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p,
+                                 c_int, c_void_p, c_int, c_void_p, c_void_p]),
+    "maya_moe_down": (c_int, [c_int, C.POINTER(MoePlan), c_int, c_int, c_int, c_size_t, c_void_p, c_void_p, c_void_p,
+                              c_void_p]),
+    "maya_moe_win_experts": (c_int, [c_int, c_int, C.POINTER(MoeWin), c_void_p]),
+    "maya_moe_win_group": (c_int, [C.POINTER(MoeWin), c_void_p]),
+    "maya_expert_scratch_bytes": (c_size_t, [c_int64, c_int64]),
+    "maya_expert_grouped": (c_int, [C.POINTER(ExpertLayout), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                    c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_float]),
+    "maya_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
+    "maya_moe_layer_scratch_bytes": (c_size_t, [C.POINTER(MoeLayerDesc), c_int]),
+    "maya_moe_layer_decode": (c_int, [C.POINTER(MoeLayerDesc), c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_size_t, c_void_p]),
+    "maya_quantize_weights_host": (c_int, [c_int, c_void_p, c_int64, c_int64, c_void_p]),
+    "maya_synth_weights": (c_int, [c_int, c_uint64, c_float, c_int64, c_int64, c_void_p, c_void_p]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """The loaded library; raises if it has not been built (python -m project_maya_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m project_maya_b200.build` "
+                               "(there is no CPU or PyTorch fallback for this path)")
+        lib = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def declared_symbols() -> list[str]:
+    return sorted(_SIGNATURES)

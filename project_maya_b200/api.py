@@ -1,0 +1,239 @@
+"""Host-side mirror of the reference's per-layer expert-FFN entry points, over the C ABI (include/maya_moe.h).
+
+Names, argument meaning and error behaviour follow the reference's C++ free functions (namespace strata::kernels,
+strata::kernels::glmf): device buffers in, device buffers out, an explicit stream, nothing allocated by the callee.
+torch is used only for device memory and streams: every function takes torch CUDA tensors (or raw integer device
+addresses) and launches this library's own CUDA kernels.  A negative status raises MayaError, as the reference's
+`native_*` family throws std::invalid_argument / std::runtime_error (native_mmvq.cu:1080-1099).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import ExpertLayout, MoeLayerDesc, MoePlan, MoeWin
+
+Q8_0, Q4_K, IQ3_S, IQ2_S = 8, 12, 21, 22
+TYPE_NAMES = {Q8_0: "Q8_0", Q4_K: "Q4_K", IQ3_S: "IQ3_S", IQ2_S: "IQ2_S"}
+STATUS = {0: "ok", -1: "bad argument", -2: "unsupported ggml type", -3: "CUDA launch failed", -4: "beyond a limit",
+          -5: "no sm_100 device"}
+INF = float("inf")
+
+
+class MayaError(RuntimeError):
+    def __init__(self, what: str, status: int):
+        super().__init__(f"{what}: {STATUS.get(status, status)} (status {status})")
+        self.status = status
+
+
+def _check(what: str, status: int) -> None:
+    if status != 0:
+        raise MayaError(what, status)
+
+
+def _ptr(t) -> int | None:
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    assert t.is_cuda and t.is_contiguous(), "device-contiguous tensor expected"
+    return t.data_ptr()
+
+
+def _stream(stream=None) -> int:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return s.cuda_stream if hasattr(s, "cuda_stream") else int(s)
+
+
+# ---------------------------------------------------------------- formats (host only: usable without a GPU)
+def row_bytes(ggml_type: int, n: int) -> int:
+    return int(_lib.load().maya_row_bytes(ggml_type, n))
+
+
+def q8_1_bytes(n_in: int, ncols: int = 1) -> int:
+    return int(_lib.load().maya_q8_1_bytes(n_in, ncols))
+
+
+def native_expert_layout(gu_type: int, d_type: int, n_embd: int, n_ff: int, up_type: int | None = None) -> ExpertLayout:
+    L = ExpertLayout()
+    _check("native_expert_layout", _lib.load().maya_expert_layout_make(gu_type, gu_type if up_type is None else up_type,
+                                                                       d_type, n_embd, n_ff, C.byref(L)))
+    return L
+
+
+def quantize_weights_host(ggml_type: int, w) -> "torch.Tensor":
+    """Host f32 rows [n_rows, n_cols] -> uint8 [n_rows, row_bytes] of GGUF blocks (this library's own quantizers)."""
+    w = torch.as_tensor(w, dtype=torch.float32).contiguous().cpu()
+    n_rows, n_cols = w.shape
+    out = torch.empty((n_rows, row_bytes(ggml_type, n_cols)), dtype=torch.uint8)
+    _check("quantize_weights_host",
+           _lib.load().maya_quantize_weights_host(ggml_type, w.data_ptr(), n_rows, n_cols, out.data_ptr()))
+    return out
+
+
+def synth_weights(ggml_type: int, seed: int, sigma: float, n_rows: int, n_cols: int, out=None, stream=None):
+    """Device: n_rows x n_cols N(0, sigma) weights quantized to ggml_type, written as blocks into `out` (uint8)."""
+    nbytes = n_rows * row_bytes(ggml_type, n_cols)
+    if out is None:
+        out = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    _check("synth_weights", _lib.load().maya_synth_weights(ggml_type, seed, sigma, n_rows, n_cols, _ptr(out), _stream(stream)))
+    return out
+
+
+# ---------------------------------------------------------------- router
+def router_top10(logits, k: int, ids=None, weights=None, stream=None):
+    """router_top10 (router_top10.hpp:17).  logits [n_tokens, n_expert] f32 -> ids i32, weights f32 [n_tokens, k]."""
+    T, E = logits.shape
+    ids = ids if ids is not None else torch.empty((T, k), dtype=torch.int32, device=logits.device)
+    weights = weights if weights is not None else torch.empty((T, k), dtype=torch.float32, device=logits.device)
+    _check("router_top10", _lib.load().maya_router_top10(_ptr(logits), T, E, k, _ptr(ids), _ptr(weights), _stream(stream)))
+    return ids, weights
+
+
+def router_sigmoid(logits, bias, k: int, w_scale: float = 1.0, norm_w: bool = True, stream=None):
+    T, E = logits.shape
+    ids = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+    _check("router_sigmoid", _lib.load().maya_router_sigmoid(_ptr(logits), _ptr(bias), T, E, k, w_scale, int(norm_w),
+                                                             _ptr(ids), _ptr(weights), _stream(stream)))
+    return ids, weights
+
+
+# ---------------------------------------------------------------- activations
+def native_quantize_q8_1(x, out=None, stream=None):
+    """native_quantize_q8_1 (native_mmvq.hpp:38).  x [ncols, n_in] f32 or bf16 -> uint8 [ncols, n_in/32*36]."""
+    x2 = x.reshape(-1, x.shape[-1])
+    ncols, n_in = x2.shape
+    out = out if out is not None else torch.empty((ncols, n_in // 32 * 36), dtype=torch.uint8, device=x.device)
+    lib = _lib.load()
+    if x.dtype == torch.bfloat16:
+        _check("quantize_q8_1", lib.maya_quantize_q8_1_bf16(_ptr(x2), _ptr(out), n_in, ncols, _stream(stream)))
+    else:
+        assert x.dtype == torch.float32
+        _check("quantize_q8_1", lib.maya_quantize_q8_1(_ptr(x2), _ptr(out), n_in, ncols, _stream(stream)))
+    return out
+
+
+def swiglu_q8_1(gate, up, limit: float = INF, out=None, stream=None):
+    n = gate.numel()
+    out = out if out is not None else torch.empty(n // 32 * 36, dtype=torch.uint8, device=gate.device)
+    _check("swiglu_q8_1", _lib.load().maya_swiglu_q8_1(_ptr(gate), _ptr(up), limit, n, _ptr(out), _stream(stream)))
+    return out
+
+
+# ---------------------------------------------------------------- GEMV
+def native_mmvq(ggml_type: int, weights, x_q8_1, n_in: int, n_out: int, ncols: int = 1, y=None, stream=None):
+    """native_mmvq (native_mmvq.hpp:109) / iq_mmvq (iq_kernels.hpp:24): y [ncols, n_out] f32."""
+    y = y if y is not None else torch.empty((ncols, n_out), dtype=torch.float32, device="cuda")
+    _check("native_mmvq", _lib.load().maya_mmvq(ggml_type, _ptr(weights), _ptr(x_q8_1), _ptr(y), n_in, n_out, ncols,
+                                               _stream(stream)))
+    return y
+
+
+# ---------------------------------------------------------------- decode experts
+def make_plan(plan_ptr, plan_w, cpu_part=None, cpu_flag=None, skip=None) -> MoePlan:
+    return MoePlan(_ptr(plan_ptr), _ptr(plan_w), _ptr(cpu_part), _ptr(cpu_flag), _ptr(skip))
+
+
+def moe_gate_up(gu_type: int, plan: MoePlan, k: int, n_embd: int, n_ff: int, limit: float, xq, hq, sh_down=None,
+                sh_type: int = 0, sh_hq=None, n_ff_sh: int = 0, sh_out=None, stream=None) -> None:
+    """glmf::moe_gate_up (glm_fast.hpp:496)."""
+    _check("moe_gate_up", _lib.load().maya_moe_gate_up(gu_type, C.byref(plan), k, n_embd, n_ff, limit, _ptr(xq), _ptr(hq),
+                                                      _ptr(sh_down), sh_type, _ptr(sh_hq), n_ff_sh, _ptr(sh_out),
+                                                      _stream(stream)))
+
+
+def moe_down(d_type: int, plan: MoePlan, k: int, n_embd: int, n_ff: int, down_off: int, hq, sh_out, out, stream=None) -> None:
+    """glmf::moe_down (glm_fast.hpp:499)."""
+    _check("moe_down", _lib.load().maya_moe_down(d_type, C.byref(plan), k, n_embd, n_ff, down_off, _ptr(hq), _ptr(sh_out),
+                                                _ptr(out), _stream(stream)))
+
+
+def moe_win_experts(gu_type: int, d_type: int, win: MoeWin, stream=None) -> None:
+    """glmf::moe_win_experts (glm_fast.hpp:465)."""
+    _check("moe_win_experts", _lib.load().maya_moe_win_experts(gu_type, d_type, C.byref(win), _stream(stream)))
+
+
+def native_expert_scratch_bytes(cap_entries: int, n_ff: int) -> int:
+    return int(_lib.load().maya_expert_scratch_bytes(cap_entries, n_ff))
+
+
+def native_expert_grouped(L: ExpertLayout, grp_ptr, grp_start, n_groups, ent_dst, ent_tok, cap_groups: int,
+                          cap_entries: int, x_q8_1, scratch, out, swiglu_limit: float = INF, stream=None) -> None:
+    """native_expert_grouped (iq_kernels.hpp:89)."""
+    _check("native_expert_grouped",
+           _lib.load().maya_expert_grouped(C.byref(L), _ptr(grp_ptr), _ptr(grp_start), _ptr(n_groups), _ptr(ent_dst),
+                                           _ptr(ent_tok), cap_groups, cap_entries, _ptr(x_q8_1), _ptr(scratch), _ptr(out),
+                                           _stream(stream), swiglu_limit))
+
+
+def moe_combine(parts, weights, shared, n_embd: int, k: int, n_tok: int = 1, y=None, stream=None):
+    """native_moe_combine[_multi] (native_moe.hpp:16-20) / moe_combine (shared_expert.hpp:98)."""
+    y = y if y is not None else torch.empty((n_tok, n_embd), dtype=torch.float32, device="cuda")
+    _check("moe_combine", _lib.load().maya_moe_combine(_ptr(parts), _ptr(weights), _ptr(shared), _ptr(y), n_embd, k, n_tok,
+                                                      _stream(stream)))
+    return y
+
+
+# ---------------------------------------------------------------- whole layer
+@dataclass
+class MoeLayerConfig:
+    n_embd: int
+    n_ff: int
+    n_expert: int
+    k: int
+    gu_type: int
+    d_type: int
+    n_ff_sh: int = 0
+    sh_gu_type: int = Q8_0
+    sh_d_type: int = Q8_0
+    limit: float = INF
+
+    @property
+    def blob_bytes(self) -> int:
+        return 2 * self.n_ff * row_bytes(self.gu_type, self.n_embd) + self.n_embd * row_bytes(self.d_type, self.n_ff)
+
+    @property
+    def shared_bytes(self) -> int:
+        if not self.n_ff_sh:
+            return 0
+        return 2 * self.n_ff_sh * row_bytes(self.sh_gu_type, self.n_embd) + self.n_embd * row_bytes(self.sh_d_type, self.n_ff_sh)
+
+
+class MoeLayer:
+    """One resident MoE layer: `experts` uint8 [n_expert, blob_bytes] on the device, optional `shared` blob.
+
+    forward(logits, x) runs route -> experts -> combine for up to 16 tokens and returns (ids, weights, out).
+    expert_range = (lo, hi) restricts this rank to experts lo..hi-1 (expert-parallel partition); the others' terms are
+    left out of `out` (another rank adds them)."""
+
+    def __init__(self, cfg: MoeLayerConfig, experts, shared=None, expert_range=None, shared_here=True, max_tokens: int = 16):
+        self.cfg = cfg
+        self.experts = experts
+        self.shared = shared
+        lo, hi = expert_range if expert_range is not None else (0, cfg.n_expert)
+        self.desc = MoeLayerDesc(cfg.n_embd, cfg.n_ff, cfg.n_expert, cfg.k, cfg.gu_type, cfg.d_type, _ptr(experts),
+                                 cfg.blob_bytes, cfg.n_ff_sh if shared is not None else 0, cfg.sh_gu_type,
+                                 cfg.sh_d_type, _ptr(shared), cfg.limit, lo, hi, int(bool(shared_here)))
+        self.max_tokens = max_tokens
+        nbytes = int(_lib.load().maya_moe_layer_scratch_bytes(C.byref(self.desc), max_tokens))
+        if nbytes == 0:
+            raise MayaError("moe_layer_scratch_bytes", -1)
+        self.scratch = torch.empty(nbytes, dtype=torch.uint8, device=experts.device)
+
+    def forward(self, logits, x, ids=None, weights=None, out=None, stream=None):
+        T = logits.shape[0]
+        dev = logits.device
+        ids = ids if ids is not None else torch.empty((T, self.cfg.k), dtype=torch.int32, device=dev)
+        weights = weights if weights is not None else torch.empty((T, self.cfg.k), dtype=torch.float32, device=dev)
+        out = out if out is not None else torch.empty((T, self.cfg.n_embd), dtype=torch.float32, device=dev)
+        assert x.dtype in (torch.float32, torch.bfloat16)
+        _check("moe_layer_decode",
+               _lib.load().maya_moe_layer_decode(C.byref(self.desc), _ptr(logits), _ptr(x), int(x.dtype == torch.bfloat16), T,
+                                                 _ptr(ids), _ptr(weights), _ptr(out), _ptr(self.scratch),
+                                                 self.scratch.numel(), _stream(stream)))
+        return ids, weights, out

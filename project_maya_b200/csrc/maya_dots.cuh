@@ -1,0 +1,254 @@
+// maya_dots.cuh - the quantized dot products: GGUF weight blocks (Q8_0, Q4_K, IQ2_S, IQ3_S) against q8_1 activations.
+//
+// Integer semantics follow llama.cpp's vec_dot_*_q8_1 as the reference transcribes them (per 32-value sub-block:
+// exact int8 dot, IQ2_S's (s0*l0 + s1*l1 + (s0+s1)/2)/4 with truncating division, IQ3_S's sum * (1 + 2*scale), Q4_K's
+// scale and min terms with the integer sum of the activation quants), so every 32-value partial is the same integer
+// the reference computes; only the order of the FP32 additions differs.
+//
+// Work split: a "call" is the part of a weight block one lane handles at once.
+//   Q8_0 : 1 call / block  (32 weights, one q8_1 block)
+//   Q4_K : 4 calls / block (64 weights: the low and high nibbles of 32 bytes, two q8_1 blocks)
+//   IQ2_S: 8 calls / block (32 weights, one q8_1 block)
+//   IQ3_S: 8 calls / block (32 weights, one q8_1 block)
+// A call first DECODES the weights into signed int8 words (codebook lookup + sign application), then dots them with
+// one or more activation columns, so several tokens reuse one decode and every column's result is bit-identical to
+// the single-column result.
+#pragma once
+
+#include "maya_common.cuh"
+
+namespace maya {
+
+// ---------------------------------------------------------------- activations in shared memory (structure of arrays)
+// q8_1 columns are re-laid out when staged: the 8 quant words of a block contiguous and 16-byte aligned, the scale as
+// f32, the integer sum of the quants (Q4_K's min term) precomputed once per token instead of once per weight row.
+struct XCols {
+    const int4* q;     // [ncols][nblk][2]
+    const float* d;    // [ncols][nblk]
+    const int* isum;   // [ncols][nblk]
+    int nblk;          // q8_1 blocks per column
+};
+__host__ __device__ inline size_t xcols_bytes(int nblk, int ncols) { return (size_t) ncols * nblk * (32 + 4 + 4); }
+
+// Carve the three arrays out of a 16-byte aligned shared buffer.
+__device__ __forceinline__ XCols xcols_carve(uint8_t* smem, int nblk, int ncols, int4** q, float** d, int** isum) {
+    *q = (int4*) smem;
+    *d = (float*) (smem + (size_t) ncols * nblk * 32);
+    *isum = (int*) (smem + (size_t) ncols * nblk * 36);
+    XCols x;
+    x.q = *q; x.d = *d; x.isum = *isum; x.nblk = nblk;
+    return x;
+}
+
+// Stage `ncols` q8_1 columns (col_stride bytes apart in global memory) into the SoA form.  All threads of the block.
+__device__ __forceinline__ void xcols_stage(const uint8_t* xq, size_t col_stride, int nblk, int ncols, int4* q, float* d,
+                                            int* isum) {
+    const int total = nblk * ncols;
+    for (int i = threadIdx.x; i < total * 8; i += blockDim.x) {
+        const int b = i >> 3, w = i & 7, c = b / nblk, kb = b - c * nblk;
+        ((int*) q)[i] = *(const int*) (xq + (size_t) c * col_stride + (size_t) kb * kQ81Bytes + 4 + 4 * w);
+    }
+    for (int b = threadIdx.x; b < total; b += blockDim.x) {
+        const int c = b / nblk, kb = b - c * nblk;
+        const uint8_t* src = xq + (size_t) c * col_stride + (size_t) kb * kQ81Bytes;
+        d[b] = ld_f16(src);
+        int s = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s = __dp4a(*(const int*) (src + 4 + 4 * w), 0x01010101, s);
+        isum[b] = s;
+    }
+}
+
+struct XQ {          // one q8_1 block in registers
+    int u[8];
+    float d;
+    int isum;
+};
+__device__ __forceinline__ XQ xq_load(const XCols& x, int col, int kb) {
+    XQ v;
+    const int b = col * x.nblk + kb;
+    const int4 a = x.q[2 * b], c = x.q[2 * b + 1];
+    v.u[0] = a.x; v.u[1] = a.y; v.u[2] = a.z; v.u[3] = a.w;
+    v.u[4] = c.x; v.u[5] = c.y; v.u[6] = c.z; v.u[7] = c.w;
+    v.d = x.d[b];
+    v.isum = x.isum[b];
+    return v;
+}
+
+// ---------------------------------------------------------------- sign masks
+// Four sign bits (bit i = weight i negative) -> a word whose byte i is 0xFF when bit i is set.  n * 0x10204080 puts
+// bit i at bit 8i+7 (the 16 partial products land on distinct bits, so nothing carries); prmt's sign-replicate mode
+// then smears each byte's top bit over the byte.
+__device__ __forceinline__ uint32_t sign_mask4(uint32_t nibble) {
+    uint32_t m;
+    const uint32_t x = nibble * 0x10204080u;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(m) : "r"(x), "r"(0u), "r"(0xBA98u));
+    return m;
+}
+// Negate the bytes of g selected by mask m (0x00 / 0xFF per byte); g's bytes are in 0..127 so no carry crosses bytes.
+__device__ __forceinline__ int apply_sign4(uint32_t g, uint32_t m) { return (int) ((g ^ m) + (m & 0x01010101u)); }
+
+// ---------------------------------------------------------------- decoded calls
+template<int T> struct Dec;
+
+template<> struct Dec<MAYA_Q8_0> {
+    static constexpr int cpb = 1, xblk = 1;
+    int w[8];
+    float d;
+    __device__ __forceinline__ void load(const uint8_t* blk, int, const uint32_t*) {
+        d = ld_f16(blk);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = (int) ld_u32_a2(blk + 2 + 4 * i);
+    }
+    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
+        const XQ v = xq_load(x, col, xb);
+        int s = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s = __dp4a(w[i], v.u[i], s);
+        return __fmul_rn(__fmul_rn(d, v.d), (float) s);
+    }
+};
+
+template<> struct Dec<MAYA_Q4_K> {
+    static constexpr int cpb = 4, xblk = 2;
+    int lo[8], hi[8];
+    int sc0, sc1, m0, m1;
+    float d, dmin;
+    __device__ __forceinline__ void load(const uint8_t* blk, int j, const uint32_t*) {
+        const uint32_t dm = ld_u32(blk);
+        d = __half2float(__ushort_as_half((uint16_t) (dm & 0xFFFF)));
+        dmin = __half2float(__ushort_as_half((uint16_t) (dm >> 16)));
+        const uint8_t* s12 = blk + 4;
+        // 6-bit scales / mins of sub-blocks 2j and 2j+1 (j < 2: plain 6-bit fields; j >= 2: 4 low bits + 2 high bits)
+        const int a = 2 * j;
+        if (j < 2) {
+            sc0 = s12[a] & 63; m0 = s12[a + 4] & 63;
+            sc1 = s12[a + 1] & 63; m1 = s12[a + 5] & 63;
+        } else {
+            sc0 = (s12[a + 4] & 0x0F) | ((s12[a - 4] >> 6) << 4); m0 = (s12[a + 4] >> 4) | ((s12[a] >> 6) << 4);
+            sc1 = (s12[a + 5] & 0x0F) | ((s12[a - 3] >> 6) << 4); m1 = (s12[a + 5] >> 4) | ((s12[a + 1] >> 6) << 4);
+        }
+        const int4* q = (const int4*) (blk + 16 + 32 * j);
+        const int4 q0 = q[0], q1 = q[1];
+        const int qq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { lo[i] = qq[i] & 0x0F0F0F0F; hi[i] = (qq[i] >> 4) & 0x0F0F0F0F; }
+    }
+    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
+        const XQ a = xq_load(x, col, xb), b = xq_load(x, col, xb + 1);
+        int s0 = 0, s1 = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { s0 = __dp4a(lo[i], a.u[i], s0); s1 = __dp4a(hi[i], b.u[i], s1); }
+        const float sd = __fadd_rn(__fmul_rn(a.d, (float) (s0 * sc0)), __fmul_rn(b.d, (float) (s1 * sc1)));
+        const float sm = __fadd_rn(__fmul_rn(a.d, (float) (a.isum * m0)), __fmul_rn(b.d, (float) (b.isum * m1)));
+        return __fsub_rn(__fmul_rn(d, sd), __fmul_rn(dmin, sm));
+    }
+};
+
+template<> struct Dec<MAYA_IQ2_S> {
+    static constexpr int cpb = 8, xblk = 1;
+    int w[8];
+    int ls0, ls1;
+    float d;
+    __device__ __forceinline__ void load(const uint8_t* blk, int c, const uint32_t* tab) {
+        d = ld_f16(blk);
+        const uint32_t qs = ld_u32_a2(blk + 2 + 4 * c), sg = ld_u32_a2(blk + 34 + 4 * c);
+        const uint32_t qh = blk[66 + c], sc = blk[74 + c];
+        ls0 = (int) (sc & 0x0F);
+        ls1 = (int) (sc >> 4);
+        const uint2* grid = (const uint2*) tab;
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const uint32_t idx = ((qs >> (8 * l)) & 0xFF) | ((qh << (8 - 2 * l)) & 0x300);
+            const uint2 g = grid[idx];
+            const uint32_t s = (sg >> (8 * l)) & 0xFF;
+            w[2 * l] = apply_sign4(g.x, sign_mask4(s & 0x0F));
+            w[2 * l + 1] = apply_sign4(g.y, sign_mask4(s >> 4));
+        }
+    }
+    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
+        const XQ v = xq_load(x, col, xb);
+        int s0 = 0, s1 = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { s0 = __dp4a(w[i], v.u[i], s0); s1 = __dp4a(w[4 + i], v.u[4 + i], s1); }
+        const int sumi = (s0 * ls0 + s1 * ls1 + (s0 + s1) / 2) / 4;
+        return __fmul_rn(__fmul_rn(d, v.d), (float) sumi);
+    }
+};
+
+template<> struct Dec<MAYA_IQ3_S> {
+    static constexpr int cpb = 8, xblk = 1;
+    int w[8];
+    int mul;
+    float d;
+    __device__ __forceinline__ void load(const uint8_t* blk, int c, const uint32_t* tab) {
+        d = ld_f16(blk);
+        const uint32_t q0 = ld_u32_a2(blk + 2 + 8 * c), q1 = ld_u32_a2(blk + 6 + 8 * c);
+        const uint32_t qh = blk[66 + c], sg = ld_u32_a2(blk + 74 + 4 * c);
+        mul = 1 + 2 * (int) ((blk[106 + (c >> 1)] >> (4 * (c & 1))) & 0x0F);
+#pragma unroll
+        for (int l = 0; l < 8; ++l) {
+            const uint32_t qb = ((l < 4 ? q0 : q1) >> (8 * (l & 3))) & 0xFF;
+            const uint32_t idx = qb | (((qh >> l) & 1) << 8);
+            w[l] = apply_sign4(tab[idx], sign_mask4((sg >> (4 * l)) & 0x0F));
+        }
+    }
+    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
+        const XQ v = xq_load(x, col, xb);
+        int s = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s = __dp4a(w[i], v.u[i], s);
+        return __fmul_rn(__fmul_rn(d, v.d), (float) (s * mul));
+    }
+};
+
+// ---------------------------------------------------------------- codebooks
+// One device copy per translation unit (no relocatable device code needed); generated at build time.
+#define MAYA_GRID_QUAL static __device__ const
+#define MAYA_IQ2S_GRID g_iq2s_grid
+#define MAYA_IQ3S_GRID g_iq3s_grid
+#include "generated/maya_iq_grids.inc"
+#undef MAYA_IQ2S_GRID
+#undef MAYA_IQ3S_GRID
+#undef MAYA_GRID_QUAL
+
+template<int T> __device__ __forceinline__ void load_tab(uint32_t* s_tab) {
+    if constexpr (Fmt<T>::tab_words > 0) {
+        const uint32_t* src = T == MAYA_IQ2_S ? (const uint32_t*) g_iq2s_grid : (const uint32_t*) g_iq3s_grid;
+        for (int i = threadIdx.x; i < Fmt<T>::tab_words; i += blockDim.x) s_tab[i] = src[i];
+    }
+}
+
+// ---------------------------------------------------------------- NR rows x NC columns, one warp
+// rows[r]: the row's first block; calls are lane-strided over the row (call c = lane, lane + 32, ...); each lane adds
+// its calls in ascending order (explicitly rounded multiplies and adds, never contracted, so a column's bits do not
+// depend on how many columns the instantiation carries), then the butterfly sum.  out[r][c].
+template<int T, int NR, int NC>
+__device__ __forceinline__ void rows_dot(const uint8_t* const* rows, const XCols& x, int ncols, int n_in, int lane,
+                                         const uint32_t* tab, float (&out)[NR][NC]) {
+    using D = Dec<T>;
+    const int ncalls = (n_in / Fmt<T>::qk) * D::cpb;
+    float acc[NR][NC];
+#pragma unroll
+    for (int r = 0; r < NR; ++r)
+#pragma unroll
+        for (int c = 0; c < NC; ++c) acc[r][c] = 0.0f;
+    for (int k = lane; k < ncalls; k += 32) {
+        const int kb = k / D::cpb, ci = k - kb * D::cpb;
+        const int xb = kb * (Fmt<T>::qk / 32) + ci * D::xblk;
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            D dec;
+            dec.load(rows[r] + (size_t) kb * Fmt<T>::bytes, ci, tab);
+#pragma unroll
+            for (int c = 0; c < NC; ++c)
+                if (c < ncols) acc[r][c] = __fadd_rn(acc[r][c], dec.dot(x, c, xb));
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r)
+#pragma unroll
+        for (int c = 0; c < NC; ++c) out[r][c] = warp_sum(acc[r][c]);
+}
+
+}  // namespace maya

@@ -1,0 +1,181 @@
+// moe_layer.cu - one decode MoE layer in one call: route -> q8_1(x) -> routed gate/up + SwiGLU -> down + combine,
+// the always-on shared expert alongside.  The sequence Glm5Model::fast_moe drives in the reference
+// (src/core/glm_fast_path.cu:6917-7100), without the tier plan: every expert is resident, the plan of a token is the
+// blob addresses of its k routed experts (0 for experts outside [expert_lo, expert_hi): another rank's).
+#include <math.h>
+
+#include "maya_internal.cuh"
+
+namespace maya {
+namespace {
+
+struct Scratch {
+    uint8_t* xq;                 // [T][n_embd/32] q8_1
+    unsigned long long* plan_ptr;  // [T][8]
+    float* plan_w;               // [T][8]
+    int* ids;                    // [T][k]
+    float* weights;              // [T][k]
+    uint8_t* hq;                 // [T*8][n_ff/32] q8_1
+    float* part;                 // [T*8][n_embd]      (T > 1)
+    unsigned long long* grp_ptr; // [T*8]
+    int* grp_start;              // [T*8 + 1]
+    int* grp_ent;                // [T*8]
+    int* n_groups;               // [1]
+    float* sh_gu;                // [T][2 * n_ff_sh]
+    uint8_t* sh_hq;              // [T][n_ff_sh/32] q8_1
+    float* sh_out;               // [T][n_embd]
+    size_t bytes;
+};
+
+size_t align_up(size_t v) { return (v + 255) & ~(size_t) 255; }
+
+Scratch carve(const maya_moe_layer& L, int T, uint8_t* base) {
+    Scratch s{};
+    size_t off = 0;
+    auto take = [&](size_t n) { uint8_t* p = base ? base + off : nullptr; off += align_up(n); return p; };
+    s.xq = take((size_t) T * (L.n_embd / 32) * kQ81Bytes);
+    s.plan_ptr = (unsigned long long*) take((size_t) T * 8 * sizeof(unsigned long long));
+    s.plan_w = (float*) take((size_t) T * 8 * sizeof(float));
+    s.ids = (int*) take((size_t) T * L.k * sizeof(int));
+    s.weights = (float*) take((size_t) T * L.k * sizeof(float));
+    s.hq = take((size_t) T * 8 * (L.n_ff / 32) * kQ81Bytes);
+    s.part = (float*) take(T > 1 ? (size_t) T * 8 * L.n_embd * sizeof(float) : 0);
+    s.grp_ptr = (unsigned long long*) take((size_t) T * 8 * sizeof(unsigned long long));
+    s.grp_start = (int*) take(((size_t) T * 8 + 1) * sizeof(int));
+    s.grp_ent = (int*) take((size_t) T * 8 * sizeof(int));
+    s.n_groups = (int*) take(sizeof(int));
+    if (L.n_ff_sh > 0) {
+        s.sh_gu = (float*) take((size_t) T * 2 * L.n_ff_sh * sizeof(float));
+        s.sh_hq = take((size_t) T * (L.n_ff_sh / 32) * kQ81Bytes);
+        s.sh_out = (float*) take((size_t) T * L.n_embd * sizeof(float));
+    }
+    s.bytes = off;
+    return s;
+}
+
+__global__ void plan_kernel(const int* __restrict__ ids, const float* __restrict__ weights, int T, int k,
+                            const uint8_t* experts, size_t stride, int lo, int hi,
+                            unsigned long long* __restrict__ plan_ptr, float* __restrict__ plan_w) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * 8) return;
+    const int t = i >> 3, j = i & 7;
+    unsigned long long p = 0ull;
+    float w = 0.0f;
+    if (j < k) {
+        const int e = ids[t * k + j];
+        w = weights[t * k + j];
+        if (e >= lo && e < hi) p = (unsigned long long) (experts + (size_t) e * stride);
+    }
+    plan_ptr[i] = p;
+    plan_w[i] = w;
+}
+
+int check_layer(const maya_moe_layer* L) {
+    if (!L || !L->experts) return MAYA_ERR_ARG;
+    if (!type_qk(L->gu_type) || !type_qk(L->d_type)) return MAYA_ERR_TYPE;
+    if (L->k < 1 || L->k > MAYA_MAX_K || L->n_expert < L->k) return MAYA_ERR_LIMIT;
+    if (L->n_embd <= 0 || L->n_ff <= 0 || L->n_embd % type_qk(L->gu_type) || L->n_ff % type_qk(L->d_type) || L->n_ff % 32 ||
+        L->n_embd % 32)
+        return MAYA_ERR_ARG;
+    if (L->n_ff_sh > 0) {
+        if (!L->shared) return MAYA_ERR_ARG;
+        if (!type_qk(L->sh_gu_type) || !type_qk(L->sh_d_type)) return MAYA_ERR_TYPE;
+        if (L->n_embd % type_qk(L->sh_gu_type) || L->n_ff_sh % type_qk(L->sh_d_type) || L->n_ff_sh % 32) return MAYA_ERR_ARG;
+    }
+    if (L->expert_lo < 0 || L->expert_hi > L->n_expert || L->expert_lo > L->expert_hi) return MAYA_ERR_ARG;
+    return MAYA_OK;
+}
+
+}  // namespace
+}  // namespace maya
+
+using namespace maya;
+
+extern "C" size_t maya_moe_layer_scratch_bytes(const maya_moe_layer* L, int n_tokens) {
+    if (check_layer(L) != MAYA_OK || n_tokens < 1 || n_tokens > MAYA_MAX_WIN_TOKENS) return 0;
+    return carve(*L, n_tokens, nullptr).bytes;
+}
+
+extern "C" int maya_moe_layer_decode(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
+                                     int n_tokens, int* ids, float* weights, float* out, void* scratch,
+                                     size_t scratch_bytes, void* stream) {
+    int st = check_layer(L);
+    if (st != MAYA_OK) return refuse(st);
+    if (n_tokens < 1 || n_tokens > MAYA_MAX_WIN_TOKENS) return refuse(MAYA_ERR_LIMIT);
+    if (!logits || !x || !out || !scratch || (((uintptr_t) scratch) & 255u)) return refuse(MAYA_ERR_ARG);
+    const int T = n_tokens;
+    const Scratch S = carve(*L, T, (uint8_t*) scratch);
+    if (S.bytes > scratch_bytes) return refuse(MAYA_ERR_LIMIT);
+    cudaStream_t s = as_stream(stream);
+    int* d_ids = ids ? ids : S.ids;
+    float* d_w = weights ? weights : S.weights;
+
+    st = maya_router_top10(logits, T, L->n_expert, L->k, d_ids, d_w, stream);
+    if (st != MAYA_OK) return st;
+    st = x_is_bf16 ? maya_quantize_q8_1_bf16((const uint16_t*) x, S.xq, L->n_embd, T, stream)
+                   : maya_quantize_q8_1((const float*) x, S.xq, L->n_embd, T, stream);
+    if (st != MAYA_OK) return st;
+    plan_kernel<<<(T * 8 + 127) / 128, 128, 0, s>>>(d_ids, d_w, T, L->k, (const uint8_t*) L->experts, L->expert_stride,
+                                                    L->expert_lo, L->expert_hi, S.plan_ptr, S.plan_w);
+    st = note_launch("moe_plan");
+    if (st != MAYA_OK) return st;
+
+    const bool shared = L->n_ff_sh > 0 && L->shared_here;
+    const uint8_t* sh_blob = (const uint8_t*) L->shared;
+    size_t sh_down_off = 0;
+    if (shared) {
+        sh_down_off = row_bytes(L->sh_gu_type, L->n_embd) * (size_t) L->n_ff_sh * 2;
+        for (int c0 = 0; c0 < T; c0 += MAYA_MAX_COLS) {   // gate and up rows are contiguous: one GEMV of 2 * n_ff_sh rows
+            const int nc = T - c0 < MAYA_MAX_COLS ? T - c0 : MAYA_MAX_COLS;
+            // column-major output [c][2 * n_ff_sh] per call: offset by the columns already done
+            st = maya_mmvq(L->sh_gu_type, sh_blob, S.xq + (size_t) c0 * (L->n_embd / 32) * kQ81Bytes,
+                           S.sh_gu + (size_t) c0 * 2 * L->n_ff_sh, L->n_embd, 2 * L->n_ff_sh, nc, stream);
+            if (st != MAYA_OK) return st;
+        }
+        for (int c = 0; c < T; ++c) {
+            st = maya_swiglu_q8_1(S.sh_gu + (size_t) c * 2 * L->n_ff_sh, S.sh_gu + (size_t) c * 2 * L->n_ff_sh + L->n_ff_sh,
+                                  L->limit, L->n_ff_sh, S.sh_hq + (size_t) c * (L->n_ff_sh / 32) * kQ81Bytes, stream);
+            if (st != MAYA_OK) return st;
+        }
+    }
+
+    const size_t up_off = row_bytes(L->gu_type, L->n_embd) * (size_t) L->n_ff;
+    const size_t down_off = 2 * up_off;
+    if (T == 1) {
+        maya_moe_plan P{S.plan_ptr, S.plan_w, nullptr, nullptr, nullptr};
+        st = maya_moe_gate_up(L->gu_type, &P, L->k, L->n_embd, L->n_ff, L->limit, S.xq, S.hq,
+                              shared ? sh_blob + sh_down_off : nullptr, L->sh_d_type, S.sh_hq, L->n_ff_sh, S.sh_out, stream);
+        if (st != MAYA_OK) return st;
+        return maya_moe_down(L->d_type, &P, L->k, L->n_embd, L->n_ff, down_off, S.hq, shared ? S.sh_out : nullptr, out,
+                             stream);
+    }
+    if (shared) {
+        for (int c0 = 0; c0 < T; c0 += MAYA_MAX_COLS) {
+            const int nc = T - c0 < MAYA_MAX_COLS ? T - c0 : MAYA_MAX_COLS;
+            st = maya_mmvq(L->sh_d_type, sh_blob + sh_down_off, S.sh_hq + (size_t) c0 * (L->n_ff_sh / 32) * kQ81Bytes,
+                           S.sh_out + (size_t) c0 * L->n_embd, L->n_ff_sh, L->n_embd, nc, stream);
+            if (st != MAYA_OK) return st;
+        }
+    }
+    maya_moe_win W{};
+    W.plan_ptr = S.plan_ptr;
+    W.plan_w = S.plan_w;
+    W.xq = S.xq;
+    W.xq_stride = (size_t) (L->n_embd / 32) * kQ81Bytes;
+    W.hq = S.hq;
+    W.part = S.part;
+    W.sh_out = shared ? S.sh_out : nullptr;
+    W.out = out;
+    W.out_stride = (size_t) L->n_embd;
+    W.grp_ptr = S.grp_ptr;
+    W.grp_start = S.grp_start;
+    W.grp_ent = S.grp_ent;
+    W.n_groups = S.n_groups;
+    W.T = T;
+    W.k = L->k;
+    W.n_embd = L->n_embd;
+    W.n_ff = L->n_ff;
+    W.limit = L->limit;
+    W.down_off = down_off;
+    return maya_moe_win_experts(L->gu_type, L->d_type, &W, stream);
+}

@@ -1,0 +1,167 @@
+"""The whole decode layer (route -> experts -> combine, shared expert alongside) through maya_moe_layer_decode, on
+the benchmark configurations: C1 in full against the committed fixtures; C2 / C3 / C5 at their full shapes on
+synthetic device-generated experts, checked against the oracle on the experts each token actually routed, and
+through size-independent properties (window == token by token bit for bit; the expert-parallel partition's partial
+outputs sum to the unpartitioned output)."""
+import hashlib
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+TOL, TIGHT = 1e-2, 2e-4
+
+
+@pytest.fixture(scope="module")
+def T(cuda):
+    import torch
+    return torch
+
+
+@pytest.fixture(scope="module")
+def api(cuda):
+    from project_maya_b200 import api as a
+    return a
+
+
+def dev(T, a, dtype=None):
+    t = T.from_numpy(np.ascontiguousarray(a))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda()
+
+
+def layer_cfg(api, cfg, with_shared=True):
+    return api.MoeLayerConfig(cfg["n_embd"], cfg["n_ff"], cfg["n_expert"], cfg["k"], cfg["gu_type"], cfg["d_type"],
+                              cfg.get("n_ff_sh", 0) if with_shared else 0, cfg.get("sh_gu_type", H.Q8_0),
+                              cfg.get("sh_d_type", H.Q8_0), cfg.get("limit", H.INF))
+
+
+def synth_layer(T, api, cfg, n_expert, seed):
+    """n_expert synthetic experts (N(0, 0.02) quantized on the device) + the shared expert when the config has one."""
+    lc = layer_cfg(api, dict(cfg, n_expert=n_expert))
+    experts = T.empty((n_expert, lc.blob_bytes), dtype=T.uint8, device="cuda")
+    H_, FF = cfg["n_embd"], cfg["n_ff"]
+    gu_bytes = 2 * FF * H.row_bytes(cfg["gu_type"], H_)
+    for e in range(n_expert):
+        api.synth_weights(cfg["gu_type"], seed * 100003 + 2 * e, 0.02, 2 * FF, H_, experts[e, :gu_bytes])
+        api.synth_weights(cfg["d_type"], seed * 100003 + 2 * e + 1, 0.02, H_, FF, experts[e, gu_bytes:])
+    shared = None
+    if cfg.get("n_ff_sh"):
+        shared = T.empty(lc.shared_bytes, dtype=T.uint8, device="cuda")
+        sgu = 2 * cfg["n_ff_sh"] * H.row_bytes(cfg["sh_gu_type"], H_)
+        api.synth_weights(cfg["sh_gu_type"], seed * 7 + 1, 0.02, 2 * cfg["n_ff_sh"], H_, shared[:sgu])
+        api.synth_weights(cfg["sh_d_type"], seed * 7 + 2, 0.02, H_, cfg["n_ff_sh"], shared[sgu:])
+    T.cuda.synchronize()
+    return lc, experts, shared
+
+
+def oracle_token(oracle, cfg, experts, shared, ids, w, x, limit=H.INF):
+    """The oracle on one token, given the routing: only the routed experts' blobs are brought to the host."""
+    H_, FF, k = cfg["n_embd"], cfg["n_ff"], cfg["k"]
+    xq = oracle.quantize_q8_1(x)
+    parts = np.stack([oracle.expert_q8_1(cfg["gu_type"], cfg["d_type"], experts[int(e)].cpu().numpy(), H_, FF, limit, xq)
+                      for e in ids])
+    sh = None
+    if shared is not None:
+        sh = oracle.expert_q8_1(cfg["sh_gu_type"], cfg["sh_d_type"], shared.cpu().numpy(), H_, cfg["n_ff_sh"], limit, xq)
+    return oracle.combine_down(parts, w, sh)
+
+
+def test_c1_full_against_fixtures(T, api, oracle):
+    sys.path.insert(0, str(GOLDEN))
+    import make_golden
+    g = np.load(GOLDEN / "c1_reference_cpu.npz")
+    cfg = H.CONFIGS["C1"]
+    blobs = make_golden.c1_experts()
+    assert hashlib.sha256(blobs.tobytes()).hexdigest() == str(g["experts_sha256"])
+    layer = api.MoeLayer(layer_cfg(api, cfg), dev(T, blobs))
+    logits = H.router_logits("C1", cfg["tokens"], cfg["n_expert"], None)
+    x = H.activations("C1", cfg["tokens"], cfg["n_embd"], "f32")
+    for t in range(cfg["tokens"]):                      # batch 1, 16 seeded tokens
+        ids, w, out = layer.forward(dev(T, logits[t:t + 1]), dev(T, x[t:t + 1]))
+        assert np.array_equal(ids.cpu().numpy()[0], g["ids"][t])                       # routing bit-exact
+        assert (np.abs(w.cpu().numpy()[0] - g["weights"][t]) / g["weights"][t]).max() <= 1e-5
+        o = out.cpu().numpy()[0]
+        assert H.rel_err(o, g["out_oracle_q8_1"][t]) <= TOL
+        assert H.rel_err(o, g["out_oracle_q8_1"][t]) <= TIGHT
+        # against the reference's CPU rows (Q8_K activations): the gate the reference holds its own two paths to
+        assert H.rel_err(o, g["out_cpu_rows"][t]) <= 3e-2
+    # the same 16 tokens as one window: the same bits
+    ids16, w16, out16 = layer.forward(dev(T, logits), dev(T, x))
+    for t in range(cfg["tokens"]):
+        _, _, one = layer.forward(dev(T, logits[t:t + 1]), dev(T, x[t:t + 1]))
+        assert T.equal(out16[t], one[0])
+
+
+@pytest.mark.parametrize("name,n_tok_check", [("C2", 3), ("C5", 2)])
+def test_full_shape_single_token(T, api, oracle, name, n_tok_check):
+    cfg = H.CONFIGS[name]
+    lc, experts, shared = synth_layer(T, api, cfg, cfg["n_expert"], seed=11)
+    layer = api.MoeLayer(lc, experts, shared)
+    logits = H.router_logits(name, 8, cfg["n_expert"], cfg.get("zipf"))
+    x = H.activations(name, 8, cfg["n_embd"], cfg["act"])
+    ids_o, w_o = oracle.router_top10(logits, cfg["k"])
+    for t in range(n_tok_check):
+        xd = dev(T, x[t:t + 1], T.bfloat16)
+        ids, w, out = layer.forward(dev(T, logits[t:t + 1]), xd)
+        assert np.array_equal(ids.cpu().numpy()[0], ids_o[t])
+        want = oracle_token(oracle, cfg, experts, shared, ids_o[t], w_o[t], x[t])
+        got = out.cpu().numpy()[0]
+        assert H.rel_err(got, want) <= TOL
+        assert H.rel_err(got, want) <= TIGHT
+
+
+def test_c3_window_of_eight(T, api, oracle):
+    cfg = H.CONFIGS["C3"]
+    n_expert = 64                                       # reduced expert count, full hidden / FFN widths
+    lc, experts, _ = synth_layer(T, api, cfg, n_expert, seed=5)
+    layer = api.MoeLayer(lc, experts)
+    logits = H.router_logits("C3", 8, n_expert, cfg["zipf"])
+    x = H.activations("C3", 8, cfg["n_embd"], "bf16")
+    ids, w, out = layer.forward(dev(T, logits), dev(T, x, T.bfloat16))
+    ids_o, w_o = oracle.router_top10(logits, cfg["k"])
+    assert np.array_equal(ids.cpu().numpy(), ids_o)
+    assert len(np.unique(ids_o)) < 8 * cfg["k"]         # the skew makes tokens share experts
+    for t in range(8):
+        _, _, one = layer.forward(dev(T, logits[t:t + 1]), dev(T, x[t:t + 1], T.bfloat16))
+        assert T.equal(out[t], one[0])                  # window == token by token, bit for bit
+    want = oracle_token(oracle, dict(cfg, n_expert=n_expert), experts, None, ids_o[0], w_o[0], x[0])
+    assert H.rel_err(out[0].cpu().numpy(), want) <= TIGHT
+
+
+def test_expert_parallel_partition_sums_to_whole(T, api, oracle):
+    cfg = dict(H.CONFIGS["C5"], n_expert=32)
+    lc, experts, _ = synth_layer(T, api, cfg, 32, seed=9)
+    logits = H.router_logits("C5", 4, 32, 1.1)
+    x = H.activations("C5", 4, cfg["n_embd"], "bf16")
+    ld, xd = dev(T, logits), dev(T, x, T.bfloat16)
+    _, _, whole = api.MoeLayer(lc, experts).forward(ld, xd)
+    parts = []
+    for n_ranks in (2, 8):
+        per = 32 // n_ranks
+        partial = [api.MoeLayer(lc, experts, expert_range=(r * per, (r + 1) * per)).forward(ld, xd)[2].cpu().numpy()
+                   for r in range(n_ranks)]
+        summed = np.stack([oracle.allreduce_in_order(np.stack([p[t] for p in partial])) for t in range(4)])
+        parts.append(summed)
+        assert H.rel_err(summed, whole.cpu().numpy()) <= 1e-5
+    # a rank with none of a token's experts contributes exact zeros
+    empty = api.MoeLayer(lc, experts, expert_range=(0, 0)).forward(ld, xd)[2]
+    assert not bool(empty.any())
+
+
+def test_layer_refusals(T, api):
+    cfg = H.CONFIGS["C1"]
+    lc = layer_cfg(api, cfg)
+    experts = T.zeros((2, lc.blob_bytes), dtype=T.uint8, device="cuda")
+    layer = api.MoeLayer(api.MoeLayerConfig(cfg["n_embd"], cfg["n_ff"], 2, 2, H.Q4_K, H.Q4_K), experts)
+    with pytest.raises(api.MayaError) as e:
+        layer.forward(T.zeros((17, 2), device="cuda"), T.zeros((17, cfg["n_embd"]), device="cuda"))
+    assert e.value.status == -4
+    with pytest.raises(api.MayaError):
+        api.MoeLayer(api.MoeLayerConfig(cfg["n_embd"], cfg["n_ff"], 2, 9, H.Q4_K, H.Q4_K), experts)
