@@ -1,0 +1,425 @@
+#!/usr/bin/env python3
+"""Benchmark of the routed-MoE expert-FFN decode layer (route -> experts -> combine, shared expert alongside).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+
+Workload (N = 1): the decode layer of the headline configuration - hidden 6144, 256 routed experts of FFN 2048 stored
+as IQ2_S plus one always-on shared expert of FFN 2048 stored as Q8_0, top-8 softmax routing, bf16 activations, batch 1,
+256 seeded tokens whose router logits are N(0,1) plus a Zipf(1.1) per-expert bias.  Expert weights are N(0, 0.02)
+quantized on the device by the library's own quantizers (synthetic data; no checkpoint is involved).  One step = one
+token through one layer.  `--layers` copies of the layer are resident and steps rotate through them, so every step's
+136.8 MB of expert blocks come from HBM, not from L2 (working set >> 126 MB).
+
+One JSON line on stdout (rank 0): `value` = tokens/s through one layer with inputs resident in HBM (CUDA-graph replay
+of the K steps, CUDA-event timed); `e2e` = the same with each step's logits and activations copied from pinned host
+memory and the output copied back, inside the timed region; `roofline` = the dominant kernel's algorithmic bytes over
+its CUDA-event duration against the measured HBM peak; `cpu_baseline` = the reference's CPU expert rows on this box's
+host cores over a bounded sample of the same tokens.
+
+`--impl reference` times the reference's own CPU implementation of the path (oracle/_ref when it was built from the
+reference tree, else the CPU restatement) with all host threads; under torchrun only rank 0 works.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from project_maya_b200 import synthetic as S  # noqa: E402
+
+CFG = dict(S.CONFIGS["C2"], limit=S.INF)
+WORKLOAD = "C2 decode: H6144 E256 FF2048 top8 IQ2_S + shared Q8_0 FF2048, bf16 acts, batch 1, 256 seeded tokens, Zipf(1.1)"
+N_TOKENS = 256
+
+
+def algorithmic_bytes_per_token(cfg=CFG) -> int:
+    routed = cfg["k"] * S.blob_bytes(cfg["gu_type"], cfg["d_type"], cfg["n_embd"], cfg["n_ff"])
+    shared = S.blob_bytes(cfg["sh_gu_type"], cfg["sh_d_type"], cfg["n_embd"], cfg["n_ff_sh"]) if cfg.get("n_ff_sh") else 0
+    return routed + shared
+
+
+def measured_peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+                 "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                 "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.reasons |= {k for k, bit in names.items() if r & bit}
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm
+def cpu_layer_tokens(tokens: list[int], threads: int):
+    """The reference's CPU expert path on `tokens` of the workload: router (double-precision host reference), the
+    routed experts through the reference's AVX-512 / AVX2 rows over Q8_K activations (rows split across the threads, as
+    its pool does), the Q8_0 shared expert through the CPU restatement of the q8_1 dot (the reference hands Q8_0 to
+    ggml-cpu, which is not in its tree), plain weighted sum.  Returns (seconds, kind, note)."""
+    from oracle.oracle import Oracle, Ref
+    orc = Oracle()
+    ref = Ref() if Ref.available() else None
+    cfg = CFG
+    Hd, FF, E, k = cfg["n_embd"], cfg["n_ff"], cfg["n_expert"], cfg["k"]
+    logits = S.router_logits("C2", N_TOKENS, E, cfg["zipf"])
+    x = S.activations("C2", N_TOKENS, Hd, "bf16")
+    t, d = cfg["gu_type"], cfg["d_type"]
+    grb, drb = S.row_bytes(t, Hd), S.row_bytes(d, FF)
+    # constructed (random valid) blocks: on the CPU the byte values do not change the work; 8 distinct experts per token
+    # are drawn from a pool larger than the last-level cache so the rows stream from DRAM as in production
+    pool_n = 24
+    rng = S.rng_for("cpu-pool")
+    pool = [S.constructed_expert(t, d, Hd, FF, rng) for _ in range(pool_n)]
+    shared = S.constructed_expert(cfg["sh_gu_type"], cfg["sh_d_type"], Hd, cfg["n_ff_sh"], rng)
+    ids, w = orc.router_f64(logits, k)
+    avx512 = True
+    ex = ThreadPoolExecutor(max_workers=threads)
+
+    def split(n):
+        step = (n + threads - 1) // threads
+        return [(i, min(n, i + step)) for i in range(0, n, step)]
+
+    def token(ti: int):
+        if ref is not None:
+            a = orc.quantize_q8_K(x[ti])
+            parts = np.zeros((k, Hd), np.float32)
+            for j in range(k):
+                blob = pool[(int(ids[ti, j]) + ti) % pool_n]
+                h = np.zeros(FF, np.float32)
+                hv = [h]
+
+                def gu(r):
+                    out = ref.gu_rows(t, blob, grb, FF * grb, Hd, [a], r[0], r[1], avx512)
+                    hv[0][r[0]:r[1]] = out[0][r[0]:r[1]]
+                list(ex.map(gu, split(FF)))
+                hq = orc.quantize_q8_K(h)
+                down = blob[2 * FF * grb:]
+
+                def dn(r):
+                    out = ref.rows(d, down, drb, FF, [hq], r[0], r[1], avx512)
+                    parts[j][r[0]:r[1]] = out[0][r[0]:r[1]]
+                list(ex.map(dn, split(Hd)))
+        else:
+            xq = orc.quantize_q8_1(x[ti])
+            parts = np.stack([orc.expert_q8_1(t, d, pool[(int(ids[ti, j]) + ti) % pool_n], Hd, FF, S.INF, xq) for j in range(k)])
+        xq = orc.quantize_q8_1(x[ti])
+        sh = orc.expert_q8_1(cfg["sh_gu_type"], cfg["sh_d_type"], shared, Hd, cfg["n_ff_sh"], S.INF, xq)
+        return orc.combine_native(parts, w[ti], sh)
+
+    token(tokens[0])    # warm-up
+    t0 = time.perf_counter()
+    for ti in tokens:
+        token(ti)
+    dt = time.perf_counter() - t0
+    ex.shutdown()
+    kind = "reference" if ref is not None else "port"
+    note = ("routed IQ2_S experts: the reference's AVX-512 CPU rows (oracle/_ref), rows split over the threads; "
+            if ref is not None else "routed experts: CPU restatement of the q8_1 path; ")
+    note += "shared Q8_0 expert: CPU restatement (OpenMP); router in double; random valid blocks from a 24-expert pool"
+    return dt, kind, note
+
+
+def reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
+    sample = 2
+    times = []
+    for _ in range(max(1, args.warmup)):
+        cpu_layer_tokens(list(range(1)), threads)
+    kind = note = None
+    for s in range(args.steps):
+        toks = [(s * sample + i) % N_TOKENS for i in range(sample)]
+        dt, kind, note = cpu_layer_tokens(toks, threads)
+        times.append(dt / sample)
+    per_tok = float(np.mean(times))
+    value = 1.0 / per_tok
+    line = {"impl": "reference", "metric": "MoE expert-FFN decode tokens/s per layer", "value": value, "unit": "tok/s/layer",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_tok * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int8 -> f32",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "sample": f"{sample} tokens per step"},
+            "cpu_baseline": {"value": value, "unit": "tok/s/layer", "cores": threads, "kind": kind,
+                             "sample": f"{sample} tokens per step; {note}"},
+            "e2e": {"value": value, "unit": "tok/s/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+def build_layers(torch, api, n_layers: int, expert_range, shared_here: bool):
+    cfg = CFG
+    lc = api.MoeLayerConfig(cfg["n_embd"], cfg["n_ff"], cfg["n_expert"], cfg["k"], cfg["gu_type"], cfg["d_type"],
+                            cfg["n_ff_sh"], cfg["sh_gu_type"], cfg["sh_d_type"], cfg["limit"])
+    Hd, FF, E = cfg["n_embd"], cfg["n_ff"], cfg["n_expert"]
+    gu = 2 * FF * S.row_bytes(cfg["gu_type"], Hd)
+    experts0 = torch.empty((E, lc.blob_bytes), dtype=torch.uint8, device="cuda")
+    for e in range(E):
+        api.synth_weights(cfg["gu_type"], 2 * e, 0.02, 2 * FF, Hd, experts0[e, :gu])
+        api.synth_weights(cfg["d_type"], 2 * e + 1, 0.02, Hd, FF, experts0[e, gu:])
+    shared0 = torch.empty(lc.shared_bytes, dtype=torch.uint8, device="cuda")
+    sgu = 2 * cfg["n_ff_sh"] * S.row_bytes(cfg["sh_gu_type"], Hd)
+    api.synth_weights(cfg["sh_gu_type"], 100001, 0.02, 2 * cfg["n_ff_sh"], Hd, shared0[:sgu])
+    api.synth_weights(cfg["sh_d_type"], 100002, 0.02, Hd, cfg["n_ff_sh"], shared0[sgu:])
+    layers = []
+    for i in range(n_layers):
+        # further layers are byte copies in their own memory: the values do not change the work, the addresses do
+        ex = experts0 if i == 0 else experts0.clone()
+        sh = shared0 if i == 0 else shared0.clone()
+        layers.append(api.MoeLayer(lc, ex, sh, expert_range=expert_range, shared_here=shared_here, max_tokens=1))
+    torch.cuda.synchronize()
+    return lc, layers
+
+
+def gpu_arm(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from project_maya_b200 import _lib, api
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this path has no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    lib = _lib.load()
+    if lib.maya_device_ok() != 0:
+        raise SystemExit("the library is built for sm_100a only")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    cfg = CFG
+    Hd, E, k = cfg["n_embd"], cfg["n_expert"], cfg["k"]
+    per = E // world
+    lc, layers = build_layers(torch, api, args.layers, (rank * per, (rank + 1) * per) if world > 1 else None, rank == 0)
+
+    logits_h = torch.from_numpy(S.router_logits("C2", N_TOKENS, E, cfg["zipf"])).pin_memory()
+    x_h = torch.from_numpy(S.bf16_bits(S.activations("C2", N_TOKENS, Hd, "bf16")).view(np.int16)).view(torch.bfloat16).pin_memory()
+    logits_d, x_d = logits_h.cuda(), x_h.cuda()
+    K, W = args.steps, args.warmup
+    out_d = torch.empty((K, Hd), dtype=torch.float32, device="cuda")
+    ids_d = torch.empty((K, k), dtype=torch.int32, device="cuda")
+    w_d = torch.empty((K, k), dtype=torch.float32, device="cuda")
+    out_h = torch.empty((K, Hd), dtype=torch.float32).pin_memory()
+    stage_l = torch.empty((K, E), dtype=torch.float32, device="cuda")
+    stage_x = torch.empty((K, Hd), dtype=torch.bfloat16, device="cuda")
+
+    def step(s: int, l_row, x_row):
+        layers[s % len(layers)].forward(l_row, x_row, ids_d[s:s + 1], w_d[s:s + 1], out_d[s:s + 1])
+        if world > 1:
+            dist.all_reduce(out_d[s:s + 1])
+
+    def step_dev(s: int):
+        tok = s % N_TOKENS
+        step(s, logits_d[tok:tok + 1], x_d[tok:tok + 1])
+
+    def step_e2e(s: int):
+        tok = s % N_TOKENS
+        stage_l[s:s + 1].copy_(logits_h[tok:tok + 1], non_blocking=True)
+        stage_x[s:s + 1].copy_(x_h[tok:tok + 1], non_blocking=True)
+        step(s, stage_l[s:s + 1], stage_x[s:s + 1])
+        out_h[s:s + 1].copy_(out_d[s:s + 1], non_blocking=True)
+
+    stream = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        for s in range(max(W, 3)):              # eager warm-up: loads every kernel, sets shared-memory attributes
+            step_dev(s)
+            step_e2e(s)
+    stream.synchronize()
+
+    use_graph = world == 1
+    launches0 = lib.maya_launch_count()
+    if use_graph:
+        g_dev, g_e2e = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_dev, stream=stream):
+            for s in range(K):
+                step_dev(s)
+        launches_per_run = lib.maya_launch_count() - launches0
+        with torch.cuda.graph(g_e2e, stream=stream):
+            for s in range(K):
+                step_e2e(s)
+        run_dev, run_e2e = g_dev.replay, g_e2e.replay
+    else:
+        def run_dev():
+            for s in range(K):
+                step_dev(s)
+
+        def run_e2e():
+            for s in range(K):
+                step_e2e(s)
+        run_dev()
+        launches_per_run = lib.maya_launch_count() - launches0
+
+    def timed(fn) -> float:
+        with torch.cuda.stream(stream):
+            fn()                                 # one untimed pass of the same K steps
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            fn()
+            e1.record(stream)
+            stream.synchronize()
+            torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    with ClockSampler(local_rank) as clocks:
+        ms_dev = timed(run_dev)
+        ms_e2e = timed(run_e2e)
+
+    # ---- the dominant kernel alone: gate/up of the routed experts (+ the shared expert's down rows in the same launch)
+    roof = None
+    if rank == 0:
+        roof = dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, min(K, 64), stream)
+
+    if rank == 0:
+        bytes_tok = algorithmic_bytes_per_token()
+        value = K / (ms_dev * 1e-3)
+        e2e = K / (ms_e2e * 1e-3)
+        peak, peak_kind = measured_peaks()
+        line = {
+            "metric": "MoE expert-FFN decode tokens/s per layer", "value": value, "unit": "tok/s/layer", "n_gpus": world,
+            "steps": K, "warmup": max(W, 3), "ms_per_step": ms_dev / K, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "int8 x int8 -> f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layers_resident": len(layers),
+                       "l2": "inputs larger than L2: steps rotate over %d resident layers and 256 tokens" % len(layers),
+                       "launch": "CUDA graph of the K steps" if use_graph else "eager launches + NCCL all-reduce of the partials",
+                       "parallelism": "1 GPU" if world == 1 else f"expert-parallel {world} x {per} experts, shared expert on rank 0"},
+            "hbm_gbs": bytes_tok * value / 1e9, "hbm_frac_of_%s_peak" % peak_kind: bytes_tok * value / 1e9 / peak,
+            "hbm_frac_of_nominal_8TBs": bytes_tok * value / 8e12,
+            "e2e": {"value": e2e, "unit": "tok/s/layer", "h2d_bytes_per_step": E * 4 + Hd * 2, "d2h_bytes_per_step": Hd * 4,
+                    "ms_per_step": ms_e2e / K},
+            "gpu_launches": int(launches_per_run),
+            "clocks": clocks.summary(),
+            "roofline": roof,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            os.environ.setdefault("OMP_NUM_THREADS", str(threads))
+            dt, kind, note = cpu_layer_tokens(list(range(4)), threads)
+            line["cpu_baseline"] = {"value": 4 / dt, "unit": "tok/s/layer", "cores": threads, "kind": kind,
+                                    "sample": "tokens 0..3 of the 256, once after a warm-up token; " + note}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, steps: int, stream) -> dict:
+    """Times maya_moe_gate_up alone (CUDA events on the launching stream) on the same rotating layers and tokens."""
+    cfg = CFG
+    Hd, FF, k = cfg["n_embd"], cfg["n_ff"], cfg["k"]
+    FFs = cfg["n_ff_sh"]
+    gu_bytes = k * 2 * FF * S.row_bytes(cfg["gu_type"], Hd)
+    sh_down_bytes = Hd * S.row_bytes(cfg["sh_d_type"], FFs)
+    sh_down_off = 2 * FFs * S.row_bytes(cfg["sh_gu_type"], Hd)
+    with torch.cuda.stream(stream):
+        ids, w = api.router_top10(logits_d, k)
+        xq = api.native_quantize_q8_1(x_d)
+        plan_w = w.contiguous()
+        hq = torch.zeros(k * (FF // 32) * 36, dtype=torch.uint8, device="cuda")
+        sh_hq = torch.zeros((FFs // 32) * 36, dtype=torch.uint8, device="cuda")
+        sh_out = torch.zeros(Hd, dtype=torch.float32, device="cuda")
+        stream.synchronize()
+        ids_h = ids.cpu().numpy()
+        plans = []
+        for s in range(steps):
+            layer = layers[s % len(layers)]
+            ptr = torch.tensor([layer.experts[int(e)].data_ptr() for e in ids_h[s % N_TOKENS]], dtype=torch.int64, device="cuda")
+            plans.append((api.make_plan(ptr, plan_w[s % N_TOKENS]), ptr, layer))
+        stream.synchronize()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for rep in range(2):                     # the first pass is a warm-up
+            for s in range(steps):
+                plan, _, layer = plans[s]
+                evs[s][0].record(stream)
+                api.moe_gate_up(cfg["gu_type"], plan, k, Hd, FF, cfg["limit"], xq[s % N_TOKENS], hq,
+                                layer.shared[sh_down_off:], cfg["sh_d_type"], sh_hq, FFs, sh_out)
+                evs[s][1].record(stream)
+            stream.synchronize()
+    us = float(np.mean([a.elapsed_time(b) for a, b in evs])) * 1e3
+    peak, kind = measured_peaks()
+    alg = gu_bytes + sh_down_bytes
+    achieved = alg / (us * 1e-6) / 1e9
+    return {"bound": "hbm", "kernel": "gate_up_kernel<IQ2_S> (routed gate/up + SwiGLU + q8_1; shared-expert down rows in the same launch)",
+            "achieved": achieved, "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": achieved / peak,
+            "algorithmic_bytes_per_launch": alg, "us_per_launch": us, "launches_timed": steps, "traffic": None}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -47,6 +47,8 @@ MAYA_API const char* maya_version(void);
 MAYA_API int maya_last_cuda_error(void);
 /* Launches refused or failed since load (glmf::launch_errors, glm_fast.cu:5803; mmq::launch_errors, moe_mmq.hpp:99). */
 MAYA_API int maya_launch_errors(void);
+/* Kernels of this library enqueued successfully since load (every entry point counts its own launches). */
+MAYA_API long long maya_launch_count(void);
 /* 0 when the current device is sm_100; MAYA_ERR_DEVICE otherwise. */
 MAYA_API int maya_device_ok(void);
 

@@ -43,6 +43,7 @@ _SIGNATURES = {
     "maya_version": (C.c_char_p, []),
     "maya_last_cuda_error": (c_int, []),
     "maya_launch_errors": (c_int, []),
+    "maya_launch_count": (C.c_longlong, []),
     "maya_device_ok": (c_int, []),
     "maya_type_supported": (c_int, [c_int]),
     "maya_row_bytes": (c_size_t, [c_int, c_int64]),

@@ -7,11 +7,12 @@
 namespace maya {
 
 static std::atomic<int> g_launch_errors{0};
+static std::atomic<long long> g_launches{0};
 static thread_local int t_last_cuda_error = 0;
 
 int note_launch(const char* what) {
     const cudaError_t e = cudaGetLastError();
-    if (e == cudaSuccess) return MAYA_OK;
+    if (e == cudaSuccess) { g_launches.fetch_add(1, std::memory_order_relaxed); return MAYA_OK; }
     t_last_cuda_error = (int) e;
     if (g_launch_errors.fetch_add(1) < 8) std::fprintf(stderr, "maya_moe: %s: %s\n", what, cudaGetErrorString(e));
     return MAYA_ERR_LAUNCH;
@@ -30,6 +31,7 @@ extern "C" {
 const char* maya_version(void) { return "maya-moe-b200 0.1 (sm_100a)"; }
 int maya_last_cuda_error(void) { return t_last_cuda_error; }
 int maya_launch_errors(void) { return g_launch_errors.load(); }
+long long maya_launch_count(void) { return g_launches.load(); }
 
 int maya_device_ok(void) {
     int dev = 0;

@@ -101,6 +101,8 @@ def test_quantize_q8_1_bytes(T, api, oracle, act):
     x = H.activations("q81", 5, 6144, act)
     x[0, :32] = 0.0
     x[1, 32:64] *= 1.0e6
+    if act == "bf16":
+        x = H.to_bf16_f32(x)
     xd = dev(T, x, T.bfloat16 if act == "bf16" else None)
     got = api.native_quantize_q8_1(xd).cpu().numpy()
     want = np.stack([oracle.quantize_q8_1(x[i]) for i in range(5)])
@@ -168,7 +170,8 @@ def run_plan(T, api, t, n_embd, n_ff, blobs, weights, x, limit, skip_entries=(),
     hq = T.zeros(k * (n_ff // 32) * 36, dtype=T.uint8, device="cuda")
     out = T.zeros(n_embd, dtype=T.float32, device="cuda")
     flag = T.ones(1, dtype=T.int32, device="cuda") if cpu_part is not None else None
-    plan = api.make_plan(plan_ptr, plan_w, dev(T, cpu_part) if cpu_part is not None else None, flag)
+    cpu_part_d = dev(T, cpu_part) if cpu_part is not None else None      # the plan holds raw addresses: keep it alive
+    plan = api.make_plan(plan_ptr, plan_w, cpu_part_d, flag)
     sh_out = None
     if shared is not None:
         sh_t, sh_ff, sh_blob = shared
