@@ -366,42 +366,27 @@ def gpu_arm(args) -> None:
 
 
 def dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, steps: int, stream) -> dict:
-    """Times maya_moe_gate_up alone (CUDA events on the launching stream) on the same rotating layers and tokens."""
+    """Times the fused layer kernel alone: one CUDA-event pair per launch on the launching stream, same rotating
+    layers and tokens as the timed loop (so every launch reads its experts from HBM)."""
     cfg = CFG
-    Hd, FF, k = cfg["n_embd"], cfg["n_ff"], cfg["k"]
-    FFs = cfg["n_ff_sh"]
-    gu_bytes = k * 2 * FF * S.row_bytes(cfg["gu_type"], Hd)
-    sh_down_bytes = Hd * S.row_bytes(cfg["sh_d_type"], FFs)
-    sh_down_off = 2 * FFs * S.row_bytes(cfg["sh_gu_type"], Hd)
+    Hd, k = cfg["n_embd"], cfg["k"]
+    ids = torch.empty((1, k), dtype=torch.int32, device="cuda")
+    w = torch.empty((1, k), dtype=torch.float32, device="cuda")
+    out = torch.empty((1, Hd), dtype=torch.float32, device="cuda")
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     with torch.cuda.stream(stream):
-        ids, w = api.router_top10(logits_d, k)
-        xq = api.native_quantize_q8_1(x_d)
-        plan_w = w.contiguous()
-        hq = torch.zeros(k * (FF // 32) * 36, dtype=torch.uint8, device="cuda")
-        sh_hq = torch.zeros((FFs // 32) * 36, dtype=torch.uint8, device="cuda")
-        sh_out = torch.zeros(Hd, dtype=torch.float32, device="cuda")
-        stream.synchronize()
-        ids_h = ids.cpu().numpy()
-        plans = []
-        for s in range(steps):
-            layer = layers[s % len(layers)]
-            ptr = torch.tensor([layer.experts[int(e)].data_ptr() for e in ids_h[s % N_TOKENS]], dtype=torch.int64, device="cuda")
-            plans.append((api.make_plan(ptr, plan_w[s % N_TOKENS]), ptr, layer))
-        stream.synchronize()
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
         for rep in range(2):                     # the first pass is a warm-up
             for s in range(steps):
-                plan, _, layer = plans[s]
+                tok = s % N_TOKENS
                 evs[s][0].record(stream)
-                api.moe_gate_up(cfg["gu_type"], plan, k, Hd, FF, cfg["limit"], xq[s % N_TOKENS], hq,
-                                layer.shared[sh_down_off:], cfg["sh_d_type"], sh_hq, FFs, sh_out)
+                layers[s % len(layers)].forward(logits_d[tok:tok + 1], x_d[tok:tok + 1], ids, w, out)
                 evs[s][1].record(stream)
             stream.synchronize()
     us = float(np.mean([a.elapsed_time(b) for a, b in evs])) * 1e3
     peak, kind = measured_peaks()
-    alg = gu_bytes + sh_down_bytes
+    alg = algorithmic_bytes_per_token()
     achieved = alg / (us * 1e-6) / 1e9
-    return {"bound": "hbm", "kernel": "gate_up_kernel<IQ2_S> (routed gate/up + SwiGLU + q8_1; shared-expert down rows in the same launch)",
+    return {"bound": "hbm", "kernel": "moe_layer_t1_kernel<IQ2_S, Q8_0> (the whole layer: route, q8_1, gate/up + SwiGLU, down, combine)",
             "achieved": achieved, "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": achieved / peak,
             "algorithmic_bytes_per_launch": alg, "us_per_launch": us, "launches_timed": steps, "traffic": None}
 

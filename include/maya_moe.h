@@ -181,9 +181,16 @@ typedef struct maya_moe_layer {
     float limit;                 /* SwiGLU clamp; INFINITY = none */
     int expert_lo, expert_hi;    /* this rank's experts [lo, hi); others contribute nothing (expert-parallel) */
     int shared_here;             /* non-zero: this rank adds the shared expert */
+    int staged;                  /* non-zero: run one token through the staged kernels (router, q8_1, gate/up, down as
+                                    separate launches) instead of the single fused kernel; same bits either way */
 } maya_moe_layer;
-/* Bytes of scratch maya_moe_layer_decode needs for n_tokens tokens. */
+/* Bytes of scratch maya_moe_layer_decode needs for n_tokens tokens.  The scratch must be 256-byte aligned and ZEROED
+ * once before its first use (it holds the fused kernel's grid-barrier counter); one scratch serves one stream at a
+ * time.  After a device-side barrier time-out (a block never arrived) the word returned by maya_moe_layer_error is
+ * non-zero and the outputs of that and later calls on the scratch are undefined. */
 MAYA_API size_t maya_moe_layer_scratch_bytes(const maya_moe_layer* L, int n_tokens);
+/* Reads the sticky barrier-error word of a layer scratch (synchronises the stream first). 0 = no error. */
+MAYA_API int maya_moe_layer_error(const maya_moe_layer* L, int n_tokens, const void* scratch, void* stream);
 /* logits [n_tokens, n_expert] f32; x [n_tokens, n_embd] f32 (x_is_bf16 == 0) or bf16 bits; out [n_tokens, n_embd] f32;
  * ids / weights [n_tokens, k] (outputs, may be NULL... then scratch holds them).  n_tokens <= MAYA_MAX_WIN_TOKENS. */
 MAYA_API int maya_moe_layer_decode(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,

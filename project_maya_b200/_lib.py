@@ -36,7 +36,7 @@ class MoeLayerDesc(C.Structure):
     _fields_ = [("n_embd", c_int), ("n_ff", c_int), ("n_expert", c_int), ("k", c_int), ("gu_type", c_int),
                 ("d_type", c_int), ("experts", c_void_p), ("expert_stride", c_size_t), ("n_ff_sh", c_int),
                 ("sh_gu_type", c_int), ("sh_d_type", c_int), ("shared", c_void_p), ("limit", c_float),
-                ("expert_lo", c_int), ("expert_hi", c_int), ("shared_here", c_int)]
+                ("expert_lo", c_int), ("expert_hi", c_int), ("shared_here", c_int), ("staged", c_int)]
 
 
 _SIGNATURES = {
@@ -67,6 +67,7 @@ _SIGNATURES = {
                                     c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_float]),
     "maya_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "maya_moe_layer_scratch_bytes": (c_size_t, [C.POINTER(MoeLayerDesc), c_int]),
+    "maya_moe_layer_error": (c_int, [C.POINTER(MoeLayerDesc), c_int, c_void_p, c_void_p]),
     "maya_moe_layer_decode": (c_int, [C.POINTER(MoeLayerDesc), c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_size_t, c_void_p]),
     "maya_quantize_weights_host": (c_int, [c_int, c_void_p, c_int64, c_int64, c_void_p]),

@@ -211,19 +211,20 @@ class MoeLayer:
     expert_range = (lo, hi) restricts this rank to experts lo..hi-1 (expert-parallel partition); the others' terms are
     left out of `out` (another rank adds them)."""
 
-    def __init__(self, cfg: MoeLayerConfig, experts, shared=None, expert_range=None, shared_here=True, max_tokens: int = 16):
+    def __init__(self, cfg: MoeLayerConfig, experts, shared=None, expert_range=None, shared_here=True, max_tokens: int = 16,
+                 staged: bool = False):
         self.cfg = cfg
         self.experts = experts
         self.shared = shared
         lo, hi = expert_range if expert_range is not None else (0, cfg.n_expert)
         self.desc = MoeLayerDesc(cfg.n_embd, cfg.n_ff, cfg.n_expert, cfg.k, cfg.gu_type, cfg.d_type, _ptr(experts),
                                  cfg.blob_bytes, cfg.n_ff_sh if shared is not None else 0, cfg.sh_gu_type,
-                                 cfg.sh_d_type, _ptr(shared), cfg.limit, lo, hi, int(bool(shared_here)))
+                                 cfg.sh_d_type, _ptr(shared), cfg.limit, lo, hi, int(bool(shared_here)), int(bool(staged)))
         self.max_tokens = max_tokens
         nbytes = int(_lib.load().maya_moe_layer_scratch_bytes(C.byref(self.desc), max_tokens))
         if nbytes == 0:
             raise MayaError("moe_layer_scratch_bytes", -1)
-        self.scratch = torch.empty(nbytes, dtype=torch.uint8, device=experts.device)
+        self.scratch = torch.zeros(nbytes, dtype=torch.uint8, device=experts.device)   # zeroed: holds a barrier counter
 
     def forward(self, logits, x, ids=None, weights=None, out=None, stream=None):
         T = logits.shape[0]
@@ -237,3 +238,7 @@ class MoeLayer:
                                                  _ptr(ids), _ptr(weights), _ptr(out), _ptr(self.scratch),
                                                  self.scratch.numel(), _stream(stream)))
         return ids, weights, out
+
+    def error(self, stream=None) -> int:
+        """The scratch's sticky device-side error word (0 = none); synchronises the stream."""
+        return int(_lib.load().maya_moe_layer_error(C.byref(self.desc), self.max_tokens, _ptr(self.scratch), _stream(stream)))

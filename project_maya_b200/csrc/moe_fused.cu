@@ -1,0 +1,292 @@
+// moe_fused.cu - one token through one MoE layer in ONE persistent kernel: route, quantize the activation, routed and
+// shared gate/up + SwiGLU, q8_1 of h, routed and shared down, weighted combine.
+//
+// The reference spends 3-6 launches a layer on this (Glm5Model::fast_moe, src/core/glm_fast_path.cu:6917-7100: router
+// GEMV launch, moe_route, moe_gate_up, moe_down; native path: 4 launches inside native_expert_grouped alone).  At
+// ~137 MB a token the whole layer is ~21 us of HBM time on a B200, so launch gaps and per-kernel tails would cost as
+// much as the work.  Here one cooperative grid of one block per SM does it:
+//
+//   phase 0 (every block, redundantly - no grid-wide dependency): warps 0-7 route the token (the same bits in every
+//            block); warps 8-31 build the replicated codebook in shared memory and quantize x to q8_1 there;
+//   phase 1  block b owns a contiguous slice of the FFN rows; its warps take (row, expert) items - gate row and up row
+//            of one expert, sharing the activation registers - and write h = SwiGLU(gate, up) as f32 to scratch;
+//            the shared expert is expert k;
+//   grid barrier (bounded spin on a counter in the caller's scratch; a time-out sets a sticky error word);
+//   phase 2  every block quantizes all (k + 1) x n_ff values of h to q8_1 in shared memory, then owns a contiguous
+//            slice of the output rows: items are (row pair, expert); the per-expert partials meet in shared memory and
+//            one thread per row runs the combine chain in plan order.
+//
+// Every (row, expert) dot, the q8_1 of h and the combine chain use the operations and order of the staged kernels
+// (moe_decode.cu), so the output is bit-identical to maya_moe_gate_up + maya_moe_down on the same plan.
+#include <cooperative_groups.h>
+
+#include "maya_dots_t1.cuh"
+#include "maya_internal.cuh"
+#include "maya_router.cuh"
+
+namespace maya {
+namespace {
+
+constexpr int kFusedThreads = 1024;
+constexpr int kRouteThreads = 256;
+constexpr int kMaxSliceRows = 96;          // output rows a block may own (n_embd / grid rounded up)
+constexpr unsigned kSpinLimit = 1u << 22;  // barrier polls before giving up (~ a second)
+
+struct FusedArgs {
+    const float* logits;       // [n_expert]
+    const void* x;             // [n_embd] f32 or bf16
+    int x_is_bf16;
+    int n_embd, n_ff, n_expert, k;
+    const uint8_t* experts;
+    size_t expert_stride;
+    int expert_lo, expert_hi;
+    const uint8_t* shared;     // NULL: none (or not on this rank)
+    int n_ff_sh;
+    float limit;
+    int* ids;                  // [k] out
+    float* weights;            // [k] out
+    float* out;                // [n_embd] out
+    float* h;                  // scratch [(k + 1)][max(n_ff, n_ff_sh)] f32
+    unsigned* sync;            // scratch: [0] arrivals, [1] epoch, [2] error
+};
+
+struct FusedShared {
+    RouterShared route;
+    unsigned long long ptr[MAYA_MAX_K + 1];
+    float w[MAYA_MAX_K];
+    float part[kMaxSliceRows][MAYA_MAX_K + 1];
+    unsigned epoch;
+};
+
+// balanced contiguous split of n rows over nb blocks
+__device__ __forceinline__ void slice(int n, int nb, int b, int& r0, int& r1) {
+    const int base = n / nb, rem = n % nb;
+    r0 = b * base + min(b, rem);
+    r1 = r0 + base + (b < rem ? 1 : 0);
+}
+
+// q8_1 of 32 values (one per lane) straight into the shared structure-of-arrays form the dots read.
+__device__ __forceinline__ void q8_1_to_smem(float v, int4* q, float* d, int* isum, int blk, int lane) {
+    const float amax = warp_max(fabsf(v));
+    const float dd = fminf(__fdiv_rn(amax, 127.0f), 65504.0f);
+    const int qi = amax == 0.0f ? 0 : (int) fmaxf(-127.0f, fminf(127.0f, roundf(__fdiv_rn(v, dd))));
+    ((int8_t*) q)[blk * 32 + lane] = (int8_t) qi;
+    int s = qi;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) {
+        d[blk] = __half2float(__float2half_rn(dd));   // the scale as the f16 block field holds it
+        isum[blk] = s;
+    }
+}
+
+__device__ __forceinline__ bool grid_barrier(unsigned* sync, unsigned epoch) {
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(&sync[0], 1u);
+        const unsigned target = (epoch + 1u) * gridDim.x;
+        unsigned spins = 0;
+        while ((int) (*(volatile unsigned*) &sync[0] - target) < 0) {
+            if (++spins > kSpinLimit) { ok = false; atomicExch(&sync[2], 1u); break; }
+            __nanosleep(20);
+        }
+        __threadfence();
+    }
+    __syncthreads();
+    return ok;
+}
+
+template<int T, int TS>
+__global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArgs A) {
+    extern __shared__ __align__(16) uint8_t s_raw[];
+    __shared__ FusedShared sh;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int NW = kFusedThreads / 32;
+    const int k = A.k, n_embd = A.n_embd, n_ff = A.n_ff;
+    const bool has_sh = TS != 0 && A.shared != nullptr;
+    const int ne = k + (has_sh ? 1 : 0);             // experts incl. the shared one (index k)
+    const int h_ld = max(n_ff, A.n_ff_sh);
+
+    // shared-memory carve-up: [replicated codebook | activation columns (x, later the h of every expert) | exp scratch]
+    uint32_t* s_tab = (uint32_t*) s_raw;
+    uint8_t* s_cols = s_raw + kRepTabBytes<T>;
+    const int nblk_x = n_embd / 32, nblk_h = h_ld / 32;
+    const int cols_blocks = max(nblk_x, (MAYA_MAX_K + 1) * nblk_h);
+    int4* cq = (int4*) s_cols;
+    float* cd = (float*) (s_cols + (size_t) cols_blocks * 32);
+    int* cs = (int*) (s_cols + (size_t) cols_blocks * 36);
+    double* s_ex = (double*) (s_cols + (size_t) cols_blocks * 40);
+
+    if (tid == 0) sh.epoch = *(volatile unsigned*) &A.sync[1];
+
+    // ---------------------------------------------------------------- phase 0
+    if (tid < kRouteThreads) {
+        using RS = NamedSync<1, kRouteThreads>;
+        const int per = (A.n_expert + kRouteThreads - 1) / kRouteThreads;
+        if (per <= 1) route_softmax<1, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
+        else if (per <= 2) route_softmax<2, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
+        else if (per <= 4) route_softmax<4, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
+        else route_softmax<8, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
+        if (tid < k) {
+            const int e = sh.route.ids[tid];
+            sh.w[tid] = sh.route.val[tid];
+            sh.ptr[tid] = (e >= A.expert_lo && e < A.expert_hi)
+                              ? (unsigned long long) (A.experts + (size_t) e * A.expert_stride) : 0ull;
+            if (blockIdx.x == 0) { A.ids[tid] = e; A.weights[tid] = sh.route.val[tid]; }
+        }
+        if (tid == 0) sh.ptr[k] = has_sh ? (unsigned long long) A.shared : 0ull;
+    } else {
+        const int t2 = tid - kRouteThreads, n2 = kFusedThreads - kRouteThreads;
+        load_tab_rep<T>(s_tab, t2, n2);
+        for (int b = (t2 >> 5); b < nblk_x; b += n2 / 32) {
+            const float v = A.x_is_bf16 ? __uint_as_float((uint32_t) ((const uint16_t*) A.x)[b * 32 + lane] << 16)
+                                        : ((const float*) A.x)[b * 32 + lane];
+            q8_1_to_smem(v, cq, cd, cs, b, lane);
+        }
+    }
+    __syncthreads();
+    XCols X;
+    X.q = cq; X.d = cd; X.isum = cs; X.nblk = nblk_x;
+
+    // ---------------------------------------------------------------- phase 1: gate / up + SwiGLU
+    {
+        int r0, r1;
+        slice(n_ff, gridDim.x, blockIdx.x, r0, r1);            // routed experts' rows
+        int q0 = 0, q1 = 0;
+        if (has_sh) slice(A.n_ff_sh, gridDim.x, blockIdx.x, q0, q1);
+        const int nr = r1 - r0, n_routed = nr * k, n_items = n_routed + (q1 - q0);
+        const size_t rb = row_bytes(T, n_embd);
+        for (int it = warp; it < n_items; it += NW) {
+            if (it < n_routed) {
+                const int e = it / nr, r = r0 + it - e * nr;
+                const unsigned long long p = sh.ptr[e];
+                if (p == 0ull) continue;
+                const uint8_t* blob = (const uint8_t*) p;
+                const uint8_t* rows[2] = {blob + (size_t) r * rb, blob + (size_t) (n_ff + r) * rb};
+                float o[2];
+                rows_dot1<T, 2>(rows, X, n_embd, lane, s_tab, o);
+                if (lane == 0) A.h[(size_t) e * h_ld + r] = swiglu(o[0], o[1], A.limit);
+            } else if constexpr (TS != 0) {
+                const int r = q0 + it - n_routed;
+                const size_t rbs = row_bytes(TS, n_embd);
+                const uint8_t* rows[2] = {A.shared + (size_t) r * rbs, A.shared + (size_t) (A.n_ff_sh + r) * rbs};
+                float o[2];
+                rows_dot1<TS, 2>(rows, X, n_embd, lane, nullptr, o);
+                if (lane == 0) A.h[(size_t) k * h_ld + r] = swiglu(o[0], o[1], A.limit);
+            }
+        }
+    }
+    const bool ok = grid_barrier(A.sync, sh.epoch);
+
+    // ---------------------------------------------------------------- phase 2: q8_1(h), down, combine
+    if (ok) {
+        for (int b = warp; b < ne * nblk_h; b += NW) {
+            const int e = b / nblk_h, kb = b - e * nblk_h;
+            const int width = e < k ? n_ff : A.n_ff_sh;
+            float v = 0.0f;
+            if (sh.ptr[e] != 0ull && kb * 32 < width) v = __ldcg(&A.h[(size_t) e * h_ld + kb * 32 + lane]);
+            q8_1_to_smem(v, cq, cd, cs, b, lane);
+        }
+        __syncthreads();
+        int o0, o1;
+        slice(n_embd, gridDim.x, blockIdx.x, o0, o1);
+        const int nrows = o1 - o0, npairs = (nrows + 1) / 2;
+        const size_t drb = row_bytes(T, n_ff), down_off = 2 * (size_t) n_ff * row_bytes(T, n_embd);
+        for (int it = warp; it < npairs * ne; it += NW) {
+            const int e = it / npairs, pr = it - e * npairs;
+            const int ra = o0 + 2 * pr, rb2 = min(ra + 1, o1 - 1);
+            const unsigned long long p = sh.ptr[e];
+            float o[2] = {0.0f, 0.0f};
+            if (p != 0ull) {
+                XCols H;
+                H.q = cq + (size_t) 2 * e * nblk_h; H.d = cd + (size_t) e * nblk_h; H.isum = cs + (size_t) e * nblk_h;
+                H.nblk = nblk_h;
+                if (e < k) {
+                    const uint8_t* base = (const uint8_t*) p + down_off;
+                    const uint8_t* rows[2] = {base + (size_t) ra * drb, base + (size_t) rb2 * drb};
+                    rows_dot1<T, 2>(rows, H, n_ff, lane, s_tab, o);
+                } else if constexpr (TS != 0) {
+                    const size_t srb = row_bytes(TS, A.n_ff_sh);
+                    const uint8_t* base = A.shared + 2 * (size_t) A.n_ff_sh * row_bytes(TS, n_embd);
+                    const uint8_t* rows[2] = {base + (size_t) ra * srb, base + (size_t) rb2 * srb};
+                    rows_dot1<TS, 2>(rows, H, A.n_ff_sh, lane, nullptr, o);
+                }
+            }
+            if (lane == 0) {
+                sh.part[2 * pr][e] = o[0];
+                if (2 * pr + 1 < nrows) sh.part[2 * pr + 1][e] = o[1];
+            }
+        }
+        __syncthreads();
+        if (tid < nrows) {
+            float m = 0.0f;
+            for (int i = 0; i < k; ++i) m = __fmaf_rn(sh.w[i], sh.ptr[i] != 0ull ? sh.part[tid][i] : 0.0f, m);
+            A.out[o0 + tid] = __fadd_rn(m, has_sh ? sh.part[tid][k] : 0.0f);
+        }
+    }
+    // the launch's last word: the next launch on this scratch (stream-ordered) starts a new epoch
+    if (blockIdx.x == 0 && tid == 0) *(volatile unsigned*) &A.sync[1] = sh.epoch + 1u;
+}
+
+template<int T, int TS>
+int launch_fused(const FusedArgs& A, cudaStream_t s) {
+    static thread_local int cached_dev = -1, cached_grid = 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int nblk_x = A.n_embd / 32, nblk_h = (A.n_ff > A.n_ff_sh ? A.n_ff : A.n_ff_sh) / 32;
+    const int cols_blocks = nblk_x > (MAYA_MAX_K + 1) * nblk_h ? nblk_x : (MAYA_MAX_K + 1) * nblk_h;
+    const size_t smem = (size_t) kRepTabBytes<T> + (size_t) cols_blocks * 40 + (size_t) A.n_expert * sizeof(double);
+    if (smem > 220 * 1024) return refuse(MAYA_ERR_LIMIT);
+    if (cached_dev != dev) {
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cached_grid = sms;
+        cached_dev = dev;
+    }
+    if (cudaFuncSetAttribute(moe_layer_t1_kernel<T, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess)
+        return note_launch("fused smem attribute");
+    int grid = cached_grid;
+    if ((A.n_embd + grid - 1) / grid > kMaxSliceRows) return refuse(MAYA_ERR_LIMIT);
+    FusedArgs args = A;
+    void* params[] = {&args};
+    cudaLaunchCooperativeKernel((const void*) moe_layer_t1_kernel<T, TS>, dim3(grid), dim3(kFusedThreads), params, smem, s);
+    return note_launch("moe_layer_t1");
+}
+
+}  // namespace
+
+// Whether the fused single-token kernel covers this layer (else the staged kernels run).
+bool fused_t1_supported(const maya_moe_layer& L) {
+    if (L.gu_type != L.d_type) return false;
+    if (L.n_ff_sh > 0 && (L.sh_gu_type != MAYA_Q8_0 || L.sh_d_type != MAYA_Q8_0)) return false;
+    if (L.n_expert > kRouteThreads * kRouterMaxPerThread) return false;
+    return true;
+}
+
+int fused_t1(const maya_moe_layer& L, const float* logits, const void* x, int x_is_bf16, int* ids, float* weights,
+             float* out, float* h_scratch, unsigned* sync, cudaStream_t s) {
+    FusedArgs A{};
+    A.logits = logits; A.x = x; A.x_is_bf16 = x_is_bf16;
+    A.n_embd = L.n_embd; A.n_ff = L.n_ff; A.n_expert = L.n_expert; A.k = L.k;
+    A.experts = (const uint8_t*) L.experts; A.expert_stride = L.expert_stride;
+    A.expert_lo = L.expert_lo; A.expert_hi = L.expert_hi;
+    const bool sh = L.n_ff_sh > 0 && L.shared_here && L.shared != nullptr;
+    A.shared = sh ? (const uint8_t*) L.shared : nullptr;
+    A.n_ff_sh = sh ? L.n_ff_sh : 0;
+    A.limit = L.limit;
+    A.ids = ids; A.weights = weights; A.out = out; A.h = h_scratch; A.sync = sync;
+#define FUSED_CASE(TT)                                                      \
+    case TT: return sh ? launch_fused<TT, MAYA_Q8_0>(A, s) : launch_fused<TT, 0>(A, s);
+    switch (L.gu_type) {
+        FUSED_CASE(MAYA_Q8_0)
+        FUSED_CASE(MAYA_Q4_K)
+        FUSED_CASE(MAYA_IQ2_S)
+        FUSED_CASE(MAYA_IQ3_S)
+        default: return refuse(MAYA_ERR_TYPE);
+    }
+#undef FUSED_CASE
+}
+
+}  // namespace maya

@@ -24,6 +24,8 @@ struct Scratch {
     float* sh_gu;                // [T][2 * n_ff_sh]
     uint8_t* sh_hq;              // [T][n_ff_sh/32] q8_1
     float* sh_out;               // [T][n_embd]
+    float* h;                    // [(k + 1)][max(n_ff, n_ff_sh)] f32: the fused single-token kernel's h
+    unsigned* sync;              // [4]: the fused kernel's barrier counter, epoch, error word (zero before first use)
     size_t bytes;
 };
 
@@ -33,6 +35,13 @@ Scratch carve(const maya_moe_layer& L, int T, uint8_t* base) {
     Scratch s{};
     size_t off = 0;
     auto take = [&](size_t n) { uint8_t* p = base ? base + off : nullptr; off += align_up(n); return p; };
+    // the fused kernel's words first: their place must not depend on T (a scratch sized for a window also serves
+    // single tokens, and the barrier counter has to survive the calls in between)
+    s.sync = (unsigned*) take(4 * sizeof(unsigned));
+    {
+        const int ld = L.n_ff > L.n_ff_sh ? L.n_ff : L.n_ff_sh;
+        s.h = (float*) take((size_t) (MAYA_MAX_K + 1) * ld * sizeof(float));
+    }
     s.xq = take((size_t) T * (L.n_embd / 32) * kQ81Bytes);
     s.plan_ptr = (unsigned long long*) take((size_t) T * 8 * sizeof(unsigned long long));
     s.plan_w = (float*) take((size_t) T * 8 * sizeof(float));
@@ -96,6 +105,15 @@ extern "C" size_t maya_moe_layer_scratch_bytes(const maya_moe_layer* L, int n_to
     return carve(*L, n_tokens, nullptr).bytes;
 }
 
+extern "C" int maya_moe_layer_error(const maya_moe_layer* L, int n_tokens, const void* scratch, void* stream) {
+    if (check_layer(L) != MAYA_OK || !scratch || n_tokens < 1 || n_tokens > MAYA_MAX_WIN_TOKENS) return MAYA_ERR_ARG;
+    const Scratch S = carve(*L, n_tokens, (uint8_t*) scratch);
+    unsigned word = 0;
+    if (cudaStreamSynchronize(as_stream(stream)) != cudaSuccess) return note_launch("layer_error sync");
+    if (cudaMemcpy(&word, S.sync + 2, sizeof(word), cudaMemcpyDeviceToHost) != cudaSuccess) return note_launch("layer_error copy");
+    return (int) word;
+}
+
 extern "C" int maya_moe_layer_decode(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
                                      int n_tokens, int* ids, float* weights, float* out, void* scratch,
                                      size_t scratch_bytes, void* stream) {
@@ -109,6 +127,8 @@ extern "C" int maya_moe_layer_decode(const maya_moe_layer* L, const float* logit
     cudaStream_t s = as_stream(stream);
     int* d_ids = ids ? ids : S.ids;
     float* d_w = weights ? weights : S.weights;
+    if (T == 1 && !L->staged && fused_t1_supported(*L))
+        return fused_t1(*L, logits, x, x_is_bf16, d_ids, d_w, out, S.h, S.sync, s);
 
     st = maya_router_top10(logits, T, L->n_expert, L->k, d_ids, d_w, stream);
     if (st != MAYA_OK) return st;

@@ -155,6 +155,62 @@ def test_expert_parallel_partition_sums_to_whole(T, api, oracle):
     assert not bool(empty.any())
 
 
+@pytest.mark.parametrize("t,shared", [(H.Q4_K, False), (H.Q8_0, False), (H.IQ2_S, True), (H.IQ3_S, True), (H.IQ3_S, False)])
+def test_fused_token_kernel_equals_staged_kernels_bitwise(T, api, oracle, t, shared):
+    """One token through the single fused kernel and through the separate launches: the same bits, and the oracle's
+    values.  Odd sizes on purpose: the FFN and output rows do not divide evenly over the blocks."""
+    n_embd, n_ff, n_expert, k = 1024, 768, 20, 6
+    cfg = dict(n_embd=n_embd, n_ff=n_ff, n_expert=n_expert, k=k, gu_type=t, d_type=t, limit=7.0)
+    if shared:
+        cfg.update(n_ff_sh=512, sh_gu_type=H.Q8_0, sh_d_type=H.Q8_0)
+    lc, experts, sh = synth_layer(T, api, cfg, n_expert, seed=21)
+    lc.limit = 7.0
+    fused = api.MoeLayer(lc, experts, sh, expert_range=(0, 17))
+    staged = api.MoeLayer(lc, experts, sh, expert_range=(0, 17), staged=True)
+    logits = H.router_logits("fused", 6, n_expert, 1.1)
+    x = H.activations("fused", 6, n_embd, "bf16")
+    ids_o, w_o = oracle.router_top10(logits, k)
+    for i in range(6):
+        ld, xd = dev(T, logits[i:i + 1]), dev(T, x[i:i + 1], T.bfloat16)
+        ids_f, w_f, out_f = fused.forward(ld, xd)
+        ids_s, w_s, out_s = staged.forward(ld, xd)
+        assert T.equal(ids_f, ids_s) and T.equal(w_f, w_s)
+        assert np.array_equal(ids_f.cpu().numpy()[0], ids_o[i])
+        assert T.equal(out_f, out_s), f"token {i}"
+    assert fused.error() == 0
+    # f32 activations and the oracle, experts 17..19 left to "another rank"
+    xf = H.activations("fused32", 1, n_embd, "f32")
+    _, _, out = fused.forward(dev(T, logits[:1]), dev(T, xf))
+    xq = oracle.quantize_q8_1(xf[0])
+    parts = np.zeros((k, n_embd), np.float32)
+    skip = np.zeros(k, np.uint8)
+    for j, e in enumerate(ids_o[0]):
+        if e < 17:
+            parts[j] = oracle.expert_q8_1(t, t, experts[int(e)].cpu().numpy(), n_embd, n_ff, 7.0, xq)
+        else:
+            skip[j] = 1
+    shv = oracle.expert_q8_1(H.Q8_0, H.Q8_0, sh.cpu().numpy(), n_embd, 512, 7.0, xq) if shared else None
+    want = oracle.combine_down(parts, w_o[0], shv, skip)
+    assert H.rel_err(out.cpu().numpy()[0], want) <= TIGHT
+
+
+def test_fused_kernel_many_calls_one_scratch(T, api):
+    """The grid barrier's counter lives in the scratch: hundreds of calls, single tokens and windows interleaved."""
+    cfg = dict(n_embd=512, n_ff=256, n_expert=8, k=4, gu_type=H.Q4_K, d_type=H.Q4_K)
+    lc, experts, _ = synth_layer(T, api, cfg, 8, seed=3)
+    layer = api.MoeLayer(lc, experts)
+    logits = dev(T, H.router_logits("many", 16, 8, None))
+    x = dev(T, H.activations("many", 16, 512, "f32"))
+    first = layer.forward(logits[:1], x[:1])[2].clone()
+    for i in range(300):
+        if i % 50 == 7:
+            layer.forward(logits, x)              # a 16-token window through the staged kernels, same scratch
+        out = layer.forward(logits[:1], x[:1])[2]
+    T.cuda.synchronize()
+    assert T.equal(out, first)
+    assert layer.error() == 0
+
+
 def test_layer_refusals(T, api):
     cfg = H.CONFIGS["C1"]
     lc = layer_cfg(api, cfg)
