@@ -162,6 +162,25 @@ MAYA_API int maya_expert_grouped(const maya_expert_layout* L, const unsigned lon
                                  const int32_t* ent_tok, int64_t cap_groups, int64_t cap_entries, const void* x_q8_1,
                                  void* scratch, float* out, void* stream, float swiglu_limit);
 
+/* No counterpart in the reference.  maya_expert_grouped for hosts that have no way to hand over scratch memory:
+ * an engine whose arena is fully committed to weights and KV cache before the first token, a plug-in running under a
+ * framework that owns the allocator, a call site inside a region where cudaMalloc is forbidden.  The q8_1 image of h
+ * (the only scratch the grouped path needs) goes into a fixed array inside the library image instead, so this call
+ * takes no scratch pointer and performs no allocation of any kind.
+ *   - Limit: maya_expert_scratch_bytes(cap_entries, n_ff) must not exceed maya_expert_static_scratch_bytes()
+ *     (2 MiB: e.g. 910 entries of FFN width 2048); beyond it the call returns MAYA_ERR_LIMIT, prints why, and
+ *     launches nothing.  The array occupies that much memory on every GPU that loads the library, until exit.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current).  Make that first call outside any stream capture.
+ *   - All calls share the one array and it keeps whatever the previous call left.  Nothing in it needs clearing: every
+ *     entry's slot is written before it is read.  Two calls that may run at the same time on one GPU (different
+ *     streams, different host threads) would overwrite each other's h: serialise them. */
+MAYA_API size_t maya_expert_static_scratch_bytes(void);
+MAYA_API int maya_expert_grouped_static(const maya_expert_layout* L, const unsigned long long* grp_ptr,
+                                        const int32_t* grp_start, const int32_t* n_groups, const int32_t* ent_dst,
+                                        const int32_t* ent_tok, int64_t cap_groups, int64_t cap_entries,
+                                        const void* x_q8_1, float* out, void* stream, float swiglu_limit);
+
 /* Combine ----------------------------------------------------------------------------------------- */
 /* native_moe_combine[_multi] (native_moe.hpp:16-20) / moe_combine (shared_expert.hpp:98): per token
  * y = parts[0] * w[0], then fused multiply-adds in expert order, + shared (NULL: none).  parts [n_tok][k][n_embd]. */

@@ -65,6 +65,9 @@ _SIGNATURES = {
     "maya_expert_scratch_bytes": (c_size_t, [c_int64, c_int64]),
     "maya_expert_grouped": (c_int, [C.POINTER(ExpertLayout), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                     c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_float]),
+    "maya_expert_static_scratch_bytes": (c_size_t, []),
+    "maya_expert_grouped_static": (c_int, [C.POINTER(ExpertLayout), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                           c_int64, c_void_p, c_void_p, c_void_p, c_float]),
     "maya_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "maya_moe_layer_scratch_bytes": (c_size_t, [C.POINTER(MoeLayerDesc), c_int]),
     "maya_moe_layer_error": (c_int, [C.POINTER(MoeLayerDesc), c_int, c_void_p, c_void_p]),

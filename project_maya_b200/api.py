@@ -171,6 +171,17 @@ def native_expert_grouped(L: ExpertLayout, grp_ptr, grp_start, n_groups, ent_dst
                                            _stream(stream), swiglu_limit))
 
 
+def native_expert_grouped_static(L: ExpertLayout, grp_ptr, grp_start, n_groups, ent_dst, ent_tok, cap_groups: int,
+                                 cap_entries: int, x_q8_1, out, swiglu_limit: float = INF, stream=None) -> None:
+    """native_expert_grouped without a scratch argument: for callers that cannot allocate or pass device scratch.
+    The q8_1 image of h lives in a 2 MiB array built into the library (see maya_expert_grouped_static in the header:
+    size limit, first call outside stream capture, calls on one GPU must not overlap)."""
+    _check("native_expert_grouped_static",
+           _lib.load().maya_expert_grouped_static(C.byref(L), _ptr(grp_ptr), _ptr(grp_start), _ptr(n_groups), _ptr(ent_dst),
+                                                  _ptr(ent_tok), cap_groups, cap_entries, _ptr(x_q8_1), _ptr(out),
+                                                  _stream(stream), swiglu_limit))
+
+
 def moe_combine(parts, weights, shared, n_embd: int, k: int, n_tok: int = 1, y=None, stream=None):
     """native_moe_combine[_multi] (native_moe.hpp:16-20) / moe_combine (shared_expert.hpp:98)."""
     y = y if y is not None else torch.empty((n_tok, n_embd), dtype=torch.float32, device="cuda")

@@ -12,6 +12,9 @@
 // entry's result does not depend on which other entries share its group.
 #include <math.h>
 
+#include <cstdio>
+#include <mutex>
+
 #include "maya_dots.cuh"
 #include "maya_internal.cuh"
 
@@ -545,6 +548,60 @@ extern "C" int maya_expert_grouped(const maya_expert_layout* L, const unsigned l
                             (size_t) (n_embd / 32) * kQ81Bytes, scratch, nullptr, 0, nullptr, 0, nullptr, s);
     if (st != MAYA_OK) return st;
     return down_groups(L->d_type, A, (int) cap_groups, n_embd, n_ff, L->down_off, scratch, out, s);
+}
+
+// ------------------------------------------------------------------------------------------------ no-allocation variant
+// Scratch for maya_expert_grouped_static lives in the library image itself: a fixed device array, present on every GPU
+// that loads the library for as long as the process lives.  In host code the array's name is only a handle; the
+// device address the kernels need comes from cudaGetSymbolAddress, asked once per device with that device current.
+constexpr size_t kStaticScratchBytes = (size_t) 2 << 20;
+static __device__ __align__(256) unsigned char g_expert_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {};
+
+// The device address of g_expert_static_scratch on the current device (nullptr + status on failure).
+int static_scratch(void** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return MAYA_ERR_DEVICE; }
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (g_static_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_expert_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            std::fprintf(stderr, "maya_moe: cudaGetSymbolAddress(static scratch): %s\n", cudaGetErrorString(e));
+            cudaGetLastError();
+            return MAYA_ERR_LAUNCH;
+        }
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return MAYA_OK;
+}
+}  // namespace
+
+extern "C" size_t maya_expert_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int maya_expert_grouped_static(const maya_expert_layout* L, const unsigned long long* grp_ptr,
+                                          const int32_t* grp_start, const int32_t* n_groups, const int32_t* ent_dst,
+                                          const int32_t* ent_tok, int64_t cap_groups, int64_t cap_entries,
+                                          const void* x_q8_1, float* out, void* stream, float swiglu_limit) {
+    if (!L) return refuse(MAYA_ERR_ARG);
+    const size_t need = maya_expert_scratch_bytes(cap_entries, L->n_ff);
+    if (cap_entries > 0 && need == 0) return refuse(MAYA_ERR_ARG);
+    if (need > kStaticScratchBytes) {
+        std::fprintf(stderr, "maya_expert_grouped_static: %lld entries of FFN width %lld need %zu bytes of scratch, the "
+                             "built-in array holds %zu; use maya_expert_grouped with caller scratch\n",
+                     (long long) cap_entries, (long long) L->n_ff, need, kStaticScratchBytes);
+        return refuse(MAYA_ERR_LIMIT);
+    }
+    void* scratch = nullptr;
+    const int st = static_scratch(&scratch);
+    if (st != MAYA_OK) return refuse(st);
+    return maya_expert_grouped(L, grp_ptr, grp_start, n_groups, ent_dst, ent_tok, cap_groups, cap_entries, x_q8_1, scratch,
+                               out, stream, swiglu_limit);
 }
 
 extern "C" int maya_moe_combine(const float* parts, const float* weights, const float* shared, float* y, int64_t n_embd,
