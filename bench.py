@@ -383,12 +383,15 @@ def dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, steps: int, 
                 evs[s][1].record(stream)
             stream.synchronize()
     us = float(np.mean([a.elapsed_time(b) for a, b in evs])) * 1e3
+    phases = layers[(steps - 1) % len(layers)].phase_ns(stream)
     peak, kind = measured_peaks()
     alg = algorithmic_bytes_per_token()
     achieved = alg / (us * 1e-6) / 1e9
     return {"bound": "hbm", "kernel": "moe_layer_t1_kernel<IQ2_S, Q8_0> (the whole layer: route, q8_1, gate/up + SwiGLU, down, combine)",
             "achieved": achieved, "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": achieved / peak,
-            "algorithmic_bytes_per_launch": alg, "us_per_launch": us, "launches_timed": steps, "traffic": None}
+            "algorithmic_bytes_per_launch": alg, "us_per_launch": us, "launches_timed": steps, "traffic": None,
+            "block0_phase_end_us": {"route+quantize": phases[1] / 1e3, "gate_up": phases[2] / 1e3, "grid_barrier": phases[3] / 1e3,
+                                    "down+combine": phases[4] / 1e3}}
 
 
 def main() -> None:

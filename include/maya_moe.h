@@ -210,6 +210,9 @@ typedef struct maya_moe_layer {
 MAYA_API size_t maya_moe_layer_scratch_bytes(const maya_moe_layer* L, int n_tokens);
 /* Reads the sticky barrier-error word of a layer scratch (synchronises the stream first). 0 = no error. */
 MAYA_API int maya_moe_layer_error(const maya_moe_layer* L, int n_tokens, const void* scratch, void* stream);
+/* Diagnostic: block 0's wall-clock stamps (ns, %globaltimer) of the last fused single-token launch on this scratch:
+ * start, end of routing/quantizing, end of its gate/up work, past the grid barrier, end.  Synchronises the stream. */
+MAYA_API int maya_moe_layer_phase_ns(const maya_moe_layer* L, const void* scratch, void* stream, unsigned long long* out5);
 /* logits [n_tokens, n_expert] f32; x [n_tokens, n_embd] f32 (x_is_bf16 == 0) or bf16 bits; out [n_tokens, n_embd] f32;
  * ids / weights [n_tokens, k] (outputs, may be NULL... then scratch holds them).  n_tokens <= MAYA_MAX_WIN_TOKENS. */
 MAYA_API int maya_moe_layer_decode(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,

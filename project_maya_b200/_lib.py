@@ -71,6 +71,7 @@ _SIGNATURES = {
     "maya_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "maya_moe_layer_scratch_bytes": (c_size_t, [C.POINTER(MoeLayerDesc), c_int]),
     "maya_moe_layer_error": (c_int, [C.POINTER(MoeLayerDesc), c_int, c_void_p, c_void_p]),
+    "maya_moe_layer_phase_ns": (c_int, [C.POINTER(MoeLayerDesc), c_void_p, c_void_p, C.POINTER(C.c_ulonglong)]),
     "maya_moe_layer_decode": (c_int, [C.POINTER(MoeLayerDesc), c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_size_t, c_void_p]),
     "maya_quantize_weights_host": (c_int, [c_int, c_void_p, c_int64, c_int64, c_void_p]),

@@ -250,6 +250,12 @@ class MoeLayer:
                                                  self.scratch.numel(), _stream(stream)))
         return ids, weights, out
 
+    def phase_ns(self, stream=None):
+        """Block 0's phase stamps of the last fused single-token launch, as offsets in ns from its start."""
+        buf = (C.c_ulonglong * 5)()
+        _check("moe_layer_phase_ns", _lib.load().maya_moe_layer_phase_ns(C.byref(self.desc), _ptr(self.scratch), _stream(stream), buf))
+        return [int(buf[i]) - int(buf[0]) for i in range(5)]
+
     def error(self, stream=None) -> int:
         """The scratch's sticky device-side error word (0 = none); synchronises the stream."""
         return int(_lib.load().maya_moe_layer_error(C.byref(self.desc), self.max_tokens, _ptr(self.scratch), _stream(stream)))

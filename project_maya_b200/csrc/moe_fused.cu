@@ -47,7 +47,7 @@ struct FusedArgs {
     float* weights;            // [k] out
     float* out;                // [n_embd] out
     float* h;                  // scratch [(k + 1)][max(n_ff, n_ff_sh)] f32
-    unsigned* sync;            // scratch: [0] arrivals, [1] epoch, [2] error
+    unsigned* sync;            // scratch: [0] arrivals, [1] epoch, [2] error, [4..13] block 0's phase time stamps (ns)
 };
 
 struct FusedShared {
@@ -78,6 +78,16 @@ __device__ __forceinline__ void q8_1_to_smem(float v, int4* q, float* d, int* is
         d[blk] = __half2float(__float2half_rn(dd));   // the scale as the f16 block field holds it
         isum[blk] = s;
     }
+}
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// block 0's wall-clock stamp of a phase boundary (a 64-bit ns count in two scratch words)
+__device__ __forceinline__ void stamp(unsigned* sync, int i) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) *(volatile unsigned long long*) &sync[4 + 2 * i] = global_ns();
 }
 
 __device__ __forceinline__ bool grid_barrier(unsigned* sync, unsigned epoch) {
@@ -120,6 +130,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     double* s_ex = (double*) (s_cols + (size_t) cols_blocks * 40);
 
     if (tid == 0) sh.epoch = *(volatile unsigned*) &A.sync[1];
+    stamp(A.sync, 0);
 
     // ---------------------------------------------------------------- phase 0
     if (tid < kRouteThreads) {
@@ -147,6 +158,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
         }
     }
     __syncthreads();
+    stamp(A.sync, 1);
     XCols X;
     X.q = cq; X.d = cd; X.isum = cs; X.nblk = nblk_x;
 
@@ -178,7 +190,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             }
         }
     }
+    __syncthreads();
+    stamp(A.sync, 2);
     const bool ok = grid_barrier(A.sync, sh.epoch);
+    stamp(A.sync, 3);
 
     // ---------------------------------------------------------------- phase 2: q8_1(h), down, combine
     if (ok) {
@@ -226,6 +241,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             A.out[o0 + tid] = __fadd_rn(m, has_sh ? sh.part[tid][k] : 0.0f);
         }
     }
+    __syncthreads();
+    stamp(A.sync, 4);
     // the launch's last word: the next launch on this scratch (stream-ordered) starts a new epoch
     if (blockIdx.x == 0 && tid == 0) *(volatile unsigned*) &A.sync[1] = sh.epoch + 1u;
 }

@@ -25,7 +25,7 @@ struct Scratch {
     uint8_t* sh_hq;              // [T][n_ff_sh/32] q8_1
     float* sh_out;               // [T][n_embd]
     float* h;                    // [(k + 1)][max(n_ff, n_ff_sh)] f32: the fused single-token kernel's h
-    unsigned* sync;              // [4]: the fused kernel's barrier counter, epoch, error word (zero before first use)
+    unsigned* sync;              // [16]: the fused kernel's barrier counter, epoch, error word (zero before first use)
     size_t bytes;
 };
 
@@ -37,7 +37,7 @@ Scratch carve(const maya_moe_layer& L, int T, uint8_t* base) {
     auto take = [&](size_t n) { uint8_t* p = base ? base + off : nullptr; off += align_up(n); return p; };
     // the fused kernel's words first: their place must not depend on T (a scratch sized for a window also serves
     // single tokens, and the barrier counter has to survive the calls in between)
-    s.sync = (unsigned*) take(4 * sizeof(unsigned));
+    s.sync = (unsigned*) take(16 * sizeof(unsigned));
     {
         const int ld = L.n_ff > L.n_ff_sh ? L.n_ff : L.n_ff_sh;
         s.h = (float*) take((size_t) (MAYA_MAX_K + 1) * ld * sizeof(float));
@@ -112,6 +112,15 @@ extern "C" int maya_moe_layer_error(const maya_moe_layer* L, int n_tokens, const
     if (cudaStreamSynchronize(as_stream(stream)) != cudaSuccess) return note_launch("layer_error sync");
     if (cudaMemcpy(&word, S.sync + 2, sizeof(word), cudaMemcpyDeviceToHost) != cudaSuccess) return note_launch("layer_error copy");
     return (int) word;
+}
+
+extern "C" int maya_moe_layer_phase_ns(const maya_moe_layer* L, const void* scratch, void* stream, unsigned long long* out5) {
+    if (check_layer(L) != MAYA_OK || !scratch || !out5) return MAYA_ERR_ARG;
+    const Scratch S = carve(*L, 1, (uint8_t*) scratch);
+    if (cudaStreamSynchronize(as_stream(stream)) != cudaSuccess) return note_launch("phase_ns sync");
+    if (cudaMemcpy(out5, S.sync + 4, 5 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess)
+        return note_launch("phase_ns copy");
+    return MAYA_OK;
 }
 
 extern "C" int maya_moe_layer_decode(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
