@@ -187,6 +187,27 @@ MAYA_API int maya_expert_grouped_static(const maya_expert_layout* L, const unsig
 MAYA_API int maya_moe_combine(const float* parts, const float* weights, const float* shared, float* y,
                               int64_t n_embd, int64_t k, int n_tok, void* stream);
 
+/* Prefill grouping and glue ------------------------------------------------------------------------ */
+/* glmb::expert_count (glm_batch.hpp:133): ids [n] (pair i = token i / k, slot i % k) -> counts[e] and the stable rank
+ * of every pair among the pairs of its expert. */
+MAYA_API int maya_expert_count(const int* ids, int n, int n_expert, int* counts, int* rank, void* stream);
+/* The per-expert bases the reference builds on the host after a device-to-host copy of the counts
+ * (src/core/glm_prefill.cu:3239-3255), here on the device: bounds[0] = 0, bounds[e + 1] = bounds[e] + counts[e]. */
+MAYA_API int maya_expert_bounds(const int* counts, int n_expert, int* bounds, void* stream);
+/* glmb::expert_scatter (glm_batch.hpp:139): row = base[ids[i]] + rank[i]; row_tok[row] = i / k; pos[i] = row. */
+MAYA_API int maya_expert_scatter(const int* ids, const int* rank, const int* base, int n, int k, int* row_tok, int* pos,
+                                 void* stream);
+/* glmb::swiglu_rows (glm_batch.hpp:141): h[r][c] = silu(min(gu[r][c], limit)) * clamp(gu[r][n_ff + c], +-limit) over
+ * rows of [gate | up]; ld_h = h's row stride (0: n_ff); h may be gu with ld_h = 2 n_ff. */
+MAYA_API int maya_swiglu_rows(const float* gu, float* h, int rows, int n_ff, float limit, int ld_h, void* stream);
+/* glmb::moe_combine (glm_batch.hpp:153): ffn[t] = sum_j w[t][j] * out[pos[t * k + j]] + sh[t] (sh NULL: none). */
+MAYA_API int maya_moe_combine_rows(const float* out, const int* pos, const float* w, const float* sh, int T, int k,
+                                   int n_embd, float* ffn, void* stream);
+/* glmb::moe_combine_add (glm_batch.hpp:150): ffn[t] += sum over the routes of t whose sorted row is in [lo, hi) of
+ * w * out[row - base]. */
+MAYA_API int maya_moe_combine_add(const float* out, int base, int lo, int hi, const int* pos, const float* w, int T, int k,
+                                  int n_embd, float* ffn, void* stream);
+
 /* Whole decode layer, one call (no single counterpart: the sequence Glm5Model::fast_moe runs,
  * src/core/glm_fast_path.cu:6917-7100: route -> gate/up -> down + combine, the shared expert alongside). */
 typedef struct maya_moe_layer {

@@ -69,6 +69,12 @@ _SIGNATURES = {
     "maya_expert_grouped_static": (c_int, [C.POINTER(ExpertLayout), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                            c_int64, c_void_p, c_void_p, c_void_p, c_float]),
     "maya_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
+    "maya_expert_count": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "maya_expert_bounds": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
+    "maya_expert_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "maya_swiglu_rows": (c_int, [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
+    "maya_moe_combine_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "maya_moe_combine_add": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "maya_moe_layer_scratch_bytes": (c_size_t, [C.POINTER(MoeLayerDesc), c_int]),
     "maya_moe_layer_error": (c_int, [C.POINTER(MoeLayerDesc), c_int, c_void_p, c_void_p]),
     "maya_moe_layer_phase_ns": (c_int, [C.POINTER(MoeLayerDesc), c_void_p, c_void_p, C.POINTER(C.c_ulonglong)]),

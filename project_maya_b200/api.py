@@ -190,6 +190,39 @@ def moe_combine(parts, weights, shared, n_embd: int, k: int, n_tok: int = 1, y=N
     return y
 
 
+# ---------------------------------------------------------------- prefill grouping
+def expert_group(ids, n_expert: int, stream=None):
+    """glmb::expert_count + the device-side bounds scan + glmb::expert_scatter.  ids [T, k] i32 ->
+    (counts [E], bounds [E + 1], pos [T * k], row_tok [T * k]) with no host round trip."""
+    T, k = ids.shape
+    n = T * k
+    dev = ids.device
+    counts = torch.empty(n_expert, dtype=torch.int32, device=dev)
+    rank = torch.empty(n, dtype=torch.int32, device=dev)
+    bounds = torch.empty(n_expert + 1, dtype=torch.int32, device=dev)
+    pos = torch.empty(n, dtype=torch.int32, device=dev)
+    row_tok = torch.empty(n, dtype=torch.int32, device=dev)
+    lib, s = _lib.load(), _stream(stream)
+    _check("expert_count", lib.maya_expert_count(_ptr(ids), n, n_expert, _ptr(counts), _ptr(rank), s))
+    _check("expert_bounds", lib.maya_expert_bounds(_ptr(counts), n_expert, _ptr(bounds), s))
+    _check("expert_scatter", lib.maya_expert_scatter(_ptr(ids), _ptr(rank), _ptr(bounds), n, k, _ptr(row_tok), _ptr(pos), s))
+    return counts, bounds, pos, row_tok
+
+
+def swiglu_rows(gu, n_ff: int, limit: float = INF, stream=None):
+    rows = gu.shape[0]
+    h = torch.empty((rows, n_ff), dtype=torch.float32, device=gu.device)
+    _check("swiglu_rows", _lib.load().maya_swiglu_rows(_ptr(gu), _ptr(h), rows, n_ff, limit, 0, _stream(stream)))
+    return h
+
+
+def moe_combine_rows(out, pos, w, sh, T: int, k: int, n_embd: int, stream=None):
+    ffn = torch.empty((T, n_embd), dtype=torch.float32, device=out.device)
+    _check("moe_combine_rows", _lib.load().maya_moe_combine_rows(_ptr(out), _ptr(pos), _ptr(w), _ptr(sh), T, k, n_embd,
+                                                                _ptr(ffn), _stream(stream)))
+    return ffn
+
+
 # ---------------------------------------------------------------- whole layer
 @dataclass
 class MoeLayerConfig:

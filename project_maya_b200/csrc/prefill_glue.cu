@@ -1,0 +1,160 @@
+// prefill_glue.cu - the prompt path's grouping and glue around the grouped expert GEMM.
+//
+// Reference entry points replaced (src/kernels/cuda/glm_batch.cu:2102-2215, include/strata/kernels/glm_batch.hpp:131-154):
+// expert_count (counts per expert + the stable rank of every routed (token, slot) pair), expert_scatter (sorted row of
+// every pair, token of every sorted row), swiglu_rows, moe_combine / moe_combine_add.  The reference copies the counts
+// to pinned host memory and builds the per-expert bases on the host (src/core/glm_prefill.cu:3239-3255); here
+// maya_expert_bounds does the exclusive scan on the device so the sequence needs no host round trip.
+#include <math.h>
+
+#include "maya_common.cuh"
+
+namespace maya {
+namespace {
+
+// One block per expert: walks all pairs in order, 1024 at a time; a pair's rank is the number of earlier pairs routed to
+// the same expert (ballot + popcount inside a warp, warp totals through shared memory).
+__global__ void __launch_bounds__(1024) expert_count_kernel(const int* __restrict__ ids, int n, int* __restrict__ counts,
+                                                            int* __restrict__ rank) {
+    const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ int s_wc[32];
+    int base = 0;
+    for (int c0 = 0; c0 < n; c0 += 1024) {
+        const int i = c0 + tid;
+        const bool m = i < n && ids[i] == e;
+        const unsigned ballot = __ballot_sync(0xffffffffu, m);
+        if (lane == 0) s_wc[warp] = __popc(ballot);
+        __syncthreads();
+        int off = base, tot = 0;
+        for (int w = 0; w < 32; ++w) {
+            const int c = s_wc[w];
+            if (w < warp) off += c;
+            tot += c;
+        }
+        if (m) rank[i] = off + __popc(ballot & ((1u << lane) - 1u));
+        base += tot;
+        __syncthreads();
+    }
+    if (tid == 0) counts[e] = base;
+}
+
+// bounds[0] = 0, bounds[e + 1] = bounds[e] + counts[e]; one block.
+__global__ void __launch_bounds__(1024) expert_bounds_kernel(const int* __restrict__ counts, int n_expert,
+                                                             int* __restrict__ bounds) {
+    __shared__ int s_part[1024];
+    const int tid = threadIdx.x, per = (n_expert + 1023) / 1024;
+    int local = 0;
+    for (int j = 0; j < per; ++j) {
+        const int e = tid * per + j;
+        if (e < n_expert) local += counts[e];
+    }
+    s_part[tid] = local;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {       // inclusive scan of the per-thread totals
+        const int v = tid >= o ? s_part[tid - o] : 0;
+        __syncthreads();
+        s_part[tid] += v;
+        __syncthreads();
+    }
+    int run = s_part[tid] - local;
+    if (tid == 0) bounds[0] = 0;
+    for (int j = 0; j < per; ++j) {
+        const int e = tid * per + j;
+        if (e < n_expert) { run += counts[e]; bounds[e + 1] = run; }
+    }
+}
+
+__global__ void __launch_bounds__(256) expert_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ rank,
+                                                             const int* __restrict__ base, int n, int k,
+                                                             int* __restrict__ row_tok, int* __restrict__ pos) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int row = base[ids[i]] + rank[i];
+    row_tok[row] = i / k;
+    pos[i] = row;
+}
+
+// h[r][c] = silu(min(g, L)) * clamp(u, +-L) over rows of [gate | up]; h may alias gu (ld_h = 2 n_ff).
+__global__ void __launch_bounds__(256) swiglu_rows_kernel(const float* gu, float* h, int64_t total, int n_ff, int ld_h,
+                                                          float limit) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int64_t r = i / n_ff;
+    const int c = (int) (i - r * n_ff);
+    const float* row = gu + r * 2 * n_ff;
+    h[r * ld_h + c] = swiglu(row[c], row[n_ff + c], limit);
+}
+
+// ffn[t] = sum_j w[t][j] * out[pos[t][j]] (plan order, m = 0 then m += w * o as the reference's loop) + sh[t]
+__global__ void __launch_bounds__(256) combine_rows_kernel(const float* __restrict__ out, const int* __restrict__ pos,
+                                                           const float* __restrict__ w, const float* __restrict__ sh,
+                                                           int k, int n_embd, float* __restrict__ ffn) {
+    const int t = blockIdx.y, e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n_embd) return;
+    float m = 0.0f;
+    for (int j = 0; j < k; ++j) m = __fmaf_rn(w[t * k + j], out[(size_t) pos[t * k + j] * n_embd + e], m);
+    ffn[(size_t) t * n_embd + e] = __fadd_rn(m, sh ? sh[(size_t) t * n_embd + e] : 0.0f);
+}
+
+// ffn[t] += sum over t's routes whose sorted row lies in [lo, hi) of w * out[row - base]
+__global__ void __launch_bounds__(256) combine_add_kernel(const float* __restrict__ out, int base, int lo, int hi,
+                                                          const int* __restrict__ pos, const float* __restrict__ w, int k,
+                                                          int n_embd, float* __restrict__ ffn) {
+    const int t = blockIdx.y, e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n_embd) return;
+    float m = 0.0f;
+    bool any = false;
+    for (int j = 0; j < k; ++j) {
+        const int p = pos[t * k + j];
+        if (p >= lo && p < hi) { m = __fmaf_rn(w[t * k + j], out[(size_t) (p - base) * n_embd + e], m); any = true; }
+    }
+    if (any) ffn[(size_t) t * n_embd + e] = __fadd_rn(ffn[(size_t) t * n_embd + e], m);
+}
+
+}  // namespace
+}  // namespace maya
+
+using namespace maya;
+
+extern "C" int maya_expert_count(const int* ids, int n, int n_expert, int* counts, int* rank, void* stream) {
+    if (n_expert <= 0) return MAYA_OK;
+    if (!counts || n < 0 || (n > 0 && (!ids || !rank))) return refuse(MAYA_ERR_ARG);
+    expert_count_kernel<<<n_expert, 1024, 0, as_stream(stream)>>>(ids, n, counts, rank);
+    return note_launch("expert_count");
+}
+extern "C" int maya_expert_bounds(const int* counts, int n_expert, int* bounds, void* stream) {
+    if (!counts || !bounds || n_expert <= 0) return refuse(MAYA_ERR_ARG);
+    expert_bounds_kernel<<<1, 1024, 0, as_stream(stream)>>>(counts, n_expert, bounds);
+    return note_launch("expert_bounds");
+}
+extern "C" int maya_expert_scatter(const int* ids, const int* rank, const int* base, int n, int k, int* row_tok, int* pos,
+                                   void* stream) {
+    if (n <= 0) return MAYA_OK;
+    if (!ids || !rank || !base || !row_tok || !pos || k <= 0) return refuse(MAYA_ERR_ARG);
+    expert_scatter_kernel<<<(n + 255) / 256, 256, 0, as_stream(stream)>>>(ids, rank, base, n, k, row_tok, pos);
+    return note_launch("expert_scatter");
+}
+extern "C" int maya_swiglu_rows(const float* gu, float* h, int rows, int n_ff, float limit, int ld_h, void* stream) {
+    if (rows <= 0) return MAYA_OK;
+    if (!gu || !h || n_ff <= 0 || ld_h < 0) return refuse(MAYA_ERR_ARG);
+    const int64_t total = (int64_t) rows * n_ff;
+    swiglu_rows_kernel<<<(unsigned) ((total + 255) / 256), 256, 0, as_stream(stream)>>>(gu, h, total, n_ff,
+                                                                                       ld_h ? ld_h : n_ff, limit);
+    return note_launch("swiglu_rows");
+}
+extern "C" int maya_moe_combine_rows(const float* out, const int* pos, const float* w, const float* sh, int T, int k,
+                                     int n_embd, float* ffn, void* stream) {
+    if (T <= 0) return MAYA_OK;
+    if (!out || !pos || !w || !ffn || k <= 0 || n_embd <= 0) return refuse(MAYA_ERR_ARG);
+    const dim3 grid((unsigned) ((n_embd + 255) / 256), (unsigned) T);
+    combine_rows_kernel<<<grid, 256, 0, as_stream(stream)>>>(out, pos, w, sh, k, n_embd, ffn);
+    return note_launch("moe_combine_rows");
+}
+extern "C" int maya_moe_combine_add(const float* out, int base, int lo, int hi, const int* pos, const float* w, int T,
+                                    int k, int n_embd, float* ffn, void* stream) {
+    if (T <= 0 || hi <= lo) return MAYA_OK;
+    if (!out || !pos || !w || !ffn || k <= 0 || n_embd <= 0) return refuse(MAYA_ERR_ARG);
+    const dim3 grid((unsigned) ((n_embd + 255) / 256), (unsigned) T);
+    combine_add_kernel<<<grid, 256, 0, as_stream(stream)>>>(out, base, lo, hi, pos, w, k, n_embd, ffn);
+    return note_launch("moe_combine_add");
+}

@@ -371,3 +371,32 @@ def test_synth_weights_are_valid_blocks(T, api, oracle, t):
     assert abs(float(vals.mean())) < 2e-3
     other = api.synth_weights(t, 1235, 0.02, n_rows, n_cols).cpu().numpy()
     assert not np.array_equal(blocks, other)
+
+
+# ------------------------------------------------------------------------------------------------ prefill grouping
+@pytest.mark.parametrize("n_tok,k,E", [(4096, 8, 256), (33, 3, 12), (1, 8, 64), (1500, 8, 2048)])
+def test_expert_group_matches_oracle(T, api, oracle, n_tok, k, E):
+    rng = H.rng_for("group", n_tok, E)
+    ids = np.stack([rng.permutation(E)[:k] for _ in range(n_tok)]).astype(np.int32)
+    counts, bounds, pos, row_tok = api.expert_group(dev(T, ids), E)
+    c_o, b_o, p_o, r_o = oracle.expert_group(ids, k, E)
+    assert np.array_equal(counts.cpu().numpy(), c_o) and np.array_equal(bounds.cpu().numpy(), b_o)
+    assert np.array_equal(pos.cpu().numpy(), p_o) and np.array_equal(row_tok.cpu().numpy(), r_o)
+    rows = np.sort(pos.cpu().numpy())
+    assert np.array_equal(rows, np.arange(n_tok * k))                    # a permutation of the sorted rows
+
+
+def test_swiglu_rows_and_combine_rows(T, api, oracle):
+    rng = H.rng_for("glue")
+    rows, n_ff, n_embd, n_tok, k = 24, 64, 96, 3, 8
+    gu = (rng.standard_normal((rows, 2 * n_ff)) * 4).astype(np.float32)
+    h = api.swiglu_rows(dev(T, gu), n_ff, 7.0).cpu().numpy()
+    want = np.stack([oracle.swiglu(gu[r, :n_ff], gu[r, n_ff:], 7.0) for r in range(rows)])
+    assert np.allclose(h, want, rtol=2e-6, atol=1e-6)
+    out = rng.standard_normal((rows, n_embd)).astype(np.float32)
+    pos = rng.permutation(rows)[: n_tok * k].astype(np.int32)
+    w = rng.random((n_tok, k)).astype(np.float32)
+    sh = rng.standard_normal((n_tok, n_embd)).astype(np.float32)
+    ffn = api.moe_combine_rows(dev(T, out), dev(T, pos), dev(T, w), dev(T, sh), n_tok, k, n_embd).cpu().numpy()
+    for t in range(n_tok):
+        assert np.array_equal(ffn[t], oracle.combine_down(out[pos[t * k:(t + 1) * k]], w[t], sh[t]))
