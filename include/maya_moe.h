@@ -240,6 +240,57 @@ MAYA_API int maya_moe_layer_decode(const maya_moe_layer* L, const float* logits,
                                    int n_tokens, int* ids, float* weights, float* out, void* scratch,
                                    size_t scratch_bytes, void* stream);
 
+/* Cross-GPU sum of expert partials -------------------------------------------------------------- */
+#define MAYA_PEER_AR_MAX_RANKS 8
+#define MAYA_PEER_AR_BLOCKS 256        /* flag words per (slot, rank): one per block of the summing kernel */
+#define MAYA_PEER_AR_FLAG_STRIDE 32    /* words between flags (128 bytes: one flag per cache line) */
+
+/* PeerArFailure (ds4_kernels.cuh:523-527): written once, by the first wait that ran out. */
+typedef struct maya_peer_ar_failure {
+    unsigned captured, sequence, observed, block, n4, rank, waited_for, pad;
+    unsigned long long elapsed_ns, timeout_ns;
+} maya_peer_ar_failure;
+
+/* PeerAr (ds4_kernels.cuh:536-547) for nm ranks.  Every rank owns, in its own HBM, a receive buffer of
+ * 2 slots x nm rows x stride floats (maya_peer_ar_recv_bytes) and 2 x nm x MAYA_PEER_AR_BLOCKS flags
+ * (maya_peer_ar_flag_bytes), both zeroed (flags start at first_seq - 1 = 0, the first call uses seq 1).
+ * peer_recv / peer_flags are DEVICE arrays of nm pointers: rank m's buffers as mapped into this rank's address space
+ * (peer access or IPC; entry mi = this rank's own).  Calls on each rank's single stream must have matching n and seq,
+ * with no skipped calls; seq wraps modulo 2^32.  A wait longer than timeout_ns sets *error (sticky: later calls return
+ * at once, leaving x as the local partial); the caller must check it after synchronising.  Not graph-replay safe with a
+ * frozen seq. */
+typedef struct maya_peer_ar {
+    float* recv;
+    float* const* peer_recv;
+    unsigned* flags;
+    unsigned* const* peer_flags;
+    unsigned* error;
+    maya_peer_ar_failure* failure;   /* optional */
+    size_t stride;                   /* floats per row, a multiple of 4, >= n */
+    unsigned long long timeout_ns;
+    int nm;
+} maya_peer_ar;
+
+MAYA_API size_t maya_peer_ar_recv_bytes(int nm, size_t stride);
+MAYA_API size_t maya_peer_ar_flag_bytes(int nm);
+/* peer_ar_preload (ds4_kernels.cuh:548): loads the kernels on the current device before any rank spins. */
+MAYA_API int maya_peer_ar_preload(void* stream);
+/* allreduce_peer (ds4_kernels.cuh:546) for nm ranks: x[n] (n % 4 == 0, 16-byte aligned) becomes the sum of the nm
+ * ranks' x in rank order - identical bits on every rank. */
+MAYA_API int maya_allreduce_peer(float* x, int n, const maya_peer_ar* a, int mi, unsigned seq, void* stream);
+/* maya_moe_layer_decode followed by that sum of `out` over the ranks.  One token: the sum runs in the epilogue of the
+ * fused layer kernel (each block pushes the output rows it just combined to every peer, then adds the peers' rows in rank
+ * order) - no separate launch.  2..16 tokens: the window kernels, then maya_allreduce_peer on out[n_tokens * n_embd]. */
+MAYA_API int maya_moe_layer_decode_ar(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
+                                      int n_tokens, int* ids, float* weights, float* out, void* scratch,
+                                      size_t scratch_bytes, const maya_peer_ar* a, int mi, unsigned seq, void* stream);
+/* Set-up helpers (startup only, they allocate and synchronise): a zeroed device buffer another process on the same
+ * machine can map. */
+MAYA_API int maya_peer_buffer_create(size_t bytes, void** ptr, unsigned char handle[64]);
+MAYA_API int maya_peer_buffer_open(const unsigned char handle[64], void** ptr);
+MAYA_API int maya_peer_buffer_close(void* ptr);
+MAYA_API int maya_peer_buffer_destroy(void* ptr);
+
 /* Synthetic expert weights (bench / test support; host-callable generators) ------------------------ */
 /* Quantize rows of f32 weights to a GGUF type (own quantizers: nearest-codeword search for the i-quants).
  * Host memory in, host memory out.  n_cols a multiple of the block size. */

@@ -39,6 +39,18 @@ class MoeLayerDesc(C.Structure):
                 ("expert_lo", c_int), ("expert_hi", c_int), ("shared_here", c_int), ("staged", c_int)]
 
 
+class PeerArFailure(C.Structure):
+    _fields_ = [("captured", C.c_uint), ("sequence", C.c_uint), ("observed", C.c_uint), ("block", C.c_uint),
+                ("n4", C.c_uint), ("rank", C.c_uint), ("waited_for", C.c_uint), ("pad", C.c_uint),
+                ("elapsed_ns", C.c_ulonglong), ("timeout_ns", C.c_ulonglong)]
+
+
+class PeerArDesc(C.Structure):
+    _fields_ = [("recv", c_void_p), ("peer_recv", c_void_p), ("flags", c_void_p), ("peer_flags", c_void_p),
+                ("error", c_void_p), ("failure", c_void_p), ("stride", c_size_t), ("timeout_ns", C.c_ulonglong),
+                ("nm", c_int)]
+
+
 _SIGNATURES = {
     "maya_version": (C.c_char_p, []),
     "maya_last_cuda_error": (c_int, []),
@@ -80,6 +92,16 @@ _SIGNATURES = {
     "maya_moe_layer_phase_ns": (c_int, [C.POINTER(MoeLayerDesc), c_void_p, c_void_p, C.POINTER(C.c_ulonglong)]),
     "maya_moe_layer_decode": (c_int, [C.POINTER(MoeLayerDesc), c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_size_t, c_void_p]),
+    "maya_peer_ar_recv_bytes": (c_size_t, [c_int, c_size_t]),
+    "maya_peer_ar_flag_bytes": (c_size_t, [c_int]),
+    "maya_peer_ar_preload": (c_int, [c_void_p]),
+    "maya_allreduce_peer": (c_int, [c_void_p, c_int, C.POINTER(PeerArDesc), c_int, C.c_uint, c_void_p]),
+    "maya_moe_layer_decode_ar": (c_int, [C.POINTER(MoeLayerDesc), c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_size_t, C.POINTER(PeerArDesc), c_int, C.c_uint, c_void_p]),
+    "maya_peer_buffer_create": (c_int, [c_size_t, C.POINTER(c_void_p), C.c_char_p]),
+    "maya_peer_buffer_open": (c_int, [C.c_char_p, C.POINTER(c_void_p)]),
+    "maya_peer_buffer_close": (c_int, [c_void_p]),
+    "maya_peer_buffer_destroy": (c_int, [c_void_p]),
     "maya_quantize_weights_host": (c_int, [c_int, c_void_p, c_int64, c_int64, c_void_p]),
     "maya_synth_weights": (c_int, [c_int, c_uint64, c_float, c_int64, c_int64, c_void_p, c_void_p]),
 }

@@ -270,13 +270,20 @@ class MoeLayer:
             raise MayaError("moe_layer_scratch_bytes", -1)
         self.scratch = torch.zeros(nbytes, dtype=torch.uint8, device=experts.device)   # zeroed: holds a barrier counter
 
-    def forward(self, logits, x, ids=None, weights=None, out=None, stream=None):
+    def forward(self, logits, x, ids=None, weights=None, out=None, stream=None, peer=None):
         T = logits.shape[0]
         dev = logits.device
         ids = ids if ids is not None else torch.empty((T, self.cfg.k), dtype=torch.int32, device=dev)
         weights = weights if weights is not None else torch.empty((T, self.cfg.k), dtype=torch.float32, device=dev)
         out = out if out is not None else torch.empty((T, self.cfg.n_embd), dtype=torch.float32, device=dev)
         assert x.dtype in (torch.float32, torch.bfloat16)
+        if peer is not None:     # expert-parallel: `out` becomes the rank-ordered sum over the group (peer.PeerRank)
+            _check("moe_layer_decode_ar",
+                   _lib.load().maya_moe_layer_decode_ar(C.byref(self.desc), _ptr(logits), _ptr(x), int(x.dtype == torch.bfloat16),
+                                                        T, _ptr(ids), _ptr(weights), _ptr(out), _ptr(self.scratch),
+                                                        self.scratch.numel(), C.byref(peer.desc), peer.mi, peer.next_seq(),
+                                                        _stream(stream)))
+            return ids, weights, out
         _check("moe_layer_decode",
                _lib.load().maya_moe_layer_decode(C.byref(self.desc), _ptr(logits), _ptr(x), int(x.dtype == torch.bfloat16), T,
                                                  _ptr(ids), _ptr(weights), _ptr(out), _ptr(self.scratch),

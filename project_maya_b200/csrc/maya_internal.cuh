@@ -33,6 +33,7 @@ int win_combine(const unsigned long long* plan_ptr, const float* plan_w, int T, 
 // The fused single-token layer kernel (moe_fused.cu).
 bool fused_t1_supported(const maya_moe_layer& L);
 int fused_t1(const maya_moe_layer& L, const float* logits, const void* x, int x_is_bf16, int* ids, float* weights,
-             float* out, float* h_scratch, unsigned* sync, cudaStream_t s);
+             float* out, float* h_scratch, unsigned* sync, const maya_peer_ar* ar, int ar_rank, unsigned ar_seq,
+             cudaStream_t s);
 
 }  // namespace maya

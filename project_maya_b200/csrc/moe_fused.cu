@@ -22,6 +22,7 @@
 
 #include "maya_dots_t1.cuh"
 #include "maya_internal.cuh"
+#include "maya_peer_ar.cuh"
 #include "maya_router.cuh"
 
 namespace maya {
@@ -47,6 +48,9 @@ struct FusedArgs {
     float* weights;            // [k] out
     float* out;                // [n_embd] out
     float* h;                  // scratch [(k + 1)][max(n_ff, n_ff_sh)] f32
+    maya_peer_ar ar;           // ar.nm >= 2: sum `out` over the ranks in the epilogue
+    int ar_rank;
+    unsigned ar_seq;
     unsigned* sync;            // scratch: [0] arrivals, [1] epoch, [2] error, [4..13] block 0's phase time stamps (ns)
 };
 
@@ -206,7 +210,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
         }
         __syncthreads();
         int o0, o1;
-        slice(n_embd, gridDim.x, blockIdx.x, o0, o1);
+        slice(n_embd / 4, gridDim.x, blockIdx.x, o0, o1);     // whole float4s: the cross-rank sum moves 16 bytes a lane
+        o0 *= 4;
+        o1 *= 4;
         const int nrows = o1 - o0, npairs = (nrows + 1) / 2;
         const size_t drb = row_bytes(T, n_ff), down_off = 2 * (size_t) n_ff * row_bytes(T, n_embd);
         for (int it = warp; it < npairs * ne; it += NW) {
@@ -241,6 +247,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             A.out[o0 + tid] = __fadd_rn(m, has_sh ? sh.part[tid][k] : 0.0f);
         }
     }
+    // ---------------------------------------------------------------- epilogue: the cross-rank sum of this block's rows
+    if (A.ar.nm >= 2) {
+        __syncthreads();
+        int u0, u1;
+        slice(n_embd / 4, gridDim.x, blockIdx.x, u0, u1);
+        peer_allreduce_block(A.out, u0, u1, A.ar, A.ar_rank, A.ar_seq, blockIdx.x);
+    }
     __syncthreads();
     stamp(A.sync, 4);
     // the launch's last word: the next launch on this scratch (stream-ordered) starts a new epoch
@@ -265,7 +278,8 @@ int launch_fused(const FusedArgs& A, cudaStream_t s) {
     if (cudaFuncSetAttribute(moe_layer_t1_kernel<T, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess)
         return note_launch("fused smem attribute");
     int grid = cached_grid;
-    if ((A.n_embd + grid - 1) / grid > kMaxSliceRows) return refuse(MAYA_ERR_LIMIT);
+    if (4 * ((A.n_embd / 4 + grid - 1) / grid) > kMaxSliceRows || A.n_embd % 4) return refuse(MAYA_ERR_LIMIT);
+    if (A.ar.nm >= 2 && grid > MAYA_PEER_AR_BLOCKS) return refuse(MAYA_ERR_LIMIT);
     FusedArgs args = A;
     void* params[] = {&args};
     cudaLaunchCooperativeKernel((const void*) moe_layer_t1_kernel<T, TS>, dim3(grid), dim3(kFusedThreads), params, smem, s);
@@ -283,8 +297,10 @@ bool fused_t1_supported(const maya_moe_layer& L) {
 }
 
 int fused_t1(const maya_moe_layer& L, const float* logits, const void* x, int x_is_bf16, int* ids, float* weights,
-             float* out, float* h_scratch, unsigned* sync, cudaStream_t s) {
+             float* out, float* h_scratch, unsigned* sync, const maya_peer_ar* ar, int ar_rank, unsigned ar_seq,
+             cudaStream_t s) {
     FusedArgs A{};
+    if (ar != nullptr) { A.ar = *ar; A.ar_rank = ar_rank; A.ar_seq = ar_seq; }
     A.logits = logits; A.x = x; A.x_is_bf16 = x_is_bf16;
     A.n_embd = L.n_embd; A.n_ff = L.n_ff; A.n_expert = L.n_expert; A.k = L.k;
     A.experts = (const uint8_t*) L.experts; A.expert_stride = L.expert_stride;

@@ -123,9 +123,30 @@ extern "C" int maya_moe_layer_phase_ns(const maya_moe_layer* L, const void* scra
     return MAYA_OK;
 }
 
+static int layer_decode(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16, int n_tokens, int* ids,
+                        float* weights, float* out, void* scratch, size_t scratch_bytes, const maya_peer_ar* ar, int mi,
+                        unsigned seq, void* stream);
+
 extern "C" int maya_moe_layer_decode(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
                                      int n_tokens, int* ids, float* weights, float* out, void* scratch,
                                      size_t scratch_bytes, void* stream) {
+    return layer_decode(L, logits, x, x_is_bf16, n_tokens, ids, weights, out, scratch, scratch_bytes, nullptr, 0, 0, stream);
+}
+
+extern "C" int maya_moe_layer_decode_ar(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
+                                        int n_tokens, int* ids, float* weights, float* out, void* scratch,
+                                        size_t scratch_bytes, const maya_peer_ar* a, int mi, unsigned seq, void* stream) {
+    if (!a || a->nm < 2 || a->nm > MAYA_PEER_AR_MAX_RANKS || mi < 0 || mi >= a->nm || !a->recv || !a->peer_recv ||
+        !a->flags || !a->peer_flags || !a->error || a->timeout_ns == 0 || a->stride % 4)
+        return refuse(MAYA_ERR_ARG);
+    if (L && n_tokens > 0 && (size_t) n_tokens * L->n_embd > a->stride) return refuse(MAYA_ERR_ARG);
+    if (out && !aligned16(out)) return refuse(MAYA_ERR_ARG);
+    return layer_decode(L, logits, x, x_is_bf16, n_tokens, ids, weights, out, scratch, scratch_bytes, a, mi, seq, stream);
+}
+
+static int layer_decode(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16, int n_tokens, int* ids,
+                        float* weights, float* out, void* scratch, size_t scratch_bytes, const maya_peer_ar* ar, int mi,
+                        unsigned seq, void* stream) {
     int st = check_layer(L);
     if (st != MAYA_OK) return refuse(st);
     if (n_tokens < 1 || n_tokens > MAYA_MAX_WIN_TOKENS) return refuse(MAYA_ERR_LIMIT);
@@ -137,7 +158,7 @@ extern "C" int maya_moe_layer_decode(const maya_moe_layer* L, const float* logit
     int* d_ids = ids ? ids : S.ids;
     float* d_w = weights ? weights : S.weights;
     if (T == 1 && !L->staged && fused_t1_supported(*L))
-        return fused_t1(*L, logits, x, x_is_bf16, d_ids, d_w, out, S.h, S.sync, s);
+        return fused_t1(*L, logits, x, x_is_bf16, d_ids, d_w, out, S.h, S.sync, ar, mi, seq, s);
 
     st = maya_router_top10(logits, T, L->n_expert, L->k, d_ids, d_w, stream);
     if (st != MAYA_OK) return st;
@@ -175,8 +196,9 @@ extern "C" int maya_moe_layer_decode(const maya_moe_layer* L, const float* logit
         st = maya_moe_gate_up(L->gu_type, &P, L->k, L->n_embd, L->n_ff, L->limit, S.xq, S.hq,
                               shared ? sh_blob + sh_down_off : nullptr, L->sh_d_type, S.sh_hq, L->n_ff_sh, S.sh_out, stream);
         if (st != MAYA_OK) return st;
-        return maya_moe_down(L->d_type, &P, L->k, L->n_embd, L->n_ff, down_off, S.hq, shared ? S.sh_out : nullptr, out,
-                             stream);
+        st = maya_moe_down(L->d_type, &P, L->k, L->n_embd, L->n_ff, down_off, S.hq, shared ? S.sh_out : nullptr, out, stream);
+        if (st != MAYA_OK || ar == nullptr) return st;
+        return maya_allreduce_peer(out, L->n_embd, ar, mi, seq, stream);
     }
     if (shared) {
         for (int c0 = 0; c0 < T; c0 += MAYA_MAX_COLS) {
@@ -206,5 +228,7 @@ extern "C" int maya_moe_layer_decode(const maya_moe_layer* L, const float* logit
     W.n_ff = L->n_ff;
     W.limit = L->limit;
     W.down_off = down_off;
-    return maya_moe_win_experts(L->gu_type, L->d_type, &W, stream);
+    st = maya_moe_win_experts(L->gu_type, L->d_type, &W, stream);
+    if (st != MAYA_OK || ar == nullptr) return st;
+    return maya_allreduce_peer(out, T * L->n_embd, ar, mi, seq, stream);
 }
