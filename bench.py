@@ -258,9 +258,15 @@ def gpu_arm(args) -> None:
     stage_l = torch.empty((K, E), dtype=torch.float32, device="cuda")
     stage_x = torch.empty((K, Hd), dtype=torch.bfloat16, device="cuda")
 
+    peer = None
+    if world > 1 and args.ar == "peer":
+        from project_maya_b200.peer import PeerGroup
+        peer = PeerGroup.over_processes(rank, world, Hd, timeout_ms=5000.0)
+        peer.device_seq = True      # sequence numbers counted on the device: the K steps can be captured in a graph
+
     def step(s: int, l_row, x_row):
-        layers[s % len(layers)].forward(l_row, x_row, ids_d[s:s + 1], w_d[s:s + 1], out_d[s:s + 1])
-        if world > 1:
+        layers[s % len(layers)].forward(l_row, x_row, ids_d[s:s + 1], w_d[s:s + 1], out_d[s:s + 1], peer=peer)
+        if world > 1 and peer is None:
             dist.all_reduce(out_d[s:s + 1])
 
     def step_dev(s: int):
@@ -282,7 +288,7 @@ def gpu_arm(args) -> None:
             step_e2e(s)
     stream.synchronize()
 
-    use_graph = world == 1
+    use_graph = world == 1 or peer is not None
     launches0 = lib.maya_launch_count()
     if use_graph:
         g_dev, g_e2e = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
@@ -343,7 +349,8 @@ def gpu_arm(args) -> None:
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "int8 x int8 -> f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "layers_resident": len(layers),
                        "l2": "inputs larger than L2: steps rotate over %d resident layers and 256 tokens" % len(layers),
-                       "launch": "CUDA graph of the K steps" if use_graph else "eager launches + NCCL all-reduce of the partials",
+                       "launch": ("CUDA graph of the K steps" + (", partial outputs summed over peer HBM in the layer kernel's epilogue" if peer is not None else ""))
+                       if use_graph else "eager launches + NCCL all-reduce of the partial outputs (comparison baseline)",
                        "parallelism": "1 GPU" if world == 1 else f"expert-parallel {world} x {per} experts, shared expert on rank 0"},
             "hbm_gbs": bytes_tok * value / 1e9, "hbm_frac_of_%s_peak" % peak_kind: bytes_tok * value / 1e9 / peak,
             "hbm_frac_of_nominal_8TBs": bytes_tok * value / 8e12,
@@ -361,6 +368,8 @@ def gpu_arm(args) -> None:
                                     "sample": "tokens 0..3 of the 256, once after a warm-up token; " + note}
         print(json.dumps(line), flush=True)
     if world > 1:
+        if peer is not None and peer.poisoned():
+            raise SystemExit("the peer all-reduce timed out: results invalid")
         dist.barrier()
         dist.destroy_process_group()
 
@@ -402,6 +411,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ar", default="peer", choices=["peer", "nccl"], help="N > 1: how the ranks' partial outputs are summed")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)

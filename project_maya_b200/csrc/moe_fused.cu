@@ -60,6 +60,9 @@ struct FusedShared {
     float w[MAYA_MAX_K];
     float part[kMaxSliceRows][MAYA_MAX_K + 1];
     unsigned epoch;
+    unsigned ar_seq;
+    int ve[MAYA_MAX_K];        // the plan entries this rank computes (blob address != 0), in plan order
+    int nv;
 };
 
 // balanced contiguous split of n rows over nb blocks
@@ -133,7 +136,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     int* cs = (int*) (s_cols + (size_t) cols_blocks * 36);
     double* s_ex = (double*) (s_cols + (size_t) cols_blocks * 40);
 
-    if (tid == 0) sh.epoch = *(volatile unsigned*) &A.sync[1];
+    if (tid == 0) {
+        sh.epoch = *(volatile unsigned*) &A.sync[1];
+        sh.ar_seq = A.ar_seq != 0u || A.ar.seq_counter == nullptr ? A.ar_seq : *(volatile unsigned*) A.ar.seq_counter + 1u;
+    }
     stamp(A.sync, 0);
 
     // ---------------------------------------------------------------- phase 0
@@ -152,6 +158,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             if (blockIdx.x == 0) { A.ids[tid] = e; A.weights[tid] = sh.route.val[tid]; }
         }
         if (tid == 0) sh.ptr[k] = has_sh ? (unsigned long long) A.shared : 0ull;
+        NamedSync<1, kRouteThreads>::sync();
+        if (tid == 0) {     // compact the entries that are this rank's: skipped ones must not leave warps idle
+            int nv = 0;
+            for (int i = 0; i < k; ++i)
+                if (sh.ptr[i] != 0ull) sh.ve[nv++] = i;
+            sh.nv = nv;
+        }
     } else {
         const int t2 = tid - kRouteThreads, n2 = kFusedThreads - kRouteThreads;
         load_tab_rep<T>(s_tab, t2, n2);
@@ -172,13 +185,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
         slice(n_ff, gridDim.x, blockIdx.x, r0, r1);            // routed experts' rows
         int q0 = 0, q1 = 0;
         if (has_sh) slice(A.n_ff_sh, gridDim.x, blockIdx.x, q0, q1);
-        const int nr = r1 - r0, n_routed = nr * k, n_items = n_routed + (q1 - q0);
+        const int nr = r1 - r0, n_routed = nr * sh.nv, n_items = n_routed + (q1 - q0);
         const size_t rb = row_bytes(T, n_embd);
         for (int it = warp; it < n_items; it += NW) {
             if (it < n_routed) {
-                const int e = it / nr, r = r0 + it - e * nr;
+                const int ei = it / nr, r = r0 + it - ei * nr, e = sh.ve[ei];
                 const unsigned long long p = sh.ptr[e];
-                if (p == 0ull) continue;
                 const uint8_t* blob = (const uint8_t*) p;
                 const uint8_t* rows[2] = {blob + (size_t) r * rb, blob + (size_t) (n_ff + r) * rb};
                 float o[2];
@@ -204,8 +216,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
         for (int b = warp; b < ne * nblk_h; b += NW) {
             const int e = b / nblk_h, kb = b - e * nblk_h;
             const int width = e < k ? n_ff : A.n_ff_sh;
+            if (sh.ptr[e] == 0ull) continue;         // another rank's expert: its column is never read
             float v = 0.0f;
-            if (sh.ptr[e] != 0ull && kb * 32 < width) v = __ldcg(&A.h[(size_t) e * h_ld + kb * 32 + lane]);
+            if (kb * 32 < width) v = __ldcg(&A.h[(size_t) e * h_ld + kb * 32 + lane]);
             q8_1_to_smem(v, cq, cd, cs, b, lane);
         }
         __syncthreads();
@@ -215,12 +228,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
         o1 *= 4;
         const int nrows = o1 - o0, npairs = (nrows + 1) / 2;
         const size_t drb = row_bytes(T, n_ff), down_off = 2 * (size_t) n_ff * row_bytes(T, n_embd);
-        for (int it = warp; it < npairs * ne; it += NW) {
-            const int e = it / npairs, pr = it - e * npairs;
+        const int nvt = sh.nv + (has_sh ? 1 : 0);
+        for (int it = warp; it < npairs * nvt; it += NW) {
+            const int ei = it / npairs, pr = it - ei * npairs;
+            const int e = ei < sh.nv ? sh.ve[ei] : k;
             const int ra = o0 + 2 * pr, rb2 = min(ra + 1, o1 - 1);
             const unsigned long long p = sh.ptr[e];
             float o[2] = {0.0f, 0.0f};
-            if (p != 0ull) {
+            {
                 XCols H;
                 H.q = cq + (size_t) 2 * e * nblk_h; H.d = cd + (size_t) e * nblk_h; H.isum = cs + (size_t) e * nblk_h;
                 H.nblk = nblk_h;
@@ -252,12 +267,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
         __syncthreads();
         int u0, u1;
         slice(n_embd / 4, gridDim.x, blockIdx.x, u0, u1);
-        peer_allreduce_block(A.out, u0, u1, A.ar, A.ar_rank, A.ar_seq, blockIdx.x);
+        peer_allreduce_block(A.out, u0, u1, A.ar, A.ar_rank, sh.ar_seq, blockIdx.x);
     }
     __syncthreads();
     stamp(A.sync, 4);
     // the launch's last word: the next launch on this scratch (stream-ordered) starts a new epoch
-    if (blockIdx.x == 0 && tid == 0) *(volatile unsigned*) &A.sync[1] = sh.epoch + 1u;
+    if (blockIdx.x == 0 && tid == 0) {
+        *(volatile unsigned*) &A.sync[1] = sh.epoch + 1u;
+        if (A.ar.nm >= 2 && A.ar_seq == 0u && A.ar.seq_counter != nullptr) *(volatile unsigned*) A.ar.seq_counter = sh.ar_seq;
+    }
 }
 
 template<int T, int TS>

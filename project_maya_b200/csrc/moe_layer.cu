@@ -141,6 +141,8 @@ extern "C" int maya_moe_layer_decode_ar(const maya_moe_layer* L, const float* lo
         return refuse(MAYA_ERR_ARG);
     if (L && n_tokens > 0 && (size_t) n_tokens * L->n_embd > a->stride) return refuse(MAYA_ERR_ARG);
     if (out && !aligned16(out)) return refuse(MAYA_ERR_ARG);
+    if (seq == 0u && (a->seq_counter == nullptr || n_tokens != 1 || (L && (L->staged || !fused_t1_supported(*L)))))
+        return refuse(MAYA_ERR_ARG);   // the device-side sequence number exists only in the fused single-token kernel
     return layer_decode(L, logits, x, x_is_bf16, n_tokens, ids, weights, out, scratch, scratch_bytes, a, mi, seq, stream);
 }
 

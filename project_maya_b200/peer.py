@@ -27,8 +27,11 @@ class PeerRank:
         self.failure = torch.zeros(C.sizeof(PeerArFailure), dtype=torch.uint8, device="cuda")
         self.recv_tab = torch.tensor(peer_recv, dtype=torch.int64, device="cuda")
         self.flag_tab = torch.tensor(peer_flags, dtype=torch.int64, device="cuda")
+        self.seq_counter = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.desc = PeerArDesc(recv_ptr, self.recv_tab.data_ptr(), flags_ptr, self.flag_tab.data_ptr(),
-                               self.error.data_ptr(), self.failure.data_ptr(), stride, int(timeout_ms * 1e6), nm)
+                               self.error.data_ptr(), self.failure.data_ptr(), stride, int(timeout_ms * 1e6), nm,
+                               self.seq_counter.data_ptr())
+        self.device_seq = False     # True: single-token layer calls take their sequence number from seq_counter
         self.seq = 0
         self.keep = keep
 

@@ -106,6 +106,24 @@ def layer_ep_worker(rank: int, world: int, port: int, q):
             want = np.stack([orc.allreduce_in_order(np.stack([p[r] for p in parts])) for r in range(parts[0].shape[0])])
             if got.cpu().numpy().tobytes() != want.tobytes():
                 bad += 1
+        # sequence numbers counted on the device: three single-token calls captured in a CUDA graph, replayed twice
+        peer.seq_counter.fill_(peer.seq)
+        peer.device_seq = True
+        ids_g = torch.empty((3, 1, k), dtype=torch.int32, device="cuda")
+        w_g = torch.empty((3, 1, k), dtype=torch.float32, device="cuda")
+        out_g = torch.zeros((3, 1, n_embd), dtype=torch.float32, device="cuda")
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for t in range(3):
+                layer.forward(ld[t:t + 1], xd[t:t + 1], ids_g[t], w_g[t], out_g[t], peer=peer)
+        for _ in range(2):
+            out_g.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            for t in range(3):
+                if out_g[t].cpu().numpy().tobytes() != results[t].cpu().numpy().tobytes():
+                    bad += 1
         # every rank holds the same bits
         mine = np.concatenate([r.cpu().numpy().reshape(-1) for r in results])
         gathered = [None] * world
