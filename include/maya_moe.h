@@ -208,6 +208,44 @@ MAYA_API int maya_moe_combine_rows(const float* out, const int* pos, const float
 MAYA_API int maya_moe_combine_add(const float* out, int base, int lo, int hi, const int* pos, const float* w, int T, int k,
                                   int n_embd, float* ffn, void* stream);
 
+/* Prompt-path grouped GEMM on the tensor cores --------------------------------------------------------- */
+/* mmq::supported (include/strata/prefill/moe_mmq.hpp:16): types the grouped GEMM takes (Q8_0 and Q4_K). */
+MAYA_API int maya_mmq_supported(int type);
+/* mmq::q8_bytes (moe_mmq.hpp:20): bytes of `rows` activation rows of `cols` values as q8_1 blocks, row after row
+ * (cols / 32 blocks of 36 bytes each; the reference pads rows to 512 values for llama.cpp's tile loader, this
+ * layout needs no padding).  0 for cols % 32 != 0. */
+MAYA_API size_t maya_mmq_q8_bytes(int64_t rows, int64_t cols);
+/* mmq::quantize (moe_mmq.hpp:34): output row i = q8_1 of row ids[i] of x (row i when ids is NULL); x has ld floats a
+ * row.  `type` is the weight type the product will use (checked with maya_mmq_supported; the layout is the same). */
+MAYA_API int maya_mmq_quantize(const float* x, const int32_t* ids, void* xq, int type, int64_t cols, int64_t ld,
+                               int64_t rows, void* stream);
+/* The same from bf16 activations (raw bf16 bits, widened to f32 exactly); ld in bf16 elements. */
+MAYA_API int maya_mmq_quantize_bf16(const uint16_t* x, const int32_t* ids, void* xq, int type, int64_t cols, int64_t ld,
+                                    int64_t rows, void* stream);
+/* mmq::Product (moe_mmq.hpp:41-53), field for field, plus two optional fields the reference has no need of. */
+typedef struct maya_mmq_product {
+    const void* w;               /* n experts' matrices, expert_bytes apart; 16-byte aligned */
+    int type;
+    int64_t w_rows, w_cols;      /* one expert's matrix: GGUF rows of w_cols values (w_cols % 256 == 0) */
+    size_t expert_bytes;         /* a whole number of the type's blocks, a multiple of 16 */
+    int n;
+    const void* xq;              /* maya_mmq_quantize's output, total_rows rows */
+    const int32_t* bounds;       /* device, n + 1 entries (more with expert_map) */
+    const int32_t* ids;          /* dst row = ids[row]; NULL: identity */
+    int64_t total_rows, max_rows;/* rows of xq; max_rows is not needed here (the grid is sized from total_rows) */
+    float* dst;
+    int64_t ld_dst;
+    const int32_t* expert_map;   /* NULL, or device table: matrix i of w uses bounds[expert_map[i]] (a staged group) */
+    unsigned* error;             /* NULL, or device word set to 1 when a bounded wait inside the kernel ran out */
+} maya_mmq_product;
+/* mmq::Context::run (moe_mmq.hpp:74): for matrix e, rows [bounds[e], bounds[e+1]) of xq times its [w_rows, w_cols]
+ * matrix into dst[ids[row]][0 .. w_rows).  w_rows % 128 == 0.  No scratch, no host synchronisation. */
+MAYA_API int maya_mmq_run(const maya_mmq_product* p, void* stream);
+/* mmq::Context::run_glu (moe_mmq.hpp:81): w_rows = 2 n_ff gate-then-up rows; dst row gets
+ * silu(min(gate, limit)) * clamp(up, +-limit) in its first n_ff floats (limit = INFINITY: plain SwiGLU), equal
+ * bit for bit to maya_mmq_run followed by maya_swiglu_rows.  n_ff % 128 == 0. */
+MAYA_API int maya_mmq_run_glu(const maya_mmq_product* p, float limit, void* stream);
+
 /* Whole decode layer, one call (no single counterpart: the sequence Glm5Model::fast_moe runs,
  * src/core/glm_fast_path.cu:6917-7100: route -> gate/up -> down + combine, the shared expert alongside). */
 typedef struct maya_moe_layer {
@@ -269,6 +307,8 @@ typedef struct maya_peer_ar {
     size_t stride;                   /* floats per row, a multiple of 4, >= n */
     unsigned long long timeout_ns;
     int nm;
+    unsigned* seq_counter;           /* optional device word (zeroed): lets maya_moe_layer_decode_ar take its sequence
+                                        number from the device (seq argument 0), so a captured CUDA graph can be replayed */
 } maya_peer_ar;
 
 MAYA_API size_t maya_peer_ar_recv_bytes(int nm, size_t stride);
@@ -280,7 +320,9 @@ MAYA_API int maya_peer_ar_preload(void* stream);
 MAYA_API int maya_allreduce_peer(float* x, int n, const maya_peer_ar* a, int mi, unsigned seq, void* stream);
 /* maya_moe_layer_decode followed by that sum of `out` over the ranks.  One token: the sum runs in the epilogue of the
  * fused layer kernel (each block pushes the output rows it just combined to every peer, then adds the peers' rows in rank
- * order) - no separate launch.  2..16 tokens: the window kernels, then maya_allreduce_peer on out[n_tokens * n_embd]. */
+ * order) - no separate launch.  2..16 tokens: the window kernels, then maya_allreduce_peer on out[n_tokens * n_embd].
+ * seq == 0 (single token only): the kernel uses *a->seq_counter + 1 and stores it back when it ends, so every rank's
+ * n-th call carries n without the host counting - the form to capture in a CUDA graph. */
 MAYA_API int maya_moe_layer_decode_ar(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
                                       int n_tokens, int* ids, float* weights, float* out, void* scratch,
                                       size_t scratch_bytes, const maya_peer_ar* a, int mi, unsigned seq, void* stream);

@@ -39,6 +39,13 @@ class MoeLayerDesc(C.Structure):
                 ("expert_lo", c_int), ("expert_hi", c_int), ("shared_here", c_int), ("staged", c_int)]
 
 
+class MmqProduct(C.Structure):
+    _fields_ = [("w", c_void_p), ("type", c_int), ("w_rows", c_int64), ("w_cols", c_int64), ("expert_bytes", c_size_t),
+                ("n", c_int), ("xq", c_void_p), ("bounds", c_void_p), ("ids", c_void_p), ("total_rows", c_int64),
+                ("max_rows", c_int64), ("dst", c_void_p), ("ld_dst", c_int64), ("expert_map", c_void_p),
+                ("error", c_void_p)]
+
+
 class PeerArFailure(C.Structure):
     _fields_ = [("captured", C.c_uint), ("sequence", C.c_uint), ("observed", C.c_uint), ("block", C.c_uint),
                 ("n4", C.c_uint), ("rank", C.c_uint), ("waited_for", C.c_uint), ("pad", C.c_uint),
@@ -48,7 +55,7 @@ class PeerArFailure(C.Structure):
 class PeerArDesc(C.Structure):
     _fields_ = [("recv", c_void_p), ("peer_recv", c_void_p), ("flags", c_void_p), ("peer_flags", c_void_p),
                 ("error", c_void_p), ("failure", c_void_p), ("stride", c_size_t), ("timeout_ns", C.c_ulonglong),
-                ("nm", c_int)]
+                ("nm", c_int), ("seq_counter", c_void_p)]
 
 
 _SIGNATURES = {
@@ -86,6 +93,12 @@ _SIGNATURES = {
     "maya_expert_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "maya_swiglu_rows": (c_int, [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
     "maya_moe_combine_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "maya_mmq_supported": (c_int, [c_int]),
+    "maya_mmq_q8_bytes": (c_size_t, [c_int64, c_int64]),
+    "maya_mmq_quantize": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p]),
+    "maya_mmq_quantize_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p]),
+    "maya_mmq_run": (c_int, [C.POINTER(MmqProduct), c_void_p]),
+    "maya_mmq_run_glu": (c_int, [C.POINTER(MmqProduct), c_float, c_void_p]),
     "maya_moe_combine_add": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "maya_moe_layer_scratch_bytes": (c_size_t, [C.POINTER(MoeLayerDesc), c_int]),
     "maya_moe_layer_error": (c_int, [C.POINTER(MoeLayerDesc), c_int, c_void_p, c_void_p]),

@@ -15,7 +15,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib
-from ._lib import ExpertLayout, MoeLayerDesc, MoePlan, MoeWin
+from ._lib import ExpertLayout, MmqProduct, MoeLayerDesc, MoePlan, MoeWin
 
 Q8_0, Q4_K, IQ3_S, IQ2_S = 8, 12, 21, 22
 TYPE_NAMES = {Q8_0: "Q8_0", Q4_K: "Q4_K", IQ3_S: "IQ3_S", IQ2_S: "IQ2_S"}
@@ -223,6 +223,44 @@ def moe_combine_rows(out, pos, w, sh, T: int, k: int, n_embd: int, stream=None):
     return ffn
 
 
+# ---------------------------------------------------------------- prompt-path grouped GEMM (tensor cores)
+def mmq_supported(ggml_type: int) -> bool:
+    """mmq::supported (include/strata/prefill/moe_mmq.hpp:16)."""
+    return bool(_lib.load().maya_mmq_supported(ggml_type))
+
+
+def mmq_q8_bytes(rows: int, cols: int) -> int:
+    """mmq::q8_bytes (moe_mmq.hpp:20)."""
+    return int(_lib.load().maya_mmq_q8_bytes(rows, cols))
+
+
+def mmq_quantize(x, ids, ggml_type: int, rows: int | None = None, xq=None, stream=None):
+    """mmq::quantize (moe_mmq.hpp:34): row i of the result = q8_1 of x[ids[i]] (x[i] when ids is None)."""
+    cols, ld = x.shape[1], x.stride(0)
+    rows = rows if rows is not None else (ids.numel() if ids is not None else x.shape[0])
+    xq = xq if xq is not None else torch.empty(max(mmq_q8_bytes(rows, cols), 16), dtype=torch.uint8, device=x.device)
+    _check("mmq_quantize", _lib.load().maya_mmq_quantize(_ptr(x), _ptr(ids), _ptr(xq), ggml_type, cols, ld, rows,
+                                                        _stream(stream)))
+    return xq
+
+
+def mmq_product(w, ggml_type: int, w_rows: int, w_cols: int, expert_bytes: int, n: int, xq, bounds, ids,
+                total_rows: int, dst, ld_dst: int, max_rows: int = 0, expert_map=None, error=None) -> MmqProduct:
+    """mmq::Product (moe_mmq.hpp:41-53).  The tensors must outlive the launch: the struct holds raw addresses."""
+    return MmqProduct(_ptr(w), ggml_type, w_rows, w_cols, expert_bytes, n, _ptr(xq), _ptr(bounds), _ptr(ids), total_rows,
+                      max_rows, _ptr(dst), ld_dst, _ptr(expert_map), _ptr(error))
+
+
+def mmq_run(p: MmqProduct, stream=None) -> None:
+    """mmq::Context::run (moe_mmq.hpp:74)."""
+    _check("mmq_run", _lib.load().maya_mmq_run(C.byref(p), _stream(stream)))
+
+
+def mmq_run_glu(p: MmqProduct, limit: float = INF, stream=None) -> None:
+    """mmq::Context::run_glu (moe_mmq.hpp:81)."""
+    _check("mmq_run_glu", _lib.load().maya_mmq_run_glu(C.byref(p), limit, _stream(stream)))
+
+
 # ---------------------------------------------------------------- whole layer
 @dataclass
 class MoeLayerConfig:
@@ -281,7 +319,8 @@ class MoeLayer:
             _check("moe_layer_decode_ar",
                    _lib.load().maya_moe_layer_decode_ar(C.byref(self.desc), _ptr(logits), _ptr(x), int(x.dtype == torch.bfloat16),
                                                         T, _ptr(ids), _ptr(weights), _ptr(out), _ptr(self.scratch),
-                                                        self.scratch.numel(), C.byref(peer.desc), peer.mi, peer.next_seq(),
+                                                        self.scratch.numel(), C.byref(peer.desc), peer.mi,
+                                                        0 if (peer.device_seq and T == 1) else peer.next_seq(),
                                                         _stream(stream)))
             return ids, weights, out
         _check("moe_layer_decode",
@@ -299,3 +338,82 @@ class MoeLayer:
     def error(self, stream=None) -> int:
         """The scratch's sticky device-side error word (0 = none); synchronises the stream."""
         return int(_lib.load().maya_moe_layer_error(C.byref(self.desc), self.max_tokens, _ptr(self.scratch), _stream(stream)))
+
+
+class MoePrefill:
+    """The prompt path of one resident layer for a chunk of up to `max_tokens` tokens, with no host round trip:
+    route -> group rows by expert -> q8_1 of the gathered rows -> gate/up grouped GEMM with SwiGLU in its write-back ->
+    q8_1 of h -> down grouped GEMM -> weighted combine (+ the shared expert as one more product over all rows).
+
+    Follows the reference's prefill_run expert sequence (src/core/glm_prefill.cu:3230-3420: expert_count, bases,
+    expert_scatter, mmq::quantize, Context::run_glu, mmq::quantize, Context::run, moe_combine), except that the bases
+    are scanned on the device.  Every buffer is allocated once, here."""
+
+    def __init__(self, cfg: MoeLayerConfig, experts, shared=None, max_tokens: int = 4096):
+        for t in (cfg.gu_type, cfg.d_type) + ((cfg.sh_gu_type, cfg.sh_d_type) if shared is not None else ()):
+            if not mmq_supported(t):
+                raise MayaError("MoePrefill: type without a grouped GEMM", -2)
+        self.cfg, self.experts, self.shared, self.max_tokens = cfg, experts, shared, max_tokens
+        dev, T, k, H, FF, E = experts.device, max_tokens, cfg.k, cfg.n_embd, cfg.n_ff, cfg.n_expert
+        i32 = dict(dtype=torch.int32, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        u8 = dict(dtype=torch.uint8, device=dev)
+        n = T * k
+        self.ids, self.weights = torch.empty((T, k), **i32), torch.empty((T, k), **f32)
+        self.counts, self.rank, self.bounds = torch.empty(E, **i32), torch.empty(n, **i32), torch.empty(E + 1, **i32)
+        self.pos, self.row_tok = torch.empty(n, **i32), torch.empty(n, **i32)
+        self.xq = torch.empty(mmq_q8_bytes(n, H), **u8)
+        self.h, self.hq = torch.empty((n, FF), **f32), torch.empty(mmq_q8_bytes(n, FF), **u8)
+        self.out, self.ffn = torch.empty((n, H), **f32), torch.empty((T, H), **f32)
+        self.err = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.down_off = 2 * FF * row_bytes(cfg.gu_type, H)
+        if shared is not None:
+            FS = cfg.n_ff_sh
+            self.sh_bounds, self._sh_T = torch.zeros(2, **i32), -1
+            self.sh_xq = torch.empty(mmq_q8_bytes(T, H), **u8)
+            self.sh_h, self.sh_hq = torch.empty((T, FS), **f32), torch.empty(mmq_q8_bytes(T, FS), **u8)
+            self.sh_out = torch.empty((T, H), **f32)
+            self.sh_down_off = 2 * FS * row_bytes(cfg.sh_gu_type, H)
+
+    def forward(self, logits, x, stream=None):
+        cfg, lib, s = self.cfg, _lib.load(), _stream(stream)
+        T, k, H, FF, E = logits.shape[0], cfg.k, cfg.n_embd, cfg.n_ff, cfg.n_expert
+        assert T <= self.max_tokens and x.shape == (T, H) and x.dtype in (torch.float32, torch.bfloat16)
+        n = T * k
+        quant = lib.maya_mmq_quantize_bf16 if x.dtype == torch.bfloat16 else lib.maya_mmq_quantize
+        ids, w = self.ids[:T], self.weights[:T]
+        _check("router_top10", lib.maya_router_top10(_ptr(logits), T, E, k, _ptr(ids), _ptr(w), s))
+        _check("expert_count", lib.maya_expert_count(_ptr(ids), n, E, _ptr(self.counts), _ptr(self.rank), s))
+        _check("expert_bounds", lib.maya_expert_bounds(_ptr(self.counts), E, _ptr(self.bounds), s))
+        _check("expert_scatter", lib.maya_expert_scatter(_ptr(ids), _ptr(self.rank), _ptr(self.bounds), n, k,
+                                                         _ptr(self.row_tok), _ptr(self.pos), s))
+        _check("mmq_quantize", quant(_ptr(x), _ptr(self.row_tok), _ptr(self.xq), cfg.gu_type, H, x.stride(0), n, s))
+        gu = mmq_product(self.experts, cfg.gu_type, 2 * FF, H, cfg.blob_bytes, E, self.xq, self.bounds, None, n, self.h, FF,
+                         error=self.err)
+        _check("mmq_run_glu", lib.maya_mmq_run_glu(C.byref(gu), cfg.limit, s))
+        _check("mmq_quantize", lib.maya_mmq_quantize(_ptr(self.h), None, _ptr(self.hq), cfg.d_type, FF, FF, n, s))
+        dn = mmq_product(self.experts.data_ptr() + self.down_off, cfg.d_type, H, FF, cfg.blob_bytes, E, self.hq, self.bounds,
+                         None, n, self.out, H, error=self.err)
+        _check("mmq_run", lib.maya_mmq_run(C.byref(dn), s))
+        sh_out = None
+        if self.shared is not None:
+            FS = cfg.n_ff_sh
+            if self._sh_T != T:      # the shared expert is one more "expert" that owns every row
+                self.sh_bounds[1], self._sh_T = T, T
+            _check("mmq_quantize", quant(_ptr(x), None, _ptr(self.sh_xq), cfg.sh_gu_type, H, x.stride(0), T, s))
+            sgu = mmq_product(self.shared, cfg.sh_gu_type, 2 * FS, H, cfg.shared_bytes, 1, self.sh_xq, self.sh_bounds, None, T,
+                              self.sh_h, FS, error=self.err)
+            _check("mmq_run_glu", lib.maya_mmq_run_glu(C.byref(sgu), cfg.limit, s))
+            _check("mmq_quantize", lib.maya_mmq_quantize(_ptr(self.sh_h), None, _ptr(self.sh_hq), cfg.sh_d_type, FS, FS, T, s))
+            sdn = mmq_product(self.shared.data_ptr() + self.sh_down_off, cfg.sh_d_type, H, FS, cfg.shared_bytes, 1, self.sh_hq,
+                              self.sh_bounds, None, T, self.sh_out, H, error=self.err)
+            _check("mmq_run", lib.maya_mmq_run(C.byref(sdn), s))
+            sh_out = self.sh_out
+        ffn = self.ffn[:T]
+        _check("moe_combine_rows", lib.maya_moe_combine_rows(_ptr(self.out), _ptr(self.pos), _ptr(w), _ptr(sh_out), T, k, H,
+                                                            _ptr(ffn), s))
+        return ids, w, ffn
+
+    def error(self) -> int:
+        """1 when a bounded wait inside a grouped-GEMM launch ran out (synchronises)."""
+        return int(self.err.item())

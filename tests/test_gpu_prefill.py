@@ -1,0 +1,224 @@
+"""The prompt path's grouped GEMM on the tensor cores (maya_mmq_quantize / maya_mmq_run / maya_mmq_run_glu) and the
+whole prompt-path layer (api.MoePrefill).
+
+Two bars.  Against the q8_1 oracle (the reference's GPU arithmetic: integer dots of q8_1 activations) the tolerance is
+1e-2 in max-norm and in L2: the tensor-core path multiplies the same q8_1-rounded activations and the same dequantized
+weights, each rounded once more to f16.  Against a float64 product of exactly those f16 operands (built here with
+numpy from the oracle's dequantizer) the tolerance is 2e-5: that one pins the kernel itself - tile layout, descriptors,
+the K loop, ragged groups - with only f32 accumulation order left over."""
+import numpy as np
+import pytest
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+TOL, PIN = 1e-2, 2e-5
+
+
+@pytest.fixture(scope="module")
+def T(cuda):
+    import torch
+    return torch
+
+
+@pytest.fixture(scope="module")
+def api(cuda):
+    from project_maya_b200 import api as a
+    return a
+
+
+def dev(T, a):
+    return T.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def synth_matrices(T, api, t, n, rows, cols, seed):
+    w = T.empty((n, rows * H.row_bytes(t, cols)), dtype=T.uint8, device="cuda")
+    for e in range(n):
+        api.synth_weights(t, seed + e, 0.02, rows, cols, w[e])
+    T.cuda.synchronize()
+    return w
+
+
+def f16_operands(oracle, t, w_host, rows, cols, xq_rows):
+    """(weights, activations) as the kernel builds them: dequantized / d*q, rounded once to f16, widened to f64."""
+    w = oracle.dequantize(t, w_host, rows * cols).reshape(rows, cols).astype(np.float16).astype(np.float64)
+    nb = cols // 32
+    blk = xq_rows.reshape(-1, nb, 36)
+    d = blk[:, :, 0:2].copy().view(np.float16).astype(np.float32)           # [rows, nb, 1]
+    q = blk[:, :, 4:].copy().view(np.int8).astype(np.float32)                # [rows, nb, 32]
+    x = (d * q).astype(np.float16).astype(np.float64).reshape(-1, cols)
+    return w, x
+
+
+COUNTS = [0, 3, 130, 128, 1, 0, 257]
+
+
+@pytest.mark.parametrize("t", [H.Q4_K, H.Q8_0])
+def test_grouped_product_ragged_groups(T, api, oracle, t):
+    n, rows, cols, n_tok = len(COUNTS), 256, 512, 40
+    w = synth_matrices(T, api, t, n, rows, cols, 11)
+    rng = H.rng_for("mmq", t)
+    x = (rng.standard_normal((n_tok, cols)) * 1.5).astype(np.float32)
+    bounds = np.concatenate([[0], np.cumsum(COUNTS)]).astype(np.int32)
+    total = int(bounds[-1])
+    row_tok = rng.integers(0, n_tok, total).astype(np.int32)
+    dst_row = rng.permutation(total + 5)[:total].astype(np.int32)            # scattered, with holes
+    xq = api.mmq_quantize(dev(T, x), dev(T, row_tok), t)
+    xq_host = xq.cpu().numpy()[: total * (cols // 32) * 36]
+    want_q = np.concatenate([oracle.quantize_q8_1(x[r]) for r in row_tok])
+    assert np.array_equal(xq_host, want_q), "mmq_quantize differs from the q8_1 oracle"
+
+    ld = rows + 64
+    dst = T.full((total + 5, ld), 7.0, dtype=T.float32, device="cuda")
+    err = T.zeros(1, dtype=T.int32, device="cuda")
+    p = api.mmq_product(w, t, rows, cols, w.shape[1], n, xq, dev(T, bounds), dev(T, dst_row), total, dst, ld, error=err)
+    api.mmq_run(p)
+    T.cuda.synchronize()
+    assert int(err.item()) == 0
+    got = dst.cpu().numpy()
+    w_host = w.cpu().numpy()
+    hit = np.zeros(total + 5, bool)
+    for e in range(n):
+        a, b = int(bounds[e]), int(bounds[e + 1])
+        if a == b:
+            continue
+        wf, xf = f16_operands(oracle, t, w_host[e], rows, cols, xq_host.reshape(total, -1)[a:b])
+        pin = xf @ wf.T
+        g = got[dst_row[a:b], :rows]
+        assert H.rel_err(g, pin) <= PIN, f"expert {e}: not the product of its f16 operands"
+        for r in (a, b - 1):                                                  # the q8_1 oracle on the group's edge rows
+            want = oracle.mmvq(t, w_host[e], xq_host.reshape(total, -1)[r], cols, rows)[0]
+            assert H.rel_err(got[dst_row[r], :rows], want) <= TOL and H.rel_l2(got[dst_row[r], :rows], want) <= TOL
+        hit[dst_row[a:b]] = True
+    assert np.all(got[:, rows:] == 7.0), "wrote past w_rows"
+    assert np.all(got[~hit] == 7.0), "wrote a row no group owns"
+
+
+@pytest.mark.parametrize("t", [H.Q4_K, H.Q8_0])
+@pytest.mark.parametrize("limit", [H.INF, 0.75])
+def test_fused_glu_equals_product_then_swiglu_bitwise(T, api, t, limit):
+    n, n_ff, cols = 4, 256, 768
+    counts = [5, 0, 200, 64]
+    w = synth_matrices(T, api, t, n, 2 * n_ff, cols, 23)
+    x = (H.rng_for("glu", t).standard_normal((sum(counts), cols)) * 2.0).astype(np.float32)
+    bounds = dev(T, np.concatenate([[0], np.cumsum(counts)]).astype(np.int32))
+    total = sum(counts)
+    xq = api.mmq_quantize(dev(T, x), None, t)
+    gu = T.zeros((total, 2 * n_ff), dtype=T.float32, device="cuda")
+    api.mmq_run(api.mmq_product(w, t, 2 * n_ff, cols, w.shape[1], n, xq, bounds, None, total, gu, 2 * n_ff))
+    want = api.swiglu_rows(gu, n_ff, limit)
+    h = T.zeros((total, n_ff), dtype=T.float32, device="cuda")
+    api.mmq_run_glu(api.mmq_product(w, t, 2 * n_ff, cols, w.shape[1], n, xq, bounds, None, total, h, n_ff), limit)
+    T.cuda.synchronize()
+    assert np.abs(gu.cpu().numpy()).max() > 0.1
+    assert T.equal(h, want)
+
+
+def test_expert_map_selects_bounds_entries(T, api):
+    """A staged group: matrix i of the product owns the rows of expert expert_map[i]."""
+    t, rows, cols = H.Q4_K, 128, 256
+    w = synth_matrices(T, api, t, 2, rows, cols, 5)
+    counts = [4, 9, 0, 6]
+    bounds = dev(T, np.concatenate([[0], np.cumsum(counts)]).astype(np.int32))
+    total = sum(counts)
+    x = H.rng_for("map").standard_normal((total, cols)).astype(np.float32)
+    xq = api.mmq_quantize(dev(T, x), None, t)
+    emap = dev(T, np.array([3, 1], np.int32))
+    dst = T.zeros((total, rows), dtype=T.float32, device="cuda")
+    api.mmq_run(api.mmq_product(w, t, rows, cols, w.shape[1], 2, xq, bounds, None, total, dst, rows, expert_map=emap))
+    ref = T.zeros((total, rows), dtype=T.float32, device="cuda")
+    for i, e in enumerate([3, 1]):
+        b = np.zeros(2, np.int32)
+        b[0], b[1] = sum(counts[:e]), sum(counts[: e + 1])
+        api.mmq_run(api.mmq_product(w[i], t, rows, cols, w.shape[1], 1, xq, dev(T, b), None, total, ref, rows))
+    T.cuda.synchronize()
+    assert T.equal(dst, ref)
+    assert float(dst[:4].abs().max()) == 0.0 and float(dst[13:].abs().max()) > 0.0
+
+
+def test_refusals(T, api):
+    t = H.Q4_K
+    w = T.zeros(128 * H.row_bytes(t, 256), dtype=T.uint8, device="cuda")
+    b = dev(T, np.array([0, 1], np.int32))
+    xq = T.zeros(api.mmq_q8_bytes(1, 256), dtype=T.uint8, device="cuda")
+    dst = T.zeros((1, 128), dtype=T.float32, device="cuda")
+    ok = lambda **kw: api.mmq_product(**{**dict(w=w, ggml_type=t, w_rows=128, w_cols=256, expert_bytes=w.numel(), n=1, xq=xq,
+                                                 bounds=b, ids=None, total_rows=1, dst=dst, ld_dst=128), **kw})
+    api.mmq_run(ok())
+    for bad in (dict(ggml_type=H.IQ2_S), dict(w_rows=100), dict(w_cols=96), dict(ld_dst=64), dict(expert_bytes=w.numel() + 8)):
+        with pytest.raises(api.MayaError):
+            api.mmq_run(ok(**bad))
+    with pytest.raises(api.MayaError):
+        api.mmq_run_glu(ok(w_rows=128), H.INF)            # n_ff = 64 is not a multiple of 128
+    assert api.mmq_q8_bytes(3, 100) == 0 and api.mmq_q8_bytes(3, 256) == 3 * 8 * 36
+    assert api.mmq_supported(H.Q8_0) and api.mmq_supported(H.Q4_K) and not api.mmq_supported(H.IQ3_S)
+
+
+# ------------------------------------------------------------------------------------------------ the whole layer
+def oracle_prefill_token(oracle, cfg, experts, ids, w, x):
+    H_, FF = cfg["n_embd"], cfg["n_ff"]
+    xq = oracle.quantize_q8_1(x)
+    parts = np.stack([oracle.expert_q8_1(cfg["gu_type"], cfg["d_type"], experts[int(e)].cpu().numpy(), H_, FF, H.INF, xq)
+                      for e in ids])
+    out = np.zeros(H_, np.float32)
+    for j in range(len(ids)):                               # glmb::moe_combine's order: m = fma(w, o, m) from 0
+        out = (np.float32(w[j]) * parts[j].astype(np.float32) + out).astype(np.float32)
+    return out
+
+
+@pytest.mark.parametrize("t,n_tok,E", [(H.Q4_K, 300, 16), (H.Q8_0, 77, 8)])
+def test_prefill_layer_small(T, api, oracle, t, n_tok, E):
+    cfg = dict(n_embd=512, n_ff=256, n_expert=E, k=4, gu_type=t, d_type=t)
+    lc = api.MoeLayerConfig(cfg["n_embd"], cfg["n_ff"], E, cfg["k"], t, t)
+    experts = T.empty((E, lc.blob_bytes), dtype=T.uint8, device="cuda")
+    gu_bytes = 2 * cfg["n_ff"] * H.row_bytes(t, cfg["n_embd"])
+    for e in range(E):
+        api.synth_weights(t, 900 + 2 * e, 0.05, 2 * cfg["n_ff"], cfg["n_embd"], experts[e, :gu_bytes])
+        api.synth_weights(t, 901 + 2 * e, 0.05, cfg["n_embd"], cfg["n_ff"], experts[e, gu_bytes:])
+    logits = H.router_logits("pf", n_tok, E, None)
+    x = H.activations("pf", n_tok, cfg["n_embd"], "f32")
+    pf = api.MoePrefill(lc, experts, max_tokens=n_tok)
+    ids, w, ffn = pf.forward(dev(T, logits), dev(T, x))
+    T.cuda.synchronize()
+    assert pf.error() == 0
+    ids_o, w_o = oracle.router_top10(logits, cfg["k"])
+    assert np.array_equal(ids.cpu().numpy(), ids_o)
+    got = ffn.cpu().numpy()
+    for tok in (0, n_tok // 2, n_tok - 1):
+        want = oracle_prefill_token(oracle, cfg, experts, ids_o[tok], w_o[tok], x[tok])
+        assert H.rel_err(got[tok], want) <= TOL and H.rel_l2(got[tok], want) <= TOL
+
+
+@pytest.mark.parametrize("t", [H.Q4_K, H.Q8_0])
+def test_prefill_c4_shape(T, api, oracle, t):
+    """Configuration C4 at its full shape (4096 tokens x top-8 over 256 experts = 32768 routed rows, bf16 activations):
+    three tokens against the oracle; row conservation (every routed pair has exactly one sorted row); and the chunk's
+    results do not depend on what else is in the chunk - the first 512 tokens alone give the same bits."""
+    c = H.CONFIGS["C4"]
+    cfg = dict(n_embd=c["n_embd"], n_ff=c["n_ff"], n_expert=c["n_expert"], k=c["k"], gu_type=t, d_type=t)
+    n_tok = c["T"]
+    lc = api.MoeLayerConfig(cfg["n_embd"], cfg["n_ff"], cfg["n_expert"], cfg["k"], t, t)
+    experts = T.empty((cfg["n_expert"], lc.blob_bytes), dtype=T.uint8, device="cuda")
+    gu_bytes = 2 * cfg["n_ff"] * H.row_bytes(t, cfg["n_embd"])
+    for e in range(cfg["n_expert"]):
+        api.synth_weights(t, 5000 + 2 * e, 0.02, 2 * cfg["n_ff"], cfg["n_embd"], experts[e, :gu_bytes])
+        api.synth_weights(t, 5001 + 2 * e, 0.02, cfg["n_embd"], cfg["n_ff"], experts[e, gu_bytes:])
+    logits = H.router_logits("c4", n_tok, cfg["n_expert"], None)
+    x = H.activations("c4", n_tok, cfg["n_embd"], "bf16")
+    x_dev = dev(T, x).to(T.bfloat16)
+    pf = api.MoePrefill(lc, experts, max_tokens=n_tok)
+    ids, w, ffn = pf.forward(dev(T, logits), x_dev)
+    T.cuda.synchronize()
+    assert pf.error() == 0
+    got = ffn.cpu().numpy().copy()
+    pos = pf.pos.cpu().numpy()
+    assert np.array_equal(np.sort(pos), np.arange(n_tok * cfg["k"]))
+    assert int(pf.bounds[-1].item()) == n_tok * cfg["k"]
+    ids_o, w_o = oracle.router_top10(logits[:4], cfg["k"])
+    assert np.array_equal(ids.cpu().numpy()[:4], ids_o)
+    for tok in (0, 1, 3):
+        want = oracle_prefill_token(oracle, cfg, experts, ids_o[tok], w_o[tok], x[tok])
+        assert H.rel_err(got[tok], want) <= TOL and H.rel_l2(got[tok], want) <= TOL
+    _, _, ffn2 = pf.forward(dev(T, logits[:512]), x_dev[:512])
+    T.cuda.synchronize()
+    assert np.array_equal(ffn2.cpu().numpy(), got[:512])
