@@ -347,14 +347,30 @@ class MoePrefill:
 
     Follows the reference's prefill_run expert sequence (src/core/glm_prefill.cu:3230-3420: expert_count, bases,
     expert_scatter, mmq::quantize, Context::run_glu, mmq::quantize, Context::run, moe_combine), except that the bases
-    are scanned on the device.  Every buffer is allocated once, here."""
+    are scanned on the device.  Every buffer is allocated once, here.
 
-    def __init__(self, cfg: MoeLayerConfig, experts, shared=None, max_tokens: int = 4096):
-        for t in (cfg.gu_type, cfg.d_type) + ((cfg.sh_gu_type, cfg.sh_d_type) if shared is not None else ()):
-            if not mmq_supported(t):
+    `experts` is uint8 [n_expert, blob_bytes] of one type (cfg.gu_type == cfg.d_type is not required), or None with
+    `pools` = [(ggml_type, blobs uint8 [n_i, blob_bytes of that type], expert ids of the n_i blobs), ...] for a layer whose
+    experts are stored in different types: one product per pool, each matrix finding its rows through the pool's
+    expert map (the reference's staged groups, moe_mmq.hpp:41-53 with bounds per group)."""
+
+    def __init__(self, cfg: MoeLayerConfig, experts, shared=None, max_tokens: int = 4096, pools=None):
+        H, FF = cfg.n_embd, cfg.n_ff
+        if pools is None:
+            pools = [((cfg.gu_type, cfg.d_type), experts, None)]
+        self.pools = []
+        for types, blobs, expert_ids in pools:
+            gt, dt = types if isinstance(types, tuple) else (types, types)
+            if not (mmq_supported(gt) and mmq_supported(dt)):
                 raise MayaError("MoePrefill: type without a grouped GEMM", -2)
-        self.cfg, self.experts, self.shared, self.max_tokens = cfg, experts, shared, max_tokens
-        dev, T, k, H, FF, E = experts.device, max_tokens, cfg.k, cfg.n_embd, cfg.n_ff, cfg.n_expert
+            stride = 2 * FF * row_bytes(gt, H) + H * row_bytes(dt, FF)
+            assert blobs.shape[1] == stride, "a pool's blobs must be [gate | up | down] of its own type"
+            emap = None if expert_ids is None else torch.as_tensor(expert_ids, dtype=torch.int32).to(blobs.device)
+            self.pools.append((gt, dt, blobs, stride, 2 * FF * row_bytes(gt, H), blobs.shape[0], emap))
+        if shared is not None and not (mmq_supported(cfg.sh_gu_type) and mmq_supported(cfg.sh_d_type)):
+            raise MayaError("MoePrefill: shared expert's type without a grouped GEMM", -2)
+        self.cfg, self.shared, self.max_tokens = cfg, shared, max_tokens
+        dev, T, k, E = self.pools[0][2].device, max_tokens, cfg.k, cfg.n_expert
         i32 = dict(dtype=torch.int32, device=dev)
         f32 = dict(dtype=torch.float32, device=dev)
         u8 = dict(dtype=torch.uint8, device=dev)
@@ -366,7 +382,6 @@ class MoePrefill:
         self.h, self.hq = torch.empty((n, FF), **f32), torch.empty(mmq_q8_bytes(n, FF), **u8)
         self.out, self.ffn = torch.empty((n, H), **f32), torch.empty((T, H), **f32)
         self.err = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.down_off = 2 * FF * row_bytes(cfg.gu_type, H)
         if shared is not None:
             FS = cfg.n_ff_sh
             self.sh_bounds, self._sh_T = torch.zeros(2, **i32), -1
@@ -387,14 +402,16 @@ class MoePrefill:
         _check("expert_bounds", lib.maya_expert_bounds(_ptr(self.counts), E, _ptr(self.bounds), s))
         _check("expert_scatter", lib.maya_expert_scatter(_ptr(ids), _ptr(self.rank), _ptr(self.bounds), n, k,
                                                          _ptr(self.row_tok), _ptr(self.pos), s))
-        _check("mmq_quantize", quant(_ptr(x), _ptr(self.row_tok), _ptr(self.xq), cfg.gu_type, H, x.stride(0), n, s))
-        gu = mmq_product(self.experts, cfg.gu_type, 2 * FF, H, cfg.blob_bytes, E, self.xq, self.bounds, None, n, self.h, FF,
-                         error=self.err)
-        _check("mmq_run_glu", lib.maya_mmq_run_glu(C.byref(gu), cfg.limit, s))
-        _check("mmq_quantize", lib.maya_mmq_quantize(_ptr(self.h), None, _ptr(self.hq), cfg.d_type, FF, FF, n, s))
-        dn = mmq_product(self.experts.data_ptr() + self.down_off, cfg.d_type, H, FF, cfg.blob_bytes, E, self.hq, self.bounds,
-                         None, n, self.out, H, error=self.err)
-        _check("mmq_run", lib.maya_mmq_run(C.byref(dn), s))
+        _check("mmq_quantize", quant(_ptr(x), _ptr(self.row_tok), _ptr(self.xq), self.pools[0][0], H, x.stride(0), n, s))
+        for gt, dt, blobs, stride, down_off, n_p, emap in self.pools:
+            gu = mmq_product(blobs, gt, 2 * FF, H, stride, n_p, self.xq, self.bounds, None, n, self.h, FF, expert_map=emap,
+                             error=self.err)
+            _check("mmq_run_glu", lib.maya_mmq_run_glu(C.byref(gu), cfg.limit, s))
+        _check("mmq_quantize", lib.maya_mmq_quantize(_ptr(self.h), None, _ptr(self.hq), self.pools[0][1], FF, FF, n, s))
+        for gt, dt, blobs, stride, down_off, n_p, emap in self.pools:
+            dn = mmq_product(blobs.data_ptr() + down_off, dt, H, FF, stride, n_p, self.hq, self.bounds, None, n, self.out, H,
+                             expert_map=emap, error=self.err)
+            _check("mmq_run", lib.maya_mmq_run(C.byref(dn), s))
         sh_out = None
         if self.shared is not None:
             FS = cfg.n_ff_sh

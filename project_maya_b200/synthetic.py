@@ -39,6 +39,16 @@ def blob_bytes(gu_type: int, d_type: int, n_embd: int, n_ff: int) -> int:
     return 2 * n_ff * row_bytes(gu_type, n_embd) + n_embd * row_bytes(d_type, n_ff)
 
 
+def expert_types(cfg_name: str, n_expert: int, types) -> np.ndarray:
+    """Seeded assignment of storage types to experts, the same number of experts for every type (C4: half Q8_0, half
+    Q4_K)."""
+    perm = rng_for(cfg_name, "types").permutation(n_expert)
+    out = np.empty(n_expert, dtype=np.int32)
+    for i, t in enumerate(types):
+        out[perm[i * n_expert // len(types):(i + 1) * n_expert // len(types)]] = t
+    return out
+
+
 def to_bf16_f32(x: np.ndarray) -> np.ndarray:
     """Round f32 to bf16 (nearest even) and widen back: what a bf16 activation holds."""
     u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)

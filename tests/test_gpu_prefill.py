@@ -189,24 +189,39 @@ def test_prefill_layer_small(T, api, oracle, t, n_tok, E):
         assert H.rel_err(got[tok], want) <= TOL and H.rel_l2(got[tok], want) <= TOL
 
 
-@pytest.mark.parametrize("t", [H.Q4_K, H.Q8_0])
-def test_prefill_c4_shape(T, api, oracle, t):
-    """Configuration C4 at its full shape (4096 tokens x top-8 over 256 experts = 32768 routed rows, bf16 activations):
-    three tokens against the oracle; row conservation (every routed pair has exactly one sorted row); and the chunk's
-    results do not depend on what else is in the chunk - the first 512 tokens alone give the same bits."""
+def build_pools(T, api, cfg, types, seed, sigma=0.02):
+    """One pool of synthetic [gate | up | down] blobs per storage type; returns (pools for MoePrefill, blob of expert e)."""
+    H_, FF = cfg["n_embd"], cfg["n_ff"]
+    pools, where = [], {}
+    for t in sorted(set(int(v) for v in types)):
+        members = [e for e in range(len(types)) if int(types[e]) == t]
+        gu_bytes = 2 * FF * H.row_bytes(t, H_)
+        blobs = T.empty((len(members), gu_bytes + H_ * H.row_bytes(t, FF)), dtype=T.uint8, device="cuda")
+        for i, e in enumerate(members):
+            api.synth_weights(t, seed + 2 * e, sigma, 2 * FF, H_, blobs[i, :gu_bytes])
+            api.synth_weights(t, seed + 2 * e + 1, sigma, H_, FF, blobs[i, gu_bytes:])
+            where[e] = (t, blobs, i)
+        pools.append((t, blobs, members))
+    T.cuda.synchronize()
+    return pools, where
+
+
+def test_prefill_c4_shape(T, api, oracle):
+    """Configuration C4 at its full shape: 4096 tokens x top-8 over 256 experts = 32768 routed rows, bf16 activations,
+    half of the experts stored as Q8_0 and half as Q4_K (seeded assignment).  Three tokens against the oracle; row
+    conservation (every routed pair has exactly one sorted row); and a chunk's results do not depend on what else is in
+    the chunk - the first 512 tokens alone give the same bits."""
     c = H.CONFIGS["C4"]
-    cfg = dict(n_embd=c["n_embd"], n_ff=c["n_ff"], n_expert=c["n_expert"], k=c["k"], gu_type=t, d_type=t)
-    n_tok = c["T"]
-    lc = api.MoeLayerConfig(cfg["n_embd"], cfg["n_ff"], cfg["n_expert"], cfg["k"], t, t)
-    experts = T.empty((cfg["n_expert"], lc.blob_bytes), dtype=T.uint8, device="cuda")
-    gu_bytes = 2 * cfg["n_ff"] * H.row_bytes(t, cfg["n_embd"])
-    for e in range(cfg["n_expert"]):
-        api.synth_weights(t, 5000 + 2 * e, 0.02, 2 * cfg["n_ff"], cfg["n_embd"], experts[e, :gu_bytes])
-        api.synth_weights(t, 5001 + 2 * e, 0.02, cfg["n_embd"], cfg["n_ff"], experts[e, gu_bytes:])
-    logits = H.router_logits("c4", n_tok, cfg["n_expert"], None)
+    cfg = dict(n_embd=c["n_embd"], n_ff=c["n_ff"], n_expert=c["n_expert"], k=c["k"])
+    n_tok, E = c["T"], c["n_expert"]
+    types = H.expert_types("C4", E, c["types"])
+    assert (types == H.Q8_0).sum() == E // 2 and (types == H.Q4_K).sum() == E // 2
+    pools, where = build_pools(T, api, cfg, types, 5000)
+    lc = api.MoeLayerConfig(cfg["n_embd"], cfg["n_ff"], E, cfg["k"], H.Q8_0, H.Q8_0)
+    logits = H.router_logits("c4", n_tok, E, None)
     x = H.activations("c4", n_tok, cfg["n_embd"], "bf16")
     x_dev = dev(T, x).to(T.bfloat16)
-    pf = api.MoePrefill(lc, experts, max_tokens=n_tok)
+    pf = api.MoePrefill(lc, None, max_tokens=n_tok, pools=pools)
     ids, w, ffn = pf.forward(dev(T, logits), x_dev)
     T.cuda.synchronize()
     assert pf.error() == 0
@@ -217,7 +232,14 @@ def test_prefill_c4_shape(T, api, oracle, t):
     ids_o, w_o = oracle.router_top10(logits[:4], cfg["k"])
     assert np.array_equal(ids.cpu().numpy()[:4], ids_o)
     for tok in (0, 1, 3):
-        want = oracle_prefill_token(oracle, cfg, experts, ids_o[tok], w_o[tok], x[tok])
+        xq = oracle.quantize_q8_1(x[tok])
+        want = np.zeros(cfg["n_embd"], np.float32)
+        seen = set()
+        for j, e in enumerate(ids_o[tok]):
+            t, blobs, i = where[int(e)]
+            seen.add(t)
+            part = oracle.expert_q8_1(t, t, blobs[i].cpu().numpy(), cfg["n_embd"], cfg["n_ff"], H.INF, xq)
+            want = (np.float32(w_o[tok][j]) * part + want).astype(np.float32)
         assert H.rel_err(got[tok], want) <= TOL and H.rel_l2(got[tok], want) <= TOL
     _, _, ffn2 = pf.forward(dev(T, logits[:512]), x_dev[:512])
     T.cuda.synchronize()
