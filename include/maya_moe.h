@@ -211,25 +211,26 @@ MAYA_API int maya_moe_combine_add(const float* out, int base, int lo, int hi, co
 /* Prompt-path grouped GEMM on the tensor cores --------------------------------------------------------- */
 /* mmq::supported (include/strata/prefill/moe_mmq.hpp:16): types the grouped GEMM takes (Q8_0 and Q4_K). */
 MAYA_API int maya_mmq_supported(int type);
-/* mmq::q8_bytes (moe_mmq.hpp:20): bytes of `rows` activation rows of `cols` values as q8_1 blocks, row after row
- * (cols / 32 blocks of 36 bytes each; the reference pads rows to 512 values for llama.cpp's tile loader, this
- * layout needs no padding).  0 for cols % 32 != 0. */
+/* mmq::q8_bytes (moe_mmq.hpp:20): bytes of `rows` quantized activation rows of `cols` values.  The rows are stored as
+ * f16: each value is d * q of the row's q8_1 image (d = f16(amax / 127) per 32 values, q = round(x / d)), the
+ * operand the f16 tensor-core product reads; cols * 2 bytes a row, no padding.  0 for cols % 32 != 0. */
 MAYA_API size_t maya_mmq_q8_bytes(int64_t rows, int64_t cols);
-/* mmq::quantize (moe_mmq.hpp:34): output row i = q8_1 of row ids[i] of x (row i when ids is NULL); x has ld floats a
- * row.  `type` is the weight type the product will use (checked with maya_mmq_supported; the layout is the same). */
+/* mmq::quantize (moe_mmq.hpp:34): output row i = the q8_1 image of row ids[i] of x (row i when ids is NULL); x has
+ * ld floats a row.  `type` is the weight type the product will use (checked with maya_mmq_supported; the layout is
+ * the same for every type). */
 MAYA_API int maya_mmq_quantize(const float* x, const int32_t* ids, void* xq, int type, int64_t cols, int64_t ld,
                                int64_t rows, void* stream);
 /* The same from bf16 activations (raw bf16 bits, widened to f32 exactly); ld in bf16 elements. */
 MAYA_API int maya_mmq_quantize_bf16(const uint16_t* x, const int32_t* ids, void* xq, int type, int64_t cols, int64_t ld,
                                     int64_t rows, void* stream);
-/* mmq::Product (moe_mmq.hpp:41-53), field for field, plus two optional fields the reference has no need of. */
+/* mmq::Product (moe_mmq.hpp:41-53), field for field, plus three optional fields the reference has no need of. */
 typedef struct maya_mmq_product {
-    const void* w;               /* n experts' matrices, expert_bytes apart; 16-byte aligned */
+    const void* w;               /* n matrices, expert_bytes apart; 16-byte aligned */
     int type;
-    int64_t w_rows, w_cols;      /* one expert's matrix: GGUF rows of w_cols values (w_cols % 256 == 0) */
+    int64_t w_rows, w_cols;      /* one matrix: GGUF rows of w_cols values (w_cols % 256 == 0) */
     size_t expert_bytes;         /* a whole number of the type's blocks, a multiple of 16 */
     int n;
-    const void* xq;              /* maya_mmq_quantize's output, total_rows rows */
+    const void* xq;              /* maya_mmq_quantize's output, total_rows rows; 16-byte aligned */
     const int32_t* bounds;       /* device, n + 1 entries (more with expert_map) */
     const int32_t* ids;          /* dst row = ids[row]; NULL: identity */
     int64_t total_rows, max_rows;/* rows of xq; max_rows is not needed here (the grid is sized from total_rows) */
@@ -237,6 +238,9 @@ typedef struct maya_mmq_product {
     int64_t ld_dst;
     const int32_t* expert_map;   /* NULL, or device table: matrix i of w uses bounds[expert_map[i]] (a staged group) */
     unsigned* error;             /* NULL, or device word set to 1 when a bounded wait inside the kernel ran out */
+    void* xq_out;                /* maya_mmq_run_glu only, NULL or [total_rows][n_ff] f16: h already quantized as
+                                    maya_mmq_quantize(h, NULL, ...) would, row = the sorted row (ids not applied);
+                                    with it dst may be NULL */
 } maya_mmq_product;
 /* mmq::Context::run (moe_mmq.hpp:74): for matrix e, rows [bounds[e], bounds[e+1]) of xq times its [w_rows, w_cols]
  * matrix into dst[ids[row]][0 .. w_rows).  w_rows % 128 == 0.  No scratch, no host synchronisation. */

@@ -43,7 +43,7 @@ class MmqProduct(C.Structure):
     _fields_ = [("w", c_void_p), ("type", c_int), ("w_rows", c_int64), ("w_cols", c_int64), ("expert_bytes", c_size_t),
                 ("n", c_int), ("xq", c_void_p), ("bounds", c_void_p), ("ids", c_void_p), ("total_rows", c_int64),
                 ("max_rows", c_int64), ("dst", c_void_p), ("ld_dst", c_int64), ("expert_map", c_void_p),
-                ("error", c_void_p)]
+                ("error", c_void_p), ("xq_out", c_void_p)]
 
 
 class PeerArFailure(C.Structure):

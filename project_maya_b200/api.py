@@ -245,10 +245,10 @@ def mmq_quantize(x, ids, ggml_type: int, rows: int | None = None, xq=None, strea
 
 
 def mmq_product(w, ggml_type: int, w_rows: int, w_cols: int, expert_bytes: int, n: int, xq, bounds, ids,
-                total_rows: int, dst, ld_dst: int, max_rows: int = 0, expert_map=None, error=None) -> MmqProduct:
+                total_rows: int, dst, ld_dst: int, max_rows: int = 0, expert_map=None, error=None, xq_out=None) -> MmqProduct:
     """mmq::Product (moe_mmq.hpp:41-53).  The tensors must outlive the launch: the struct holds raw addresses."""
     return MmqProduct(_ptr(w), ggml_type, w_rows, w_cols, expert_bytes, n, _ptr(xq), _ptr(bounds), _ptr(ids), total_rows,
-                      max_rows, _ptr(dst), ld_dst, _ptr(expert_map), _ptr(error))
+                      max_rows, _ptr(dst), ld_dst, _ptr(expert_map), _ptr(error), _ptr(xq_out))
 
 
 def mmq_run(p: MmqProduct, stream=None) -> None:
@@ -379,14 +379,14 @@ class MoePrefill:
         self.counts, self.rank, self.bounds = torch.empty(E, **i32), torch.empty(n, **i32), torch.empty(E + 1, **i32)
         self.pos, self.row_tok = torch.empty(n, **i32), torch.empty(n, **i32)
         self.xq = torch.empty(mmq_q8_bytes(n, H), **u8)
-        self.h, self.hq = torch.empty((n, FF), **f32), torch.empty(mmq_q8_bytes(n, FF), **u8)
+        self.hq = torch.empty(mmq_q8_bytes(n, FF), **u8)
         self.out, self.ffn = torch.empty((n, H), **f32), torch.empty((T, H), **f32)
         self.err = torch.zeros(1, dtype=torch.int32, device=dev)
         if shared is not None:
             FS = cfg.n_ff_sh
             self.sh_bounds, self._sh_T = torch.zeros(2, **i32), -1
             self.sh_xq = torch.empty(mmq_q8_bytes(T, H), **u8)
-            self.sh_h, self.sh_hq = torch.empty((T, FS), **f32), torch.empty(mmq_q8_bytes(T, FS), **u8)
+            self.sh_hq = torch.empty(mmq_q8_bytes(T, FS), **u8)
             self.sh_out = torch.empty((T, H), **f32)
             self.sh_down_off = 2 * FS * row_bytes(cfg.sh_gu_type, H)
 
@@ -404,10 +404,9 @@ class MoePrefill:
                                                          _ptr(self.row_tok), _ptr(self.pos), s))
         _check("mmq_quantize", quant(_ptr(x), _ptr(self.row_tok), _ptr(self.xq), self.pools[0][0], H, x.stride(0), n, s))
         for gt, dt, blobs, stride, down_off, n_p, emap in self.pools:
-            gu = mmq_product(blobs, gt, 2 * FF, H, stride, n_p, self.xq, self.bounds, None, n, self.h, FF, expert_map=emap,
-                             error=self.err)
+            gu = mmq_product(blobs, gt, 2 * FF, H, stride, n_p, self.xq, self.bounds, None, n, None, FF, expert_map=emap,
+                             error=self.err, xq_out=self.hq)        # h leaves the product already quantized
             _check("mmq_run_glu", lib.maya_mmq_run_glu(C.byref(gu), cfg.limit, s))
-        _check("mmq_quantize", lib.maya_mmq_quantize(_ptr(self.h), None, _ptr(self.hq), self.pools[0][1], FF, FF, n, s))
         for gt, dt, blobs, stride, down_off, n_p, emap in self.pools:
             dn = mmq_product(blobs.data_ptr() + down_off, dt, H, FF, stride, n_p, self.hq, self.bounds, None, n, self.out, H,
                              expert_map=emap, error=self.err)
@@ -419,9 +418,8 @@ class MoePrefill:
                 self.sh_bounds[1], self._sh_T = T, T
             _check("mmq_quantize", quant(_ptr(x), None, _ptr(self.sh_xq), cfg.sh_gu_type, H, x.stride(0), T, s))
             sgu = mmq_product(self.shared, cfg.sh_gu_type, 2 * FS, H, cfg.shared_bytes, 1, self.sh_xq, self.sh_bounds, None, T,
-                              self.sh_h, FS, error=self.err)
+                              None, FS, error=self.err, xq_out=self.sh_hq)
             _check("mmq_run_glu", lib.maya_mmq_run_glu(C.byref(sgu), cfg.limit, s))
-            _check("mmq_quantize", lib.maya_mmq_quantize(_ptr(self.sh_h), None, _ptr(self.sh_hq), cfg.sh_d_type, FS, FS, T, s))
             sdn = mmq_product(self.shared.data_ptr() + self.sh_down_off, cfg.sh_d_type, H, FS, cfg.shared_bytes, 1, self.sh_hq,
                               self.sh_bounds, None, T, self.sh_out, H, error=self.err)
             _check("mmq_run", lib.maya_mmq_run(C.byref(sdn), s))

@@ -2,8 +2,8 @@
 half of the experts stored as Q8_0 and half as Q4_K, bf16 activations).  `python bench.py --workload prefill` calls
 `run`; one JSON line comes back.
 
-A step is one whole prompt-path layer over one 4096-token chunk (route, group, quantize, gate/up + SwiGLU product,
-quantize, down product, combine).  Steps rotate over `layers` layer copies (2 x 7.3 GB of expert blobs by default), so no
+A step is one whole prompt-path layer over one 4096-token chunk (route, group, quantize, gate/up + SwiGLU product that
+writes h already quantized, down product, combine).  Steps rotate over `layers` layer copies (2 x 7.3 GB of expert blobs by default), so no
 step finds its weights in L2.  The dominant kernel is the grouped GEMM; it is timed by itself with CUDA events and
 reported against the measured dense bf16 peak: its algorithmic work is 2 * rows * (3 * n_embd * n_ff) flops per layer
 (rows = tokens * k), whatever padding its 128-row groups carry.
@@ -100,8 +100,8 @@ def run(steps: int, warmup: int, layers: int, clock_sampler=None) -> dict:
     def products_only(s):
         p = pf[s % layers]
         for gt, dt_, blobs, stride, down_off, n_p, emap in p.pools:
-            api.mmq_run_glu(api.mmq_product(blobs, gt, 2 * FF, Hd, stride, n_p, p.xq, p.bounds, None, rows, p.h, FF,
-                                            expert_map=emap, error=p.err), lc.limit, stream=stream)
+            api.mmq_run_glu(api.mmq_product(blobs, gt, 2 * FF, Hd, stride, n_p, p.xq, p.bounds, None, rows, None, FF,
+                                            expert_map=emap, error=p.err, xq_out=p.hq), lc.limit, stream=stream)
         for gt, dt_, blobs, stride, down_off, n_p, emap in p.pools:
             api.mmq_run(api.mmq_product(blobs.data_ptr() + down_off, dt_, Hd, FF, stride, n_p, p.hq, p.bounds, None, rows,
                                         p.out, Hd, expert_map=emap, error=p.err), stream=stream)

@@ -1,25 +1,31 @@
 // mmq_tc.cu - the prompt path's grouped-by-expert GEMM over quantized expert matrices on the 5th-generation tensor
 // cores: for every expert e, the activation rows [bounds[e], bounds[e+1]) times its [w_rows, w_cols] quantized matrix.
 //
-// Replaces mmq::quantize / mmq::Context::run / run_glu (include/strata/prefill/moe_mmq.hpp:59-99, src/prefill/
+// Replaces mmq::quantize / mmq::Context::run / run_glu (include/strata/prefill/moe_mmq.hpp:34-81, src/prefill/
 // moe_mmq.cu:114-228), which wrap llama.cpp's int8 `mma.sync` MMQ kernels (not part of the reference tree).  The
 // reference rounds activations to q8_1 and multiplies integers with per-32 scales; an integer tcgen05 contraction
-// would have to leave tensor memory every 32 values of K to apply those scales, so here both operands are expanded to
-// f16 in shared memory - weights dequantized exactly as the format defines (f32, rounded once to f16), activations as
-// d * q of their q8_1 image (the reference's rounding of x, kept so that results stay within its tolerance) - and
-// multiplied by `tcgen05.mma.kind::f16` with f32 accumulators in tensor memory.
+// would have to leave tensor memory every 32 values of K to apply those scales, so here both operands are f16:
+// activations are stored once as d * q of their q8_1 image (the reference's rounding of x, kept so that results stay
+// within its tolerance), weights are expanded from their GGUF blocks in shared memory, and `tcgen05.mma.kind::f16`
+// accumulates in f32 in tensor memory.
 //
-// One block = one 128-row slab of the weight matrix (gate and up slabs together for the fused SwiGLU form) x up to 128
-// activation rows of one expert.  K advances 64 values a step through a 3-stage ring of shared-memory tiles: all 256
-// threads dequantize a stage, one thread issues the four K = 16 MMAs of the stage and commits them to the stage's
-// mbarrier, and the threads go on to the next stage while the tensor core works.  The epilogue reads the accumulators
-// with tcgen05.ld (lane = weight row, column = activation row), applies SwiGLU for the fused form and writes
-// dst[row][weight row] so that a warp stores 32 consecutive floats.
-//
-// Which expert and which of its 128-row groups a block handles is found on the device from `bounds` (a scan in shared
-// memory), so no count ever travels to the host; the launch only needs an upper bound of the number of groups.
-// Every mbarrier wait is bounded; a wait that runs out sets the error word and the block frees its tensor memory and
-// returns.
+// One block = a slab of 256 weight rows (128 gate + 128 up rows for the fused SwiGLU form) x up to 256 activation
+// rows of one expert: two M = 128 accumulators of N = rows (rounded up to 16) columns.  Warp roles:
+//   warp 8      one lane: TMA loads of raw weight blocks, 64 rows x 256 K-values a "unit", into a ring of units;
+//   warp 10     one lane: TMA loads of the activation tile of each 32-value K step, straight into the operand layout
+//               (the f16 rows are described to the TMA engine as (8 values, row, 16-byte chunk) so that a box lands as
+//               [chunk][row][16 bytes], the tensor core's K-major layout without swizzle);
+//   warps 0..7  one thread per weight row: expand 32 K-values of the row per step into the A tile (packed half2
+//               arithmetic: Q8_0 w = q * d; Q4_K w = fma(q, d * sc, -(dmin * m)));
+//   warp 9      one lane: four tcgen05.mma per step (2 accumulators x 2 K = 16 halves), commit -> the step's buffers
+//               are free again;
+//   warps 0..7  afterwards: the epilogue - tcgen05.ld (lane = weight row, column = activation row), SwiGLU, optional
+//               q8_1 rounding of h for the next product, stores of 32 consecutive floats per warp.
+// Which expert and which 256-row group of it a block handles is found on the device from `bounds`; no count travels
+// to the host.  Every mbarrier wait is bounded: a wait that runs out sets the error word, the roles stop, copies in
+// flight are waited for (bounded), tensor memory is freed and the block returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
 #include <cuda_fp16.h>
 
 #include <cstdio>
@@ -30,95 +36,142 @@
 namespace maya {
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64, kStages = 3, kMmqThreads = 256;
-constexpr int kTileBytes = BM * BK * 2;     // 16 KB: one operand tile of f16
-
-__device__ __forceinline__ uint4 pack8(const float* v) {
-    __half2 a = __floats2half2_rn(v[0], v[1]), b = __floats2half2_rn(v[2], v[3]);
-    __half2 c = __floats2half2_rn(v[4], v[5]), d = __floats2half2_rn(v[6], v[7]);
-    uint4 r;
-    r.x = *(uint32_t*) &a; r.y = *(uint32_t*) &b; r.z = *(uint32_t*) &c; r.w = *(uint32_t*) &d;
-    return r;
-}
-// 32 consecutive K-values of one row into the tile: chunks c0 .. c0 + 3
-__device__ __forceinline__ void store32(uint8_t* tile, int rows, int r, int c0, const float* v) {
-#pragma unroll
-    for (int c = 0; c < 4; ++c) *(uint4*) (tile + (size_t) (c0 + c) * rows * 16 + r * 16) = pack8(v + 8 * c);
-}
-
-// weights of row `row`, K-tile kt (64 values), half h (32 values) -> f32
-template<int T>
-__device__ __forceinline__ void dequant32(const uint8_t* row, int kt, int h, float* v) {
-    if constexpr (T == MAYA_Q4_K) {
-        const uint8_t* blk = row + (size_t) (kt >> 2) * 144;
-        const int j = kt & 3, sb = 2 * j + h;
-        const uint32_t dm = ld_u32(blk);
-        const float d = __half2float(__ushort_as_half((uint16_t) (dm & 0xFFFF)));
-        const float dmin = __half2float(__ushort_as_half((uint16_t) (dm >> 16)));
-        const uint8_t* s12 = blk + 4;
-        int sc, mn;
-        if (sb < 4) { sc = s12[sb] & 63; mn = s12[sb + 4] & 63; }
-        else { sc = (s12[sb + 4] & 0x0F) | ((s12[sb - 4] >> 6) << 4); mn = (s12[sb + 4] >> 4) | ((s12[sb] >> 6) << 4); }
-        const float dl = d * (float) sc, ml = dmin * (float) mn;
-        const uint4 q0 = *(const uint4*) (blk + 16 + 32 * j), q1 = *(const uint4*) (blk + 32 + 32 * j);
-        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t x = h ? (w[i] >> 4) : w[i];
-#pragma unroll
-            for (int b = 0; b < 4; ++b) v[4 * i + b] = dl * (float) ((x >> (8 * b)) & 0x0F) - ml;
-        }
-    } else {   // Q8_0
-        const uint8_t* blk = row + (size_t) (2 * kt + h) * 34;
-        const float d = ld_f16(blk);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const uint32_t x = ld_u16(blk + 2 + 2 * i);
-            v[2 * i] = d * (float) (int8_t) (x & 0xFF);
-            v[2 * i + 1] = d * (float) (int8_t) (x >> 8);
-        }
-    }
-}
-
-// activation row (q8_1 blocks), K-tile kt, half h -> f32 values d * q
-__device__ __forceinline__ void act32(const uint8_t* xrow, int kt, int h, float* v) {
-    const uint8_t* b = xrow + (size_t) (2 * kt + h) * kQ81Bytes;
-    const float d = ld_f16(b);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t x = ld_u32(b + 4 + 4 * i);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) v[4 * i + j] = d * (float) (int8_t) ((x >> (8 * j)) & 0xFF);
-    }
-}
+constexpr int TM = 256;                 // weight rows of a block
+constexpr int TN = 256;                 // most activation rows of a block
+constexpr int BK = 32;                  // K values of one step
+constexpr int kSt = 3;                  // operand stages
+constexpr int kUnitRows = 64;           // weight rows of one raw unit
+constexpr int kDqWarps = 8;
+constexpr int kMmqThreads = (kDqWarps + 3) * 32;
+constexpr int kATile = TM * BK * 2;     // 16 KB
+constexpr int kBTile = TN * BK * 2;     // 16 KB (the first 8 KB when the block has <= 128 rows)
+constexpr int kStageBytes = kATile + kBTile;
+constexpr uint32_t kAccCols = 256;      // columns between the two accumulators
+constexpr int kMaxUnits = 12;
+template<int T> constexpr int kRawRow = T == MAYA_Q4_K ? 144 : 272;         // bytes of 256 K-values of one row
+template<int T> constexpr int kUnitBytes = kUnitRows * kRawRow<T>;
+template<int T> constexpr int kUnits = T == MAYA_Q4_K ? 12 : 7;
+template<int T> constexpr size_t kSmemBytes = (size_t) kSt * kStageBytes + (size_t) kUnits<T> * kUnitBytes<T>;
 
 struct MmqArgs {
-    const uint8_t* w;
-    size_t expert_bytes;
     int w_rows, w_cols;          // rows of one output (n_ff for the fused form: gate rows, then up rows), K
-    int n;                       // experts of this product
-    const int* expert_map;       // optional: expert i of the product is entry expert_map[i] of bounds
-    const uint8_t* xq;           // q8_1 rows, w_cols / 32 blocks each
+    int n;                       // matrices of this product
+    const int* expert_map;       // optional: matrix i owns the rows of bounds entry expert_map[i]
     const int* bounds;
     const int* ids;              // optional dst row of a sorted row
-    float* dst;
+    float* dst;                  // optional for the fused form
     int64_t ld_dst;
+    __half* xq_out;              // fused form, optional: q8_1-rounded h as f16, [sorted row][w_rows]
     float limit;
     unsigned* error;             // optional sticky error word
 };
 
-template<int T, bool GLU>
-__global__ void __launch_bounds__(kMmqThreads, 1) mmq_kernel(MmqArgs A) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ int s_scan[kMmqThreads];
-    __shared__ uint64_t s_done[kStages];
-    __shared__ uint64_t s_final;
-    __shared__ uint32_t s_tmem;
-    __shared__ int s_fail;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *(uint32_t*) &h; }
+__device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *(__half2*) &u; }
+// bytes (lo, hi) of x -> the half2 (1024 + lo, 1024 + hi): 0x64 is the high byte of 1024.0 in f16
+__device__ __forceinline__ __half2 bytes01_plus1024(uint32_t x) { return bits_h2(__byte_perm(x, 0x64646464u, 0x4140)); }
+__device__ __forceinline__ __half2 bytes23_plus1024(uint32_t x) { return bits_h2(__byte_perm(x, 0x64646464u, 0x4342)); }
 
-    // ---- which (expert, 128-row group) is blockIdx.y: inclusive scan of the per-expert group counts
-    //      (256 experts at a time; `base` carries the groups of the experts before the current 256)
+// The one-value-per-lane q8_1 rounding of maya_mmq_quantize: d = min(amax / 127, 65504) kept as f16, q = round(v / d)
+// clamped to +-127, result f16(d) * q.
+__device__ __forceinline__ __half q8_1_round_warp(float v) {
+    const float amax = __uint_as_float(__reduce_max_sync(0xFFFFFFFFu, __float_as_uint(fabsf(v))));
+    const float d = fminf(__fdiv_rn(amax, 127.0f), 65504.0f);
+    const float q = amax == 0.0f ? 0.0f : fmaxf(-127.0f, fminf(127.0f, roundf(__fdiv_rn(v, d))));
+    return __float2half_rn(__half2float(__float2half_rn(d)) * q);
+}
+
+// ---- Q4_K: the 16-byte header of a 144-byte block -> d * sc and -(dmin * m) of its 8 sub-blocks, as half2 pairs
+struct Q4Scales { __half2 dl[8], nml[8]; };
+__device__ __forceinline__ void q4k_scales(const uint4 hdr, Q4Scales& S) {
+    const __half2 dd = bits_h2(hdr.x);
+    const __half2 d2 = __low2half2(dd), m2 = __high2half2(dd);
+    const uint32_t s[3] = {hdr.y, hdr.z, hdr.w};
+    auto byte = [&](int i) -> uint32_t { return (s[i >> 2] >> (8 * (i & 3))) & 0xFF; };
+    const __half2 k1024 = __float2half2_rn(1024.0f);
+#pragma unroll
+    for (int sb = 0; sb < 8; ++sb) {
+        uint32_t sc, mn;
+        if (sb < 4) { sc = byte(sb) & 63; mn = byte(sb + 4) & 63; }
+        else { sc = (byte(sb + 4) & 0x0F) | ((byte(sb - 4) >> 6) << 4); mn = (byte(sb + 4) >> 4) | ((byte(sb) >> 6) << 4); }
+        const __half2 sc2 = __hsub2(bits_h2(0x64006400u | sc | (sc << 16)), k1024);      // exact
+        const __half2 mn2 = __hsub2(bits_h2(0x64006400u | mn | (mn << 16)), k1024);
+        S.dl[sb] = __hmul2(d2, sc2);
+        S.nml[sb] = __hneg2(__hmul2(m2, mn2));
+    }
+}
+// 32 weights of sub-block (2p + hi) from the 32 quant bytes of pair p
+__device__ __forceinline__ void q4k_stage(const uint4 qa, const uint4 qb, int hi, __half2 dl, __half2 nml, uint4 (&o)[4]) {
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    const __half2 k1024 = __float2half2_rn(1024.0f);
+    uint32_t r[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t x = (hi ? (w[i] >> 4) : w[i]) & 0x0F0F0F0Fu;
+        r[2 * i] = h2_bits(__hfma2(__hsub2(bytes01_plus1024(x), k1024), dl, nml));
+        r[2 * i + 1] = h2_bits(__hfma2(__hsub2(bytes23_plus1024(x), k1024), dl, nml));
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[c] = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+}
+// ---- Q8_0: block J (34 bytes) of a 272-byte raw row, read as three aligned 16-byte words
+template<int J>
+__device__ __forceinline__ void q80_stage(const uint8_t* rrow, uint4 (&o)[4]) {
+    constexpr int kBase = (34 * J) / 16 * 16, kOff = 34 * J - kBase;     // kOff = 0, 2, ..., 14
+    const uint4 a = *(const uint4*) (rrow + kBase), b = *(const uint4*) (rrow + kBase + 16), c = *(const uint4*) (rrow + kBase + 32);
+    const uint32_t w[12] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w, c.x, c.y, c.z, c.w};
+    const uint32_t dw = w[kOff / 4];
+    const __half dh = __ushort_as_half((unsigned short) ((kOff % 4) ? (dw >> 16) : (dw & 0xFFFF)));
+    const __half2 d2 = __half2half2(dh), k1152 = __float2half2_rn(1152.0f);
+    uint32_t r[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        constexpr int kQ = kOff + 2;
+        uint32_t x;
+        if constexpr (kQ % 4 == 0) x = w[kQ / 4 + i];
+        else x = __byte_perm(w[kQ / 4 + i], w[kQ / 4 + i + 1], 0x5432);
+        x ^= 0x80808080u;                                                  // q + 128 as unsigned bytes
+        r[2 * i] = h2_bits(__hmul2(__hsub2(bytes01_plus1024(x), k1152), d2));
+        r[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes23_plus1024(x), k1152), d2));
+    }
+#pragma unroll
+    for (int c2 = 0; c2 < 4; ++c2) o[c2] = make_uint4(r[4 * c2], r[4 * c2 + 1], r[4 * c2 + 2], r[4 * c2 + 3]);
+}
+
+struct Pipe {                       // static shared memory of a block
+    uint64_t a_full[kSt], b_full[kSt], empty[kSt];
+    uint64_t raw_full[kMaxUnits], raw_empty[kMaxUnits];
+    uint64_t final;
+    uint32_t tmem;
+    int fail;
+    int scan[kMmqThreads];
+};
+
+__device__ __forceinline__ bool failed(const Pipe& P) { return *(volatile const int*) &P.fail != 0; }
+// Bounded wait; false when this wait ran out (the block's failure flag is then set) or another role has failed.
+__device__ __forceinline__ bool wait_or_fail(Pipe& P, uint64_t* bar, uint32_t parity) {
+    for (unsigned i = 0; i < (1u << 21); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 128) {
+            __nanosleep(64);
+            if ((i & 255) == 0 && failed(P)) return false;
+        }
+    }
+    *(volatile int*) &P.fail = 1;
+    return false;
+}
+
+template<int T, bool GLU>
+__global__ void __launch_bounds__(kMmqThreads, 1)
+mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x128,
+           const __grid_constant__ CUtensorMap tm_x256, const MmqArgs A) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ Pipe P;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int NU = kUnits<T>;
+
+    // ---- which (matrix, 256-row group) is blockIdx.y: inclusive scan of the per-matrix group counts, kMmqThreads
+    //      matrices at a time; `base` carries the groups of the matrices before
     int found_e = -1, found_g = 0;
     {
         int base = 0;
@@ -127,26 +180,26 @@ __global__ void __launch_bounds__(kMmqThreads, 1) mmq_kernel(MmqArgs A) {
             int cnt = 0;
             if (e < A.n) {
                 const int be = A.expert_map ? A.expert_map[e] : e;
-                cnt = (A.bounds[be + 1] - A.bounds[be] + BN - 1) / BN;
+                cnt = (A.bounds[be + 1] - A.bounds[be] + TN - 1) / TN;
             }
-            s_scan[tid] = cnt;
+            P.scan[tid] = cnt;
             __syncthreads();
             for (int o = 1; o < kMmqThreads; o <<= 1) {
-                const int v = tid >= o ? s_scan[tid - o] : 0;
+                const int v = tid >= o ? P.scan[tid - o] : 0;
                 __syncthreads();
-                s_scan[tid] += v;
+                P.scan[tid] += v;
                 __syncthreads();
             }
-            const int total = s_scan[kMmqThreads - 1];
+            const int total = P.scan[kMmqThreads - 1];
             const int want = (int) blockIdx.y - base;
             if (want < total) {
                 int lo = 0, hi = kMmqThreads - 1;       // the first entry whose inclusive sum exceeds `want`
                 while (lo < hi) {
                     const int mid = (lo + hi) >> 1;
-                    if (s_scan[mid] > want) hi = mid; else lo = mid + 1;
+                    if (P.scan[mid] > want) hi = mid; else lo = mid + 1;
                 }
                 found_e = e0 + lo;
-                found_g = want - (lo > 0 ? s_scan[lo - 1] : 0);
+                found_g = want - (lo > 0 ? P.scan[lo - 1] : 0);
             }
             base += total;
             __syncthreads();
@@ -154,107 +207,181 @@ __global__ void __launch_bounds__(kMmqThreads, 1) mmq_kernel(MmqArgs A) {
     }
     if (found_e < 0) return;                        // beyond the last group: uniform for the whole block
     const int be = A.expert_map ? A.expert_map[found_e] : found_e;
-    const int row0 = A.bounds[be] + found_g * BN;
-    const int nrows = min(BN, A.bounds[be + 1] - row0);
-    const int m0 = (int) blockIdx.x * BM;
-    const int K = A.w_cols, nkt = K / BK;
-    const size_t rbw = row_bytes(T, K);
-    const uint8_t* wexp = A.w + (size_t) found_e * A.expert_bytes;
-    const size_t xrb = (size_t) (K / 32) * kQ81Bytes;
+    const int row0 = A.bounds[be] + found_g * TN;
+    const int nrows = min(TN, A.bounds[be + 1] - row0);
+    const bool big = nrows > 128;                   // the activation tile holds 256 rows instead of 128
+    const int m0 = (int) blockIdx.x * (GLU ? 128 : TM);
+    const int nkt = A.w_cols / BK, nkb = A.w_cols / 256;
 
-    constexpr int NA = GLU ? 2 : 1;
-    constexpr int kStageBytes = (NA + 1) * kTileBytes;
-    constexpr uint32_t kCols = GLU ? 256 : 128;
-
+    uint8_t* const raw = smem + (size_t) kSt * kStageBytes;
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(&s_done[s], 1);
-        mbar_init(&s_final, 1);
-        s_fail = 0;
+        for (int s = 0; s < kSt; ++s) { mbar_init(&P.a_full[s], kDqWarps); mbar_init(&P.b_full[s], 1); mbar_init(&P.empty[s], 1); }
+        for (int u = 0; u < NU; ++u) { mbar_init(&P.raw_full[u], 1); mbar_init(&P.raw_empty[u], 2); }
+        mbar_init(&P.final, 1);
+        P.fail = 0;
     }
     mbar_fence_init();
-    if (warp == 0) tmem_alloc(&s_tmem, kCols);
+    if (warp == 0) tmem_alloc(&P.tmem, 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = s_tmem;
-    constexpr uint32_t idesc = idesc_f16(BM, BN);
+    const uint32_t tmem = P.tmem;
 
-    const int r = tid & 127, h = tid >> 7;          // this thread's row of every tile and its 32-value half
-    bool ok = true;
-    for (int kt = 0; kt < nkt; ++kt) {
-        const int s = kt % kStages;
-        if (kt >= kStages && ok) {
-            if (!mbar_wait(&s_done[s], ((kt / kStages) - 1) & 1)) ok = false;
+    if (warp < kDqWarps) {
+        // ------------------------------------------------------------ weight expansion: thread = row `tid` of the slab
+        const int slab = tid >> 6;
+        const uint8_t* const rbase = raw + (size_t) (tid & 63) * kRawRow<T>;
+        bool ok = true;
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            const int u = kb * 4 + slab, slot = u % NU;
+            if (!wait_or_fail(P, &P.raw_full[slot], (u / NU) & 1)) { ok = false; break; }
+            const uint8_t* rrow = rbase + (size_t) slot * kUnitBytes<T>;
+            auto put = [&](int j, const uint4 (&o)[4]) {
+                const int kt = kb * 8 + j, s = kt % kSt;
+                uint8_t* at = smem + (size_t) s * kStageBytes + tid * 16;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) *(uint4*) (at + c * (TM * 16)) = o[c];
+                fence_proxy_async();                 // these generic-proxy writes before the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&P.a_full[s]);
+            };
+            auto ready = [&](int j) -> bool {        // stage of step kb * 8 + j free again?
+                const int kt = kb * 8 + j;
+                return kt < kSt || wait_or_fail(P, &P.empty[kt % kSt], ((kt / kSt) - 1) & 1);
+            };
+            uint4 o[4];
+            if constexpr (T == MAYA_Q4_K) {
+                Q4Scales S;
+                q4k_scales(*(const uint4*) rrow, S);
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                    const uint4 qa = *(const uint4*) (rrow + 16 + 32 * p), qb = *(const uint4*) (rrow + 32 + 32 * p);
+#pragma unroll
+                    for (int hi = 0; hi < 2; ++hi) {
+                        q4k_stage(qa, qb, hi, S.dl[2 * p + hi], S.nml[2 * p + hi], o);
+                        if (!ready(2 * p + hi)) { ok = false; break; }
+                        put(2 * p + hi, o);
+                    }
+                    if (!ok) break;
+                }
+            } else {
+#define MAYA_Q80_STEP(J) if (ok) { q80_stage<J>(rrow, o); if (!ready(J)) ok = false; else put(J, o); }
+                MAYA_Q80_STEP(0) MAYA_Q80_STEP(1) MAYA_Q80_STEP(2) MAYA_Q80_STEP(3)
+                MAYA_Q80_STEP(4) MAYA_Q80_STEP(5) MAYA_Q80_STEP(6) MAYA_Q80_STEP(7)
+#undef MAYA_Q80_STEP
+            }
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&P.raw_empty[slot]);      // the unit may be overwritten
         }
-        uint8_t* stage = smem + (size_t) s * kStageBytes;
-        float v[32];
+        // ------------------------------------------------------------ epilogue
+        if (ok && !wait_or_fail(P, &P.final, 0)) ok = false;
+        tc_fence_after();
         if (ok) {
+            const int q = warp & 3, c_lo = (warp >> 2) * 128;
+            const uint32_t lane_base = tmem + ((uint32_t) (32 * q) << 16);
+            for (int c0 = c_lo; c0 < c_lo + 128 && c0 < nrows; c0 += 32) {
+                float v[32];
+                if constexpr (GLU) {
+                    float up[32];
+                    tmem_ld32(lane_base + c0, v);
+                    tmem_ld32(lane_base + kAccCols + c0, up);
+                    const int m = m0 + 32 * q + lane;
 #pragma unroll
-            for (int a = 0; a < NA; ++a) {
-                dequant32<T>(wexp + (size_t) (a * A.w_rows + m0 + r) * rbw, kt, h, v);
-                store32(stage + a * kTileBytes, BM, r, 4 * h, v);
-            }
-            if (r < nrows) act32(A.xq + (size_t) (row0 + r) * xrb, kt, h, v);
-            else {
+                    for (int j = 0; j < 32; ++j) {
+                        if (c0 + j < nrows) {                     // uniform in the warp
+                            const float h = swiglu(v[j], up[j], A.limit);
+                            const int row = row0 + c0 + j;
+                            if (A.dst) A.dst[(int64_t) (A.ids ? A.ids[row] : row) * A.ld_dst + m] = h;
+                            if (A.xq_out) A.xq_out[(int64_t) row * A.w_rows + m] = q8_1_round_warp(h);
+                        }
+                    }
+                } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = 0.0f;
-            }
-            store32(stage + NA * kTileBytes, BN, r, 4 * h, v);
-        }
-        fence_proxy_async();                         // my shared-memory writes before the tensor core's reads
-        if (!ok) s_fail = 1;
-        __syncthreads();
-        if (s_fail) { ok = false; }
-        if (tid == 0 && ok) {
-            tc_fence_after();
-            const uint32_t a_base = smem_u32(stage), b_base = smem_u32(stage + NA * kTileBytes);
+                    for (int a = 0; a < 2; ++a) {
+                        if (m0 + 128 * a >= A.w_rows) break;
+                        tmem_ld32(lane_base + a * kAccCols + c0, v);
+                        const int m = m0 + 128 * a + 32 * q + lane;
 #pragma unroll
-            for (int kk = 0; kk < BK / 16; ++kk) {
-                const uint64_t bd = smem_desc(b_base + kk * 2 * BN * 16, BN * 16, 128);
-#pragma unroll
-                for (int a = 0; a < NA; ++a) {
-                    const uint64_t ad = smem_desc(a_base + a * kTileBytes + kk * 2 * BM * 16, BM * 16, 128);
-                    mma_f16_ss(tmem + a * BN, ad, bd, idesc, (kt > 0 || kk > 0) ? 1u : 0u);
-                }
-            }
-            mma_commit(&s_done[s]);
-            if (kt == nkt - 1) mma_commit(&s_final);
-        }
-    }
-    // ---- epilogue: warps 0..3 own the four 32-lane quadrants of tensor memory
-    if (ok && !mbar_wait(&s_final, 0)) ok = false;
-    tc_fence_after();
-    if (ok && warp < 4) {
-        const int m = m0 + 32 * warp + lane;         // this thread's weight row
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-            if (c0 >= nrows) break;
-            float g[32];
-            tmem_ld32(tmem + ((uint32_t) (32 * warp) << 16) + c0, g);
-            if constexpr (GLU) {
-                float u[32];
-                tmem_ld32(tmem + ((uint32_t) (32 * warp) << 16) + BN + c0, u);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) g[j] = swiglu(g[j], u[j], A.limit);
-            }
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                if (c0 + j < nrows) {
-                    const int row = row0 + c0 + j;
-                    const int64_t drow = A.ids ? A.ids[row] : row;
-                    A.dst[drow * A.ld_dst + m] = g[j];
+                        for (int j = 0; j < 32; ++j) {
+                            if (c0 + j < nrows) {
+                                const int row = row0 + c0 + j;
+                                A.dst[(int64_t) (A.ids ? A.ids[row] : row) * A.ld_dst + m] = v[j];
+                            }
+                        }
+                    }
                 }
             }
         }
+    } else if (warp == kDqWarps) {
+        // ------------------------------------------------------------ raw weight units (one lane)
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                for (int sl = 0; sl < 4; ++sl) {
+                    const int u = kb * 4 + sl, slot = u % NU;
+                    if (u >= NU && !wait_or_fail(P, &P.raw_empty[slot], ((u / NU) - 1) & 1)) { ok = false; break; }
+                    const int wrow = GLU ? (sl < 2 ? m0 + 64 * sl : A.w_rows + m0 + 64 * (sl - 2)) : m0 + 64 * sl;
+                    mbar_expect_tx(&P.raw_full[slot], kUnitBytes<T>);
+                    tma_load_3d(raw + (size_t) slot * kUnitBytes<T>, &tm_w, &P.raw_full[slot], kb * (kRawRow<T> / 4), wrow, found_e);
+                    issued = u + 1;
+                }
+            }
+            if (!ok)                                             // let the copies in flight land before the block ends
+                for (int u = max(0, issued - NU); u < issued; ++u) wait_or_fail(P, &P.raw_full[u % NU], (u / NU) & 1);
+        }
+    } else if (warp == kDqWarps + 1) {
+        // ------------------------------------------------------------ tensor-core issue (one lane)
+        if (lane == 0) {
+            const int n_mma = max(16, (nrows + 15) & ~15);
+            const uint32_t idesc = (1u << 4) | ((uint32_t) (n_mma >> 3) << 17) | ((uint32_t) (128 >> 4) << 24);
+            const uint32_t lbo_b = big ? TN * 16 : 128 * 16;
+            bool ok = true;
+            for (int kt = 0; kt < nkt; ++kt) {
+                const int s = kt % kSt;
+                if (!wait_or_fail(P, &P.a_full[s], (kt / kSt) & 1) || !wait_or_fail(P, &P.b_full[s], (kt / kSt) & 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_base = smem_u32(smem + (size_t) s * kStageBytes), b_base = a_base + kATile;
+#pragma unroll
+                for (int kk = 0; kk < 2; ++kk) {
+                    const uint64_t bd = smem_desc(b_base + kk * 2 * lbo_b, lbo_b, 128);
+#pragma unroll
+                    for (int a = 0; a < 2; ++a) {
+                        const uint64_t ad = smem_desc(a_base + a * (128 * 16) + kk * 2 * (TM * 16), TM * 16, 128);
+                        mma_f16_ss(tmem + a * kAccCols, ad, bd, idesc, (kt > 0 || kk > 0) ? 1u : 0u);
+                    }
+                }
+                mma_commit(&P.empty[s]);
+            }
+            if (ok) mma_commit(&P.final);
+        }
+    } else {
+        // ------------------------------------------------------------ activation tiles (one lane)
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int kt = 0; kt < nkt; ++kt) {
+                const int s = kt % kSt;
+                if (kt >= kSt && !wait_or_fail(P, &P.empty[s], ((kt / kSt) - 1) & 1)) { ok = false; break; }
+                mbar_expect_tx(&P.b_full[s], big ? kBTile : kBTile / 2);
+                tma_load_3d(smem + (size_t) s * kStageBytes + kATile, big ? &tm_x256 : &tm_x128, &P.b_full[s], 0, row0, kt * 4);
+                issued = kt + 1;
+            }
+            if (!ok)
+                for (int kt = max(0, issued - kSt); kt < issued; ++kt) wait_or_fail(P, &P.b_full[kt % kSt], (kt / kSt) & 1);
+        }
     }
-    if (!ok && tid == 0 && A.error != nullptr) atomicExch(A.error, 1u);
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, kCols);
+    if (warp == 0) tmem_dealloc(tmem, 512);
+    if (tid == 0 && failed(P) && A.error != nullptr) atomicExch(A.error, 1u);
 }
 
+// x rows (gathered through ids) -> f16 rows of their q8_1 image: one warp per 32 values
 template<typename X>
 __global__ void __launch_bounds__(256) mmq_quantize_kernel(const X* __restrict__ x, const int* __restrict__ ids,
-                                                           uint8_t* __restrict__ xq, int64_t cols, int64_t ld,
+                                                           __half* __restrict__ xq, int64_t cols, int64_t ld,
                                                            int64_t n_blocks) {
     const int lane = threadIdx.x & 31;
     const int64_t b = (int64_t) blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -264,7 +391,7 @@ __global__ void __launch_bounds__(256) mmq_quantize_kernel(const X* __restrict__
     float v;
     if constexpr (sizeof(X) == 2) v = __uint_as_float((uint32_t) x[src * ld + kb * 32 + lane] << 16);   // bf16 bits, widened exactly
     else v = x[src * ld + kb * 32 + lane];
-    q8_1_store_warp(v, xq + b * kQ81Bytes, lane);
+    xq[b * 32 + lane] = q8_1_round_warp(v);
 }
 
 template<typename X>
@@ -274,39 +401,79 @@ int launch_quantize(const X* x, const int32_t* ids, void* xq, int type, int64_t 
     if (!x || !xq || cols <= 0 || cols % 32 || ld < cols) return refuse(MAYA_ERR_ARG);
     const int64_t nb = rows * (cols / 32);
     if ((nb + 7) / 8 > 0x7FFFFFFF) return refuse(MAYA_ERR_LIMIT);
-    mmq_quantize_kernel<X><<<(unsigned) ((nb + 7) / 8), 256, 0, as_stream(stream)>>>(x, ids, (uint8_t*) xq, cols, ld, nb);
+    mmq_quantize_kernel<X><<<(unsigned) ((nb + 7) / 8), 256, 0, as_stream(stream)>>>(x, ids, (__half*) xq, cols, ld, nb);
     return note_launch("mmq_quantize");
 }
 
+// ---- tensor maps (driver entry point looked up once; the library does not link libcuda)
+PFN_cuTensorMapEncodeTiled encode_fn() {
+    static PFN_cuTensorMapEncodeTiled fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return (PFN_cuTensorMapEncodeTiled) p;
+    }();
+    return fn;
+}
+bool make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, const cuuint64_t (&dim)[3], const cuuint64_t (&stride)[2],
+              const cuuint32_t (&box)[3]) {
+    PFN_cuTensorMapEncodeTiled fn = encode_fn();
+    if (!fn) return false;
+    const cuuint32_t es[3] = {1, 1, 1};
+    return fn(m, dt, 3, const_cast<void*>(base), dim, stride, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template<int T, bool GLU>
-int launch_mmq(const MmqArgs& A, int64_t total_rows, cudaStream_t s) {
-    constexpr size_t smem = (size_t) kStages * ((GLU ? 3 : 2) * kTileBytes);
+int launch_mmq(const maya_mmq_product* p, const MmqArgs& A, cudaStream_t s) {
+    const int64_t mat_rows = p->w_rows, K = p->w_cols;
+    const size_t rbw = row_bytes(T, K);
+    CUtensorMap tw, tx128, tx256;
+    {   // weights as 32-bit words: (word in row, row in matrix, matrix); a box = 256 K-values of 64 rows
+        const cuuint64_t dim[3] = {(cuuint64_t) (rbw / 4), (cuuint64_t) mat_rows, (cuuint64_t) p->n};
+        const cuuint64_t st[2] = {(cuuint64_t) rbw, (cuuint64_t) p->expert_bytes};
+        const cuuint32_t box[3] = {(cuuint32_t) (kRawRow<T> / 4), kUnitRows, 1};
+        if (!make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, p->w, dim, st, box)) return note_launch("mmq weight tensor map");
+    }
+    {   // activations: (8 values, row, 16-byte chunk of the row) so that a box lands as [chunk][row][16 bytes]
+        const cuuint64_t dim[3] = {8, (cuuint64_t) p->total_rows, (cuuint64_t) (K / 8)};
+        const cuuint64_t st[2] = {(cuuint64_t) K * 2, 16};
+        const cuuint32_t b128[3] = {8, 128, BK / 8}, b256[3] = {8, 256, BK / 8};
+        if (!make_map(&tx128, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p->xq, dim, st, b128) ||
+            !make_map(&tx256, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p->xq, dim, st, b256))
+            return note_launch("mmq activation tensor map");
+    }
+    constexpr size_t smem = kSmemBytes<T>;
     if (cudaFuncSetAttribute(mmq_kernel<T, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess)
         return note_launch("mmq smem attribute");
-    const int64_t groups = total_rows / BN + A.n;     // an upper bound of sum(ceil(rows_e / 128)), known without the counts
+    const int64_t groups = p->total_rows / TN + p->n;   // an upper bound of sum(ceil(rows_e / 256)), known without the counts
     if (groups > 65535) return refuse(MAYA_ERR_LIMIT);
-    const dim3 grid((unsigned) (A.w_rows / BM), (unsigned) groups);
-    mmq_kernel<T, GLU><<<grid, kMmqThreads, smem, s>>>(A);
+    const int slab = GLU ? 128 : TM;
+    const dim3 grid((unsigned) ((A.w_rows + slab - 1) / slab), (unsigned) groups);
+    mmq_kernel<T, GLU><<<grid, kMmqThreads, smem, s>>>(tw, tx128, tx256, A);
     return note_launch("mmq");
 }
 
 int run_product(const maya_mmq_product* p, bool glu, float limit, cudaStream_t s) {
-    if (!p || !p->w || !p->xq || !p->bounds || !p->dst) return refuse(MAYA_ERR_ARG);
+    if (!p || !p->w || !p->xq || !p->bounds) return refuse(MAYA_ERR_ARG);
+    if (!p->dst && !(glu && p->xq_out)) return refuse(MAYA_ERR_ARG);
     if (p->type != MAYA_Q4_K && p->type != MAYA_Q8_0) return refuse(MAYA_ERR_TYPE);
     if (p->n <= 0 || p->total_rows <= 0) return MAYA_OK;
     const int64_t out_rows = glu ? p->w_rows / 2 : p->w_rows;
-    if (p->w_cols <= 0 || p->w_cols % 256 || out_rows <= 0 || out_rows % BM || (glu && p->w_rows % 2)) return refuse(MAYA_ERR_ARG);
-    if (p->expert_bytes % (size_t) type_bytes(p->type) || p->ld_dst < out_rows) {
-        std::fprintf(stderr, "maya_mmq_run: expert_bytes %zu is not a whole number of blocks, or ld_dst too small\n", p->expert_bytes);
+    if (p->w_cols <= 0 || p->w_cols % 256 || out_rows <= 0 || out_rows % 128 || (glu && p->w_rows % 2)) return refuse(MAYA_ERR_ARG);
+    if (p->expert_bytes % (size_t) type_bytes(p->type) || p->expert_bytes % 16 || (p->dst && p->ld_dst < out_rows)) {
+        std::fprintf(stderr, "maya_mmq_run: expert_bytes %zu is not a whole number of blocks and of 16 bytes, or ld_dst too small\n",
+                     p->expert_bytes);
         return refuse(MAYA_ERR_ARG);
     }
-    if (!aligned16(p->w) || p->expert_bytes % 16) return refuse(MAYA_ERR_ARG);
+    if (!aligned16(p->w) || !aligned16(p->xq) || (p->xq_out && !aligned16(p->xq_out))) return refuse(MAYA_ERR_ARG);
     MmqArgs A{};
-    A.w = (const uint8_t*) p->w; A.expert_bytes = p->expert_bytes; A.w_rows = (int) out_rows; A.w_cols = (int) p->w_cols;
-    A.n = p->n; A.expert_map = p->expert_map; A.xq = (const uint8_t*) p->xq; A.bounds = p->bounds; A.ids = p->ids;
-    A.dst = p->dst; A.ld_dst = p->ld_dst; A.limit = limit; A.error = p->error;
-    if (p->type == MAYA_Q4_K) return glu ? launch_mmq<MAYA_Q4_K, true>(A, p->total_rows, s) : launch_mmq<MAYA_Q4_K, false>(A, p->total_rows, s);
-    return glu ? launch_mmq<MAYA_Q8_0, true>(A, p->total_rows, s) : launch_mmq<MAYA_Q8_0, false>(A, p->total_rows, s);
+    A.w_rows = (int) out_rows; A.w_cols = (int) p->w_cols; A.n = p->n; A.expert_map = p->expert_map; A.bounds = p->bounds;
+    A.ids = p->ids; A.dst = p->dst; A.ld_dst = p->ld_dst; A.xq_out = glu ? (__half*) p->xq_out : nullptr; A.limit = limit;
+    A.error = p->error;
+    if (p->type == MAYA_Q4_K) return glu ? launch_mmq<MAYA_Q4_K, true>(p, A, s) : launch_mmq<MAYA_Q4_K, false>(p, A, s);
+    return glu ? launch_mmq<MAYA_Q8_0, true>(p, A, s) : launch_mmq<MAYA_Q8_0, false>(p, A, s);
 }
 
 }  // namespace
@@ -317,7 +484,7 @@ using namespace maya;
 extern "C" int maya_mmq_supported(int type) { return type == MAYA_Q4_K || type == MAYA_Q8_0; }
 extern "C" size_t maya_mmq_q8_bytes(int64_t rows, int64_t cols) {
     if (rows <= 0 || cols <= 0 || cols % 32) return 0;
-    return (size_t) rows * (size_t) (cols / 32) * kQ81Bytes;
+    return (size_t) rows * (size_t) cols * sizeof(__half);
 }
 extern "C" int maya_mmq_quantize(const float* x, const int32_t* ids, void* xq, int type, int64_t cols, int64_t ld,
                                  int64_t rows, void* stream) {

@@ -3,8 +3,8 @@ whole prompt-path layer (api.MoePrefill).
 
 Two bars.  Against the q8_1 oracle (the reference's GPU arithmetic: integer dots of q8_1 activations) the tolerance is
 1e-2 in max-norm and in L2: the tensor-core path multiplies the same q8_1-rounded activations and the same dequantized
-weights, each rounded once more to f16.  Against a float64 product of exactly those f16 operands (built here with
-numpy from the oracle's dequantizer) the tolerance is 2e-5: that one pins the kernel itself - tile layout, descriptors,
+weights, each rounded to f16.  Against a float64 product of exactly those f16 operands (built here with numpy: the
+oracle's q8_1 blocks as d * q, Q8_0 weights as q * d, Q4_K weights through the kernel's packed-half steps) the tolerance is 2e-5: that one pins the kernel itself - tile layout, descriptors,
 the K loop, ragged groups - with only f32 accumulation order left over."""
 import numpy as np
 import pytest
@@ -39,15 +39,42 @@ def synth_matrices(T, api, t, n, rows, cols, seed):
     return w
 
 
-def f16_operands(oracle, t, w_host, rows, cols, xq_rows):
-    """(weights, activations) as the kernel builds them: dequantized / d*q, rounded once to f16, widened to f64."""
-    w = oracle.dequantize(t, w_host, rows * cols).reshape(rows, cols).astype(np.float16).astype(np.float64)
-    nb = cols // 32
-    blk = xq_rows.reshape(-1, nb, 36)
-    d = blk[:, :, 0:2].copy().view(np.float16).astype(np.float32)           # [rows, nb, 1]
-    q = blk[:, :, 4:].copy().view(np.int8).astype(np.float32)                # [rows, nb, 32]
-    x = (d * q).astype(np.float16).astype(np.float64).reshape(-1, cols)
-    return w, x
+def q4k_f16_weights(raw, rows, cols):
+    """Q4_K weights as the kernel's packed-half arithmetic makes them: dl = f16(d * sc), ml = f16(dmin * m),
+    w = f16(q * dl - ml) with the product and difference exact before the one rounding (a fused multiply-add)."""
+    blk = np.ascontiguousarray(raw).reshape(rows, cols // 256, 144)
+    d = blk[:, :, 0:2].copy().view(np.float16).astype(np.float32)            # [rows, nb, 1]
+    dmin = blk[:, :, 2:4].copy().view(np.float16).astype(np.float32)
+    sc8 = blk[:, :, 4:16].astype(np.int32)
+    qs = blk[:, :, 16:144]
+    out = np.empty((rows, cols // 256, 8, 32), np.float64)
+    for sb in range(8):
+        if sb < 4:
+            sc, mn = sc8[:, :, sb] & 63, sc8[:, :, sb + 4] & 63
+        else:
+            sc = (sc8[:, :, sb + 4] & 0x0F) | ((sc8[:, :, sb - 4] >> 6) << 4)
+            mn = (sc8[:, :, sb + 4] >> 4) | ((sc8[:, :, sb] >> 6) << 4)
+        dl = (d[:, :, 0] * sc).astype(np.float16).astype(np.float64)
+        ml = (dmin[:, :, 0] * mn).astype(np.float16).astype(np.float64)
+        q = qs[:, :, 32 * (sb // 2):32 * (sb // 2) + 32]
+        q = ((q >> 4) if sb & 1 else (q & 0x0F)).astype(np.float64)
+        out[:, :, sb, :] = (q * dl[:, :, None] - ml[:, :, None]).astype(np.float16).astype(np.float64)
+    return out.reshape(rows, cols)
+
+
+def q8_1_image(oracle, x_rows):
+    """f16 rows d * q of the oracle's q8_1 blocks: what maya_mmq_quantize stores."""
+    rows, cols = x_rows.shape
+    blk = np.stack([oracle.quantize_q8_1(r) for r in x_rows]).reshape(rows, cols // 32, 36)
+    d = blk[:, :, 0:2].copy().view(np.float16).astype(np.float32)
+    q = blk[:, :, 4:].copy().view(np.int8).astype(np.float32)
+    return (d * q).astype(np.float16).reshape(rows, cols)
+
+
+def f16_weights(oracle, t, w_host, rows, cols):
+    if t == H.Q4_K:
+        return q4k_f16_weights(w_host, rows, cols)
+    return oracle.dequantize(t, w_host, rows * cols).reshape(rows, cols).astype(np.float16).astype(np.float64)
 
 
 COUNTS = [0, 3, 130, 128, 1, 0, 257]
@@ -64,9 +91,9 @@ def test_grouped_product_ragged_groups(T, api, oracle, t):
     row_tok = rng.integers(0, n_tok, total).astype(np.int32)
     dst_row = rng.permutation(total + 5)[:total].astype(np.int32)            # scattered, with holes
     xq = api.mmq_quantize(dev(T, x), dev(T, row_tok), t)
-    xq_host = xq.cpu().numpy()[: total * (cols // 32) * 36]
-    want_q = np.concatenate([oracle.quantize_q8_1(x[r]) for r in row_tok])
-    assert np.array_equal(xq_host, want_q), "mmq_quantize differs from the q8_1 oracle"
+    xq_host = xq.cpu().numpy().view(np.float16).reshape(total, cols)
+    assert np.array_equal(xq_host, q8_1_image(oracle, x[row_tok])), "mmq_quantize differs from the q8_1 oracle's d * q"
+    xq_blocks = [oracle.quantize_q8_1(x[r]) for r in row_tok]
 
     ld = rows + 64
     dst = T.full((total + 5, ld), 7.0, dtype=T.float32, device="cuda")
@@ -82,12 +109,12 @@ def test_grouped_product_ragged_groups(T, api, oracle, t):
         a, b = int(bounds[e]), int(bounds[e + 1])
         if a == b:
             continue
-        wf, xf = f16_operands(oracle, t, w_host[e], rows, cols, xq_host.reshape(total, -1)[a:b])
+        wf, xf = f16_weights(oracle, t, w_host[e], rows, cols), xq_host[a:b].astype(np.float64)
         pin = xf @ wf.T
         g = got[dst_row[a:b], :rows]
         assert H.rel_err(g, pin) <= PIN, f"expert {e}: not the product of its f16 operands"
         for r in (a, b - 1):                                                  # the q8_1 oracle on the group's edge rows
-            want = oracle.mmvq(t, w_host[e], xq_host.reshape(total, -1)[r], cols, rows)[0]
+            want = oracle.mmvq(t, w_host[e], xq_blocks[r], cols, rows)[0]
             assert H.rel_err(got[dst_row[r], :rows], want) <= TOL and H.rel_l2(got[dst_row[r], :rows], want) <= TOL
         hit[dst_row[a:b]] = True
     assert np.all(got[:, rows:] == 7.0), "wrote past w_rows"
@@ -109,9 +136,14 @@ def test_fused_glu_equals_product_then_swiglu_bitwise(T, api, t, limit):
     want = api.swiglu_rows(gu, n_ff, limit)
     h = T.zeros((total, n_ff), dtype=T.float32, device="cuda")
     api.mmq_run_glu(api.mmq_product(w, t, 2 * n_ff, cols, w.shape[1], n, xq, bounds, None, total, h, n_ff), limit)
+    # ... and with the q8_1 rounding of h in the write-back: the same bits as quantizing h afterwards
+    hq = T.zeros(api.mmq_q8_bytes(total, n_ff), dtype=T.uint8, device="cuda")
+    api.mmq_run_glu(api.mmq_product(w, t, 2 * n_ff, cols, w.shape[1], n, xq, bounds, None, total, None, n_ff, xq_out=hq), limit)
+    want_hq = api.mmq_quantize(want, None, t)
     T.cuda.synchronize()
     assert np.abs(gu.cpu().numpy()).max() > 0.1
     assert T.equal(h, want)
+    assert T.equal(hq, want_hq)
 
 
 def test_expert_map_selects_bounds_entries(T, api):
@@ -150,7 +182,7 @@ def test_refusals(T, api):
             api.mmq_run(ok(**bad))
     with pytest.raises(api.MayaError):
         api.mmq_run_glu(ok(w_rows=128), H.INF)            # n_ff = 64 is not a multiple of 128
-    assert api.mmq_q8_bytes(3, 100) == 0 and api.mmq_q8_bytes(3, 256) == 3 * 8 * 36
+    assert api.mmq_q8_bytes(3, 100) == 0 and api.mmq_q8_bytes(3, 256) == 3 * 256 * 2
     assert api.mmq_supported(H.Q8_0) and api.mmq_supported(H.Q4_K) and not api.mmq_supported(H.IQ3_S)
 
 
