@@ -414,12 +414,14 @@ def main() -> None:
     ap.add_argument("--ar", default="peer", choices=["peer", "nccl"], help="N > 1: how the ranks' partial outputs are summed")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
                     help="decode: the headline single-token layer (C2); prefill: the 4096-token prompt chunk (C4), 1 GPU")
+    ap.add_argument("--prefill-scale", type=int, default=1,
+                    help="prefill only: divide experts and tokens by this (a reduced case for profiler captures)")
     args = ap.parse_args()
     if args.workload == "prefill" and args.impl == "ours":
         from project_maya_b200 import bench_prefill
         steps = args.steps if args.steps != 256 else 8
         sampler = ClockSampler(0)
-        line = bench_prefill.run(steps, args.warmup if args.warmup != 8 else 3, min(args.layers, 2), sampler)
+        line = bench_prefill.run(steps, args.warmup if args.warmup != 8 else 3, min(args.layers, 2), sampler, args.prefill_scale)
         line["clocks"] = sampler.summary()
         print(json.dumps(line))
         return

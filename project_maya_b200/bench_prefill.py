@@ -29,8 +29,8 @@ def tensor_peak() -> tuple[float, str]:
     return 1590.0, "fallback"
 
 
-def build_pools(torch, api, seed: int):
-    Hd, FF, E = CFG["n_embd"], CFG["n_ff"], CFG["n_expert"]
+def build_pools(torch, api, seed: int, E: int):
+    Hd, FF = CFG["n_embd"], CFG["n_ff"]
     types = S.expert_types("C4", E, CFG["types"])
     pools = []
     for t in sorted(set(int(v) for v in types)):
@@ -45,15 +45,17 @@ def build_pools(torch, api, seed: int):
     return pools
 
 
-def run(steps: int, warmup: int, layers: int, clock_sampler=None) -> dict:
+def run(steps: int, warmup: int, layers: int, clock_sampler=None, scale: int = 1) -> dict:
+    """scale > 1 divides both the number of experts and the number of tokens (the rows per expert stay the same): a
+    reduced case of the same kernels for profiler captures; the headline configuration is scale = 1."""
     import torch
 
     from . import _lib, api
 
     lib = _lib.load()
-    Hd, FF, E, k, T = CFG["n_embd"], CFG["n_ff"], CFG["n_expert"], CFG["k"], CFG["T"]
+    Hd, FF, E, k, T = CFG["n_embd"], CFG["n_ff"], CFG["n_expert"] // scale, CFG["k"], CFG["T"] // scale
     lc = api.MoeLayerConfig(Hd, FF, E, k, S.Q8_0, S.Q8_0)
-    pf = [api.MoePrefill(lc, None, max_tokens=T, pools=build_pools(torch, api, 7000 + 100000 * i)) for i in range(layers)]
+    pf = [api.MoePrefill(lc, None, max_tokens=T, pools=build_pools(torch, api, 7000 + 100000 * i, E)) for i in range(layers)]
     logits_h = torch.from_numpy(S.router_logits("C4", T, E, None)).pin_memory()
     x_h = torch.from_numpy(S.bf16_bits(S.activations("C4", T, Hd, "bf16")).view(np.int16)).view(torch.bfloat16).pin_memory()
     logits_d, x_d = logits_h.cuda(), x_h.cuda()
@@ -117,7 +119,8 @@ def run(steps: int, warmup: int, layers: int, clock_sampler=None) -> dict:
         "n_gpus": 1, "steps": steps, "warmup": W, "ms_per_step": dt / steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands from q8_1 x GGUF blocks, f32 accumulate",
         "data": "synthetic",
-        "config": {"workload": "C4 prefill: 4096 tokens, hidden 6144, 256 experts of FFN 2048 (128 Q8_0 + 128 Q4_K), top-8",
+        "config": {"workload": f"C4 prefill: {T} tokens, hidden 6144, {E} experts of FFN 2048 (half Q8_0, half Q4_K), top-8"
+                               + ("" if scale == 1 else f" [reduced 1/{scale} case]"),
                    "layers_rotated": layers, "l2": f"inputs larger than L2: {weight_bytes / 1e9:.1f} GB of expert blobs per layer"},
         "e2e": {"value": steps * T / dt_e2e, "unit": "tok/s/layer",
                 "h2d_bytes_per_step": int(logits_h.numel() * 4 + x_h.numel() * 2), "d2h_bytes_per_step": int(out_h.numel() * 4)},

@@ -9,19 +9,21 @@
 // within its tolerance), weights are expanded from their GGUF blocks in shared memory, and `tcgen05.mma.kind::f16`
 // accumulates in f32 in tensor memory.
 //
-// One block = a slab of 256 weight rows (128 gate + 128 up rows for the fused SwiGLU form) x up to 256 activation
-// rows of one expert: two M = 128 accumulators of N = rows (rounded up to 16) columns.  Warp roles:
+// One block = a slab of 256 weight rows (128 gate + 128 up rows for the fused SwiGLU form) x up to 192 activation
+// rows of one expert: two M = 128 accumulators of N = rows (rounded up to 16) columns in tensor memory.  The expanded
+// weights are the A operand and live in tensor memory too (lane = weight row, the layout a thread-per-row expansion
+// produces by itself), so shared memory carries only raw blocks and activations: an SM's 128 bytes/clock of shared
+// memory cannot feed two f16 operands of M = N = 128 products at the tensor core's rate.  Warp roles:
 //   warp 8      one lane: TMA loads of raw weight blocks, 64 rows x 256 K-values a "unit", into a ring of units;
-//   warp 10     one lane: TMA loads of the activation tile of each 32-value K step, straight into the operand layout
-//               (the f16 rows are described to the TMA engine as (8 values, row, 16-byte chunk) so that a box lands as
-//               [chunk][row][16 bytes], the tensor core's K-major layout without swizzle);
-//   warps 0..7  one thread per weight row: expand 32 K-values of the row per step into the A tile (packed half2
-//               arithmetic: Q8_0 w = q * d; Q4_K w = fma(q, d * sc, -(dmin * m)));
-//   warp 9      one lane: four tcgen05.mma per step (2 accumulators x 2 K = 16 halves), commit -> the step's buffers
-//               are free again;
+//   warp 10     one lane: TMA loads of activation tiles, 128 (+ 64) rows x 64 K-values, in the 128-byte swizzle layout
+//               the tensor core reads at full rate;
+//   warps 0..7  one thread per weight row: expand 32 K-values of the row per step (packed half2 arithmetic: Q8_0
+//               w = q * d; Q4_K w = fma(q, d * sc, -(dmin * m))) and tcgen05.st them into the row's lane;
+//   warp 9      one lane: tcgen05.mma per step (2 accumulators x 2 K = 16 halves, A from tensor memory, B from shared
+//               memory; twice as many when the block has more than 128 rows), commits -> the step's buffers are free;
 //   warps 0..7  afterwards: the epilogue - tcgen05.ld (lane = weight row, column = activation row), SwiGLU, optional
 //               q8_1 rounding of h for the next product, stores of 32 consecutive floats per warp.
-// Which expert and which 256-row group of it a block handles is found on the device from `bounds`; no count travels
+// Which expert and which 192-row group of it a block handles is found on the device from `bounds`; no count travels
 // to the host.  Every mbarrier wait is bounded: a wait that runs out sets the error word, the roles stop, copies in
 // flight are waited for (bounded), tensor memory is freed and the block returns.
 #include <cuda.h>
@@ -37,21 +39,22 @@ namespace maya {
 namespace {
 
 constexpr int TM = 256;                 // weight rows of a block
-constexpr int TN = 256;                 // most activation rows of a block
+constexpr int TN = 192;                 // most activation rows of a block
 constexpr int BK = 32;                  // K values of one step
-constexpr int kSt = 3;                  // operand stages
+constexpr int kSt = 4;                  // stages of expanded weights (A operand, in tensor memory)
+constexpr int kBRing = 64 * 1024;       // activation tiles (64 K-values each) in flight: 4 of 128 rows, or 2 of 128 + 64 rows
 constexpr int kUnitRows = 64;           // weight rows of one raw unit
 constexpr int kDqWarps = 8;
 constexpr int kMmqThreads = (kDqWarps + 3) * 32;
-constexpr int kATile = TM * BK * 2;     // 16 KB
-constexpr int kBTile = TN * BK * 2;     // 16 KB (the first 8 KB when the block has <= 128 rows)
-constexpr int kStageBytes = kATile + kBTile;
-constexpr uint32_t kAccCols = 256;      // columns between the two accumulators
-constexpr int kMaxUnits = 12;
+constexpr int kBBox = 128 * 64 * 2;     // 16 KB: 128 activation rows x 64 K-values, 128-byte swizzle
+constexpr uint32_t kAccCols = TN;       // tensor-memory columns: accumulator 0 at 0, accumulator 1 at 192,
+constexpr uint32_t kACol = 2 * TN;      // the A operand's stages from 384: per stage 16 columns for each accumulator
+constexpr int kMaxUnits = 16;
 template<int T> constexpr int kRawRow = T == MAYA_Q4_K ? 144 : 272;         // bytes of 256 K-values of one row
 template<int T> constexpr int kUnitBytes = kUnitRows * kRawRow<T>;
-template<int T> constexpr int kUnits = T == MAYA_Q4_K ? 12 : 7;
-template<int T> constexpr size_t kSmemBytes = (size_t) kSt * kStageBytes + (size_t) kUnits<T> * kUnitBytes<T>;
+template<int T> constexpr int kUnits = T == MAYA_Q4_K ? 16 : 9;
+constexpr int kBOff = 0, kRawOff = kBRing;
+template<int T> constexpr size_t kSmemBytes = (size_t) kRawOff + (size_t) kUnits<T> * kUnitBytes<T>;
 
 struct MmqArgs {
     int w_rows, w_cols;          // rows of one output (n_ff for the fused form: gate rows, then up rows), K
@@ -64,7 +67,10 @@ struct MmqArgs {
     __half* xq_out;              // fused form, optional: q8_1-rounded h as f16, [sorted row][w_rows]
     float limit;
     unsigned* error;             // optional sticky error word
+    unsigned long long* probe;   // optional: cycle counters summed over the blocks (maya_mmq_set_probe)
 };
+
+unsigned long long* g_probe = nullptr;
 
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *(uint32_t*) &h; }
 __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *(__half2*) &u; }
@@ -101,29 +107,25 @@ __device__ __forceinline__ void q4k_scales(const uint4 hdr, Q4Scales& S) {
     }
 }
 // 32 weights of sub-block (2p + hi) from the 32 quant bytes of pair p
-__device__ __forceinline__ void q4k_stage(const uint4 qa, const uint4 qb, int hi, __half2 dl, __half2 nml, uint4 (&o)[4]) {
+__device__ __forceinline__ void q4k_stage(const uint4 qa, const uint4 qb, int hi, __half2 dl, __half2 nml, uint32_t (&r)[16]) {
     const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
     const __half2 k1024 = __float2half2_rn(1024.0f);
-    uint32_t r[16];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const uint32_t x = (hi ? (w[i] >> 4) : w[i]) & 0x0F0F0F0Fu;
         r[2 * i] = h2_bits(__hfma2(__hsub2(bytes01_plus1024(x), k1024), dl, nml));
         r[2 * i + 1] = h2_bits(__hfma2(__hsub2(bytes23_plus1024(x), k1024), dl, nml));
     }
-#pragma unroll
-    for (int c = 0; c < 4; ++c) o[c] = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
 }
 // ---- Q8_0: block J (34 bytes) of a 272-byte raw row, read as three aligned 16-byte words
 template<int J>
-__device__ __forceinline__ void q80_stage(const uint8_t* rrow, uint4 (&o)[4]) {
+__device__ __forceinline__ void q80_stage(const uint8_t* rrow, uint32_t (&r)[16]) {
     constexpr int kBase = (34 * J) / 16 * 16, kOff = 34 * J - kBase;     // kOff = 0, 2, ..., 14
     const uint4 a = *(const uint4*) (rrow + kBase), b = *(const uint4*) (rrow + kBase + 16), c = *(const uint4*) (rrow + kBase + 32);
     const uint32_t w[12] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w, c.x, c.y, c.z, c.w};
     const uint32_t dw = w[kOff / 4];
     const __half dh = __ushort_as_half((unsigned short) ((kOff % 4) ? (dw >> 16) : (dw & 0xFFFF)));
     const __half2 d2 = __half2half2(dh), k1152 = __float2half2_rn(1152.0f);
-    uint32_t r[16];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         constexpr int kQ = kOff + 2;
@@ -134,12 +136,10 @@ __device__ __forceinline__ void q80_stage(const uint8_t* rrow, uint4 (&o)[4]) {
         r[2 * i] = h2_bits(__hmul2(__hsub2(bytes01_plus1024(x), k1152), d2));
         r[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes23_plus1024(x), k1152), d2));
     }
-#pragma unroll
-    for (int c2 = 0; c2 < 4; ++c2) o[c2] = make_uint4(r[4 * c2], r[4 * c2 + 1], r[4 * c2 + 2], r[4 * c2 + 3]);
 }
 
 struct Pipe {                       // static shared memory of a block
-    uint64_t a_full[kSt], b_full[kSt], empty[kSt];
+    uint64_t a_full[kSt], a_empty[kSt], b_full[4], b_empty[4];
     uint64_t raw_full[kMaxUnits], raw_empty[kMaxUnits];
     uint64_t final;
     uint32_t tmem;
@@ -163,14 +163,14 @@ __device__ __forceinline__ bool wait_or_fail(Pipe& P, uint64_t* bar, uint32_t pa
 
 template<int T, bool GLU>
 __global__ void __launch_bounds__(kMmqThreads, 1)
-mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x128,
-           const __grid_constant__ CUtensorMap tm_x256, const MmqArgs A) {
-    extern __shared__ __align__(128) uint8_t smem[];
+mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+           const __grid_constant__ CUtensorMap tm_x64, const MmqArgs A) {
+    extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ Pipe P;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int NU = kUnits<T>;
 
-    // ---- which (matrix, 256-row group) is blockIdx.y: inclusive scan of the per-matrix group counts, kMmqThreads
+    // ---- which (matrix, 192-row group) is blockIdx.y: inclusive scan of the per-matrix group counts, kMmqThreads
     //      matrices at a time; `base` carries the groups of the matrices before
     int found_e = -1, found_g = 0;
     {
@@ -206,16 +206,22 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
         }
     }
     if (found_e < 0) return;                        // beyond the last group: uniform for the whole block
+    const long long t_start = clock64();
+    const bool probing = A.probe != nullptr;
+    long long c_wait0 = 0, c_wait1 = 0;
     const int be = A.expert_map ? A.expert_map[found_e] : found_e;
     const int row0 = A.bounds[be] + found_g * TN;
     const int nrows = min(TN, A.bounds[be + 1] - row0);
-    const bool big = nrows > 128;                   // the activation tile holds 256 rows instead of 128
+    const bool big = nrows > 128;                   // the activation tile is a 128-row box and a 64-row box
+    const uint32_t b_stage = big ? kBBox + kBBox / 2 : kBBox;
+    const int nbs = big ? 2 : 4;                    // activation stages in flight
     const int m0 = (int) blockIdx.x * (GLU ? 128 : TM);
     const int nkt = A.w_cols / BK, nkb = A.w_cols / 256;
 
-    uint8_t* const raw = smem + (size_t) kSt * kStageBytes;
+    uint8_t* const raw = smem + kRawOff;
     if (tid == 0) {
-        for (int s = 0; s < kSt; ++s) { mbar_init(&P.a_full[s], kDqWarps); mbar_init(&P.b_full[s], 1); mbar_init(&P.empty[s], 1); }
+        for (int s = 0; s < kSt; ++s) { mbar_init(&P.a_full[s], kDqWarps); mbar_init(&P.a_empty[s], 1); }
+        for (int s = 0; s < 4; ++s) { mbar_init(&P.b_full[s], 1); mbar_init(&P.b_empty[s], 1); }
         for (int u = 0; u < NU; ++u) { mbar_init(&P.raw_full[u], 1); mbar_init(&P.raw_empty[u], 2); }
         mbar_init(&P.final, 1);
         P.fail = 0;
@@ -231,25 +237,35 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
         // ------------------------------------------------------------ weight expansion: thread = row `tid` of the slab
         const int slab = tid >> 6;
         const uint8_t* const rbase = raw + (size_t) (tid & 63) * kRawRow<T>;
+        // rows 0..127 feed accumulator 0, rows 128..255 accumulator 1; a warp reaches the 32 lanes of its quadrant
+        const uint32_t a_lane = tmem + ((uint32_t) (32 * (warp & 3)) << 16) + kACol + (warp >> 2) * 16;
         bool ok = true;
         for (int kb = 0; kb < nkb && ok; ++kb) {
             const int u = kb * 4 + slab, slot = u % NU;
-            if (!wait_or_fail(P, &P.raw_full[slot], (u / NU) & 1)) { ok = false; break; }
+            {
+                const long long t0 = probing ? clock64() : 0;
+                if (!wait_or_fail(P, &P.raw_full[slot], (u / NU) & 1)) { ok = false; break; }
+                if (probing) c_wait0 += clock64() - t0;
+            }
             const uint8_t* rrow = rbase + (size_t) slot * kUnitBytes<T>;
-            auto put = [&](int j, const uint4 (&o)[4]) {
+            auto put = [&](int j, const uint32_t (&o)[16]) {     // this row's 32 values -> its lane of the A operand's stage
                 const int kt = kb * 8 + j, s = kt % kSt;
-                uint8_t* at = smem + (size_t) s * kStageBytes + tid * 16;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) *(uint4*) (at + c * (TM * 16)) = o[c];
-                fence_proxy_async();                 // these generic-proxy writes before the tensor core's reads
+                tmem_st16(a_lane + s * 32, o);
+                tmem_wait_st();
+                tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&P.a_full[s]);
             };
             auto ready = [&](int j) -> bool {        // stage of step kb * 8 + j free again?
                 const int kt = kb * 8 + j;
-                return kt < kSt || wait_or_fail(P, &P.empty[kt % kSt], ((kt / kSt) - 1) & 1);
+                if (kt < kSt) return true;
+                const long long t0 = probing ? clock64() : 0;
+                if (!wait_or_fail(P, &P.a_empty[kt % kSt], ((kt / kSt) - 1) & 1)) return false;
+                if (probing) c_wait1 += clock64() - t0;
+                tc_fence_after();
+                return true;
             };
-            uint4 o[4];
+            uint32_t o[16];
             if constexpr (T == MAYA_Q4_K) {
                 Q4Scales S;
                 q4k_scales(*(const uint4*) rrow, S);
@@ -275,43 +291,95 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             if (lane == 0) mbar_arrive(&P.raw_empty[slot]);      // the unit may be overwritten
         }
         // ------------------------------------------------------------ epilogue
+        const long long t_loop = clock64();
         if (ok && !wait_or_fail(P, &P.final, 0)) ok = false;
         tc_fence_after();
+        named_bar_sync(3, kDqWarps * 32);            // every expansion warp gets here (all waits are bounded) ...
+        ok = !failed(P);                             // ... and they agree: the epilogue's barriers need all of them
+        const long long t_epi = clock64();
         if (ok) {
-            const int q = warp & 3, c_lo = (warp >> 2) * 128;
+            // The tile leaves through shared memory (the raw ring is free now): the warps drop their lanes' values
+            // into [activation row][weight row] order, then one bulk copy per activation row writes it out.  Two
+            // buffers alternate; a buffer is reused once the copies that read it have finished reading.
+            const int q = warp & 3, hs = warp >> 2;
             const uint32_t lane_base = tmem + ((uint32_t) (32 * q) << 16);
-            for (int c0 = c_lo; c0 < c_lo + 128 && c0 < nrows; c0 += 32) {
-                float v[32];
-                if constexpr (GLU) {
-                    float up[32];
-                    tmem_ld32(lane_base + c0, v);
-                    tmem_ld32(lane_base + kAccCols + c0, up);
-                    const int m = m0 + 32 * q + lane;
+            uint8_t* const stg = smem + kRawOff;
+            constexpr int kThreadsEpi = kDqWarps * 32;
+            if constexpr (GLU) {
+                constexpr int kBuf = 64 * 128 * 2 + 64 * 128 * 4;        // 64 rows of h: f16 image, then f32
+                const int nch = (nrows + 63) / 64;
+                for (int c = 0; c < nch; ++c) {
+                    __half* b16 = (__half*) (stg + (size_t) (c & 1) * kBuf);
+                    float* b32 = (float*) (stg + (size_t) (c & 1) * kBuf + 64 * 128 * 2);
+                    const int col0 = 64 * c + 32 * hs;
+                    if (col0 < nrows) {
+                        float v[32], up[32];
+                        tmem_ld32(lane_base + col0, v);
+                        tmem_ld32(lane_base + kAccCols + col0, up);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (c0 + j < nrows) {                     // uniform in the warp
-                            const float h = swiglu(v[j], up[j], A.limit);
-                            const int row = row0 + c0 + j;
-                            if (A.dst) A.dst[(int64_t) (A.ids ? A.ids[row] : row) * A.ld_dst + m] = h;
-                            if (A.xq_out) A.xq_out[(int64_t) row * A.w_rows + m] = q8_1_round_warp(h);
+                        for (int j = 0; j < 32; ++j) v[j] = swiglu(v[j], up[j], A.limit);
+                        const int at = (32 * hs) * 128 + 32 * q + lane;
+                        if (A.xq_out) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) b16[at + j * 128] = q8_1_round_warp(v[j]);
+                        }
+                        if (A.dst) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) b32[at + j * 128] = v[j];
                         }
                     }
-                } else {
-#pragma unroll
-                    for (int a = 0; a < 2; ++a) {
-                        if (m0 + 128 * a >= A.w_rows) break;
-                        tmem_ld32(lane_base + a * kAccCols + c0, v);
-                        const int m = m0 + 128 * a + 32 * q + lane;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (c0 + j < nrows) {
-                                const int row = row0 + c0 + j;
-                                A.dst[(int64_t) (A.ids ? A.ids[row] : row) * A.ld_dst + m] = v[j];
-                            }
+                    fence_proxy_async();
+                    named_bar_sync(1, kThreadsEpi);
+                    if (warp < 2) {                                      // 64 lanes: one activation row each
+                        const int rin = 32 * warp + lane, col = 64 * c + rin;
+                        if (col < nrows) {
+                            const int row = row0 + col;
+                            if (A.xq_out) bulk_store(A.xq_out + (int64_t) row * A.w_rows + m0, b16 + rin * 128, 128 * 2);
+                            if (A.dst) bulk_store(A.dst + (int64_t) (A.ids ? A.ids[row] : row) * A.ld_dst + m0, b32 + rin * 128, 128 * 4);
                         }
+                        bulk_commit();
+                        bulk_wait_read<1>();                             // the other buffer's copies have read it
                     }
+                    named_bar_sync(2, kThreadsEpi);
+                }
+            } else {
+                constexpr int kBuf = 32 * TM * 4;                        // 32 rows x 256 weight rows of f32
+                const bool have = m0 + 128 * hs < A.w_rows;              // this warp's accumulator exists
+                const uint32_t row_bytes_out = (uint32_t) min(TM, A.w_rows - m0) * 4;
+                const int nch = (nrows + 31) / 32;
+                for (int c = 0; c < nch; ++c) {
+                    float* buf = (float*) (stg + (size_t) (c & 1) * kBuf);
+                    if (have) {
+                        float v[32];
+                        tmem_ld32(lane_base + hs * kAccCols + 32 * c, v);
+                        const int at = 128 * hs + 32 * q + lane;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) buf[at + j * TM] = v[j];
+                    }
+                    fence_proxy_async();
+                    named_bar_sync(1, kThreadsEpi);
+                    if (warp == 0) {
+                        const int col = 32 * c + lane;
+                        if (col < nrows) {
+                            const int row = row0 + col;
+                            bulk_store(A.dst + (int64_t) (A.ids ? A.ids[row] : row) * A.ld_dst + m0, buf + lane * TM, row_bytes_out);
+                        }
+                        bulk_commit();
+                        bulk_wait_read<1>();
+                    }
+                    named_bar_sync(2, kThreadsEpi);
                 }
             }
+            if (warp < 2) bulk_wait<0>();                                // every copy of this block has landed
+        }
+        if (probing && tid == 0) {
+            atomicAdd(A.probe + 0, (unsigned long long) c_wait0);
+            atomicAdd(A.probe + 1, (unsigned long long) c_wait1);
+            atomicAdd(A.probe + 2, (unsigned long long) (t_loop - t_start));
+            atomicAdd(A.probe + 6, (unsigned long long) (t_epi - t_loop));
+            atomicAdd(A.probe + 7, (unsigned long long) (clock64() - t_epi));
+            atomicAdd(A.probe + 8, 1ull);
+            atomicAdd(A.probe + 9, (unsigned long long) nkt);
         }
     } else if (warp == kDqWarps) {
         // ------------------------------------------------------------ raw weight units (one lane)
@@ -334,42 +402,54 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
     } else if (warp == kDqWarps + 1) {
         // ------------------------------------------------------------ tensor-core issue (one lane)
         if (lane == 0) {
+            // one product of N = rows rounded up to 16 per accumulator and K = 16: an M = 128 product costs the tensor
+            // core max(N / 2, ~84) cycles whatever N is, so the rows are never split into two products
             const int n_mma = max(16, (nrows + 15) & ~15);
             const uint32_t idesc = (1u << 4) | ((uint32_t) (n_mma >> 3) << 17) | ((uint32_t) (128 >> 4) << 24);
-            const uint32_t lbo_b = big ? TN * 16 : 128 * 16;
             bool ok = true;
             for (int kt = 0; kt < nkt; ++kt) {
-                const int s = kt % kSt;
-                if (!wait_or_fail(P, &P.a_full[s], (kt / kSt) & 1) || !wait_or_fail(P, &P.b_full[s], (kt / kSt) & 1)) { ok = false; break; }
+                const int s = kt % kSt, kb2 = kt >> 1, sb = kb2 % nbs;
+                const long long t0 = probing ? clock64() : 0;
+                if (!(kt & 1) && !wait_or_fail(P, &P.b_full[sb], (kb2 / nbs) & 1)) { ok = false; break; }
+                const long long t1 = probing ? clock64() : 0;
+                if (!wait_or_fail(P, &P.a_full[s], (kt / kSt) & 1)) { ok = false; break; }
+                if (probing) { c_wait0 += t1 - t0; c_wait1 += clock64() - t1; }
                 tc_fence_after();
-                const uint32_t a_base = smem_u32(smem + (size_t) s * kStageBytes), b_base = a_base + kATile;
+                const uint32_t b_base = smem_u32(smem + kBOff) + sb * b_stage + (kt & 1) * 64;
 #pragma unroll
                 for (int kk = 0; kk < 2; ++kk) {
-                    const uint64_t bd = smem_desc(b_base + kk * 2 * lbo_b, lbo_b, 128);
+                    const uint32_t acc = (kt > 0 || kk > 0) ? 1u : 0u;
+                    const uint64_t bd = smem_desc_sw128(b_base + kk * 32);   // the 64-row box continues the 128-row box's layout
 #pragma unroll
-                    for (int a = 0; a < 2; ++a) {
-                        const uint64_t ad = smem_desc(a_base + a * (128 * 16) + kk * 2 * (TM * 16), TM * 16, 128);
-                        mma_f16_ss(tmem + a * kAccCols, ad, bd, idesc, (kt > 0 || kk > 0) ? 1u : 0u);
-                    }
+                    for (int a = 0; a < 2; ++a)
+                        mma_f16_ts(tmem + a * kAccCols, tmem + kACol + s * 32 + a * 16 + kk * 8, bd, idesc, acc);
                 }
-                mma_commit(&P.empty[s]);
+                mma_commit(&P.a_empty[s]);
+                if (kt & 1) mma_commit(&P.b_empty[sb]);
             }
             if (ok) mma_commit(&P.final);
+            if (probing) {
+                atomicAdd(A.probe + 3, (unsigned long long) c_wait0);
+                atomicAdd(A.probe + 4, (unsigned long long) c_wait1);
+                atomicAdd(A.probe + 5, (unsigned long long) (clock64() - t_start));
+            }
         }
     } else {
         // ------------------------------------------------------------ activation tiles (one lane)
         if (lane == 0) {
             int issued = 0;
             bool ok = true;
-            for (int kt = 0; kt < nkt; ++kt) {
-                const int s = kt % kSt;
-                if (kt >= kSt && !wait_or_fail(P, &P.empty[s], ((kt / kSt) - 1) & 1)) { ok = false; break; }
-                mbar_expect_tx(&P.b_full[s], big ? kBTile : kBTile / 2);
-                tma_load_3d(smem + (size_t) s * kStageBytes + kATile, big ? &tm_x256 : &tm_x128, &P.b_full[s], 0, row0, kt * 4);
-                issued = kt + 1;
+            for (int kb2 = 0; kb2 < nkt / 2; ++kb2) {
+                const int sb = kb2 % nbs;
+                if (kb2 >= nbs && !wait_or_fail(P, &P.b_empty[sb], ((kb2 / nbs) - 1) & 1)) { ok = false; break; }
+                uint8_t* bt = smem + kBOff + (size_t) sb * b_stage;
+                mbar_expect_tx(&P.b_full[sb], b_stage);
+                tma_load_2d(bt, &tm_x, &P.b_full[sb], kb2 * 64, row0);
+                if (big) tma_load_2d(bt + kBBox, &tm_x64, &P.b_full[sb], kb2 * 64, row0 + 128);
+                issued = kb2 + 1;
             }
             if (!ok)
-                for (int kt = max(0, issued - kSt); kt < issued; ++kt) wait_or_fail(P, &P.b_full[kt % kSt], (kt / kSt) & 1);
+                for (int kb2 = max(0, issued - nbs); kb2 < issued; ++kb2) wait_or_fail(P, &P.b_full[kb2 % nbs], (kb2 / nbs) & 1);
         }
     }
     tc_fence_before();
@@ -416,12 +496,12 @@ PFN_cuTensorMapEncodeTiled encode_fn() {
     }();
     return fn;
 }
-bool make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, const cuuint64_t (&dim)[3], const cuuint64_t (&stride)[2],
-              const cuuint32_t (&box)[3]) {
+bool make_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, const void* base, const cuuint64_t* dim, const cuuint64_t* stride,
+              const cuuint32_t* box, CUtensorMapSwizzle swizzle) {
     PFN_cuTensorMapEncodeTiled fn = encode_fn();
     if (!fn) return false;
     const cuuint32_t es[3] = {1, 1, 1};
-    return fn(m, dt, 3, const_cast<void*>(base), dim, stride, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+    return fn(m, dt, (cuuint32_t) rank, const_cast<void*>(base), dim, stride, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -429,29 +509,30 @@ template<int T, bool GLU>
 int launch_mmq(const maya_mmq_product* p, const MmqArgs& A, cudaStream_t s) {
     const int64_t mat_rows = p->w_rows, K = p->w_cols;
     const size_t rbw = row_bytes(T, K);
-    CUtensorMap tw, tx128, tx256;
+    CUtensorMap tw, tx, tx64;
     {   // weights as 32-bit words: (word in row, row in matrix, matrix); a box = 256 K-values of 64 rows
         const cuuint64_t dim[3] = {(cuuint64_t) (rbw / 4), (cuuint64_t) mat_rows, (cuuint64_t) p->n};
         const cuuint64_t st[2] = {(cuuint64_t) rbw, (cuuint64_t) p->expert_bytes};
         const cuuint32_t box[3] = {(cuuint32_t) (kRawRow<T> / 4), kUnitRows, 1};
-        if (!make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, p->w, dim, st, box)) return note_launch("mmq weight tensor map");
+        if (!make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, p->w, dim, st, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return note_launch("mmq weight tensor map");
     }
-    {   // activations: (8 values, row, 16-byte chunk of the row) so that a box lands as [chunk][row][16 bytes]
-        const cuuint64_t dim[3] = {8, (cuuint64_t) p->total_rows, (cuuint64_t) (K / 8)};
-        const cuuint64_t st[2] = {(cuuint64_t) K * 2, 16};
-        const cuuint32_t b128[3] = {8, 128, BK / 8}, b256[3] = {8, 256, BK / 8};
-        if (!make_map(&tx128, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p->xq, dim, st, b128) ||
-            !make_map(&tx256, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p->xq, dim, st, b256))
+    {   // activations: f16 [row][K]; a box = 64 K-values (128 bytes) of 128 or 64 rows, written with the 128-byte swizzle
+        const cuuint64_t dim[2] = {(cuuint64_t) K, (cuuint64_t) p->total_rows};
+        const cuuint64_t st[1] = {(cuuint64_t) K * 2};
+        const cuuint32_t box[2] = {64, 128}, box64[2] = {64, 64};
+        if (!make_map(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xq, dim, st, box, CU_TENSOR_MAP_SWIZZLE_128B) ||
+            !make_map(&tx64, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xq, dim, st, box64, CU_TENSOR_MAP_SWIZZLE_128B))
             return note_launch("mmq activation tensor map");
     }
     constexpr size_t smem = kSmemBytes<T>;
     if (cudaFuncSetAttribute(mmq_kernel<T, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess)
         return note_launch("mmq smem attribute");
-    const int64_t groups = p->total_rows / TN + p->n;   // an upper bound of sum(ceil(rows_e / 256)), known without the counts
+    const int64_t groups = p->total_rows / TN + p->n;   // an upper bound of sum(ceil(rows_e / 192)), known without the counts
     if (groups > 65535) return refuse(MAYA_ERR_LIMIT);
     const int slab = GLU ? 128 : TM;
     const dim3 grid((unsigned) ((A.w_rows + slab - 1) / slab), (unsigned) groups);
-    mmq_kernel<T, GLU><<<grid, kMmqThreads, smem, s>>>(tw, tx128, tx256, A);
+    mmq_kernel<T, GLU><<<grid, kMmqThreads, smem, s>>>(tw, tx, tx64, A);
     return note_launch("mmq");
 }
 
@@ -468,10 +549,11 @@ int run_product(const maya_mmq_product* p, bool glu, float limit, cudaStream_t s
         return refuse(MAYA_ERR_ARG);
     }
     if (!aligned16(p->w) || !aligned16(p->xq) || (p->xq_out && !aligned16(p->xq_out))) return refuse(MAYA_ERR_ARG);
+    if (p->dst && (!aligned16(p->dst) || p->ld_dst % 4)) return refuse(MAYA_ERR_ARG);      // rows leave as 16-byte aligned bulk copies
     MmqArgs A{};
     A.w_rows = (int) out_rows; A.w_cols = (int) p->w_cols; A.n = p->n; A.expert_map = p->expert_map; A.bounds = p->bounds;
     A.ids = p->ids; A.dst = p->dst; A.ld_dst = p->ld_dst; A.xq_out = glu ? (__half*) p->xq_out : nullptr; A.limit = limit;
-    A.error = p->error;
+    A.error = p->error; A.probe = g_probe;
     if (p->type == MAYA_Q4_K) return glu ? launch_mmq<MAYA_Q4_K, true>(p, A, s) : launch_mmq<MAYA_Q4_K, false>(p, A, s);
     return glu ? launch_mmq<MAYA_Q8_0, true>(p, A, s) : launch_mmq<MAYA_Q8_0, false>(p, A, s);
 }
@@ -494,6 +576,7 @@ extern "C" int maya_mmq_quantize_bf16(const uint16_t* x, const int32_t* ids, voi
                                       int64_t rows, void* stream) {
     return launch_quantize<uint16_t>(x, ids, xq, type, cols, ld, rows, stream);
 }
+extern "C" void maya_mmq_set_probe(unsigned long long* counters) { g_probe = counters; }
 extern "C" int maya_mmq_run(const maya_mmq_product* p, void* stream) { return run_product(p, false, 0.0f, as_stream(stream)); }
 extern "C" int maya_mmq_run_glu(const maya_mmq_product* p, float limit, void* stream) {
     return run_product(p, true, limit, as_stream(stream));
