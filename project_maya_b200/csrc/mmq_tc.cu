@@ -9,21 +9,23 @@
 // within its tolerance), weights are expanded from their GGUF blocks in shared memory, and `tcgen05.mma.kind::f16`
 // accumulates in f32 in tensor memory.
 //
-// One block = a slab of 256 weight rows (128 gate + 128 up rows for the fused SwiGLU form) x up to 192 activation
+// One block = a slab of 256 weight rows (128 gate + 128 up rows for the fused SwiGLU form) x up to 160 activation
 // rows of one expert: two M = 128 accumulators of N = rows (rounded up to 16) columns in tensor memory.  The expanded
 // weights are the A operand and live in tensor memory too (lane = weight row, the layout a thread-per-row expansion
 // produces by itself), so shared memory carries only raw blocks and activations: an SM's 128 bytes/clock of shared
 // memory cannot feed two f16 operands of M = N = 128 products at the tensor core's rate.  Warp roles:
-//   warp 8      one lane: TMA loads of raw weight blocks, 64 rows x 256 K-values a "unit", into a ring of units;
-//   warp 10     one lane: TMA loads of activation tiles, 128 (+ 64) rows x 64 K-values, in the 128-byte swizzle layout
+//   warp 16     one lane: TMA loads of raw weight blocks, 64 rows x 256 K-values a "unit", into a ring of units;
+//   warp 18     one lane: TMA loads of activation tiles, 128 (+ 32) rows x 64 K-values, in the 128-byte swizzle layout
 //               the tensor core reads at full rate;
-//   warps 0..7  one thread per weight row: expand 32 K-values of the row per step (packed half2 arithmetic: Q8_0
-//               w = q * d; Q4_K w = fma(q, d * sc, -(dmin * m))) and tcgen05.st them into the row's lane;
-//   warp 9      one lane: tcgen05.mma per step (2 accumulators x 2 K = 16 halves, A from tensor memory, B from shared
-//               memory; twice as many when the block has more than 128 rows), commits -> the step's buffers are free;
-//   warps 0..7  afterwards: the epilogue - tcgen05.ld (lane = weight row, column = activation row), SwiGLU, optional
-//               q8_1 rounding of h for the next product, stores of 32 consecutive floats per warp.
-// Which expert and which 192-row group of it a block handles is found on the device from `bounds`; no count travels
+//   warps 0..15 two teams of 8 warps that take alternate K steps; in a team one thread per weight row expands 32
+//               K-values of the row per step (packed half2 arithmetic: Q8_0 w = q * d; Q4_K w = fma(q, d * sc,
+//               -(dmin * m))) and tcgen05.st-s them into the row's lane;
+//   warps 17,19 one lane each, one accumulator each: two tcgen05.mma per step (2 K = 16 halves, A from tensor memory,
+//               B from shared memory), one commit per two steps -> the steps' buffers are free (a single thread
+//               cannot issue products as fast as the tensor core retires them unless its loop is a few instructions);
+//   warps 0..15 afterwards: the epilogue - tcgen05.ld (lane = weight row, column = activation row), SwiGLU, optional
+//               q8_1 rounding of h for the next product, then through shared memory: one bulk copy per activation row.
+// Which expert and which 160-row group of it a block handles is found on the device from `bounds`; no count travels
 // to the host.  Every mbarrier wait is bounded: a wait that runs out sets the error word, the roles stop, copies in
 // flight are waited for (bounded), tensor memory is freed and the block returns.
 #include <cuda.h>
@@ -39,22 +41,25 @@ namespace maya {
 namespace {
 
 constexpr int TM = 256;                 // weight rows of a block
-constexpr int TN = 192;                 // most activation rows of a block
+constexpr int TN = 160;                 // most activation rows of a block
 constexpr int BK = 32;                  // K values of one step
-constexpr int kSt = 4;                  // stages of expanded weights (A operand, in tensor memory)
-constexpr int kBRing = 64 * 1024;       // activation tiles (64 K-values each) in flight: 4 of 128 rows, or 2 of 128 + 64 rows
+constexpr int kSt = 6;                  // stages of expanded weights (the A operand, in tensor memory)
 constexpr int kUnitRows = 64;           // weight rows of one raw unit
-constexpr int kDqWarps = 8;
-constexpr int kMmqThreads = (kDqWarps + 3) * 32;
+constexpr int kDqWarps = 16;            // two teams of 8
+constexpr int kMmqThreads = (kDqWarps + 4) * 32;   // + raw-unit loader, issuer of accumulator 0, activation loader, issuer of accumulator 1
 constexpr int kBBox = 128 * 64 * 2;     // 16 KB: 128 activation rows x 64 K-values, 128-byte swizzle
-constexpr uint32_t kAccCols = TN;       // tensor-memory columns: accumulator 0 at 0, accumulator 1 at 192,
-constexpr uint32_t kACol = 2 * TN;      // the A operand's stages from 384: per stage 16 columns for each accumulator
-constexpr int kMaxUnits = 16;
+constexpr int kBStage = kBBox + 32 * 64 * 2;   // + the 32-row box of a block with more than 128 rows: 20 KB
+constexpr uint32_t kAccCols = TN;       // tensor-memory columns: accumulator 0 at 0, accumulator 1 at 160,
+constexpr uint32_t kACol = 2 * TN;      // the A operand's 6 stages from 320: per stage 16 columns for each accumulator
+constexpr int kMaxUnits = 12;
+constexpr int kDone = 16;               // ring of "pair of K steps consumed" barriers (one tcgen05.commit per pair: a commit
+                                        // costs the tensor pipe about as much as a product)
 template<int T> constexpr int kRawRow = T == MAYA_Q4_K ? 144 : 272;         // bytes of 256 K-values of one row
 template<int T> constexpr int kUnitBytes = kUnitRows * kRawRow<T>;
-template<int T> constexpr int kUnits = T == MAYA_Q4_K ? 16 : 9;
-constexpr int kBOff = 0, kRawOff = kBRing;
-template<int T> constexpr size_t kSmemBytes = (size_t) kRawOff + (size_t) kUnits<T> * kUnitBytes<T>;
+template<int T> constexpr int kUnits = T == MAYA_Q4_K ? 10 : 8;             // raw units in flight
+template<int T> constexpr int kBStages = T == MAYA_Q4_K ? 6 : 4;            // activation tiles (64 K-values) in flight
+template<int T> constexpr int kBRing = kBStages<T> * kBStage;
+template<int T> constexpr size_t kSmemBytes = (size_t) kBRing<T> + (size_t) kUnits<T> * kUnitBytes<T>;
 
 struct MmqArgs {
     int w_rows, w_cols;          // rows of one output (n_ff for the fused form: gate rows, then up rows), K
@@ -139,7 +144,8 @@ __device__ __forceinline__ void q80_stage(const uint8_t* rrow, uint32_t (&r)[16]
 }
 
 struct Pipe {                       // static shared memory of a block
-    uint64_t a_full[kSt], a_empty[kSt], b_full[4], b_empty[4];
+    uint64_t a_full[kSt], b_full[6];
+    uint64_t done[kDone];            // done[p % kDone]: the products of K-step pair p (64 K-values) have completed
     uint64_t raw_full[kMaxUnits], raw_empty[kMaxUnits];
     uint64_t final;
     uint32_t tmem;
@@ -152,7 +158,7 @@ __device__ __forceinline__ bool failed(const Pipe& P) { return *(volatile const 
 __device__ __forceinline__ bool wait_or_fail(Pipe& P, uint64_t* bar, uint32_t parity) {
     for (unsigned i = 0; i < (1u << 21); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (i > 128) {
+        if (i > 4096) {                          // try_wait itself suspends the thread for a while; back off only late
             __nanosleep(64);
             if ((i & 255) == 0 && failed(P)) return false;
         }
@@ -164,13 +170,13 @@ __device__ __forceinline__ bool wait_or_fail(Pipe& P, uint64_t* bar, uint32_t pa
 template<int T, bool GLU>
 __global__ void __launch_bounds__(kMmqThreads, 1)
 mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-           const __grid_constant__ CUtensorMap tm_x64, const MmqArgs A) {
+           const __grid_constant__ CUtensorMap tm_x32, const MmqArgs A) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ Pipe P;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    constexpr int NU = kUnits<T>;
+    constexpr int NU = kUnits<T>, NB = kBStages<T>;
 
-    // ---- which (matrix, 192-row group) is blockIdx.y: inclusive scan of the per-matrix group counts, kMmqThreads
+    // ---- which (matrix, 160-row group) is blockIdx.y: inclusive scan of the per-matrix group counts, kMmqThreads
     //      matrices at a time; `base` carries the groups of the matrices before
     int found_e = -1, found_g = 0;
     {
@@ -212,18 +218,17 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
     const int be = A.expert_map ? A.expert_map[found_e] : found_e;
     const int row0 = A.bounds[be] + found_g * TN;
     const int nrows = min(TN, A.bounds[be + 1] - row0);
-    const bool big = nrows > 128;                   // the activation tile is a 128-row box and a 64-row box
-    const uint32_t b_stage = big ? kBBox + kBBox / 2 : kBBox;
-    const int nbs = big ? 2 : 4;                    // activation stages in flight
+    const bool big = nrows > 128;                   // the activation tile is a 128-row box and a 32-row box
     const int m0 = (int) blockIdx.x * (GLU ? 128 : TM);
     const int nkt = A.w_cols / BK, nkb = A.w_cols / 256;
 
-    uint8_t* const raw = smem + kRawOff;
+    uint8_t* const raw = smem + kBRing<T>;
     if (tid == 0) {
-        for (int s = 0; s < kSt; ++s) { mbar_init(&P.a_full[s], kDqWarps); mbar_init(&P.a_empty[s], 1); }
-        for (int s = 0; s < 4; ++s) { mbar_init(&P.b_full[s], 1); mbar_init(&P.b_empty[s], 1); }
-        for (int u = 0; u < NU; ++u) { mbar_init(&P.raw_full[u], 1); mbar_init(&P.raw_empty[u], 2); }
-        mbar_init(&P.final, 1);
+        for (int s = 0; s < kSt; ++s) mbar_init(&P.a_full[s], 8);
+        for (int s = 0; s < NB; ++s) mbar_init(&P.b_full[s], 1);
+        for (int s = 0; s < kDone; ++s) mbar_init(&P.done[s], 2);      // both issuers commit
+        for (int u = 0; u < NU; ++u) { mbar_init(&P.raw_full[u], 1); mbar_init(&P.raw_empty[u], 4); }
+        mbar_init(&P.final, 2);
         P.fail = 0;
     }
     mbar_fence_init();
@@ -234,35 +239,50 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
     const uint32_t tmem = P.tmem;
 
     if (warp < kDqWarps) {
-        // ------------------------------------------------------------ weight expansion: thread = row `tid` of the slab
-        const int slab = tid >> 6;
-        const uint8_t* const rbase = raw + (size_t) (tid & 63) * kRawRow<T>;
+        // ------------------------------------------------------------ weight expansion
+        // Two teams of 8 warps; in each, thread = one of the slab's 256 rows.  Team t expands the K steps kt with
+        // kt % 2 == t, so that a step's latency (shared-memory reads, the packed-half chain, the tensor-memory store
+        // and its wait) overlaps the other team's step.
+        const int team = warp >> 3, row = tid & 255, w8 = warp & 7;
+        const bool timing = probing && warp == 0;
+        const int slab = row >> 6;
+        const uint8_t* const rbase = raw + (size_t) (row & 63) * kRawRow<T>;
         // rows 0..127 feed accumulator 0, rows 128..255 accumulator 1; a warp reaches the 32 lanes of its quadrant
-        const uint32_t a_lane = tmem + ((uint32_t) (32 * (warp & 3)) << 16) + kACol + (warp >> 2) * 16;
+        const uint32_t a_lane = tmem + ((uint32_t) (32 * (w8 & 3)) << 16) + kACol + (w8 >> 2) * 16;
         bool ok = true;
+        uint32_t pend[16];
+        int pend_kt = -1;
         for (int kb = 0; kb < nkb && ok; ++kb) {
             const int u = kb * 4 + slab, slot = u % NU;
             {
-                const long long t0 = probing ? clock64() : 0;
+                const long long t0 = timing ? clock64() : 0;
                 if (!wait_or_fail(P, &P.raw_full[slot], (u / NU) & 1)) { ok = false; break; }
-                if (probing) c_wait0 += clock64() - t0;
+                if (timing) c_wait0 += clock64() - t0;
             }
             const uint8_t* rrow = rbase + (size_t) slot * kUnitBytes<T>;
-            auto put = [&](int j, const uint32_t (&o)[16]) {     // this row's 32 values -> its lane of the A operand's stage
-                const int kt = kb * 8 + j, s = kt % kSt;
+            // A step is expanded into registers first and stored one step later: while this team waits for its stage
+            // to come free it already holds the next step's values (one more step of slack at no tensor-memory cost).
+            auto put = [&](int kt, const uint32_t (&o)[16]) -> bool {   // the row's 32 values of step kt -> its lane
+                const int s = kt % kSt;
+                if (kt >= kSt) {                     // the stage was last read by step kt - kSt, of pair (kt - kSt) / 2
+                    const int pp = (kt - kSt) >> 1;
+                    const long long t0 = timing ? clock64() : 0;
+                    if (!wait_or_fail(P, &P.done[pp % kDone], (pp / kDone) & 1)) return false;
+                    if (timing) c_wait1 += clock64() - t0;
+                    tc_fence_after();
+                }
                 tmem_st16(a_lane + s * 32, o);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&P.a_full[s]);
+                return true;
             };
-            auto ready = [&](int j) -> bool {        // stage of step kb * 8 + j free again?
-                const int kt = kb * 8 + j;
-                if (kt < kSt) return true;
-                const long long t0 = probing ? clock64() : 0;
-                if (!wait_or_fail(P, &P.a_empty[kt % kSt], ((kt / kSt) - 1) & 1)) return false;
-                if (probing) c_wait1 += clock64() - t0;
-                tc_fence_after();
+            auto rotate = [&](int j, uint32_t (&cur)[16]) -> bool {     // store the pending step, keep `cur` pending
+                if (pend_kt >= 0 && !put(pend_kt, pend)) return false;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) pend[i] = cur[i];
+                pend_kt = kb * 8 + j;
                 return true;
             };
             uint32_t o[16];
@@ -270,25 +290,33 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                 Q4Scales S;
                 q4k_scales(*(const uint4*) rrow, S);
 #pragma unroll
-                for (int p = 0; p < 4; ++p) {
+                for (int p = 0; p < 4; ++p) {        // team 0: the low nibbles (sub-block 2p), team 1: the high ones
                     const uint4 qa = *(const uint4*) (rrow + 16 + 32 * p), qb = *(const uint4*) (rrow + 32 + 32 * p);
-#pragma unroll
-                    for (int hi = 0; hi < 2; ++hi) {
-                        q4k_stage(qa, qb, hi, S.dl[2 * p + hi], S.nml[2 * p + hi], o);
-                        if (!ready(2 * p + hi)) { ok = false; break; }
-                        put(2 * p + hi, o);
-                    }
-                    if (!ok) break;
+                    if (team == 0) q4k_stage(qa, qb, 0, S.dl[2 * p], S.nml[2 * p], o);
+                    else q4k_stage(qa, qb, 1, S.dl[2 * p + 1], S.nml[2 * p + 1], o);
+                    if (!rotate(2 * p + team, o)) { ok = false; break; }
                 }
             } else {
-#define MAYA_Q80_STEP(J) if (ok) { q80_stage<J>(rrow, o); if (!ready(J)) ok = false; else put(J, o); }
-                MAYA_Q80_STEP(0) MAYA_Q80_STEP(1) MAYA_Q80_STEP(2) MAYA_Q80_STEP(3)
-                MAYA_Q80_STEP(4) MAYA_Q80_STEP(5) MAYA_Q80_STEP(6) MAYA_Q80_STEP(7)
+#define MAYA_Q80_STEP(J) if (ok) { q80_stage<J>(rrow, o); ok = rotate(J, o); }
+                if (team == 0) { MAYA_Q80_STEP(0) MAYA_Q80_STEP(2) MAYA_Q80_STEP(4) MAYA_Q80_STEP(6) }
+                else { MAYA_Q80_STEP(1) MAYA_Q80_STEP(3) MAYA_Q80_STEP(5) MAYA_Q80_STEP(7) }
 #undef MAYA_Q80_STEP
             }
             if (!ok) break;
             __syncwarp();
-            if (lane == 0) mbar_arrive(&P.raw_empty[slot]);      // the unit may be overwritten
+            if (lane == 0) mbar_arrive(&P.raw_empty[slot]);      // 4 warps read a unit; after the 4th it may be overwritten
+        }
+        if (ok && pend_kt >= 0) {                    // the last step is still in registers
+            const int s = pend_kt % kSt, pp = (pend_kt - kSt) >> 1;
+            if (pend_kt >= kSt && !wait_or_fail(P, &P.done[pp % kDone], (pp / kDone) & 1)) ok = false;
+            if (ok) {
+                tc_fence_after();
+                tmem_st16(a_lane + s * 32, pend);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&P.a_full[s]);
+            }
         }
         // ------------------------------------------------------------ epilogue
         const long long t_loop = clock64();
@@ -298,20 +326,19 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
         ok = !failed(P);                             // ... and they agree: the epilogue's barriers need all of them
         const long long t_epi = clock64();
         if (ok) {
-            // The tile leaves through shared memory (the raw ring is free now): the warps drop their lanes' values
-            // into [activation row][weight row] order, then one bulk copy per activation row writes it out.  Two
-            // buffers alternate; a buffer is reused once the copies that read it have finished reading.
-            const int q = warp & 3, hs = warp >> 2;
+            // The tile leaves through shared memory (both rings are free now: every load was consumed): the warps drop
+            // their lanes' values into [activation row][weight row] order, then one bulk copy per activation row
+            // writes it out.
+            const int q = warp & 3, hs = warp >> 2;                      // hs = 0..3
             const uint32_t lane_base = tmem + ((uint32_t) (32 * q) << 16);
-            uint8_t* const stg = smem + kRawOff;
+            uint8_t* const stg = smem;
             constexpr int kThreadsEpi = kDqWarps * 32;
             if constexpr (GLU) {
-                constexpr int kBuf = 64 * 128 * 2 + 64 * 128 * 4;        // 64 rows of h: f16 image, then f32
-                const int nch = (nrows + 63) / 64;
-                for (int c = 0; c < nch; ++c) {
-                    __half* b16 = (__half*) (stg + (size_t) (c & 1) * kBuf);
-                    float* b32 = (float*) (stg + (size_t) (c & 1) * kBuf + 64 * 128 * 2);
-                    const int col0 = 64 * c + 32 * hs;
+                // 16 warps = 4 lane quadrants x 4 groups of 32 activation rows: 128 rows a pass
+                __half* b16 = (__half*) stg;                             // [128 rows][128] f16 image of h
+                float* b32 = (float*) (stg + 128 * 128 * 2);             // [128 rows][128] h
+                for (int c0 = 0; c0 < nrows; c0 += 128) {
+                    const int col0 = c0 + 32 * hs;
                     if (col0 < nrows) {
                         float v[32], up[32];
                         tmem_ld32(lane_base + col0, v);
@@ -330,47 +357,48 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                     }
                     fence_proxy_async();
                     named_bar_sync(1, kThreadsEpi);
-                    if (warp < 2) {                                      // 64 lanes: one activation row each
-                        const int rin = 32 * warp + lane, col = 64 * c + rin;
+                    if (warp < 4) {                                      // 128 lanes: one activation row each
+                        const int rin = 32 * warp + lane, col = c0 + rin;
                         if (col < nrows) {
-                            const int row = row0 + col;
-                            if (A.xq_out) bulk_store(A.xq_out + (int64_t) row * A.w_rows + m0, b16 + rin * 128, 128 * 2);
-                            if (A.dst) bulk_store(A.dst + (int64_t) (A.ids ? A.ids[row] : row) * A.ld_dst + m0, b32 + rin * 128, 128 * 4);
+                            const int row_g = row0 + col;
+                            if (A.xq_out) bulk_store(A.xq_out + (int64_t) row_g * A.w_rows + m0, b16 + rin * 128, 128 * 2);
+                            if (A.dst) bulk_store(A.dst + (int64_t) (A.ids ? A.ids[row_g] : row_g) * A.ld_dst + m0, b32 + rin * 128, 128 * 4);
                         }
                         bulk_commit();
-                        bulk_wait_read<1>();                             // the other buffer's copies have read it
+                        bulk_wait_read<0>();                             // the buffer has been read: the next pass may fill it
                     }
                     named_bar_sync(2, kThreadsEpi);
                 }
             } else {
-                constexpr int kBuf = 32 * TM * 4;                        // 32 rows x 256 weight rows of f32
-                const bool have = m0 + 128 * hs < A.w_rows;              // this warp's accumulator exists
+                // 16 warps = 4 lane quadrants x 2 accumulators x 2 groups of 32 activation rows: 64 rows a pass
+                const int acc = hs & 1, grp = hs >> 1;
+                const bool have = m0 + 128 * acc < A.w_rows;             // this warp's accumulator exists
                 const uint32_t row_bytes_out = (uint32_t) min(TM, A.w_rows - m0) * 4;
-                const int nch = (nrows + 31) / 32;
-                for (int c = 0; c < nch; ++c) {
-                    float* buf = (float*) (stg + (size_t) (c & 1) * kBuf);
-                    if (have) {
+                float* buf = (float*) stg;                               // [64 rows][256] f32
+                for (int c0 = 0; c0 < nrows; c0 += 64) {
+                    const int col0 = c0 + 32 * grp;
+                    if (have && col0 < nrows) {
                         float v[32];
-                        tmem_ld32(lane_base + hs * kAccCols + 32 * c, v);
-                        const int at = 128 * hs + 32 * q + lane;
+                        tmem_ld32(lane_base + acc * kAccCols + col0, v);
+                        const int at = (32 * grp) * TM + 128 * acc + 32 * q + lane;
 #pragma unroll
                         for (int j = 0; j < 32; ++j) buf[at + j * TM] = v[j];
                     }
                     fence_proxy_async();
                     named_bar_sync(1, kThreadsEpi);
-                    if (warp == 0) {
-                        const int col = 32 * c + lane;
+                    if (warp < 2) {
+                        const int rin = 32 * warp + lane, col = c0 + rin;
                         if (col < nrows) {
-                            const int row = row0 + col;
-                            bulk_store(A.dst + (int64_t) (A.ids ? A.ids[row] : row) * A.ld_dst + m0, buf + lane * TM, row_bytes_out);
+                            const int row_g = row0 + col;
+                            bulk_store(A.dst + (int64_t) (A.ids ? A.ids[row_g] : row_g) * A.ld_dst + m0, buf + rin * TM, row_bytes_out);
                         }
                         bulk_commit();
-                        bulk_wait_read<1>();
+                        bulk_wait_read<0>();
                     }
                     named_bar_sync(2, kThreadsEpi);
                 }
             }
-            if (warp < 2) bulk_wait<0>();                                // every copy of this block has landed
+            if (warp < 4) bulk_wait<0>();                                // every copy of this block has landed
         }
         if (probing && tid == 0) {
             atomicAdd(A.probe + 0, (unsigned long long) c_wait0);
@@ -399,57 +427,63 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             if (!ok)                                             // let the copies in flight land before the block ends
                 for (int u = max(0, issued - NU); u < issued; ++u) wait_or_fail(P, &P.raw_full[u % NU], (u / NU) & 1);
         }
-    } else if (warp == kDqWarps + 1) {
-        // ------------------------------------------------------------ tensor-core issue (one lane)
+    } else if (warp == kDqWarps + 1 || warp == kDqWarps + 3) {
+        // ------------------------------------------------------------ tensor-core issue (one lane of two warps: one
+        //                                                              accumulator each, on different schedulers)
         if (lane == 0) {
-            // one product of N = rows rounded up to 16 per accumulator and K = 16: an M = 128 product costs the tensor
-            // core max(N / 2, ~84) cycles whatever N is, so the rows are never split into two products
+            const int my = warp == kDqWarps + 1 ? 0 : 1;
+            // One product of N = rows rounded up to 16 per accumulator and K = 16: an M = 128 product occupies the
+            // tensor core for N / 2 cycles, but only if this thread can issue one that often - a single thread's
+            // instruction stream is the limit, so everything here is precomputed or kept incrementally (no divisions,
+            // no descriptor construction, the ready barrier tested once before falling into the bounded wait).
             const int n_mma = max(16, (nrows + 15) & ~15);
             const uint32_t idesc = (1u << 4) | ((uint32_t) (n_mma >> 3) << 17) | ((uint32_t) (128 >> 4) << 24);
+            const uint64_t bdesc0 = smem_desc_sw128(smem_u32(smem));
+            const uint32_t a0 = tmem + kACol + my * 16, d0 = tmem + my * kAccCols;
+            int s = 0, sb = 0;                       // A stage of the next step, activation slot of the next pair
+            uint32_t ph_a = 0, ph_b = 0, acc = 0;    // their barriers' phases; 0 = overwrite the accumulators (first product)
+            const int npairs = nkt / 2;
             bool ok = true;
-            for (int kt = 0; kt < nkt; ++kt) {
-                const int s = kt % kSt, kb2 = kt >> 1, sb = kb2 % nbs;
-                const long long t0 = probing ? clock64() : 0;
-                if (!(kt & 1) && !wait_or_fail(P, &P.b_full[sb], (kb2 / nbs) & 1)) { ok = false; break; }
-                const long long t1 = probing ? clock64() : 0;
-                if (!wait_or_fail(P, &P.a_full[s], (kt / kSt) & 1)) { ok = false; break; }
-                if (probing) { c_wait0 += t1 - t0; c_wait1 += clock64() - t1; }
-                tc_fence_after();
-                const uint32_t b_base = smem_u32(smem + kBOff) + sb * b_stage + (kt & 1) * 64;
+            for (int kp = 0; kp < npairs; ++kp) {
+                if (!mbar_try_wait(&P.b_full[sb], ph_b) && !wait_or_fail(P, &P.b_full[sb], ph_b)) { ok = false; break; }
+                const uint64_t bd = bdesc0 + (uint64_t) ((uint32_t) sb * (kBStage >> 4));
 #pragma unroll
-                for (int kk = 0; kk < 2; ++kk) {
-                    const uint32_t acc = (kt > 0 || kk > 0) ? 1u : 0u;
-                    const uint64_t bd = smem_desc_sw128(b_base + kk * 32);   // the 64-row box continues the 128-row box's layout
-#pragma unroll
-                    for (int a = 0; a < 2; ++a)
-                        mma_f16_ts(tmem + a * kAccCols, tmem + kACol + s * 32 + a * 16 + kk * 8, bd, idesc, acc);
+                for (int h = 0; h < 2; ++h) {
+                    if (!mbar_try_wait(&P.a_full[s], ph_a) && !wait_or_fail(P, &P.a_full[s], ph_a)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t at = a0 + s * 32;
+                    mma_f16_ts(d0, at, bd + (h * 4), idesc, acc);
+                    acc = 1;
+                    mma_f16_ts(d0, at + 8, bd + (h * 4 + 2), idesc, 1);
+                    if (++s == kSt) { s = 0; ph_a ^= 1; }
                 }
-                mma_commit(&P.a_empty[s]);
-                if (kt & 1) mma_commit(&P.b_empty[sb]);
+                if (!ok) break;
+                mma_commit(&P.done[kp & (kDone - 1)]);
+                if (++sb == NB) { sb = 0; ph_b ^= 1; }
             }
             if (ok) mma_commit(&P.final);
-            if (probing) {
-                atomicAdd(A.probe + 3, (unsigned long long) c_wait0);
-                atomicAdd(A.probe + 4, (unsigned long long) c_wait1);
-                atomicAdd(A.probe + 5, (unsigned long long) (clock64() - t_start));
-            }
+            if (probing && my == 0) atomicAdd(A.probe + 5, (unsigned long long) (clock64() - t_start));
         }
-    } else {
+    } else if (warp == kDqWarps + 2) {
         // ------------------------------------------------------------ activation tiles (one lane)
         if (lane == 0) {
             int issued = 0;
             bool ok = true;
+            const uint32_t tx_bytes = big ? kBStage : kBBox;
             for (int kb2 = 0; kb2 < nkt / 2; ++kb2) {
-                const int sb = kb2 % nbs;
-                if (kb2 >= nbs && !wait_or_fail(P, &P.b_empty[sb], ((kb2 / nbs) - 1) & 1)) { ok = false; break; }
-                uint8_t* bt = smem + kBOff + (size_t) sb * b_stage;
-                mbar_expect_tx(&P.b_full[sb], b_stage);
+                const int sb = kb2 % NB;
+                if (kb2 >= NB) {                             // the slot was last read by pair kb2 - NB
+                    const int pp = kb2 - NB;
+                    if (!wait_or_fail(P, &P.done[pp % kDone], (pp / kDone) & 1)) { ok = false; break; }
+                }
+                uint8_t* bt = smem + (size_t) sb * kBStage;
+                mbar_expect_tx(&P.b_full[sb], tx_bytes);
                 tma_load_2d(bt, &tm_x, &P.b_full[sb], kb2 * 64, row0);
-                if (big) tma_load_2d(bt + kBBox, &tm_x64, &P.b_full[sb], kb2 * 64, row0 + 128);
+                if (big) tma_load_2d(bt + kBBox, &tm_x32, &P.b_full[sb], kb2 * 64, row0 + 128);
                 issued = kb2 + 1;
             }
             if (!ok)
-                for (int kb2 = max(0, issued - nbs); kb2 < issued; ++kb2) wait_or_fail(P, &P.b_full[kb2 % nbs], (kb2 / nbs) & 1);
+                for (int kb2 = max(0, issued - NB); kb2 < issued; ++kb2) wait_or_fail(P, &P.b_full[kb2 % NB], (kb2 / NB) & 1);
         }
     }
     tc_fence_before();
@@ -509,7 +543,7 @@ template<int T, bool GLU>
 int launch_mmq(const maya_mmq_product* p, const MmqArgs& A, cudaStream_t s) {
     const int64_t mat_rows = p->w_rows, K = p->w_cols;
     const size_t rbw = row_bytes(T, K);
-    CUtensorMap tw, tx, tx64;
+    CUtensorMap tw, tx, tx32;
     {   // weights as 32-bit words: (word in row, row in matrix, matrix); a box = 256 K-values of 64 rows
         const cuuint64_t dim[3] = {(cuuint64_t) (rbw / 4), (cuuint64_t) mat_rows, (cuuint64_t) p->n};
         const cuuint64_t st[2] = {(cuuint64_t) rbw, (cuuint64_t) p->expert_bytes};
@@ -517,22 +551,22 @@ int launch_mmq(const maya_mmq_product* p, const MmqArgs& A, cudaStream_t s) {
         if (!make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, p->w, dim, st, box, CU_TENSOR_MAP_SWIZZLE_NONE))
             return note_launch("mmq weight tensor map");
     }
-    {   // activations: f16 [row][K]; a box = 64 K-values (128 bytes) of 128 or 64 rows, written with the 128-byte swizzle
+    {   // activations: f16 [row][K]; a box = 64 K-values (128 bytes) of 128 or 32 rows, written with the 128-byte swizzle
         const cuuint64_t dim[2] = {(cuuint64_t) K, (cuuint64_t) p->total_rows};
         const cuuint64_t st[1] = {(cuuint64_t) K * 2};
-        const cuuint32_t box[2] = {64, 128}, box64[2] = {64, 64};
+        const cuuint32_t box[2] = {64, 128}, box32[2] = {64, 32};
         if (!make_map(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xq, dim, st, box, CU_TENSOR_MAP_SWIZZLE_128B) ||
-            !make_map(&tx64, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xq, dim, st, box64, CU_TENSOR_MAP_SWIZZLE_128B))
+            !make_map(&tx32, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xq, dim, st, box32, CU_TENSOR_MAP_SWIZZLE_128B))
             return note_launch("mmq activation tensor map");
     }
     constexpr size_t smem = kSmemBytes<T>;
     if (cudaFuncSetAttribute(mmq_kernel<T, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess)
         return note_launch("mmq smem attribute");
-    const int64_t groups = p->total_rows / TN + p->n;   // an upper bound of sum(ceil(rows_e / 192)), known without the counts
+    const int64_t groups = p->total_rows / TN + p->n;   // an upper bound of sum(ceil(rows_e / 160)), known without the counts
     if (groups > 65535) return refuse(MAYA_ERR_LIMIT);
     const int slab = GLU ? 128 : TM;
     const dim3 grid((unsigned) ((A.w_rows + slab - 1) / slab), (unsigned) groups);
-    mmq_kernel<T, GLU><<<grid, kMmqThreads, smem, s>>>(tw, tx, tx64, A);
+    mmq_kernel<T, GLU><<<grid, kMmqThreads, smem, s>>>(tw, tx, tx32, A);
     return note_launch("mmq");
 }
 
