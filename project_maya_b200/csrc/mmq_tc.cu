@@ -43,14 +43,14 @@ namespace {
 constexpr int TM = 256;                 // weight rows of a block
 constexpr int TN = 160;                 // most activation rows of a block
 constexpr int BK = 32;                  // K values of one step
-constexpr int kSt = 6;                  // stages of expanded weights (the A operand, in tensor memory)
+constexpr int kSt = 3;                  // stages of expanded weights (the A operand, in tensor memory), 64 K-values each
 constexpr int kUnitRows = 64;           // weight rows of one raw unit
 constexpr int kDqWarps = 16;            // two teams of 8
 constexpr int kMmqThreads = (kDqWarps + 4) * 32;   // + raw-unit loader, issuer of accumulator 0, activation loader, issuer of accumulator 1
 constexpr int kBBox = 128 * 64 * 2;     // 16 KB: 128 activation rows x 64 K-values, 128-byte swizzle
 constexpr int kBStage = kBBox + 32 * 64 * 2;   // + the 32-row box of a block with more than 128 rows: 20 KB
 constexpr uint32_t kAccCols = TN;       // tensor-memory columns: accumulator 0 at 0, accumulator 1 at 160,
-constexpr uint32_t kACol = 2 * TN;      // the A operand's 6 stages from 320: per stage 16 columns for each accumulator
+constexpr uint32_t kACol = 2 * TN;      // the A operand's 3 stages from 320: per stage 32 columns for each accumulator
 constexpr int kMaxUnits = 12;
 constexpr int kDone = 16;               // ring of "pair of K steps consumed" barriers (one tcgen05.commit per pair: a commit
                                         // costs the tensor pipe about as much as a product)
@@ -112,7 +112,7 @@ __device__ __forceinline__ void q4k_scales(const uint4 hdr, Q4Scales& S) {
     }
 }
 // 32 weights of sub-block (2p + hi) from the 32 quant bytes of pair p
-__device__ __forceinline__ void q4k_stage(const uint4 qa, const uint4 qb, int hi, __half2 dl, __half2 nml, uint32_t (&r)[16]) {
+__device__ __forceinline__ void q4k_stage(const uint4 qa, const uint4 qb, int hi, __half2 dl, __half2 nml, uint32_t* r) {
     const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
     const __half2 k1024 = __float2half2_rn(1024.0f);
 #pragma unroll
@@ -124,7 +124,7 @@ __device__ __forceinline__ void q4k_stage(const uint4 qa, const uint4 qb, int hi
 }
 // ---- Q8_0: block J (34 bytes) of a 272-byte raw row, read as three aligned 16-byte words
 template<int J>
-__device__ __forceinline__ void q80_stage(const uint8_t* rrow, uint32_t (&r)[16]) {
+__device__ __forceinline__ void q80_stage(const uint8_t* rrow, uint32_t* r) {
     constexpr int kBase = (34 * J) / 16 * 16, kOff = 34 * J - kBase;     // kOff = 0, 2, ..., 14
     const uint4 a = *(const uint4*) (rrow + kBase), b = *(const uint4*) (rrow + kBase + 16), c = *(const uint4*) (rrow + kBase + 32);
     const uint32_t w[12] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w, c.x, c.y, c.z, c.w};
@@ -214,6 +214,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
     if (found_e < 0) return;                        // beyond the last group: uniform for the whole block
     const long long t_start = clock64();
     const bool probing = A.probe != nullptr;
+    const bool tracing = probing && blockIdx.x == 0 && blockIdx.y == 0;   // development: time stamps of K-step pairs 20..27 in probe[16..]
     long long c_wait0 = 0, c_wait1 = 0;
     const int be = A.expert_map ? A.expert_map[found_e] : found_e;
     const int row0 = A.bounds[be] + found_g * TN;
@@ -248,10 +249,8 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
         const int slab = row >> 6;
         const uint8_t* const rbase = raw + (size_t) (row & 63) * kRawRow<T>;
         // rows 0..127 feed accumulator 0, rows 128..255 accumulator 1; a warp reaches the 32 lanes of its quadrant
-        const uint32_t a_lane = tmem + ((uint32_t) (32 * (w8 & 3)) << 16) + kACol + (w8 >> 2) * 16;
+        const uint32_t a_lane = tmem + ((uint32_t) (32 * (w8 & 3)) << 16) + kACol + (w8 >> 2) * 32;
         bool ok = true;
-        uint32_t pend[16];
-        int pend_kt = -1;
         for (int kb = 0; kb < nkb && ok; ++kb) {
             const int u = kb * 4 + slab, slot = u % NU;
             {
@@ -260,63 +259,53 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                 if (timing) c_wait0 += clock64() - t0;
             }
             const uint8_t* rrow = rbase + (size_t) slot * kUnitBytes<T>;
-            // A step is expanded into registers first and stored one step later: while this team waits for its stage
-            // to come free it already holds the next step's values (one more step of slack at no tensor-memory cost).
-            auto put = [&](int kt, const uint32_t (&o)[16]) -> bool {   // the row's 32 values of step kt -> its lane
-                const int s = kt % kSt;
-                if (kt >= kSt) {                     // the stage was last read by step kt - kSt, of pair (kt - kSt) / 2
-                    const int pp = (kt - kSt) >> 1;
+            auto put = [&](int kp, const uint32_t (&o)[32]) -> bool {   // the row's 64 values of pair kp -> its lane
+                const int s = kp % kSt;
+                if (kp >= kSt) {                     // the stage was last read by pair kp - kSt
+                    const int pp = kp - kSt;
                     const long long t0 = timing ? clock64() : 0;
-                    if (!wait_or_fail(P, &P.done[pp % kDone], (pp / kDone) & 1)) return false;
+                    if (!wait_or_fail(P, &P.done[pp & (kDone - 1)], (pp / kDone) & 1)) return false;
                     if (timing) c_wait1 += clock64() - t0;
                     tc_fence_after();
                 }
-                tmem_st16(a_lane + s * 32, o);
+                const long long ta = tracing ? clock64() : 0;
+                tmem_st32(a_lane + s * 64, o);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&P.a_full[s]);
+                if (tracing && w8 == 0 && lane == 0 && kp >= 20 && kp < 28) {
+                    A.probe[16 + (kp - 20) * 8 + 0] = (unsigned long long) (ta - t_start);         // stage seen free
+                    A.probe[16 + (kp - 20) * 8 + 1] = (unsigned long long) (clock64() - t_start);  // arrived
+                }
                 return true;
             };
-            auto rotate = [&](int j, uint32_t (&cur)[16]) -> bool {     // store the pending step, keep `cur` pending
-                if (pend_kt >= 0 && !put(pend_kt, pend)) return false;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) pend[i] = cur[i];
-                pend_kt = kb * 8 + j;
-                return true;
-            };
-            uint32_t o[16];
+            uint32_t o[32];
             if constexpr (T == MAYA_Q4_K) {
                 Q4Scales S;
                 q4k_scales(*(const uint4*) rrow, S);
 #pragma unroll
-                for (int p = 0; p < 4; ++p) {        // team 0: the low nibbles (sub-block 2p), team 1: the high ones
+                for (int i = 0; i < 2; ++i) {        // the 64 values of quant pair p: low nibbles, then high nibbles
+                    const int p = 2 * i + team;
                     const uint4 qa = *(const uint4*) (rrow + 16 + 32 * p), qb = *(const uint4*) (rrow + 32 + 32 * p);
-                    if (team == 0) q4k_stage(qa, qb, 0, S.dl[2 * p], S.nml[2 * p], o);
-                    else q4k_stage(qa, qb, 1, S.dl[2 * p + 1], S.nml[2 * p + 1], o);
-                    if (!rotate(2 * p + team, o)) { ok = false; break; }
+                    if (team == 0) {
+                        q4k_stage(qa, qb, 0, S.dl[4 * i], S.nml[4 * i], o);
+                        q4k_stage(qa, qb, 1, S.dl[4 * i + 1], S.nml[4 * i + 1], o + 16);
+                    } else {
+                        q4k_stage(qa, qb, 0, S.dl[4 * i + 2], S.nml[4 * i + 2], o);
+                        q4k_stage(qa, qb, 1, S.dl[4 * i + 3], S.nml[4 * i + 3], o + 16);
+                    }
+                    if (!put(kb * 4 + p, o)) { ok = false; break; }
                 }
             } else {
-#define MAYA_Q80_STEP(J) if (ok) { q80_stage<J>(rrow, o); ok = rotate(J, o); }
-                if (team == 0) { MAYA_Q80_STEP(0) MAYA_Q80_STEP(2) MAYA_Q80_STEP(4) MAYA_Q80_STEP(6) }
-                else { MAYA_Q80_STEP(1) MAYA_Q80_STEP(3) MAYA_Q80_STEP(5) MAYA_Q80_STEP(7) }
-#undef MAYA_Q80_STEP
+#define MAYA_Q80_PAIR(PP) if (ok) { q80_stage<2 * (PP)>(rrow, o); q80_stage<2 * (PP) + 1>(rrow, o + 16); ok = put(kb * 4 + (PP), o); }
+                if (team == 0) { MAYA_Q80_PAIR(0) MAYA_Q80_PAIR(2) }
+                else { MAYA_Q80_PAIR(1) MAYA_Q80_PAIR(3) }
+#undef MAYA_Q80_PAIR
             }
             if (!ok) break;
             __syncwarp();
             if (lane == 0) mbar_arrive(&P.raw_empty[slot]);      // 4 warps read a unit; after the 4th it may be overwritten
-        }
-        if (ok && pend_kt >= 0) {                    // the last step is still in registers
-            const int s = pend_kt % kSt, pp = (pend_kt - kSt) >> 1;
-            if (pend_kt >= kSt && !wait_or_fail(P, &P.done[pp % kDone], (pp / kDone) & 1)) ok = false;
-            if (ok) {
-                tc_fence_after();
-                tmem_st16(a_lane + s * 32, pend);
-                tmem_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&P.a_full[s]);
-            }
         }
         // ------------------------------------------------------------ epilogue
         const long long t_loop = clock64();
@@ -334,71 +323,65 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             uint8_t* const stg = smem;
             constexpr int kThreadsEpi = kDqWarps * 32;
             if constexpr (GLU) {
-                // 16 warps = 4 lane quadrants x 4 groups of 32 activation rows: 128 rows a pass
-                __half* b16 = (__half*) stg;                             // [128 rows][128] f16 image of h
-                float* b32 = (float*) (stg + 128 * 128 * 2);             // [128 rows][128] h
-                for (int c0 = 0; c0 < nrows; c0 += 128) {
-                    const int col0 = c0 + 32 * hs;
-                    if (col0 < nrows) {
-                        float v[32], up[32];
-                        tmem_ld32(lane_base + col0, v);
-                        tmem_ld32(lane_base + kAccCols + col0, up);
+                // 16 warps = 4 lane quadrants x 4 groups; a group takes every 4th chunk of 8 activation rows, so the
+                // groups stay balanced whatever the row count.  One pass: the whole tile fits in shared memory.
+                __half* b16 = (__half*) stg;                             // [rows][128] f16 image of h
+                float* b32 = (float*) (stg + TN * 128 * 2);              // [rows][128] h
+                const int nchunk = (nrows + 7) >> 3;
+                const int mcol = 32 * q + lane;
+                for (int c = hs; c < nchunk; c += 4) {
+                    const int col0 = 8 * c;
+                    float v[8], up[8];
+                    tmem_ld8(lane_base + col0, v);
+                    tmem_ld8(lane_base + kAccCols + col0, up);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = swiglu(v[j], up[j], A.limit);
-                        const int at = (32 * hs) * 128 + 32 * q + lane;
-                        if (A.xq_out) {
+                    for (int j = 0; j < 8; ++j) v[j] = swiglu(v[j], up[j], A.limit);
+                    if (A.xq_out) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) b16[at + j * 128] = q8_1_round_warp(v[j]);
-                        }
-                        if (A.dst) {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) b32[at + j * 128] = v[j];
-                        }
+                        for (int j = 0; j < 8; ++j)
+                            if (col0 + j < nrows) b16[(col0 + j) * 128 + mcol] = q8_1_round_warp(v[j]);      // uniform in the warp
                     }
-                    fence_proxy_async();
-                    named_bar_sync(1, kThreadsEpi);
-                    if (warp < 4) {                                      // 128 lanes: one activation row each
-                        const int rin = 32 * warp + lane, col = c0 + rin;
-                        if (col < nrows) {
-                            const int row_g = row0 + col;
-                            if (A.xq_out) bulk_store(A.xq_out + (int64_t) row_g * A.w_rows + m0, b16 + rin * 128, 128 * 2);
-                            if (A.dst) bulk_store(A.dst + (int64_t) (A.ids ? A.ids[row_g] : row_g) * A.ld_dst + m0, b32 + rin * 128, 128 * 4);
-                        }
-                        bulk_commit();
-                        bulk_wait_read<0>();                             // the buffer has been read: the next pass may fill it
+                    if (A.dst) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (col0 + j < nrows) b32[(col0 + j) * 128 + mcol] = v[j];
                     }
-                    named_bar_sync(2, kThreadsEpi);
+                }
+                fence_proxy_async();
+                named_bar_sync(1, kThreadsEpi);
+                if (tid < nrows) {                                       // one activation row each
+                    const int row_g = row0 + tid;
+                    if (A.xq_out) bulk_store(A.xq_out + (int64_t) row_g * A.w_rows + m0, b16 + tid * 128, 128 * 2);
+                    if (A.dst) bulk_store(A.dst + (int64_t) (A.ids ? A.ids[row_g] : row_g) * A.ld_dst + m0, b32 + tid * 128, 128 * 4);
+                    bulk_commit();
                 }
             } else {
-                // 16 warps = 4 lane quadrants x 2 accumulators x 2 groups of 32 activation rows: 64 rows a pass
+                // 16 warps = 4 lane quadrants x 2 accumulators x 2 groups that take alternate chunks of 16 activation rows
                 const int acc = hs & 1, grp = hs >> 1;
                 const bool have = m0 + 128 * acc < A.w_rows;             // this warp's accumulator exists
                 const uint32_t row_bytes_out = (uint32_t) min(TM, A.w_rows - m0) * 4;
-                float* buf = (float*) stg;                               // [64 rows][256] f32
-                for (int c0 = 0; c0 < nrows; c0 += 64) {
-                    const int col0 = c0 + 32 * grp;
-                    if (have && col0 < nrows) {
-                        float v[32];
-                        tmem_ld32(lane_base + acc * kAccCols + col0, v);
-                        const int at = (32 * grp) * TM + 128 * acc + 32 * q + lane;
+                float* buf = (float*) stg;                               // [rows][256] f32
+                const int nchunk = (nrows + 15) >> 4;
+                const int mcol = 128 * acc + 32 * q + lane;
+                if (have) {
+                    for (int c = grp; c < nchunk; c += 2) {
+                        const int col0 = 16 * c;
+                        float v[16];
+                        tmem_ld16(lane_base + acc * kAccCols + col0, v);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) buf[at + j * TM] = v[j];
+                        for (int j = 0; j < 16; ++j)
+                            if (col0 + j < nrows) buf[(col0 + j) * TM + mcol] = v[j];
                     }
-                    fence_proxy_async();
-                    named_bar_sync(1, kThreadsEpi);
-                    if (warp < 2) {
-                        const int rin = 32 * warp + lane, col = c0 + rin;
-                        if (col < nrows) {
-                            const int row_g = row0 + col;
-                            bulk_store(A.dst + (int64_t) (A.ids ? A.ids[row_g] : row_g) * A.ld_dst + m0, buf + rin * TM, row_bytes_out);
-                        }
-                        bulk_commit();
-                        bulk_wait_read<0>();
-                    }
-                    named_bar_sync(2, kThreadsEpi);
+                }
+                fence_proxy_async();
+                named_bar_sync(1, kThreadsEpi);
+                if (tid < nrows) {
+                    const int row_g = row0 + tid;
+                    bulk_store(A.dst + (int64_t) (A.ids ? A.ids[row_g] : row_g) * A.ld_dst + m0, buf + tid * TM, row_bytes_out);
+                    bulk_commit();
                 }
             }
-            if (warp < 4) bulk_wait<0>();                                // every copy of this block has landed
+            if (tid < nrows) bulk_wait_read<0>();                        // the copies have read shared memory: the block may end
         }
         if (probing && tid == 0) {
             atomicAdd(A.probe + 0, (unsigned long long) c_wait0);
@@ -439,30 +422,38 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             const int n_mma = max(16, (nrows + 15) & ~15);
             const uint32_t idesc = (1u << 4) | ((uint32_t) (n_mma >> 3) << 17) | ((uint32_t) (128 >> 4) << 24);
             const uint64_t bdesc0 = smem_desc_sw128(smem_u32(smem));
-            const uint32_t a0 = tmem + kACol + my * 16, d0 = tmem + my * kAccCols;
-            int s = 0, sb = 0;                       // A stage of the next step, activation slot of the next pair
-            uint32_t ph_a = 0, ph_b = 0, acc = 0;    // their barriers' phases; 0 = overwrite the accumulators (first product)
+            const uint32_t b_hi = (uint32_t) (bdesc0 >> 32), b_lo0 = (uint32_t) bdesc0, b_lo_end = b_lo0 + NB * (kBStage >> 4);
+            const uint32_t a0 = tmem + kACol + my * 32, a_end = a0 + kSt * 64, d0 = tmem + my * kAccCols;
+            const uint32_t bfull0 = smem_u32(&P.b_full[0]), afull0 = smem_u32(&P.a_full[0]), done0 = smem_u32(&P.done[0]);
+            uint32_t b_lo = b_lo0, at = a0, bfull = bfull0, afull = afull0;   // of the next pair of K steps
+            uint32_t ph_a = 0, ph_b = 0, first = 0;  // the barriers' phases; first = 0: the first product overwrites
             const int npairs = nkt / 2;
             bool ok = true;
             for (int kp = 0; kp < npairs; ++kp) {
-                if (!mbar_try_wait(&P.b_full[sb], ph_b) && !wait_or_fail(P, &P.b_full[sb], ph_b)) { ok = false; break; }
-                const uint64_t bd = bdesc0 + (uint64_t) ((uint32_t) sb * (kBStage >> 4));
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    if (!mbar_try_wait(&P.a_full[s], ph_a) && !wait_or_fail(P, &P.a_full[s], ph_a)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t at = a0 + s * 32;
-                    mma_f16_ts(d0, at, bd + (h * 4), idesc, acc);
-                    acc = 1;
-                    mma_f16_ts(d0, at + 8, bd + (h * 4 + 2), idesc, 1);
-                    if (++s == kSt) { s = 0; ph_a ^= 1; }
+                if (!mbar_test_wait_addr(bfull, ph_b)) {         // not there yet: the bounded wait (timed when probing)
+                    const long long t0 = probing ? clock64() : 0;
+                    if (!wait_or_fail(P, &P.b_full[(bfull - bfull0) >> 3], ph_b)) { ok = false; break; }
+                    if (probing) c_wait0 += clock64() - t0;
                 }
-                if (!ok) break;
-                mma_commit(&P.done[kp & (kDone - 1)]);
-                if (++sb == NB) { sb = 0; ph_b ^= 1; }
+                if (!mbar_test_wait_addr(afull, ph_a)) {
+                    const long long t0 = probing ? clock64() : 0;
+                    if (!wait_or_fail(P, &P.a_full[(afull - afull0) >> 3], ph_a)) { ok = false; break; }
+                    if (probing) c_wait1 += clock64() - t0;
+                }
+                tc_fence_after();
+                mma_f16_ts_x4_commit(d0, at, b_lo, b_hi, idesc, first, done0 + ((kp & (kDone - 1)) << 3));
+                first = 1;
+                at += 64; afull += 8;
+                if (at == a_end) { at = a0; afull = afull0; ph_a ^= 1; }
+                b_lo += kBStage >> 4; bfull += 8;
+                if (b_lo == b_lo_end) { b_lo = b_lo0; bfull = bfull0; ph_b ^= 1; }
             }
             if (ok) mma_commit(&P.final);
-            if (probing && my == 0) atomicAdd(A.probe + 5, (unsigned long long) (clock64() - t_start));
+            if (probing && my == 0) {
+                atomicAdd(A.probe + 3, (unsigned long long) c_wait0);
+                atomicAdd(A.probe + 4, (unsigned long long) c_wait1);
+                atomicAdd(A.probe + 5, (unsigned long long) (clock64() - t_start));
+            }
         }
     } else if (warp == kDqWarps + 2) {
         // ------------------------------------------------------------ activation tiles (one lane)
@@ -492,20 +483,48 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
     if (tid == 0 && failed(P) && A.error != nullptr) atomicExch(A.error, 1u);
 }
 
-// x rows (gathered through ids) -> f16 rows of their q8_1 image: one warp per 32 values
+// x rows (gathered through ids) -> f16 rows of their q8_1 image.  A thread owns 8 consecutive values (one 16-byte
+// store), the 4 threads of a 32-value block find its amax with two shuffles.
 template<typename X>
 __global__ void __launch_bounds__(256) mmq_quantize_kernel(const X* __restrict__ x, const int* __restrict__ ids,
                                                            __half* __restrict__ xq, int64_t cols, int64_t ld,
-                                                           int64_t n_blocks) {
-    const int lane = threadIdx.x & 31;
-    const int64_t b = (int64_t) blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (b >= n_blocks) return;
-    const int64_t bpr = cols / 32, row = b / bpr, kb = b - row * bpr;
+                                                           int64_t n_chunks) {
+    const int64_t i = (int64_t) blockIdx.x * 256 + threadIdx.x;
+    const bool live = i < n_chunks;                  // n_chunks is a multiple of 4: a block's 4 threads live together
+    const int64_t cpr = cols / 8, row = live ? i / cpr : 0, c = live ? i - row * cpr : 0;
     const int64_t src = ids ? ids[row] : row;
-    float v;
-    if constexpr (sizeof(X) == 2) v = __uint_as_float((uint32_t) x[src * ld + kb * 32 + lane] << 16);   // bf16 bits, widened exactly
-    else v = x[src * ld + kb * 32 + lane];
-    xq[b * 32 + lane] = q8_1_round_warp(v);
+    float v[8];
+    if (live) {
+        if constexpr (sizeof(X) == 2) {              // bf16 bits, widened exactly
+            const uint4 u = *(const uint4*) (x + src * ld + c * 8);
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { v[2 * k] = __uint_as_float(w[k] << 16); v[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u); }
+        } else {
+            const float4 a = *(const float4*) (x + src * ld + c * 8), b = *(const float4*) (x + src * ld + c * 8 + 4);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = 0.0f;
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    const float d = fminf(__fdiv_rn(amax, 127.0f), 65504.0f), dh = __half2float(__float2half_rn(d));
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float q0 = 0.0f, q1 = 0.0f;
+        if (amax != 0.0f) {
+            q0 = fmaxf(-127.0f, fminf(127.0f, roundf(__fdiv_rn(v[2 * k], d))));
+            q1 = fmaxf(-127.0f, fminf(127.0f, roundf(__fdiv_rn(v[2 * k + 1], d))));
+        }
+        o[k] = h2_bits(__floats2half2_rn(dh * q0, dh * q1));
+    }
+    if (live) *(uint4*) (xq + row * cols + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 template<typename X>
@@ -513,9 +532,10 @@ int launch_quantize(const X* x, const int32_t* ids, void* xq, int type, int64_t 
     if (!maya_mmq_supported(type)) return refuse(MAYA_ERR_TYPE);
     if (rows <= 0) return MAYA_OK;
     if (!x || !xq || cols <= 0 || cols % 32 || ld < cols) return refuse(MAYA_ERR_ARG);
-    const int64_t nb = rows * (cols / 32);
-    if ((nb + 7) / 8 > 0x7FFFFFFF) return refuse(MAYA_ERR_LIMIT);
-    mmq_quantize_kernel<X><<<(unsigned) ((nb + 7) / 8), 256, 0, as_stream(stream)>>>(x, ids, (__half*) xq, cols, ld, nb);
+    if (!aligned16(x) || !aligned16(xq) || (ld * sizeof(X)) % 16) return refuse(MAYA_ERR_ARG);   // 16-byte loads and stores
+    const int64_t nc = rows * (cols / 8);
+    if ((nc + 255) / 256 > 0x7FFFFFFF) return refuse(MAYA_ERR_LIMIT);
+    mmq_quantize_kernel<X><<<(unsigned) ((nc + 255) / 256), 256, 0, as_stream(stream)>>>(x, ids, (__half*) xq, cols, ld, nc);
     return note_launch("mmq_quantize");
 }
 
