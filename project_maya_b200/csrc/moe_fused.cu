@@ -168,10 +168,21 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     } else {
         const int t2 = tid - kRouteThreads, n2 = kFusedThreads - kRouteThreads;
         load_tab_rep<T>(s_tab, t2, n2);
-        for (int b = (t2 >> 5); b < nblk_x; b += n2 / 32) {
-            const float v = A.x_is_bf16 ? __uint_as_float((uint32_t) ((const uint16_t*) A.x)[b * 32 + lane] << 16)
-                                        : ((const float*) A.x)[b * 32 + lane];
-            q8_1_to_smem(v, cq, cd, cs, b, lane);
+        // the token's activations: 8 loads in flight per lane before the first is used (they come from HBM)
+        constexpr int NW2 = (kFusedThreads - kRouteThreads) / 32;
+        for (int b0 = (t2 >> 5); b0 < nblk_x; b0 += 8 * NW2) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int b = b0 + i * NW2;
+                v[i] = 0.0f;
+                if (b < nblk_x)
+                    v[i] = A.x_is_bf16 ? __uint_as_float((uint32_t) ((const uint16_t*) A.x)[b * 32 + lane] << 16)
+                                       : ((const float*) A.x)[b * 32 + lane];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (b0 + i * NW2 < nblk_x) q8_1_to_smem(v[i], cq, cd, cs, b0 + i * NW2, lane);
         }
     }
     __syncthreads();
@@ -213,13 +224,23 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
 
     // ---------------------------------------------------------------- phase 2: q8_1(h), down, combine
     if (ok) {
-        for (int b = warp; b < ne * nblk_h; b += NW) {
-            const int e = b / nblk_h, kb = b - e * nblk_h;
-            const int width = e < k ? n_ff : A.n_ff_sh;
-            if (sh.ptr[e] == 0ull) continue;         // another rank's expert: its column is never read
-            float v = 0.0f;
-            if (kb * 32 < width) v = __ldcg(&A.h[(size_t) e * h_ld + kb * 32 + lane]);
-            q8_1_to_smem(v, cq, cd, cs, b, lane);
+        // every block needs all of h: 8 loads in flight per lane before the first is used (one L2 round trip per 8
+        // blocks of 32 values instead of one per block)
+        for (int b0 = warp; b0 < ne * nblk_h; b0 += 8 * NW) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int b = b0 + i * NW, e = b / nblk_h, kb = b - e * nblk_h;
+                v[i] = 0.0f;
+                if (b < ne * nblk_h && sh.ptr[e] != 0ull && kb * 32 < (e < k ? n_ff : A.n_ff_sh))
+                    v[i] = __ldcg(&A.h[(size_t) e * h_ld + kb * 32 + lane]);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int b = b0 + i * NW;
+                if (b < ne * nblk_h && sh.ptr[b / nblk_h] != 0ull)   // another rank's expert: its column is never read
+                    q8_1_to_smem(v[i], cq, cd, cs, b, lane);
+            }
         }
         __syncthreads();
         int o0, o1;
