@@ -201,7 +201,7 @@ def reference_arm(args) -> None:
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
-def build_layers(torch, api, n_layers: int, expert_range, shared_here: bool):
+def build_layers(torch, api, n_layers: int, expert_range, shared_range):
     cfg = CFG
     lc = api.MoeLayerConfig(cfg["n_embd"], cfg["n_ff"], cfg["n_expert"], cfg["k"], cfg["gu_type"], cfg["d_type"],
                             cfg["n_ff_sh"], cfg["sh_gu_type"], cfg["sh_d_type"], cfg["limit"])
@@ -220,7 +220,7 @@ def build_layers(torch, api, n_layers: int, expert_range, shared_here: bool):
         # further layers are byte copies in their own memory: the values do not change the work, the addresses do
         ex = experts0 if i == 0 else experts0.clone()
         sh = shared0 if i == 0 else shared0.clone()
-        layers.append(api.MoeLayer(lc, ex, sh, expert_range=expert_range, shared_here=shared_here, max_tokens=1))
+        layers.append(api.MoeLayer(lc, ex, sh, expert_range=expert_range, shared_range=shared_range, max_tokens=1))
     torch.cuda.synchronize()
     return lc, layers
 
@@ -245,7 +245,9 @@ def gpu_arm(args) -> None:
     cfg = CFG
     Hd, E, k = cfg["n_embd"], cfg["n_expert"], cfg["k"]
     per = E // world
-    lc, layers = build_layers(torch, api, args.layers, (rank * per, (rank + 1) * per) if world > 1 else None, rank == 0)
+    wid = cfg["n_ff_sh"] // world            # every rank holds 1 / world of the shared expert's width
+    lc, layers = build_layers(torch, api, args.layers, (rank * per, (rank + 1) * per) if world > 1 else None,
+                              (rank * wid, (rank + 1) * wid) if world > 1 else None)
 
     logits_h = torch.from_numpy(S.router_logits("C2", N_TOKENS, E, cfg["zipf"])).pin_memory()
     x_h = torch.from_numpy(S.bf16_bits(S.activations("C2", N_TOKENS, Hd, "bf16")).view(np.int16)).view(torch.bfloat16).pin_memory()
@@ -336,7 +338,7 @@ def gpu_arm(args) -> None:
     # ---- the dominant kernel alone: gate/up of the routed experts (+ the shared expert's down rows in the same launch)
     roof = None
     if rank == 0:
-        roof = dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, min(K, 64), stream)
+        roof = dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, min(K, 64), stream, world)
 
     if rank == 0:
         bytes_tok = algorithmic_bytes_per_token()
@@ -351,7 +353,7 @@ def gpu_arm(args) -> None:
                        "l2": "inputs larger than L2: steps rotate over %d resident layers and 256 tokens" % len(layers),
                        "launch": ("CUDA graph of the K steps" + (", partial outputs summed over peer HBM in the layer kernel's epilogue" if peer is not None else ""))
                        if use_graph else "eager launches + NCCL all-reduce of the partial outputs (comparison baseline)",
-                       "parallelism": "1 GPU" if world == 1 else f"expert-parallel {world} x {per} experts, shared expert on rank 0"},
+                       "parallelism": "1 GPU" if world == 1 else f"expert-parallel {world} x {per} experts, shared expert width-sliced {world} x {cfg['n_ff_sh'] // world}"},
             "hbm_gbs": bytes_tok * value / 1e9, "hbm_frac_of_%s_peak" % peak_kind: bytes_tok * value / 1e9 / peak,
             "hbm_frac_of_nominal_8TBs": bytes_tok * value / 8e12,
             "e2e": {"value": e2e, "unit": "tok/s/layer", "h2d_bytes_per_step": E * 4 + Hd * 2, "d2h_bytes_per_step": Hd * 4,
@@ -374,7 +376,12 @@ def gpu_arm(args) -> None:
         dist.destroy_process_group()
 
 
-def dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, steps: int, stream) -> dict:
+# dram__bytes_read.sum + dram__bytes_write.sum of one moe_layer_t1_kernel launch of this workload on one GPU, from the ncu
+# capture summarised in profiles/moe_layer_t1_kernel_C2.md (the algorithmic bytes are 136.8 MB: no re-reads)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 140.6e6
+
+
+def dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, steps: int, stream, world: int = 1) -> dict:
     """Times the fused layer kernel alone: one CUDA-event pair per launch on the launching stream, same rotating
     layers and tokens as the timed loop (so every launch reads its experts from HBM)."""
     cfg = CFG
@@ -394,11 +401,12 @@ def dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, steps: int, 
     us = float(np.mean([a.elapsed_time(b) for a, b in evs])) * 1e3
     phases = layers[(steps - 1) % len(layers)].phase_ns(stream)
     peak, kind = measured_peaks()
-    alg = algorithmic_bytes_per_token()
+    alg = algorithmic_bytes_per_token() // world        # N > 1: this rank's mean share (its experts, its slice of the shared one)
     achieved = alg / (us * 1e-6) / 1e9
     return {"bound": "hbm", "kernel": "moe_layer_t1_kernel<IQ2_S, Q8_0> (the whole layer: route, q8_1, gate/up + SwiGLU, down, combine)",
             "achieved": achieved, "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": achieved / peak,
-            "algorithmic_bytes_per_launch": alg, "us_per_launch": us, "launches_timed": steps, "traffic": None,
+            "algorithmic_bytes_per_launch": alg, "us_per_launch": us, "launches_timed": steps,
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
             "block0_phase_end_us": {"route+quantize": phases[1] / 1e3, "gate_up": phases[2] / 1e3, "grid_barrier": phases[3] / 1e3,
                                     "down+combine": phases[4] / 1e3}}
 

@@ -272,6 +272,12 @@ typedef struct maya_moe_layer {
     int shared_here;             /* non-zero: this rank adds the shared expert */
     int staged;                  /* non-zero: run one token through the staged kernels (router, q8_1, gate/up, down as
                                     separate launches) instead of the single fused kernel; same bits either way */
+    int sh_lo, sh_hi;            /* with shared_here: this rank's slice [sh_lo, sh_hi) of the shared expert's FFN width
+                                    (multiples of 32; 0, 0 = all of it): its gate/up rows and the same columns of the down
+                                    rows, so that the ranks' partial outputs add up to the shared expert's output (the
+                                    width-sliced placement; summed in another order than on one rank, so equal to it
+                                    only to rounding).  A proper slice needs the single fused kernel (one token, Q8_0
+                                    shared expert): otherwise the call is refused */
 } maya_moe_layer;
 /* Bytes of scratch maya_moe_layer_decode needs for n_tokens tokens.  The scratch must be 256-byte aligned and ZEROED
  * once before its first use (it holds the fused kernel's grid-barrier counter); one scratch serves one stream at a

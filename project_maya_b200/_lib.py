@@ -36,7 +36,8 @@ class MoeLayerDesc(C.Structure):
     _fields_ = [("n_embd", c_int), ("n_ff", c_int), ("n_expert", c_int), ("k", c_int), ("gu_type", c_int),
                 ("d_type", c_int), ("experts", c_void_p), ("expert_stride", c_size_t), ("n_ff_sh", c_int),
                 ("sh_gu_type", c_int), ("sh_d_type", c_int), ("shared", c_void_p), ("limit", c_float),
-                ("expert_lo", c_int), ("expert_hi", c_int), ("shared_here", c_int), ("staged", c_int)]
+                ("expert_lo", c_int), ("expert_hi", c_int), ("shared_here", c_int), ("staged", c_int), ("sh_lo", c_int),
+                ("sh_hi", c_int)]
 
 
 class MmqProduct(C.Structure):

@@ -43,6 +43,8 @@ struct FusedArgs {
     int expert_lo, expert_hi;
     const uint8_t* shared;     // NULL: none (or not on this rank)
     int n_ff_sh;
+    int sh_lo, sh_hi;          // this rank's slice of the shared expert's FFN width (multiples of 32): its gate/up rows
+                               // and the same columns of every down row; the ranks' partial outputs add up
     float limit;
     int* ids;                  // [k] out
     float* weights;            // [k] out
@@ -195,7 +197,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
         int r0, r1;
         slice(n_ff, gridDim.x, blockIdx.x, r0, r1);            // routed experts' rows
         int q0 = 0, q1 = 0;
-        if (has_sh) slice(A.n_ff_sh, gridDim.x, blockIdx.x, q0, q1);
+        if (has_sh) {
+            slice(A.sh_hi - A.sh_lo, gridDim.x, blockIdx.x, q0, q1);
+            q0 += A.sh_lo;
+            q1 += A.sh_lo;
+        }
         const int nr = r1 - r0, n_routed = nr * sh.nv, n_items = n_routed + (q1 - q0);
         const size_t rb = row_bytes(T, n_embd);
         for (int it = warp; it < n_items; it += NW) {
@@ -217,6 +223,28 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             }
         }
     }
+    int o0, o1;
+    slice(n_embd / 4, gridDim.x, blockIdx.x, o0, o1);         // whole float4s: the cross-rank sum moves 16 bytes a lane
+    o0 *= 4;
+    o1 *= 4;
+    const int nrows = o1 - o0, npairs = (nrows + 1) / 2;
+    const size_t drb = row_bytes(T, n_ff), down_off = 2 * (size_t) n_ff * row_bytes(T, n_embd);
+    const int nvt = sh.nv + (has_sh ? 1 : 0);
+    auto down_rows = [&](int it, const uint8_t*& base, size_t& pitch, size_t& bytes, int& e, int& ra, int& rb2) {
+        const int ei = it / npairs, pr = it - ei * npairs;
+        e = ei < sh.nv ? sh.ve[ei] : k;
+        ra = o0 + 2 * pr;
+        rb2 = min(ra + 1, o1 - 1);
+        if (e < k) {
+            base = (const uint8_t*) sh.ptr[e] + down_off;
+            pitch = drb;
+            bytes = drb;
+        } else {                                     // this rank's columns [sh_lo, sh_hi) of the shared expert's down rows
+            pitch = row_bytes(TS, A.n_ff_sh);
+            base = A.shared + 2 * (size_t) A.n_ff_sh * row_bytes(TS, n_embd) + row_bytes(TS, A.sh_lo);
+            bytes = row_bytes(TS, A.sh_hi - A.sh_lo);
+        }
+    };
     __syncthreads();
     stamp(A.sync, 2);
     const bool ok = grid_barrier(A.sync, sh.epoch);
@@ -232,7 +260,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             for (int i = 0; i < 8; ++i) {
                 const int b = b0 + i * NW, e = b / nblk_h, kb = b - e * nblk_h;
                 v[i] = 0.0f;
-                if (b < ne * nblk_h && sh.ptr[e] != 0ull && kb * 32 < (e < k ? n_ff : A.n_ff_sh))
+                if (b < ne * nblk_h && sh.ptr[e] != 0ull && (e < k ? kb * 32 < n_ff : (kb * 32 >= A.sh_lo && kb * 32 < A.sh_hi)))
                     v[i] = __ldcg(&A.h[(size_t) e * h_ld + kb * 32 + lane]);
             }
 #pragma unroll
@@ -243,32 +271,22 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             }
         }
         __syncthreads();
-        int o0, o1;
-        slice(n_embd / 4, gridDim.x, blockIdx.x, o0, o1);     // whole float4s: the cross-rank sum moves 16 bytes a lane
-        o0 *= 4;
-        o1 *= 4;
-        const int nrows = o1 - o0, npairs = (nrows + 1) / 2;
-        const size_t drb = row_bytes(T, n_ff), down_off = 2 * (size_t) n_ff * row_bytes(T, n_embd);
-        const int nvt = sh.nv + (has_sh ? 1 : 0);
         for (int it = warp; it < npairs * nvt; it += NW) {
-            const int ei = it / npairs, pr = it - ei * npairs;
-            const int e = ei < sh.nv ? sh.ve[ei] : k;
-            const int ra = o0 + 2 * pr, rb2 = min(ra + 1, o1 - 1);
-            const unsigned long long p = sh.ptr[e];
+            const uint8_t* base; size_t pitch, bytes; int e, ra, rb2;
+            down_rows(it, base, pitch, bytes, e, ra, rb2);
+            const int pr = (ra - o0) >> 1;
             float o[2] = {0.0f, 0.0f};
             {
                 XCols H;
                 H.q = cq + (size_t) 2 * e * nblk_h; H.d = cd + (size_t) e * nblk_h; H.isum = cs + (size_t) e * nblk_h;
                 H.nblk = nblk_h;
+                const uint8_t* rows[2] = {base + (size_t) ra * pitch, base + (size_t) rb2 * pitch};
                 if (e < k) {
-                    const uint8_t* base = (const uint8_t*) p + down_off;
-                    const uint8_t* rows[2] = {base + (size_t) ra * drb, base + (size_t) rb2 * drb};
                     rows_dot1<T, 2>(rows, H, n_ff, lane, s_tab, o);
                 } else if constexpr (TS != 0) {
-                    const size_t srb = row_bytes(TS, A.n_ff_sh);
-                    const uint8_t* base = A.shared + 2 * (size_t) A.n_ff_sh * row_bytes(TS, n_embd);
-                    const uint8_t* rows[2] = {base + (size_t) ra * srb, base + (size_t) rb2 * srb};
-                    rows_dot1<TS, 2>(rows, H, A.n_ff_sh, lane, nullptr, o);
+                    const int b0 = A.sh_lo / 32;
+                    H.q += 2 * b0; H.d += b0; H.isum += b0; H.nblk = (A.sh_hi - A.sh_lo) / 32;
+                    rows_dot1<TS, 2>(rows, H, A.sh_hi - A.sh_lo, lane, nullptr, o);
                 }
             }
             if (lane == 0) {
@@ -344,9 +362,11 @@ int fused_t1(const maya_moe_layer& L, const float* logits, const void* x, int x_
     A.n_embd = L.n_embd; A.n_ff = L.n_ff; A.n_expert = L.n_expert; A.k = L.k;
     A.experts = (const uint8_t*) L.experts; A.expert_stride = L.expert_stride;
     A.expert_lo = L.expert_lo; A.expert_hi = L.expert_hi;
-    const bool sh = L.n_ff_sh > 0 && L.shared_here && L.shared != nullptr;
+    const bool sh = L.n_ff_sh > 0 && L.shared_here && L.shared != nullptr && !(L.sh_hi > 0 && L.sh_hi <= L.sh_lo);
     A.shared = sh ? (const uint8_t*) L.shared : nullptr;
     A.n_ff_sh = sh ? L.n_ff_sh : 0;
+    A.sh_lo = sh ? L.sh_lo : 0;
+    A.sh_hi = sh ? (L.sh_hi > 0 ? L.sh_hi : L.n_ff_sh) : 0;
     A.limit = L.limit;
     A.ids = ids; A.weights = weights; A.out = out; A.h = h_scratch; A.sync = sync;
 #define FUSED_CASE(TT)                                                      \

@@ -92,6 +92,9 @@ int check_layer(const maya_moe_layer* L) {
         if (L->n_embd % type_qk(L->sh_gu_type) || L->n_ff_sh % type_qk(L->sh_d_type) || L->n_ff_sh % 32) return MAYA_ERR_ARG;
     }
     if (L->expert_lo < 0 || L->expert_hi > L->n_expert || L->expert_lo > L->expert_hi) return MAYA_ERR_ARG;
+    if (L->sh_lo != 0 || L->sh_hi != 0) {            // a slice of the shared expert's width
+        if (L->sh_lo < 0 || L->sh_hi > L->n_ff_sh || L->sh_lo > L->sh_hi || L->sh_lo % 32 || L->sh_hi % 32) return MAYA_ERR_ARG;
+    }
     return MAYA_OK;
 }
 
@@ -161,6 +164,8 @@ static int layer_decode(const maya_moe_layer* L, const float* logits, const void
     float* d_w = weights ? weights : S.weights;
     if (T == 1 && !L->staged && fused_t1_supported(*L))
         return fused_t1(*L, logits, x, x_is_bf16, d_ids, d_w, out, S.h, S.sync, ar, mi, seq, s);
+    if (L->n_ff_sh > 0 && L->shared_here && (L->sh_lo != 0 || (L->sh_hi != 0 && L->sh_hi != L->n_ff_sh)))
+        return refuse(MAYA_ERR_ARG);                 // only the fused kernel slices the shared expert
 
     st = maya_router_top10(logits, T, L->n_expert, L->k, d_ids, d_w, stream);
     if (st != MAYA_OK) return st;

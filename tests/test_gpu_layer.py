@@ -155,6 +155,32 @@ def test_expert_parallel_partition_sums_to_whole(T, api, oracle):
     assert not bool(empty.any())
 
 
+@pytest.mark.parametrize("n_ranks", [2, 8])
+def test_width_sliced_shared_expert_sums_to_whole(T, api, oracle, n_ranks):
+    """Expert-parallel ranks that each hold 1/n of the shared expert's FFN width (its gate/up rows and the same
+    columns of the down rows): the rank-ordered sum of the partial outputs is the one-rank output up to the order of
+    the shared expert's down sums; a slice that the staged kernels would have to run is refused."""
+    cfg = dict(H.CONFIGS["C2"], n_expert=16)
+    lc, experts, shared = synth_layer(T, api, cfg, 16, seed=21)
+    logits = H.router_logits("C2", 3, 16, 1.1)
+    x = H.activations("C2", 3, cfg["n_embd"], "bf16")
+    ld, xd = dev(T, logits), dev(T, x, T.bfloat16)
+    per, wid = 16 // n_ranks, cfg["n_ff_sh"] // n_ranks
+    for t in range(3):
+        whole = api.MoeLayer(lc, experts, shared).forward(ld[t:t + 1], xd[t:t + 1])[2].cpu().numpy()[0]
+        partial = [api.MoeLayer(lc, experts, shared, expert_range=(r * per, (r + 1) * per),
+                                shared_range=(r * wid, (r + 1) * wid)).forward(ld[t:t + 1], xd[t:t + 1])[2].cpu().numpy()[0]
+                   for r in range(n_ranks)]
+        summed = oracle.allreduce_in_order(np.stack(partial))
+        assert H.rel_err(summed, whole) <= 1e-5
+        assert np.abs(partial[-1]).max() > 0            # every rank carries a share
+    sliced = api.MoeLayer(lc, experts, shared, shared_range=(0, wid))
+    with pytest.raises(api.MayaError):
+        sliced.forward(ld[:2], xd[:2])                   # two tokens: the staged kernels do not slice
+    with pytest.raises(api.MayaError):
+        api.MoeLayer(lc, experts, shared, shared_range=(16, wid)).forward(ld[:1], xd[:1])     # not a multiple of 32
+
+
 @pytest.mark.parametrize("t,shared", [(H.Q4_K, False), (H.Q8_0, False), (H.IQ2_S, True), (H.IQ3_S, True), (H.IQ3_S, False)])
 def test_fused_token_kernel_equals_staged_kernels_bitwise(T, api, oracle, t, shared):
     """One token through the single fused kernel and through the separate launches: the same bits, and the oracle's
