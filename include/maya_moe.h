@@ -209,7 +209,8 @@ MAYA_API int maya_moe_combine_add(const float* out, int base, int lo, int hi, co
                                   int n_embd, float* ffn, void* stream);
 
 /* Prompt-path grouped GEMM on the tensor cores --------------------------------------------------------- */
-/* mmq::supported (include/strata/prefill/moe_mmq.hpp:16): types the grouped GEMM takes (Q8_0 and Q4_K). */
+/* mmq::supported (include/strata/prefill/moe_mmq.hpp:16) / gemm_iq_f16_grouped's iq_supported (iq_kernels.hpp:38-61):
+ * types the grouped GEMM takes: Q8_0, Q4_K, IQ2_S, IQ3_S (the i-quants need w_cols % 2048 == 0: 16-byte aligned rows). */
 MAYA_API int maya_mmq_supported(int type);
 /* mmq::q8_bytes (moe_mmq.hpp:20): bytes of `rows` quantized activation rows of `cols` values.  The rows are stored as
  * f16: each value is d * q of the row's q8_1 image (d = f16(amax / 127) per 32 values, q = round(x / d)), the

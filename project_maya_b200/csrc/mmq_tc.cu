@@ -33,6 +33,7 @@
 #include <cuda_fp16.h>
 
 #include <cstdio>
+#include <cstring>
 
 #include "maya_internal.cuh"
 #include "maya_tcgen05.cuh"
@@ -51,17 +52,33 @@ constexpr int kBBox = 128 * 64 * 2;     // 16 KB: 128 activation rows x 64 K-val
 constexpr int kBStage = kBBox + 32 * 64 * 2;   // + the 32-row box of a block with more than 128 rows: 20 KB
 constexpr uint32_t kAccCols = TN;       // tensor-memory columns: accumulator 0 at 0, accumulator 1 at 160,
 constexpr uint32_t kACol = 2 * TN;      // the A operand's 3 stages from 320: per stage 32 columns for each accumulator
-constexpr int kMaxUnits = 12;
+constexpr int kMaxUnits = 16;
 constexpr int kDone = 16;               // ring of "pair of K steps consumed" barriers (one tcgen05.commit per pair: a commit
                                         // costs the tensor pipe about as much as a product)
-template<int T> constexpr int kRawRow = T == MAYA_Q4_K ? 144 : 272;         // bytes of 256 K-values of one row
+// Raw weight units.  Q8_0 / Q4_K: a row's 256 K-values are 272 / 144 bytes, a multiple of 16, so a unit is one tiled TMA
+// box (64 rows).  IQ2_S / IQ3_S blocks are 82 / 110 bytes: a unit is 64 per-row bulk copies of the 16-byte aligned
+// window around the row's block (96 / 128 bytes), rows 112 / 144 bytes apart in shared memory (an odd number of
+// 16-byte words: a warp's 16-byte reads of 32 rows fall in different banks).
+template<int T> constexpr bool kIq = T == MAYA_IQ2_S || T == MAYA_IQ3_S;
+template<int T> constexpr int kBlkBytes = T == MAYA_IQ2_S ? 82 : T == MAYA_IQ3_S ? 110 : 0;
+template<int T> constexpr int kWin = T == MAYA_IQ2_S ? 96 : 128;
+template<int T> constexpr int kRawRow = T == MAYA_Q4_K ? 144 : T == MAYA_Q8_0 ? 272 : T == MAYA_IQ2_S ? 112 : 144;
 template<int T> constexpr int kUnitBytes = kUnitRows * kRawRow<T>;
-template<int T> constexpr int kUnits = T == MAYA_Q4_K ? 10 : 8;             // raw units in flight
+template<int T> constexpr int kUnits = T == MAYA_Q4_K ? 10 : T == MAYA_Q8_0 ? 8 : T == MAYA_IQ2_S ? 14 : 12;   // raw units in flight
 template<int T> constexpr int kBStages = T == MAYA_Q4_K ? 6 : 4;            // activation tiles (64 K-values) in flight
 template<int T> constexpr int kBRing = kBStages<T> * kBStage;
-template<int T> constexpr size_t kSmemBytes = (size_t) kBRing<T> + (size_t) kUnits<T> * kUnitBytes<T>;
+// i-quants: the codebook as f16 (IQ2_S 1024 x 8 values, IQ3_S 512 x 4 values) and the 256 sign patterns as f16 sign masks
+template<int T> constexpr int kGridBytes = T == MAYA_IQ2_S ? 1024 * 16 : T == MAYA_IQ3_S ? 512 * 8 : 0;
+template<int T> constexpr int kTabBytes = kIq<T> ? kGridBytes<T> + 256 * 16 : 0;
+template<int T> constexpr int kTabOff = kBRing<T> + kUnits<T> * kUnitBytes<T>;
+template<int T> constexpr size_t kSmemBytes = (size_t) kTabOff<T> + kTabBytes<T>;
+static_assert(kUnits<MAYA_Q4_K> <= kMaxUnits && kUnits<MAYA_Q8_0> <= kMaxUnits && kUnits<MAYA_IQ2_S> <= kMaxUnits &&
+              kUnits<MAYA_IQ3_S> <= kMaxUnits, "one mbarrier pair per raw unit");
 
 struct MmqArgs {
+    const uint8_t* w;            // the matrices (the i-quant path copies row windows itself; the others go through tm_w)
+    size_t expert_bytes;
+    int mat_rows;                // rows of one matrix (2 n_ff for the fused form)
     int w_rows, w_cols;          // rows of one output (n_ff for the fused form: gate rows, then up rows), K
     int n;                       // matrices of this product
     const int* expert_map;       // optional: matrix i owns the rows of bounds entry expert_map[i]
@@ -140,6 +157,76 @@ __device__ __forceinline__ void q80_stage(const uint8_t* rrow, uint32_t* r) {
         x ^= 0x80808080u;                                                  // q + 128 as unsigned bytes
         r[2 * i] = h2_bits(__hmul2(__hsub2(bytes01_plus1024(x), k1152), d2));
         r[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes23_plus1024(x), k1152), d2));
+    }
+}
+
+// ---- i-quants.  `w` = the row's window as 32-bit words; the block starts OFF bytes into it (OFF is even and the same
+// for all rows of a K block: every field position is a compile-time constant).
+template<int BYTE> __device__ __forceinline__ uint32_t win_u32(const uint32_t* w) {
+    constexpr int i = BYTE / 4, r = BYTE % 4;
+    if constexpr (r == 0) return w[i];
+    else if constexpr (r == 1) return __byte_perm(w[i], w[i + 1], 0x4321);
+    else if constexpr (r == 2) return __byte_perm(w[i], w[i + 1], 0x5432);
+    else return __byte_perm(w[i], w[i + 1], 0x6543);
+}
+template<int BYTE> __device__ __forceinline__ uint32_t win_u8(const uint32_t* w) { return (w[BYTE / 4] >> (8 * (BYTE % 4))) & 0xFF; }
+template<int BYTE> __device__ __forceinline__ float win_f16(const uint32_t* w) {
+    return __half2float(__ushort_as_half((unsigned short) ((w[BYTE / 4] >> (8 * (BYTE % 4))) & 0xFFFF)));
+}
+// IQ2_S (ggml dequantize_row_iq2_s): sub-block ib32 of 32 values: y = d (0.5 + ls) 0.25 * grid[qs | qh bits] * sign;
+// here dl = f16(d (2 ls + 1) / 8) and w = dl * grid (one more f16 rounding), the sign XOR-ed into dl.
+template<int OFF, int PP>
+__device__ __forceinline__ void iq2s_pair(const uint32_t* w, const uint4* grid, const uint4* sgn, uint32_t* o) {
+    const float d = win_f16<OFF>(w);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int ib = 2 * PP + h;
+        const uint32_t qs4 = h ? win_u32<OFF + 2 + 4 * (2 * PP + 1)>(w) : win_u32<OFF + 2 + 4 * (2 * PP)>(w);
+        const uint32_t sg4 = h ? win_u32<OFF + 34 + 4 * (2 * PP + 1)>(w) : win_u32<OFF + 34 + 4 * (2 * PP)>(w);
+        const uint32_t qh = h ? win_u8<OFF + 66 + 2 * PP + 1>(w) : win_u8<OFF + 66 + 2 * PP>(w);
+        const uint32_t sc = h ? win_u8<OFF + 74 + 2 * PP + 1>(w) : win_u8<OFF + 74 + 2 * PP>(w);
+        (void) ib;
+        const uint32_t dl0 = h2_bits(__float2half2_rn(d * (float) (2 * (sc & 15) + 1) * 0.125f));
+        const uint32_t dl1 = h2_bits(__float2half2_rn(d * (float) (2 * (sc >> 4) + 1) * 0.125f));
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const uint32_t idx = ((qs4 >> (8 * l)) & 0xFF) | ((qh << (8 - 2 * l)) & 0x300);
+            const uint4 G = grid[idx], M = sgn[(sg4 >> (8 * l)) & 0xFF];
+            const uint32_t dl = l < 2 ? dl0 : dl1;
+            uint32_t* r = o + 16 * h + 4 * l;
+            r[0] = h2_bits(__hmul2(bits_h2(G.x), bits_h2(dl ^ M.x)));
+            r[1] = h2_bits(__hmul2(bits_h2(G.y), bits_h2(dl ^ M.y)));
+            r[2] = h2_bits(__hmul2(bits_h2(G.z), bits_h2(dl ^ M.z)));
+            r[3] = h2_bits(__hmul2(bits_h2(G.w), bits_h2(dl ^ M.w)));
+        }
+    }
+}
+// IQ3_S (ggml dequantize_row_iq3_s): y = d (1 + 2 scale) * grid[qs | qh bit] * sign; 4 values per codebook entry.
+template<int OFF, int PP>
+__device__ __forceinline__ void iq3s_pair(const uint32_t* w, const uint2* grid, const uint4* sgn, uint32_t* o) {
+    const float d = win_f16<OFF>(w);
+    const uint32_t scb = win_u8<OFF + 106 + PP>(w);                    // scales[ib32 / 2]: low nibble ib32 even, high odd
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t q0 = h ? win_u32<OFF + 2 + 8 * (2 * PP + 1)>(w) : win_u32<OFF + 2 + 8 * (2 * PP)>(w);
+        const uint32_t q1 = h ? win_u32<OFF + 6 + 8 * (2 * PP + 1)>(w) : win_u32<OFF + 6 + 8 * (2 * PP)>(w);
+        const uint32_t qh = h ? win_u8<OFF + 66 + 2 * PP + 1>(w) : win_u8<OFF + 66 + 2 * PP>(w);
+        const uint32_t sg4 = h ? win_u32<OFF + 74 + 4 * (2 * PP + 1)>(w) : win_u32<OFF + 74 + 4 * (2 * PP)>(w);
+        const uint32_t nib = h ? (scb >> 4) : (scb & 15);
+        const uint32_t db = h2_bits(__float2half2_rn(d * (float) (1 + 2 * nib)));
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const uint32_t q = l < 2 ? q0 : q1;
+            const uint32_t i1 = ((q >> (16 * (l & 1))) & 0xFF) | ((qh << (8 - 2 * l)) & 256);
+            const uint32_t i2 = ((q >> (16 * (l & 1) + 8)) & 0xFF) | ((qh << (7 - 2 * l)) & 256);
+            const uint2 G1 = grid[i1], G2 = grid[i2];
+            const uint4 M = sgn[(sg4 >> (8 * l)) & 0xFF];
+            uint32_t* r = o + 16 * h + 4 * l;
+            r[0] = h2_bits(__hmul2(bits_h2(G1.x), bits_h2(db ^ M.x)));
+            r[1] = h2_bits(__hmul2(bits_h2(G1.y), bits_h2(db ^ M.y)));
+            r[2] = h2_bits(__hmul2(bits_h2(G2.x), bits_h2(db ^ M.z)));
+            r[3] = h2_bits(__hmul2(bits_h2(G2.y), bits_h2(db ^ M.w)));
+        }
     }
 }
 
@@ -232,6 +319,37 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
         mbar_init(&P.final, 2);
         P.fail = 0;
     }
+    if constexpr (kIq<T>) {                         // the codebook as f16 and the sign masks, once per block
+        uint4* sgn = (uint4*) (smem + kTabOff<T> + kGridBytes<T>);
+        for (int i = tid; i < 256; i += kMmqThreads) {
+            uint4 m;
+            const uint32_t b = (uint32_t) i;       // bit j of the pattern: value j is negative; two values per f16 pair
+            m.x = ((b & 1u) << 15) | ((b & 2u) << 30);
+            m.y = ((b & 4u) << 13) | ((b & 8u) << 28);
+            m.z = ((b & 16u) << 11) | ((b & 32u) << 26);
+            m.w = ((b & 64u) << 9) | ((b & 128u) << 24);
+            sgn[i] = m;
+        }
+        const __half2 k1024 = __float2half2_rn(1024.0f);
+        if constexpr (T == MAYA_IQ2_S) {
+            uint4* grid = (uint4*) (smem + kTabOff<T>);
+            for (int i = tid; i < 1024; i += kMmqThreads) {
+                const uint2 g = ((const uint2*) g_iq2s_grid)[i];
+                uint4 v;
+                v.x = h2_bits(__hsub2(bytes01_plus1024(g.x), k1024)); v.y = h2_bits(__hsub2(bytes23_plus1024(g.x), k1024));
+                v.z = h2_bits(__hsub2(bytes01_plus1024(g.y), k1024)); v.w = h2_bits(__hsub2(bytes23_plus1024(g.y), k1024));
+                grid[i] = v;
+            }
+        } else {
+            uint2* grid = (uint2*) (smem + kTabOff<T>);
+            for (int i = tid; i < 512; i += kMmqThreads) {
+                const uint32_t g = g_iq3s_grid[i];
+                uint2 v;
+                v.x = h2_bits(__hsub2(bytes01_plus1024(g), k1024)); v.y = h2_bits(__hsub2(bytes23_plus1024(g), k1024));
+                grid[i] = v;
+            }
+        }
+    }
     mbar_fence_init();
     if (warp == 0) tmem_alloc(&P.tmem, 512);
     tc_fence_before();
@@ -281,7 +399,42 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                 return true;
             };
             uint32_t o[32];
-            if constexpr (T == MAYA_Q4_K) {
+            if constexpr (kIq<T>) {
+                constexpr int NWD = kWin<T> / 4;
+                uint32_t wv[NWD];
+#pragma unroll
+                for (int i = 0; i < NWD / 4; ++i) {
+                    const uint4 v = *(const uint4*) (rrow + 16 * i);
+                    wv[4 * i] = v.x; wv[4 * i + 1] = v.y; wv[4 * i + 2] = v.z; wv[4 * i + 3] = v.w;
+                }
+                const uint4* sgn = (const uint4*) (smem + kTabOff<T> + kGridBytes<T>);
+                // the block's offset in its window, (kb * block bytes) % 16, has period 8 in kb: 8 unrolled variants
+#define MAYA_IQ_PAIRS(OFF)                                                                                          \
+    if constexpr (T == MAYA_IQ2_S) {                                                                               \
+        const uint4* grid = (const uint4*) (smem + kTabOff<T>);                                                    \
+        if (team == 0) { iq2s_pair<OFF, 0>(wv, grid, sgn, o); ok = put(kb * 4 + 0, o);                             \
+                         if (ok) { iq2s_pair<OFF, 2>(wv, grid, sgn, o); ok = put(kb * 4 + 2, o); } }              \
+        else { iq2s_pair<OFF, 1>(wv, grid, sgn, o); ok = put(kb * 4 + 1, o);                                       \
+               if (ok) { iq2s_pair<OFF, 3>(wv, grid, sgn, o); ok = put(kb * 4 + 3, o); } }                        \
+    } else {                                                                                                       \
+        const uint2* grid = (const uint2*) (smem + kTabOff<T>);                                                    \
+        if (team == 0) { iq3s_pair<OFF, 0>(wv, grid, sgn, o); ok = put(kb * 4 + 0, o);                             \
+                         if (ok) { iq3s_pair<OFF, 2>(wv, grid, sgn, o); ok = put(kb * 4 + 2, o); } }              \
+        else { iq3s_pair<OFF, 1>(wv, grid, sgn, o); ok = put(kb * 4 + 1, o);                                       \
+               if (ok) { iq3s_pair<OFF, 3>(wv, grid, sgn, o); ok = put(kb * 4 + 3, o); } }                        \
+    }
+                switch ((kb * kBlkBytes<T>) & 15) {
+                    case 0: MAYA_IQ_PAIRS(0) break;
+                    case 2: MAYA_IQ_PAIRS(2) break;
+                    case 4: MAYA_IQ_PAIRS(4) break;
+                    case 6: MAYA_IQ_PAIRS(6) break;
+                    case 8: MAYA_IQ_PAIRS(8) break;
+                    case 10: MAYA_IQ_PAIRS(10) break;
+                    case 12: MAYA_IQ_PAIRS(12) break;
+                    default: MAYA_IQ_PAIRS(14) break;
+                }
+#undef MAYA_IQ_PAIRS
+            } else if constexpr (T == MAYA_Q4_K) {
                 Q4Scales S;
                 q4k_scales(*(const uint4*) rrow, S);
 #pragma unroll
@@ -391,6 +544,36 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             atomicAdd(A.probe + 7, (unsigned long long) (clock64() - t_epi));
             atomicAdd(A.probe + 8, 1ull);
             atomicAdd(A.probe + 9, (unsigned long long) nkt);
+        }
+    } else if (warp == kDqWarps && kIq<T>) {
+        // ------------------------------------------------------------ raw weight units of the i-quants: the whole warp,
+        //                                                              a lane copies the windows of rows lane, lane + 32
+        if constexpr (kIq<T>) {
+            const size_t rbw = row_bytes(T, A.w_cols);
+            const uint8_t* wexp = A.w + (size_t) found_e * A.expert_bytes;
+            int issued = 0;
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const size_t koff = ((size_t) kb * kBlkBytes<T>) & ~(size_t) 15;
+                const uint32_t wbytes = (uint32_t) min((size_t) kWin<T>, rbw - koff);     // never past the end of the row
+                for (int sl = 0; sl < 4; ++sl) {
+                    const int u = kb * 4 + sl, slot = u % NU;
+                    if (u >= NU && !wait_or_fail(P, &P.raw_empty[slot], ((u / NU) - 1) & 1)) { ok = false; break; }
+                    const int wrow = GLU ? (sl < 2 ? m0 + 64 * sl : A.w_rows + m0 + 64 * (sl - 2)) : m0 + 64 * sl;
+                    const int valid = max(0, min(kUnitRows, A.mat_rows - wrow));     // rows of the unit that exist
+                    if (lane == 0) {
+                        if (valid > 0) mbar_expect_tx(&P.raw_full[slot], (uint32_t) valid * wbytes);
+                        else mbar_arrive(&P.raw_full[slot]);
+                    }
+                    __syncwarp();
+                    uint8_t* ubase = raw + (size_t) slot * kUnitBytes<T>;
+                    for (int rr = lane; rr < valid; rr += 32)
+                        bulk_load(ubase + rr * kRawRow<T>, wexp + (size_t) (wrow + rr) * rbw + koff, wbytes, &P.raw_full[slot]);
+                    issued = u + 1;
+                }
+            }
+            if (!ok)                                             // let the copies in flight land before the block ends
+                for (int u = max(0, issued - NU); u < issued; ++u) wait_or_fail(P, &P.raw_full[u % NU], (u / NU) & 1);
         }
     } else if (warp == kDqWarps) {
         // ------------------------------------------------------------ raw weight units (one lane)
@@ -564,7 +747,8 @@ int launch_mmq(const maya_mmq_product* p, const MmqArgs& A, cudaStream_t s) {
     const int64_t mat_rows = p->w_rows, K = p->w_cols;
     const size_t rbw = row_bytes(T, K);
     CUtensorMap tw, tx, tx32;
-    {   // weights as 32-bit words: (word in row, row in matrix, matrix); a box = 256 K-values of 64 rows
+    std::memset(&tw, 0, sizeof(tw));
+    if constexpr (!kIq<T>) {   // weights as 32-bit words: (word in row, row in matrix, matrix); a box = 256 K-values of 64 rows
         const cuuint64_t dim[3] = {(cuuint64_t) (rbw / 4), (cuuint64_t) mat_rows, (cuuint64_t) p->n};
         const cuuint64_t st[2] = {(cuuint64_t) rbw, (cuuint64_t) p->expert_bytes};
         const cuuint32_t box[3] = {(cuuint32_t) (kRawRow<T> / 4), kUnitRows, 1};
@@ -593,7 +777,8 @@ int launch_mmq(const maya_mmq_product* p, const MmqArgs& A, cudaStream_t s) {
 int run_product(const maya_mmq_product* p, bool glu, float limit, cudaStream_t s) {
     if (!p || !p->w || !p->xq || !p->bounds) return refuse(MAYA_ERR_ARG);
     if (!p->dst && !(glu && p->xq_out)) return refuse(MAYA_ERR_ARG);
-    if (p->type != MAYA_Q4_K && p->type != MAYA_Q8_0) return refuse(MAYA_ERR_TYPE);
+    if (!maya_mmq_supported(p->type)) return refuse(MAYA_ERR_TYPE);
+    if ((p->type == MAYA_IQ2_S || p->type == MAYA_IQ3_S) && p->w_cols % 2048) return refuse(MAYA_ERR_ARG);   // 16-byte aligned rows
     if (p->n <= 0 || p->total_rows <= 0) return MAYA_OK;
     const int64_t out_rows = glu ? p->w_rows / 2 : p->w_rows;
     if (p->w_cols <= 0 || p->w_cols % 256 || out_rows <= 0 || out_rows % 128 || (glu && p->w_rows % 2)) return refuse(MAYA_ERR_ARG);
@@ -605,11 +790,16 @@ int run_product(const maya_mmq_product* p, bool glu, float limit, cudaStream_t s
     if (!aligned16(p->w) || !aligned16(p->xq) || (p->xq_out && !aligned16(p->xq_out))) return refuse(MAYA_ERR_ARG);
     if (p->dst && (!aligned16(p->dst) || p->ld_dst % 4)) return refuse(MAYA_ERR_ARG);      // rows leave as 16-byte aligned bulk copies
     MmqArgs A{};
+    A.w = (const uint8_t*) p->w; A.expert_bytes = p->expert_bytes; A.mat_rows = (int) p->w_rows;
     A.w_rows = (int) out_rows; A.w_cols = (int) p->w_cols; A.n = p->n; A.expert_map = p->expert_map; A.bounds = p->bounds;
     A.ids = p->ids; A.dst = p->dst; A.ld_dst = p->ld_dst; A.xq_out = glu ? (__half*) p->xq_out : nullptr; A.limit = limit;
     A.error = p->error; A.probe = g_probe;
-    if (p->type == MAYA_Q4_K) return glu ? launch_mmq<MAYA_Q4_K, true>(p, A, s) : launch_mmq<MAYA_Q4_K, false>(p, A, s);
-    return glu ? launch_mmq<MAYA_Q8_0, true>(p, A, s) : launch_mmq<MAYA_Q8_0, false>(p, A, s);
+    switch (p->type) {
+        case MAYA_Q4_K: return glu ? launch_mmq<MAYA_Q4_K, true>(p, A, s) : launch_mmq<MAYA_Q4_K, false>(p, A, s);
+        case MAYA_Q8_0: return glu ? launch_mmq<MAYA_Q8_0, true>(p, A, s) : launch_mmq<MAYA_Q8_0, false>(p, A, s);
+        case MAYA_IQ2_S: return glu ? launch_mmq<MAYA_IQ2_S, true>(p, A, s) : launch_mmq<MAYA_IQ2_S, false>(p, A, s);
+        default: return glu ? launch_mmq<MAYA_IQ3_S, true>(p, A, s) : launch_mmq<MAYA_IQ3_S, false>(p, A, s);
+    }
 }
 
 }  // namespace
@@ -617,7 +807,9 @@ int run_product(const maya_mmq_product* p, bool glu, float limit, cudaStream_t s
 
 using namespace maya;
 
-extern "C" int maya_mmq_supported(int type) { return type == MAYA_Q4_K || type == MAYA_Q8_0; }
+extern "C" int maya_mmq_supported(int type) {
+    return type == MAYA_Q4_K || type == MAYA_Q8_0 || type == MAYA_IQ2_S || type == MAYA_IQ3_S;
+}
 extern "C" size_t maya_mmq_q8_bytes(int64_t rows, int64_t cols) {
     if (rows <= 0 || cols <= 0 || cols % 32) return 0;
     return (size_t) rows * (size_t) cols * sizeof(__half);

@@ -71,18 +71,49 @@ def q8_1_image(oracle, x_rows):
     return (d * q).astype(np.float16).reshape(rows, cols)
 
 
+def iq_f16_weights(oracle, t, raw, rows, cols):
+    """IQ2_S / IQ3_S weights as the kernel makes them: the sub-block scale rounded to f16 (IQ2_S d (2 ls + 1) / 8, IQ3_S
+    d (1 + 2 s)), times the codebook magnitude, rounded to f16 once more, with the sign.  The magnitudes and signs are
+    recovered from the oracle's exact dequantization (magnitude = |y| / exact scale, a small integer)."""
+    bb = 82 if t == H.IQ2_S else 110
+    blk = np.ascontiguousarray(raw).reshape(rows, cols // 256, bb)
+    d = blk[:, :, 0:2].copy().view(np.float16).astype(np.float32)[:, :, 0]                    # [rows, nb]
+    y = oracle.dequantize(t, raw, rows * cols).reshape(rows, cols // 256, 8, 32).astype(np.float64)
+    if t == H.IQ2_S:
+        sc = blk[:, :, 74:82].astype(np.int32)                                                # [rows, nb, 8]
+        ls = np.stack([sc & 15, sc >> 4], axis=-1)                                            # per half sub-block of 16
+        mult = (2 * ls + 1).astype(np.float32) * np.float32(0.125)                            # [rows, nb, 8, 2]
+        exact = (d[:, :, None, None] * mult).astype(np.float64)
+        sc16 = (d[:, :, None, None] * mult).astype(np.float16).astype(np.float64)
+        exact = np.repeat(exact, 16, axis=-1)
+        sc16 = np.repeat(sc16, 16, axis=-1)                                                   # [rows, nb, 8, 32]
+    else:
+        sb = blk[:, :, 106:110].astype(np.int32)                                              # [rows, nb, 4]
+        nib = np.stack([sb & 15, sb >> 4], axis=-1).reshape(rows, cols // 256, 8)
+        mult = (1 + 2 * nib).astype(np.float32)
+        exact = np.repeat((d[:, :, None] * mult).astype(np.float64)[..., None], 32, axis=-1)
+        sc16 = np.repeat((d[:, :, None] * mult).astype(np.float16).astype(np.float64)[..., None], 32, axis=-1)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        mag = np.where(exact != 0, np.rint(np.abs(y) / exact), 0.0)
+    w = (sc16 * mag).astype(np.float16).astype(np.float64) * np.where(y < 0, -1.0, 1.0)
+    return w.reshape(rows, cols)
+
+
 def f16_weights(oracle, t, w_host, rows, cols):
     if t == H.Q4_K:
         return q4k_f16_weights(w_host, rows, cols)
+    if t in (H.IQ2_S, H.IQ3_S):
+        return iq_f16_weights(oracle, t, w_host, rows, cols)
     return oracle.dequantize(t, w_host, rows * cols).reshape(rows, cols).astype(np.float16).astype(np.float64)
 
 
 COUNTS = [0, 3, 130, 128, 1, 0, 257]
 
 
-@pytest.mark.parametrize("t", [H.Q4_K, H.Q8_0])
+@pytest.mark.parametrize("t", [H.Q4_K, H.Q8_0, H.IQ2_S, H.IQ3_S])
 def test_grouped_product_ragged_groups(T, api, oracle, t):
-    n, rows, cols, n_tok = len(COUNTS), 256, 512, 40
+    n, rows, n_tok = len(COUNTS), 256, 40
+    cols = 2048 if t in (H.IQ2_S, H.IQ3_S) else 512        # the i-quants need rows that start on 16 bytes
     w = synth_matrices(T, api, t, n, rows, cols, 11)
     rng = H.rng_for("mmq", t)
     x = (rng.standard_normal((n_tok, cols)) * 1.5).astype(np.float32)
@@ -121,10 +152,11 @@ def test_grouped_product_ragged_groups(T, api, oracle, t):
     assert np.all(got[~hit] == 7.0), "wrote a row no group owns"
 
 
-@pytest.mark.parametrize("t", [H.Q4_K, H.Q8_0])
+@pytest.mark.parametrize("t", [H.Q4_K, H.Q8_0, H.IQ2_S, H.IQ3_S])
 @pytest.mark.parametrize("limit", [H.INF, 0.75])
 def test_fused_glu_equals_product_then_swiglu_bitwise(T, api, t, limit):
-    n, n_ff, cols = 4, 256, 768
+    n, n_ff = 4, 256
+    cols = 2048 if t in (H.IQ2_S, H.IQ3_S) else 768
     counts = [5, 0, 200, 64]
     w = synth_matrices(T, api, t, n, 2 * n_ff, cols, 23)
     x = (H.rng_for("glu", t).standard_normal((sum(counts), cols)) * 2.0).astype(np.float32)
@@ -183,7 +215,7 @@ def test_refusals(T, api):
     with pytest.raises(api.MayaError):
         api.mmq_run_glu(ok(w_rows=128), H.INF)            # n_ff = 64 is not a multiple of 128
     assert api.mmq_q8_bytes(3, 100) == 0 and api.mmq_q8_bytes(3, 256) == 3 * 256 * 2
-    assert api.mmq_supported(H.Q8_0) and api.mmq_supported(H.Q4_K) and not api.mmq_supported(H.IQ3_S)
+    assert all(api.mmq_supported(x) for x in (H.Q8_0, H.Q4_K, H.IQ2_S, H.IQ3_S)) and not api.mmq_supported(2)
 
 
 # ------------------------------------------------------------------------------------------------ the whole layer
@@ -198,9 +230,10 @@ def oracle_prefill_token(oracle, cfg, experts, ids, w, x):
     return out
 
 
-@pytest.mark.parametrize("t,n_tok,E", [(H.Q4_K, 300, 16), (H.Q8_0, 77, 8)])
+@pytest.mark.parametrize("t,n_tok,E", [(H.Q4_K, 300, 16), (H.Q8_0, 77, 8), (H.IQ2_S, 200, 8), (H.IQ3_S, 90, 4)])
 def test_prefill_layer_small(T, api, oracle, t, n_tok, E):
-    cfg = dict(n_embd=512, n_ff=256, n_expert=E, k=4, gu_type=t, d_type=t)
+    iq = t in (H.IQ2_S, H.IQ3_S)
+    cfg = dict(n_embd=2048 if iq else 512, n_ff=2048 if iq else 256, n_expert=E, k=4, gu_type=t, d_type=t)
     lc = api.MoeLayerConfig(cfg["n_embd"], cfg["n_ff"], E, cfg["k"], t, t)
     experts = T.empty((E, lc.blob_bytes), dtype=T.uint8, device="cuda")
     gu_bytes = 2 * cfg["n_ff"] * H.row_bytes(t, cfg["n_embd"])
