@@ -9,6 +9,8 @@ and the reference's data directory.  Writes:
   router_reference_cases.npz  the four input distributions of the reference's router test (its generator and seed;
                               first 16 of the 64 tokens, 512 experts, k = 10) with the ids / weights its own host
                               reference gives
+  glm5_synth_moe_layer1.npz   layer 1 of data/glm5-synth.gguf (expert, shared-expert and router tensors, F32) with llama.cpp's
+                              captured inputs and outputs of its MoE block for 8 tokens (data/glm5-synth-dumps/ffn_*-1.f32)
   glm5_synth_router.npz       the sigmoid router's golden vectors captured from llama.cpp that the reference ships
                               (data/glm5-synth-dumps/ffn_moe_{logits,topk,weights}-{1..5}.f32) with the selection bias
                               and weight scale read from data/glm5-synth.gguf
@@ -75,6 +77,34 @@ def glm5_router() -> None:
                         ids=np.stack(topk), weights=np.stack(weights), w_scale=np.float32(scale), layers=np.array(layers))
 
 
+def glm5_moe_layer(layer: int = 1) -> None:
+    """Layer `layer` of data/glm5-synth.gguf (F32 tensors: 12 experts of 128 x 64, top-3 sigmoid routing, one shared
+    expert) read through the package's own loader, with llama.cpp's captured activations of that layer for 8 tokens:
+    the normed hidden state that enters the MoE block, the routing, the routed output, the shared expert's output."""
+    import gguf
+    from project_maya_b200 import gguf_loader
+    path = REFERENCE / "data" / "glm5-synth.gguf"
+    L = gguf_loader.read_moe_layer(path, layer)
+    rd = gguf.GGUFReader(str(path))
+    meta = {}
+    for name, f in rd.fields.items():
+        for key in ("expert_weights_scale", "expert_used_count", "swiglu_clamp_exp", "swiglu_clamp_shexp"):
+            if name.endswith(key):
+                meta[key] = float(np.asarray(f.parts[f.data[min(layer, len(f.data) - 1)]]).reshape(-1)[0])
+    dumps = REFERENCE / "data" / "glm5-synth-dumps"
+    d = lambda n, dt=np.float32: np.fromfile(dumps / f"{n}-{layer}.f32", dtype=dt)
+    n_tok = d("ffn_norm").size // L.n_embd
+    k = int(meta["expert_used_count"])
+    np.savez_compressed(
+        HERE / "glm5_synth_moe_layer1.npz", layer=np.int32(layer), gate=L.gate, up=L.up, down=L.down, router=L.router,
+        router_bias=L.router_bias, sh_gate=L.sh_gate, sh_up=L.sh_up, sh_down=L.sh_down,
+        x=d("ffn_norm").reshape(n_tok, L.n_embd), logits=d("ffn_moe_logits").reshape(n_tok, L.n_expert),
+        ids=d("ffn_moe_topk", np.int32).reshape(n_tok, k), weights=d("ffn_moe_weights").reshape(n_tok, k),
+        moe_out=d("ffn_moe_out").reshape(n_tok, L.n_embd), shexp=d("ffn_shexp").reshape(n_tok, L.n_embd),
+        out=d("ffn_out").reshape(n_tok, L.n_embd), w_scale=np.float32(meta["expert_weights_scale"]),
+        clamp=np.float32(meta["swiglu_clamp_exp"]), clamp_sh=np.float32(meta["swiglu_clamp_shexp"]))
+
+
 def c1_experts():
     """The C1 layer's synthetic experts: N(0, 0.02) weights quantized to Q4_K by the library's host quantizer."""
     from project_maya_b200 import api
@@ -118,6 +148,7 @@ def main() -> None:
     ref, orc = Ref(), Oracle()
     router_cases(ref)
     glm5_router()
+    glm5_moe_layer(1)
     c1_reference(ref, orc)
     for p in sorted(HERE.glob("*.npz")):
         print(p.name, p.stat().st_size)
