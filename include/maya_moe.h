@@ -203,6 +203,11 @@ MAYA_API int maya_swiglu_rows(const float* gu, float* h, int rows, int n_ff, flo
 /* glmb::moe_combine (glm_batch.hpp:153): ffn[t] = sum_j w[t][j] * out[pos[t * k + j]] + sh[t] (sh NULL: none). */
 MAYA_API int maya_moe_combine_rows(const float* out, const int* pos, const float* w, const float* sh, int T, int k,
                                    int n_embd, float* ffn, void* stream);
+/* The same for an expert-parallel rank (no counterpart: the reference's prompt path is single-GPU): only the routes
+ * whose expert id (ids [T * k]) lies in [e_lo, e_hi) are summed - the other sorted rows were never computed on this
+ * rank - so that the ranks' ffn add up to maya_moe_combine_rows' (sh: on one rank only). */
+MAYA_API int maya_moe_combine_rows_local(const float* out, const int* pos, const float* w, const int* ids, int e_lo,
+                                         int e_hi, const float* sh, int T, int k, int n_embd, float* ffn, void* stream);
 /* glmb::moe_combine_add (glm_batch.hpp:150): ffn[t] += sum over the routes of t whose sorted row is in [lo, hi) of
  * w * out[row - base]. */
 MAYA_API int maya_moe_combine_add(const float* out, int base, int lo, int hi, const int* pos, const float* w, int T, int k,

@@ -351,15 +351,32 @@ class MoePrefill:
     expert_scatter, mmq::quantize, Context::run_glu, mmq::quantize, Context::run, moe_combine), except that the bases
     are scanned on the device.  Every buffer is allocated once, here.
 
+    expert_range = (lo, hi) makes this an expert-parallel rank: only experts lo..hi-1 are multiplied and combined, and
+    the returned ffn is this rank's partial sum (the ranks' results add up; pass `shared` on one rank only).
+
     `experts` is uint8 [n_expert, blob_bytes] of one type (cfg.gu_type == cfg.d_type is not required), or None with
     `pools` = [(ggml_type, blobs uint8 [n_i, blob_bytes of that type], expert ids of the n_i blobs), ...] for a layer whose
     experts are stored in different types: one product per pool, each matrix finding its rows through the pool's
     expert map (the reference's staged groups, moe_mmq.hpp:41-53 with bounds per group)."""
 
-    def __init__(self, cfg: MoeLayerConfig, experts, shared=None, max_tokens: int = 4096, pools=None):
+    def __init__(self, cfg: MoeLayerConfig, experts, shared=None, max_tokens: int = 4096, pools=None, expert_range=None):
         H, FF = cfg.n_embd, cfg.n_ff
+        self.expert_range = expert_range         # (lo, hi): an expert-parallel rank's experts; ffn is then its partial sum
         if pools is None:
-            pools = [((cfg.gu_type, cfg.d_type), experts, None)]
+            if expert_range is None:
+                pools = [((cfg.gu_type, cfg.d_type), experts, None)]
+            else:                                # this rank's blobs only (a view), found through an expert map
+                lo, hi = expert_range
+                pools = [((cfg.gu_type, cfg.d_type), experts[lo:hi], list(range(lo, hi)))] if hi > lo else []
+        elif expert_range is not None:
+            lo, hi = expert_range
+            kept = []
+            for types, blobs, expert_ids in pools:
+                sel = [i for i, e in enumerate(expert_ids) if lo <= e < hi]
+                if sel:
+                    kept.append((types, blobs[sel[0]:sel[-1] + 1] if sel == list(range(sel[0], sel[-1] + 1)) else blobs[sel].contiguous(),
+                                 [expert_ids[i] for i in sel]))
+            pools = kept
         self.pools = []
         for types, blobs, expert_ids in pools:
             gt, dt = types if isinstance(types, tuple) else (types, types)
@@ -372,7 +389,7 @@ class MoePrefill:
         if shared is not None and not (mmq_supported(cfg.sh_gu_type) and mmq_supported(cfg.sh_d_type)):
             raise MayaError("MoePrefill: shared expert's type without a grouped GEMM", -2)
         self.cfg, self.shared, self.max_tokens = cfg, shared, max_tokens
-        dev, T, k, E = self.pools[0][2].device, max_tokens, cfg.k, cfg.n_expert
+        dev, T, k, E = (self.pools[0][2].device if self.pools else experts.device), max_tokens, cfg.k, cfg.n_expert
         i32 = dict(dtype=torch.int32, device=dev)
         f32 = dict(dtype=torch.float32, device=dev)
         u8 = dict(dtype=torch.uint8, device=dev)
@@ -404,7 +421,8 @@ class MoePrefill:
         _check("expert_bounds", lib.maya_expert_bounds(_ptr(self.counts), E, _ptr(self.bounds), s))
         _check("expert_scatter", lib.maya_expert_scatter(_ptr(ids), _ptr(self.rank), _ptr(self.bounds), n, k,
                                                          _ptr(self.row_tok), _ptr(self.pos), s))
-        _check("mmq_quantize", quant(_ptr(x), _ptr(self.row_tok), _ptr(self.xq), self.pools[0][0], H, x.stride(0), n, s))
+        qtype = self.pools[0][0] if self.pools else cfg.gu_type
+        _check("mmq_quantize", quant(_ptr(x), _ptr(self.row_tok), _ptr(self.xq), qtype, H, x.stride(0), n, s))
         for gt, dt, blobs, stride, down_off, n_p, emap in self.pools:
             gu = mmq_product(blobs, gt, 2 * FF, H, stride, n_p, self.xq, self.bounds, None, n, None, FF, expert_map=emap,
                              error=self.err, xq_out=self.hq)        # h leaves the product already quantized
@@ -427,8 +445,13 @@ class MoePrefill:
             _check("mmq_run", lib.maya_mmq_run(C.byref(sdn), s))
             sh_out = self.sh_out
         ffn = self.ffn[:T]
-        _check("moe_combine_rows", lib.maya_moe_combine_rows(_ptr(self.out), _ptr(self.pos), _ptr(w), _ptr(sh_out), T, k, H,
-                                                            _ptr(ffn), s))
+        if self.expert_range is None:
+            _check("moe_combine_rows", lib.maya_moe_combine_rows(_ptr(self.out), _ptr(self.pos), _ptr(w), _ptr(sh_out), T, k, H,
+                                                                _ptr(ffn), s))
+        else:
+            _check("moe_combine_rows_local",
+                   lib.maya_moe_combine_rows_local(_ptr(self.out), _ptr(self.pos), _ptr(w), _ptr(ids), self.expert_range[0],
+                                                   self.expert_range[1], _ptr(sh_out), T, k, H, _ptr(ffn), s))
         return ids, w, ffn
 
     def error(self) -> int:

@@ -96,6 +96,22 @@ __global__ void __launch_bounds__(256) combine_rows_kernel(const float* __restri
     ffn[(size_t) t * n_embd + e] = __fadd_rn(m, sh ? sh[(size_t) t * n_embd + e] : 0.0f);
 }
 
+// the same over this rank's experts only: a route whose expert id is outside [e_lo, e_hi) contributes an exact zero
+// (its sorted row was never computed here); the ranks' results add up to combine_rows_kernel's
+__global__ void __launch_bounds__(256) combine_rows_local_kernel(const float* __restrict__ out, const int* __restrict__ pos,
+                                                                 const float* __restrict__ w, const int* __restrict__ ids,
+                                                                 int e_lo, int e_hi, const float* __restrict__ sh, int k,
+                                                                 int n_embd, float* __restrict__ ffn) {
+    const int t = blockIdx.y, e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n_embd) return;
+    float m = 0.0f;
+    for (int j = 0; j < k; ++j) {
+        const int id = ids[t * k + j];
+        if (id >= e_lo && id < e_hi) m = __fmaf_rn(w[t * k + j], out[(size_t) pos[t * k + j] * n_embd + e], m);
+    }
+    ffn[(size_t) t * n_embd + e] = __fadd_rn(m, sh ? sh[(size_t) t * n_embd + e] : 0.0f);
+}
+
 // ffn[t] += sum over t's routes whose sorted row lies in [lo, hi) of w * out[row - base]
 __global__ void __launch_bounds__(256) combine_add_kernel(const float* __restrict__ out, int base, int lo, int hi,
                                                           const int* __restrict__ pos, const float* __restrict__ w, int k,
@@ -149,6 +165,14 @@ extern "C" int maya_moe_combine_rows(const float* out, const int* pos, const flo
     const dim3 grid((unsigned) ((n_embd + 255) / 256), (unsigned) T);
     combine_rows_kernel<<<grid, 256, 0, as_stream(stream)>>>(out, pos, w, sh, k, n_embd, ffn);
     return note_launch("moe_combine_rows");
+}
+extern "C" int maya_moe_combine_rows_local(const float* out, const int* pos, const float* w, const int* ids, int e_lo,
+                                           int e_hi, const float* sh, int T, int k, int n_embd, float* ffn, void* stream) {
+    if (T <= 0) return MAYA_OK;
+    if (!out || !pos || !w || !ids || !ffn || k <= 0 || n_embd <= 0 || e_lo > e_hi) return refuse(MAYA_ERR_ARG);
+    const dim3 grid((unsigned) ((n_embd + 255) / 256), (unsigned) T);
+    combine_rows_local_kernel<<<grid, 256, 0, as_stream(stream)>>>(out, pos, w, ids, e_lo, e_hi, sh, k, n_embd, ffn);
+    return note_launch("moe_combine_rows_local");
 }
 extern "C" int maya_moe_combine_add(const float* out, int base, int lo, int hi, const int* pos, const float* w, int T,
                                     int k, int n_embd, float* ffn, void* stream) {

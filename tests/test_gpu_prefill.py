@@ -309,3 +309,42 @@ def test_prefill_c4_shape(T, api, oracle):
     _, _, ffn2 = pf.forward(dev(T, logits[:512]), x_dev[:512])
     T.cuda.synchronize()
     assert np.array_equal(ffn2.cpu().numpy(), got[:512])
+
+
+def test_c5_batch64_through_prompt_path_and_expert_parallel_partition(T, api, oracle):
+    """Configuration C5's 64-token batch (IQ3_S experts, Zipf-skewed routing) through the prompt path: a few tokens
+    against the oracle, and the expert-parallel partition - each of 4 ranks computes only its 1/4 of the experts and
+    combines only their rows - adds up (rank order) to the one-rank result up to summation order."""
+    c = H.CONFIGS["C5"]
+    E, k, Hd, FF, n_tok = 32, c["k"], c["n_embd"], c["n_ff"], 64
+    t = c["gu_type"]
+    cfg = dict(n_embd=Hd, n_ff=FF, n_expert=E, k=k, gu_type=t, d_type=t)
+    lc = api.MoeLayerConfig(Hd, FF, E, k, t, t)
+    experts = T.empty((E, lc.blob_bytes), dtype=T.uint8, device="cuda")
+    gu_bytes = 2 * FF * H.row_bytes(t, Hd)
+    for e in range(E):
+        api.synth_weights(t, 7700 + 2 * e, 0.02, 2 * FF, Hd, experts[e, :gu_bytes])
+        api.synth_weights(t, 7701 + 2 * e, 0.02, Hd, FF, experts[e, gu_bytes:])
+    T.cuda.synchronize()
+    logits = H.router_logits("C5", n_tok, E, 1.1)
+    x = H.activations("C5", n_tok, Hd, "bf16")
+    ld, xd = dev(T, logits), dev(T, x).to(T.bfloat16)
+    whole = api.MoePrefill(lc, experts, max_tokens=n_tok)
+    ids, w, ffn = whole.forward(ld, xd)
+    T.cuda.synchronize()
+    assert whole.error() == 0
+    got = ffn.cpu().numpy().copy()
+    ids_o, w_o = oracle.router_top10(logits, k)
+    assert np.array_equal(ids.cpu().numpy(), ids_o)
+    for tok in (0, 31, 63):
+        want = oracle_prefill_token(oracle, cfg, experts, ids_o[tok], w_o[tok], x[tok])
+        assert H.rel_err(got[tok], want) <= TOL and H.rel_l2(got[tok], want) <= TOL
+    n_ranks, per = 4, E // 4
+    partial = []
+    for r in range(n_ranks):
+        rank = api.MoePrefill(lc, experts, max_tokens=n_tok, expert_range=(r * per, (r + 1) * per))
+        partial.append(rank.forward(ld, xd)[2].cpu().numpy().copy())
+        assert rank.error() == 0
+    summed = np.stack([oracle.allreduce_in_order(np.stack([p[tk] for p in partial])) for tk in range(n_tok)])
+    assert H.rel_err(summed, got) <= 1e-5
+    assert all(np.abs(p).max() > 0 for p in partial)
