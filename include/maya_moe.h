@@ -263,6 +263,15 @@ MAYA_API int maya_mmq_run_glu(const maya_mmq_product* p, float limit, void* stre
  * [8] blocks; [9] K steps.  NULL switches it off. */
 MAYA_API void maya_mmq_set_probe(unsigned long long* counters);
 
+/* The producer in front of the layer: glmf::rms_q8 (glm_fast.hpp:534: h += add; x = rms(h) * norm_w, eps inside the
+ * square root) and the router job of the GEMV batch Glm5Model::fast_moe issues next (glm_fast_path.cu:6925:
+ * logits = router_w . x, router_w [n_expert][n_embd] F32 or BF16 bits) in ONE launch, so that a decode layer is this call
+ * plus maya_moe_layer_decode.  add may be NULL; h_out (the updated residual stream, NULL: not wanted) must not be h when
+ * add is given.  x_out is f32 [n_embd]; its q8_1 image is made inside the layer kernel. */
+MAYA_API int maya_rms_router(const float* h, const float* add, const float* norm_w, float eps, int n_embd,
+                             const void* router_w, int router_is_bf16, int n_expert, float* h_out, float* x_out,
+                             float* logits, void* stream);
+
 /* Whole decode layer, one call (no single counterpart: the sequence Glm5Model::fast_moe runs,
  * src/core/glm_fast_path.cu:6917-7100: route -> gate/up -> down + combine, the shared expert alongside). */
 typedef struct maya_moe_layer {

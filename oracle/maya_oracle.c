@@ -518,6 +518,31 @@ ORC_API void orc_allreduce_in_order(const float* parts, int nm, int64_t n, float
     }
 }
 
+/* ------------------------------------------------------------------ the producer in front of the layer
+ * rms_q8_kernel (glm_fast.cu:5669-5697): t = h (+ add); inv = rsqrtf(sum(t^2) / n + eps); x = t * inv * w.  The
+ * reference sums the squares in float in an unspecified (tree) order: here the sum is taken in double and rounded once,
+ * which every float order matches to a few ulp.  Then the router job of glm_fast_path.cu:6925: logits = router_w . x
+ * (float products; summed here in double).  router_w [n_expert][n] as f32. */
+ORC_API void orc_rms_router(const float* h, const float* add, const float* w, float eps, int n, const float* router_w,
+                            int n_expert, float* h_out, float* x, float* logits) {
+    double ss = 0.0;
+    for (int e = 0; e < n; ++e) {
+        const float t = add ? h[e] + add[e] : h[e];
+        if (h_out) h_out[e] = t;
+        ss += (double) t * (double) t;
+    }
+    const float inv = 1.0f / sqrtf((float) ss / (float) n + eps);
+    for (int e = 0; e < n; ++e) {
+        const float t = add ? h[e] + add[e] : h[e];
+        x[e] = t * inv * w[e];
+    }
+    for (int ex = 0; ex < n_expert; ++ex) {
+        double acc = 0.0;
+        for (int e = 0; e < n; ++e) acc += (double) router_w[(size_t) ex * n + e] * (double) x[e];
+        logits[ex] = (float) acc;
+    }
+}
+
 /* ------------------------------------------------------------------ prefill grouping
  * glmb::expert_count / expert_scatter (glm_batch.cu:2102-2133): counts[e]; a stable rank per (token, slot)
  * pair i in ascending i; row = base[id] + rank; row_tok[row] = i / k; pos[i] = row. */

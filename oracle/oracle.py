@@ -38,7 +38,7 @@ def _u8(a) -> np.ndarray:
 class Oracle:
     def __init__(self, path: Path | None = None):
         path = path or HERE / "_build" / "libmaya_oracle.so"
-        if not path.exists():
+        if not path.exists() or path.stat().st_mtime < (HERE / "maya_oracle.c").stat().st_mtime:   # missing or stale
             import importlib.util
             spec = importlib.util.spec_from_file_location("maya_oracle_build", HERE / "build.py")
             mod = importlib.util.module_from_spec(spec)
@@ -148,6 +148,16 @@ class Oracle:
                                          C.c_float(w_scale), int(norm_w), _p(ids, _i32p), _p(w, _f32p))
         assert rc == 0
         return ids, w
+
+    def rms_router(self, h, add, w, eps, router_w):
+        """(h + add, x = rms(h + add) * w, logits = router_w . x)"""
+        h, w, router_w = _f32(h).reshape(-1), _f32(w).reshape(-1), _f32(router_w)
+        a = _f32(add).reshape(-1) if add is not None else None
+        n, E = h.size, router_w.shape[0]
+        h_out, x, logits = np.empty(n, np.float32), np.empty(n, np.float32), np.empty(E, np.float32)
+        self.lib.orc_rms_router(_p(h, _f32p), _p(a, _f32p) if a is not None else None, _p(w, _f32p), C.c_float(eps), n,
+                                _p(router_w, _f32p), E, _p(h_out, _f32p), _p(x, _f32p), _p(logits, _f32p))
+        return h_out, x, logits
 
     # ---- misc
     def allreduce_in_order(self, parts) -> np.ndarray:

@@ -94,6 +94,8 @@ _SIGNATURES = {
     "maya_expert_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "maya_swiglu_rows": (c_int, [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
     "maya_moe_combine_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "maya_rms_router": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                c_void_p]),
     "maya_mmq_supported": (c_int, [c_int]),
     "maya_mmq_q8_bytes": (c_size_t, [c_int64, c_int64]),
     "maya_mmq_quantize": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p]),

@@ -223,6 +223,20 @@ def moe_combine_rows(out, pos, w, sh, T: int, k: int, n_embd: int, stream=None):
     return ffn
 
 
+# ---------------------------------------------------------------- the producer in front of the layer
+def rms_router(h, add, norm_w, eps: float, router_w, h_out=None, stream=None):
+    """glmf::rms_q8 (glm_fast.hpp:534) + the router GEMV (glm_fast_path.cu:6925) in one launch: returns (x f32 [n_embd],
+    logits f32 [n_expert]); h_out receives h + add when given.  router_w: [n_expert, n_embd] f32 or bf16."""
+    n_embd, n_expert = h.numel(), router_w.shape[0]
+    assert router_w.dtype in (torch.float32, torch.bfloat16) and router_w.shape[1] == n_embd
+    x = torch.empty(n_embd, dtype=torch.float32, device=h.device)
+    logits = torch.empty(n_expert, dtype=torch.float32, device=h.device)
+    _check("rms_router", _lib.load().maya_rms_router(_ptr(h), _ptr(add), _ptr(norm_w), eps, n_embd, _ptr(router_w),
+                                                    int(router_w.dtype == torch.bfloat16), n_expert, _ptr(h_out), _ptr(x),
+                                                    _ptr(logits), _stream(stream)))
+    return x, logits
+
+
 # ---------------------------------------------------------------- prompt-path grouped GEMM (tensor cores)
 def mmq_supported(ggml_type: int) -> bool:
     """mmq::supported (include/strata/prefill/moe_mmq.hpp:16)."""

@@ -247,3 +247,39 @@ def test_layer_refusals(T, api):
     assert e.value.status == -4
     with pytest.raises(api.MayaError):
         api.MoeLayer(api.MoeLayerConfig(cfg["n_embd"], cfg["n_ff"], 2, 9, H.Q4_K, H.Q4_K), experts)
+
+
+@pytest.mark.parametrize("router_dtype", ["f32", "bf16"])
+def test_rms_router_and_two_launch_layer(T, api, oracle, router_dtype):
+    """maya_rms_router (residual add + RMS norm + router logits, one launch) against the oracle, and a decode layer
+    as two launches: that kernel, then the fused layer kernel on its x and logits - the routing and the output are the
+    oracle's on the same numbers."""
+    cfg = dict(H.CONFIGS["C2"], n_expert=32)
+    lc, experts, shared = synth_layer(T, api, cfg, 32, seed=33)
+    Hd, E = cfg["n_embd"], 32
+    rng = H.rng_for("rms-router-gpu", router_dtype)
+    h = rng.standard_normal(Hd).astype(np.float32)
+    add = (0.2 * rng.standard_normal(Hd)).astype(np.float32)
+    nw = (1.0 + 0.1 * rng.standard_normal(Hd)).astype(np.float32)
+    rw = (0.08 * rng.standard_normal((E, Hd))).astype(np.float32)
+    if router_dtype == "bf16":
+        rw = H.to_bf16_f32(rw)
+    rw_d = dev(T, rw, T.bfloat16 if router_dtype == "bf16" else None)
+    h_out = T.empty(Hd, dtype=T.float32, device="cuda")
+    x, logits = api.rms_router(dev(T, h), dev(T, add), dev(T, nw), 1e-5, rw_d, h_out=h_out)
+    T.cuda.synchronize()
+    ho, xo, lo = oracle.rms_router(h, add, nw, 1e-5, rw)
+    assert np.array_equal(h_out.cpu().numpy(), ho)
+    assert H.rel_err(x.cpu().numpy(), xo) <= 2e-6
+    assert np.abs(logits.cpu().numpy() - lo).max() <= 2e-5
+    with pytest.raises(api.MayaError):                       # in place with an add: other blocks would read the sum
+        hd = dev(T, h)
+        api.rms_router(hd, dev(T, add), dev(T, nw), 1e-5, rw_d, h_out=hd)
+    # launch 2: the layer on the first launch's outputs
+    ids, w, out = api.MoeLayer(lc, experts, shared).forward(logits.reshape(1, E), x.reshape(1, Hd))
+    T.cuda.synchronize()
+    lg, xg = logits.cpu().numpy().reshape(1, E), x.cpu().numpy()
+    ids_o, w_o = oracle.router_top10(lg, cfg["k"])
+    assert np.array_equal(ids.cpu().numpy(), ids_o)
+    want = oracle_token(oracle, cfg, experts, shared, ids_o[0], w_o[0], xg)
+    assert H.rel_err(out.cpu().numpy()[0], want) <= TIGHT

@@ -214,3 +214,26 @@ def test_expert_group(oracle):
     counts, bounds, pos, row_tok = oracle.expert_group(ids, 2, 4)
     assert counts.tolist() == [1, 2, 0, 3] and bounds.tolist() == [0, 1, 3, 3, 6]
     assert pos.tolist() == [3, 1, 2, 0, 4, 5] and row_tok.tolist() == [1, 0, 1, 0, 2, 2]
+
+
+def test_rms_router_against_float64(oracle):
+    """glmf::rms_q8's norm and the router GEMV: the oracle against a float64 evaluation, and against llama.cpp's captured
+    router logits of the synthetic GGUF layer (x = the captured FFN input, unit norm weights undone by construction)."""
+    rng = H.rng_for("rms-router")
+    n, E, eps = 1536, 40, 1e-5
+    h, add = rng.standard_normal(n).astype(np.float32), (0.1 * rng.standard_normal(n)).astype(np.float32)
+    w = (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+    rw = (0.05 * rng.standard_normal((E, n))).astype(np.float32)
+    h_out, x, logits = oracle.rms_router(h, add, w, eps, rw)
+    t = h.astype(np.float64) + add.astype(np.float64)
+    x64 = t / np.sqrt((t * t).mean() + eps) * w
+    assert np.array_equal(h_out, h + add)
+    assert np.abs(x - x64).max() <= 2e-6 * np.abs(x64).max()
+    assert np.abs(logits - rw.astype(np.float64) @ x64).max() <= 1e-5
+    g = np.load(GOLDEN / "glm5_synth_moe_layer1.npz")
+    xin = g["x"][3]
+    # choose norm weights that undo the normalisation, so that x == the captured input and the logits must be llama.cpp's
+    inv = 1.0 / np.sqrt((xin.astype(np.float64) ** 2).mean() + eps)
+    _, x2, lg = oracle.rms_router(xin, None, (np.ones_like(xin) / inv).astype(np.float32), eps, g["router"])
+    assert np.abs(x2 - xin).max() <= 1e-6
+    assert np.abs(lg - g["logits"][3]).max() <= 1e-5
