@@ -275,7 +275,38 @@ def gpu_arm(args) -> None:
         tok = s % N_TOKENS
         step(s, logits_d[tok:tok + 1], x_d[tok:tok + 1])
 
-    def step_e2e(s: int):
+    # End to end: every step copies its inputs from pinned host memory and its output back, inside the timed region.
+    # The copies run on their own streams, as a serving engine would issue them: step s's inputs may be up to
+    # E2E_DEPTH steps ahead of the layer kernel (a ring of staging slots), its output leaves while step s + 1 computes.
+    E2E_DEPTH = 4
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def run_e2e_steps():
+        cur = torch.cuda.current_stream()
+        s_in.wait_stream(cur)
+        s_out.wait_stream(cur)
+        done = []
+        for s in range(K):
+            tok = s % N_TOKENS
+            with torch.cuda.stream(s_in):
+                if s >= E2E_DEPTH:
+                    s_in.wait_event(done[s - E2E_DEPTH])
+                stage_l[s:s + 1].copy_(logits_h[tok:tok + 1], non_blocking=True)
+                stage_x[s:s + 1].copy_(x_h[tok:tok + 1], non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(s_in)
+            cur.wait_event(ready)
+            step(s, stage_l[s:s + 1], stage_x[s:s + 1])
+            ev = torch.cuda.Event()
+            ev.record(cur)
+            done.append(ev)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev)
+                out_h[s:s + 1].copy_(out_d[s:s + 1], non_blocking=True)
+        cur.wait_stream(s_in)
+        cur.wait_stream(s_out)
+
+    def step_e2e(s: int):                      # the unpipelined form, for the eager warm-up only
         tok = s % N_TOKENS
         stage_l[s:s + 1].copy_(logits_h[tok:tok + 1], non_blocking=True)
         stage_x[s:s + 1].copy_(x_h[tok:tok + 1], non_blocking=True)
@@ -299,17 +330,14 @@ def gpu_arm(args) -> None:
                 step_dev(s)
         launches_per_run = lib.maya_launch_count() - launches0
         with torch.cuda.graph(g_e2e, stream=stream):
-            for s in range(K):
-                step_e2e(s)
+            run_e2e_steps()
         run_dev, run_e2e = g_dev.replay, g_e2e.replay
     else:
         def run_dev():
             for s in range(K):
                 step_dev(s)
 
-        def run_e2e():
-            for s in range(K):
-                step_e2e(s)
+        run_e2e = run_e2e_steps
         run_dev()
         launches_per_run = lib.maya_launch_count() - launches0
 
@@ -351,7 +379,8 @@ def gpu_arm(args) -> None:
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "int8 x int8 -> f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "layers_resident": len(layers),
                        "l2": "inputs larger than L2: steps rotate over %d resident layers and 256 tokens" % len(layers),
-                       "launch": ("CUDA graph of the K steps" + (", partial outputs summed over peer HBM in the layer kernel's epilogue" if peer is not None else ""))
+                       "launch": ("CUDA graph of the K steps" + (", partial outputs summed over peer HBM in the layer kernel's epilogue" if peer is not None else "")),
+                       "e2e_pipeline": f"input copies up to {E2E_DEPTH} steps ahead on a copy stream, output copy on a third stream"
                        if use_graph else "eager launches + NCCL all-reduce of the partial outputs (comparison baseline)",
                        "parallelism": "1 GPU" if world == 1 else f"expert-parallel {world} x {per} experts, shared expert width-sliced {world} x {cfg['n_ff_sh'] // world}"},
             "hbm_gbs": bytes_tok * value / 1e9, "hbm_frac_of_%s_peak" % peak_kind: bytes_tok * value / 1e9 / peak,

@@ -71,6 +71,8 @@ def run(steps: int, warmup: int, layers: int, clock_sampler=None, scale: int = 1
             e0.record(stream)
             for s in range(n):
                 fn(s)
+            stream.wait_stream(s_in)                      # the side streams' copies belong to the timed region
+            stream.wait_stream(s_out)
             e1.record(stream)
         stream.synchronize()
         torch.cuda.synchronize()
@@ -79,11 +81,37 @@ def run(steps: int, warmup: int, layers: int, clock_sampler=None, scale: int = 1
     def step_dev(s):
         pf[s % layers].forward(logits_d, x_d, stream=stream)
 
+    # end to end: a step's inputs come from pinned host memory and its result goes back, inside the timed region; the
+    # copies run on their own streams (two staging slots each way), so chunk s + 1 arrives while chunk s is computed
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    stage = [(torch.empty_like(logits_d), torch.empty_like(x_d)) for _ in range(2)]
+    outs = [torch.empty((T, Hd), dtype=torch.float32, device="cuda") for _ in range(2)]
+    e2e_state = {"done": [], "copied": []}
+
     def step_e2e(s):
-        stage_l.copy_(logits_h, non_blocking=True)
-        stage_x.copy_(x_h, non_blocking=True)
-        _, _, ffn = pf[s % layers].forward(stage_l, stage_x, stream=stream)
-        out_h.copy_(ffn, non_blocking=True)
+        sl, sx = stage[s % 2]
+        done, copied = e2e_state["done"], e2e_state["copied"]
+        with torch.cuda.stream(s_in):
+            if len(done) >= 2:
+                s_in.wait_event(done[-2])                 # the step that last read this staging slot
+            sl.copy_(logits_h, non_blocking=True)
+            sx.copy_(x_h, non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record(s_in)
+        stream.wait_event(ready)
+        if len(copied) >= 2:
+            stream.wait_event(copied[-2])                 # the output slot has left for the host
+        _, _, ffn = pf[s % layers].forward(sl, sx, stream=stream)
+        outs[s % 2].copy_(ffn, non_blocking=True)         # on `stream`: frees the layer's own buffer for step s + layers
+        ev = torch.cuda.Event()
+        ev.record(stream)
+        done.append(ev)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev)
+            out_h.copy_(outs[s % 2], non_blocking=True)
+            cp = torch.cuda.Event()
+            cp.record(s_out)
+            copied.append(cp)
 
     timed(step_dev, W)
     timed(step_e2e, W)
