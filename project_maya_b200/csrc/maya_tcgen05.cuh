@@ -109,22 +109,22 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
         : "memory");
 }
 // The products of 64 K-values (four K = 16 steps) into one accumulator and the commit that follows them, as one block of
-// instructions for a lean issuing thread: A at a_tmem + 8 columns per step, B descriptor's address word b_lo + 2 per
-// step (32 bytes inside the 128-byte swizzle row), `first` = 0 makes the first product overwrite the accumulator.
-__device__ __forceinline__ void mma_f16_ts_x4_commit(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
-                                                     uint32_t first, uint32_t bar_smem) {
+// instructions for a lean issuing thread.  The four B descriptors (already assembled: address word + 2 per step, 32 bytes
+// inside the 128-byte swizzle row) and the A column (8 per step) are computed by the caller BEFORE it waits for the
+// operands, so that nothing but the products stands between the wait and the tensor core.  `first` = 0 makes the first
+// product overwrite the accumulator.
+__device__ __forceinline__ void mma_f16_ts_x4_commit(uint32_t d_tmem, uint32_t a_tmem, uint64_t b0, uint64_t b1, uint64_t b2,
+                                                     uint64_t b3, uint32_t idesc, uint32_t first, uint32_t bar_smem) {
     asm volatile(
-        "{\n\t.reg .pred p, t;\n\t.reg .b64 b0, b1, b2, b3;\n\t.reg .b32 l1, l2, l3, a1, a2, a3;\n\t"
-        "setp.ne.b32 p, %5, 0;\n\tsetp.eq.b32 t, %7, 0;\n\t"
-        "add.u32 l1, %2, 2;\n\tadd.u32 l2, %2, 4;\n\tadd.u32 l3, %2, 6;\n\t"
+        "{\n\t.reg .pred p, t;\n\t.reg .b32 a1, a2, a3;\n\t"
+        "setp.ne.b32 p, %7, 0;\n\tsetp.eq.b32 t, %9, 0;\n\t"
         "add.u32 a1, %1, 8;\n\tadd.u32 a2, %1, 16;\n\tadd.u32 a3, %1, 24;\n\t"
-        "mov.b64 b0, {%2, %3};\n\tmov.b64 b1, {l1, %3};\n\tmov.b64 b2, {l2, %3};\n\tmov.b64 b3, {l3, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], b0, %4, {%7, %7, %7, %7}, p;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %4, {%7, %7, %7, %7}, t;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %4, {%7, %7, %7, %7}, t;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %4, {%7, %7, %7, %7}, t;\n\t"
-        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(first), "r"(bar_smem), "r"(0u)
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %6, {%9, %9, %9, %9}, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], %3, %6, {%9, %9, %9, %9}, t;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], %4, %6, {%9, %9, %9, %9}, t;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], %5, %6, {%9, %9, %9, %9}, t;\n\t"
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%8];\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b0), "l"(b1), "l"(b2), "l"(b3), "r"(idesc), "r"(first), "r"(bar_smem), "r"(0u)
         : "memory");
 }
 // one look at the barrier at shared address `bar_smem`

@@ -613,18 +613,23 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             const int npairs = nkt / 2;
             bool ok = true;
             for (int kp = 0; kp < npairs; ++kp) {
-                if (!mbar_test_wait_addr(bfull, ph_b)) {         // not there yet: the bounded wait (timed when probing)
+                // everything the products need, before the waits
+                const uint64_t hi = (uint64_t) b_hi << 32;
+                const uint64_t d0b = hi | b_lo, d1b = hi | (b_lo + 2), d2b = hi | (b_lo + 4), d3b = hi | (b_lo + 6);
+                const uint32_t done_bar = done0 + ((kp & (kDone - 1)) << 3);
+                const bool rb = mbar_test_wait_addr(bfull, ph_b), ra = mbar_test_wait_addr(afull, ph_a);
+                if (!rb) {                                       // not there yet: the bounded wait (timed when probing)
                     const long long t0 = probing ? clock64() : 0;
                     if (!wait_or_fail(P, &P.b_full[(bfull - bfull0) >> 3], ph_b)) { ok = false; break; }
                     if (probing) c_wait0 += clock64() - t0;
                 }
-                if (!mbar_test_wait_addr(afull, ph_a)) {
+                if (!ra) {
                     const long long t0 = probing ? clock64() : 0;
                     if (!wait_or_fail(P, &P.a_full[(afull - afull0) >> 3], ph_a)) { ok = false; break; }
                     if (probing) c_wait1 += clock64() - t0;
                 }
                 tc_fence_after();
-                mma_f16_ts_x4_commit(d0, at, b_lo, b_hi, idesc, first, done0 + ((kp & (kDone - 1)) << 3));
+                mma_f16_ts_x4_commit(d0, at, d0b, d1b, d2b, d3b, idesc, first, done_bar);
                 first = 1;
                 at += 64; afull += 8;
                 if (at == a_end) { at = a0; afull = afull0; ph_a ^= 1; }
