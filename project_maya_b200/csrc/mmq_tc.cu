@@ -301,7 +301,6 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
     if (found_e < 0) return;                        // beyond the last group: uniform for the whole block
     const long long t_start = clock64();
     const bool probing = A.probe != nullptr;
-    const bool tracing = probing && blockIdx.x == 0 && blockIdx.y == 0;   // development: time stamps of K-step pairs 20..27 in probe[16..]
     long long c_wait0 = 0, c_wait1 = 0;
     const int be = A.expert_map ? A.expert_map[found_e] : found_e;
     const int row0 = A.bounds[be] + found_g * TN;
@@ -386,16 +385,11 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                     if (timing) c_wait1 += clock64() - t0;
                     tc_fence_after();
                 }
-                const long long ta = tracing ? clock64() : 0;
                 tmem_st32(a_lane + s * 64, o);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&P.a_full[s]);
-                if (tracing && w8 == 0 && lane == 0 && kp >= 20 && kp < 28) {
-                    A.probe[16 + (kp - 20) * 8 + 0] = (unsigned long long) (ta - t_start);         // stage seen free
-                    A.probe[16 + (kp - 20) * 8 + 1] = (unsigned long long) (clock64() - t_start);  // arrived
-                }
                 return true;
             };
             uint32_t o[32];
