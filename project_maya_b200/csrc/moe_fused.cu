@@ -202,24 +202,33 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             q0 += A.sh_lo;
             q1 += A.sh_lo;
         }
-        const int nr = r1 - r0, n_routed = nr * sh.nv, n_items = n_routed + (q1 - q0);
+        // an item = two FFN rows of one expert: their gate rows and up rows, four weight rows sharing the activation
+        // registers (more loads in flight per warp than one row pair: the field loads' latency is what the warps wait for)
+        const int nr = r1 - r0, np = (nr + 1) / 2, n_routed = np * sh.nv, nq = (q1 - q0 + 1) / 2, n_items = n_routed + nq;
         const size_t rb = row_bytes(T, n_embd);
         for (int it = warp; it < n_items; it += NW) {
             if (it < n_routed) {
-                const int ei = it / nr, r = r0 + it - ei * nr, e = sh.ve[ei];
-                const unsigned long long p = sh.ptr[e];
-                const uint8_t* blob = (const uint8_t*) p;
-                const uint8_t* rows[2] = {blob + (size_t) r * rb, blob + (size_t) (n_ff + r) * rb};
-                float o[2];
-                rows_dot1<T, 2>(rows, X, n_embd, lane, s_tab, o);
-                if (lane == 0) A.h[(size_t) e * h_ld + r] = swiglu(o[0], o[1], A.limit);
+                const int ei = it / np, ra = r0 + 2 * (it - ei * np), rb2 = min(ra + 1, r1 - 1), e = sh.ve[ei];
+                const uint8_t* blob = (const uint8_t*) sh.ptr[e];
+                const uint8_t* rows[4] = {blob + (size_t) ra * rb, blob + (size_t) (n_ff + ra) * rb,
+                                          blob + (size_t) rb2 * rb, blob + (size_t) (n_ff + rb2) * rb};
+                float o[4];
+                rows_dot1<T, 4>(rows, X, n_embd, lane, s_tab, o);
+                if (lane == 0) {
+                    A.h[(size_t) e * h_ld + ra] = swiglu(o[0], o[1], A.limit);
+                    if (rb2 != ra) A.h[(size_t) e * h_ld + rb2] = swiglu(o[2], o[3], A.limit);
+                }
             } else if constexpr (TS != 0) {
-                const int r = q0 + it - n_routed;
+                const int ra = q0 + 2 * (it - n_routed), rb2 = min(ra + 1, q1 - 1);
                 const size_t rbs = row_bytes(TS, n_embd);
-                const uint8_t* rows[2] = {A.shared + (size_t) r * rbs, A.shared + (size_t) (A.n_ff_sh + r) * rbs};
-                float o[2];
-                rows_dot1<TS, 2>(rows, X, n_embd, lane, nullptr, o);
-                if (lane == 0) A.h[(size_t) k * h_ld + r] = swiglu(o[0], o[1], A.limit);
+                const uint8_t* rows[4] = {A.shared + (size_t) ra * rbs, A.shared + (size_t) (A.n_ff_sh + ra) * rbs,
+                                          A.shared + (size_t) rb2 * rbs, A.shared + (size_t) (A.n_ff_sh + rb2) * rbs};
+                float o[4];
+                rows_dot1<TS, 4>(rows, X, n_embd, lane, nullptr, o);
+                if (lane == 0) {
+                    A.h[(size_t) k * h_ld + ra] = swiglu(o[0], o[1], A.limit);
+                    if (rb2 != ra) A.h[(size_t) k * h_ld + rb2] = swiglu(o[2], o[3], A.limit);
+                }
             }
         }
     }
