@@ -95,10 +95,21 @@ template<> struct Dec<MAYA_Q8_0> {
     static constexpr int cpb = 1, xblk = 1;
     int w[8];
     float d;
+    // A block is 34 bytes at a 2-byte aligned address: 8 aligned 32-bit loads from the word that holds its first byte,
+    // the tail as one or two 16-bit loads (never past the block), then one prmt per quant word with a selector that
+    // depends on the alignment - instead of 17 two-byte loads.
     __device__ __forceinline__ void load(const uint8_t* blk, int, const uint32_t*) {
-        d = ld_f16(blk);
+        const bool odd = (((uintptr_t) blk) & 2u) != 0;               // the block starts in the upper half of a word
+        const uint8_t* base = blk - (odd ? 2 : 0);
+        uint32_t W[9];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) w[i] = (int) ld_u32_a2(blk + 2 + 4 * i);
+        for (int i = 0; i < 8; ++i) W[i] = ld_u32(base + 4 * i);
+        W[8] = ld_u16(base + 32);
+        if (odd) W[8] |= ld_u16(base + 34) << 16;
+        d = __half2float(__ushort_as_half((unsigned short) (odd ? W[0] >> 16 : W[0] & 0xFFFFu)));
+        const uint32_t sel = odd ? 0x7654u : 0x5432u;                  // quant word i = bytes 2.. of W[i] : W[i+1], or W[i+1]
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = (int) __byte_perm(W[i], W[i + 1], sel);
     }
     __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
         const XQ v = xq_load(x, col, xb);

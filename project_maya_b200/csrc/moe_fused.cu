@@ -56,6 +56,8 @@ struct FusedArgs {
     unsigned* sync;            // scratch: [0] arrivals, [1] epoch, [2] error, [4..13] block 0's phase time stamps (ns)
 };
 
+constexpr int kUnitBatch = 4;   // units of 32 FFN rows a block works on at a time (64 four-row items: two per warp)
+
 struct FusedShared {
     RouterShared route;
     unsigned long long ptr[MAYA_MAX_K + 1];
@@ -65,6 +67,7 @@ struct FusedShared {
     unsigned ar_seq;
     int ve[MAYA_MAX_K];        // the plan entries this rank computes (blob address != 0), in plan order
     int nv;
+    float hbuf[kUnitBatch][32];   // the h values of the (expert, 32-row group) units this block is working on
 };
 
 // balanced contiguous split of n rows over nb blocks
@@ -192,44 +195,53 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     XCols X;
     X.q = cq; X.d = cd; X.isum = cs; X.nblk = nblk_x;
 
-    // ---------------------------------------------------------------- phase 1: gate / up + SwiGLU
+    // ---------------------------------------------------------------- phase 1: gate / up + SwiGLU + q8_1(h)
+    // A unit = 32 consecutive FFN rows of one expert = one q8_1 block of its h; block b takes units b, b + grid, ...
+    // The block that computed a unit also rounds it to q8_1 and writes the block to the scratch, so that after the grid
+    // barrier every block only COPIES the (k + 1) x n_ff / 32 blocks into shared memory (23 KB on the benchmark layer)
+    // instead of all 148 reading the same f32 h and rounding it again (that cost 12 us of L2 contention and arithmetic).
+    // The q8_1 image in the scratch: [unit][32] int8, then [unit] f32 scales, then [unit] int sums (unit = e * nblk_h + g).
+    int8_t* const gq = (int8_t*) A.h;
+    float* const gd = (float*) (gq + (size_t) ne * nblk_h * 32);
+    int* const gs = (int*) (gd + (size_t) ne * nblk_h);
     {
-        int r0, r1;
-        slice(n_ff, gridDim.x, blockIdx.x, r0, r1);            // routed experts' rows
-        int q0 = 0, q1 = 0;
-        if (has_sh) {
-            slice(A.sh_hi - A.sh_lo, gridDim.x, blockIdx.x, q0, q1);
-            q0 += A.sh_lo;
-            q1 += A.sh_lo;
-        }
-        // an item = two FFN rows of one expert: their gate rows and up rows, four weight rows sharing the activation
-        // registers (more loads in flight per warp than one row pair: the field loads' latency is what the warps wait for)
-        const int nr = r1 - r0, np = (nr + 1) / 2, n_routed = np * sh.nv, nq = (q1 - q0 + 1) / 2, n_items = n_routed + nq;
+        const int ng = n_ff / 32, units_r = sh.nv * ng, ng_sh = has_sh ? (A.sh_hi - A.sh_lo) / 32 : 0, U = units_r + ng_sh;
         const size_t rb = row_bytes(T, n_embd);
-        for (int it = warp; it < n_items; it += NW) {
-            if (it < n_routed) {
-                const int ei = it / np, ra = r0 + 2 * (it - ei * np), rb2 = min(ra + 1, r1 - 1), e = sh.ve[ei];
-                const uint8_t* blob = (const uint8_t*) sh.ptr[e];
-                const uint8_t* rows[4] = {blob + (size_t) ra * rb, blob + (size_t) (n_ff + ra) * rb,
-                                          blob + (size_t) rb2 * rb, blob + (size_t) (n_ff + rb2) * rb};
+        for (int u0 = blockIdx.x; u0 < U; u0 += gridDim.x * kUnitBatch) {
+            int nu = 0;                                          // units of this batch: u0, u0 + grid, ...
+            for (int u = u0; u < U && nu < kUnitBatch; u += gridDim.x) ++nu;
+            // an item = two FFN rows of a unit: their gate rows and up rows, four weight rows sharing the activation
+            // registers (more field loads in flight per warp than one row pair)
+            for (int it = warp; it < nu * 16; it += NW) {
+                const int j = it >> 4, u = u0 + j * (int) gridDim.x, ra_in = 2 * (it & 15);
                 float o[4];
-                rows_dot1<T, 4>(rows, X, n_embd, lane, s_tab, o);
-                if (lane == 0) {
-                    A.h[(size_t) e * h_ld + ra] = swiglu(o[0], o[1], A.limit);
-                    if (rb2 != ra) A.h[(size_t) e * h_ld + rb2] = swiglu(o[2], o[3], A.limit);
+                if (u < units_r) {
+                    const int ei = u / ng, ra = (u - ei * ng) * 32 + ra_in, e = sh.ve[ei];
+                    const uint8_t* blob = (const uint8_t*) sh.ptr[e];
+                    const uint8_t* rows[4] = {blob + (size_t) ra * rb, blob + (size_t) (n_ff + ra) * rb,
+                                              blob + (size_t) (ra + 1) * rb, blob + (size_t) (n_ff + ra + 1) * rb};
+                    rows_dot1<T, 4>(rows, X, n_embd, lane, s_tab, o);
+                } else if constexpr (TS != 0) {
+                    const int ra = A.sh_lo + (u - units_r) * 32 + ra_in;
+                    const size_t rbs = row_bytes(TS, n_embd);
+                    const uint8_t* rows[4] = {A.shared + (size_t) ra * rbs, A.shared + (size_t) (A.n_ff_sh + ra) * rbs,
+                                              A.shared + (size_t) (ra + 1) * rbs, A.shared + (size_t) (A.n_ff_sh + ra + 1) * rbs};
+                    rows_dot1<TS, 4>(rows, X, n_embd, lane, nullptr, o);
                 }
-            } else if constexpr (TS != 0) {
-                const int ra = q0 + 2 * (it - n_routed), rb2 = min(ra + 1, q1 - 1);
-                const size_t rbs = row_bytes(TS, n_embd);
-                const uint8_t* rows[4] = {A.shared + (size_t) ra * rbs, A.shared + (size_t) (A.n_ff_sh + ra) * rbs,
-                                          A.shared + (size_t) rb2 * rbs, A.shared + (size_t) (A.n_ff_sh + rb2) * rbs};
-                float o[4];
-                rows_dot1<TS, 4>(rows, X, n_embd, lane, nullptr, o);
                 if (lane == 0) {
-                    A.h[(size_t) k * h_ld + ra] = swiglu(o[0], o[1], A.limit);
-                    if (rb2 != ra) A.h[(size_t) k * h_ld + rb2] = swiglu(o[2], o[3], A.limit);
+                    sh.hbuf[j][ra_in] = swiglu(o[0], o[1], A.limit);
+                    sh.hbuf[j][ra_in + 1] = swiglu(o[2], o[3], A.limit);
                 }
             }
+            __syncthreads();
+            if (warp < nu) {                                     // one warp rounds one unit
+                const int u = u0 + warp * (int) gridDim.x;
+                int e, g;
+                if (u < units_r) { const int ei = u / ng; e = sh.ve[ei]; g = u - ei * ng; }
+                else { e = k; g = A.sh_lo / 32 + (u - units_r); }
+                q8_1_to_smem(sh.hbuf[warp][lane], (int4*) gq, gd, gs, e * nblk_h + g, lane);
+            }
+            __syncthreads();
         }
     }
     int o0, o1;
@@ -261,23 +273,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
 
     // ---------------------------------------------------------------- phase 2: q8_1(h), down, combine
     if (ok) {
-        // every block needs all of h: 8 loads in flight per lane before the first is used (one L2 round trip per 8
-        // blocks of 32 values instead of one per block)
-        for (int b0 = warp; b0 < ne * nblk_h; b0 += 8 * NW) {
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int b = b0 + i * NW, e = b / nblk_h, kb = b - e * nblk_h;
-                v[i] = 0.0f;
-                if (b < ne * nblk_h && sh.ptr[e] != 0ull && (e < k ? kb * 32 < n_ff : (kb * 32 >= A.sh_lo && kb * 32 < A.sh_hi)))
-                    v[i] = __ldcg(&A.h[(size_t) e * h_ld + kb * 32 + lane]);
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int b = b0 + i * NW;
-                if (b < ne * nblk_h && sh.ptr[b / nblk_h] != 0ull)   // another rank's expert: its column is never read
-                    q8_1_to_smem(v[i], cq, cd, cs, b, lane);
-            }
+        // every block needs all of q8_1(h): a plain copy of what the producers wrote (through L2: other SMs wrote it)
+        {
+            const int nb = ne * nblk_h;
+            const uint4* src = (const uint4*) gq;
+            uint4* dst = (uint4*) cq;
+            for (int i = tid; i < nb * 2; i += kFusedThreads) dst[i] = __ldcg(src + i);
+            for (int i = tid; i < nb; i += kFusedThreads) { cd[i] = __ldcg(gd + i); cs[i] = __ldcg(gs + i); }
         }
         __syncthreads();
         for (int it = warp; it < npairs * nvt; it += NW) {
