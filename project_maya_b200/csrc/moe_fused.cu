@@ -244,10 +244,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             __syncthreads();
         }
     }
+    // Output rows of this block.  With a cross-rank sum in the epilogue the slice is whole float4s (it moves 16 bytes a
+    // lane); without one, whole row pairs: with 6144 rows over 148 blocks that is 20-21 pairs a block instead of 10-11
+    // quads, i.e. at most 189 (pair, expert) items = 6 rounds of the 32 warps where 44 rows would need a 7th for 6 items.
     int o0, o1;
-    slice(n_embd / 4, gridDim.x, blockIdx.x, o0, o1);         // whole float4s: the cross-rank sum moves 16 bytes a lane
-    o0 *= 4;
-    o1 *= 4;
+    const int gran = A.ar.nm >= 2 ? 4 : 2;
+    slice(n_embd / gran, gridDim.x, blockIdx.x, o0, o1);
+    o0 *= gran;
+    o1 *= gran;
     const int nrows = o1 - o0, npairs = (nrows + 1) / 2;
     const size_t drb = row_bytes(T, n_ff), down_off = 2 * (size_t) n_ff * row_bytes(T, n_embd);
     const int nvt = sh.nv + (has_sh ? 1 : 0);
