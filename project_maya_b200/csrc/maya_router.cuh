@@ -5,8 +5,15 @@
 // inv = (float) (1 / sum); p = (float) (ex * inv); a stable descending top-k (ties -> lower index); weights
 // renormalised in double by max(sum of the k weights, 2^-14).
 //
-// What differs is only how the selection is carried out: one thread group per token; p lives in registers, each warp
-// keeps its running arg-max and the k rounds cost one shuffle tree plus one shared-memory exchange each.
+// What differs is only how the result is reached, never its bits:
+//   * the sum: 1 / sum is rounded to float, so a tree sum decides it whenever the float results at both ends of the
+//     tree sum's error interval agree (all terms are positive: any summation order is within (n + 16) * 2^-52 of any
+//     other); only when they disagree - about once in a million tokens - one thread repeats the ascending sum;
+//   * the selection: with one expert per thread, every thread counts the experts that beat it (keys = value bits over
+//     inverted index, unique, so the ranks are a permutation) and ranks 0..k-1 write themselves out: one pass instead of
+//     k rounds of arg-max; with more experts per thread p lives in registers, each warp keeps its running arg-max and the
+//     k rounds cost one shuffle tree plus one shared-memory exchange each;
+//   * the renormalisation: one thread per selected expert divides.
 //
 // The thread group is `nt` threads (a multiple of 32) that synchronise through `Sync::sync()`: the whole block
 // (__syncthreads) or a named barrier when only part of a block routes.
@@ -34,6 +41,7 @@ struct RouterShared {
     int ids[64];
     float val[64];
     float inv;
+    double rd[kRouterMaxWarps];
 };
 
 // k rounds of arg-max over `sel` (expert e = j * nt + tid), "greater value, or equal value and lower index" - the
@@ -75,11 +83,37 @@ __device__ __forceinline__ void select_topk(float (&sel)[PER], const float (&val
     }
 }
 
+// Selection by rank for one expert per thread (nt >= n_expert).  `keys`: n_expert 64-bit words of shared memory.  p >= 0
+// (or NaN): its bit pattern orders like the value; the low word makes equal values rank by ascending index, the stable
+// descending order.  The keys are distinct whatever p holds, so exactly one thread has each rank.
+template<class Sync>
+__device__ __forceinline__ void select_rank(float p, int n_expert, int k, int tid, unsigned long long* keys,
+                                            RouterShared& sh) {
+    const unsigned long long mine = ((unsigned long long) __float_as_uint(p) << 32) | (unsigned) (0xffffffffu - (unsigned) tid);
+    if (tid < n_expert) keys[tid] = mine;
+    Sync::sync();
+    if (tid < n_expert) {
+        int rank = 0;
+        const int n2 = n_expert & ~1;
+        const ulonglong2* k2 = (const ulonglong2*) keys;
+#pragma unroll 8
+        for (int j = 0; j < n2 / 2; ++j) {
+            const ulonglong2 o = k2[j];
+            rank += (o.x > mine) + (o.y > mine);
+        }
+        if (n2 < n_expert) rank += keys[n2] > mine;
+        if (rank < k) { sh.ids[rank] = tid; sh.val[rank] = p; }
+    }
+    Sync::sync();
+}
+
 // One token's softmax routing by the calling thread group.  l: n_expert logits; s_ex: n_expert doubles of shared
-// memory.  On return (after the group's last sync) sh.ids[0..k) hold the ids and sh.val[0..k) the renormalised weights.
+// memory, 16-byte aligned.  On return (after the group's last sync) sh.ids[0..k) hold the ids and sh.val[0..k) the
+// renormalised weights.
 template<int PER, class Sync>
 __device__ __forceinline__ void route_softmax(const float* __restrict__ l, int n_expert, int k, int tid, int nt,
                                               double* s_ex, RouterShared& sh) {
+    const int nw = nt >> 5;
     float lv[PER];
     float mx = -INFINITY;
 #pragma unroll
@@ -92,37 +126,50 @@ __device__ __forceinline__ void route_softmax(const float* __restrict__ l, int n
     if ((tid & 31) == 0) sh.rv[tid >> 5] = mx;
     Sync::sync();
     mx = sh.rv[0];
-    for (int q = 1; q < (nt >> 5); ++q) mx = fmaxf(mx, sh.rv[q]);
-    Sync::sync();
+    for (int q = 1; q < nw; ++q) mx = fmaxf(mx, sh.rv[q]);
 
-    double ex[PER];
+    double ex[PER], part = 0.0;
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
         const int e = j * nt + tid;
         ex[j] = e < n_expert ? exp((double) lv[j] - (double) mx) : 0.0;
         if (e < n_expert) s_ex[e] = ex[j];
+        part += ex[j];
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if ((tid & 31) == 0) sh.rd[tid >> 5] = part;
     Sync::sync();
-    if (tid == 0) {
-        double sum = 0.0;
-        for (int e = 0; e < n_expert; ++e) sum += s_ex[e];   // one thread, ascending: the reference's bits
-        sh.inv = (float) (1.0 / sum);
+    double tree = sh.rd[0];
+    for (int q = 1; q < nw; ++q) tree += sh.rd[q];
+    // every thread holds the same tree sum; the ascending sum lies within tol of it
+    const double tol = (double) (n_expert + 16) * 2.220446049250313e-16;
+    float inv = (float) (1.0 / (tree * (1.0 - tol)));
+    if (inv != (float) (1.0 / (tree * (1.0 + tol)))) {     // group-uniform
+        if (tid == 0) {
+            double sum = 0.0;
+            for (int e = 0; e < n_expert; ++e) sum += s_ex[e];   // one thread, ascending: the reference's bits
+            sh.inv = (float) (1.0 / sum);
+        }
+        Sync::sync();
+        inv = sh.inv;
+        Sync::sync();                                            // s_ex is reused below
     }
-    Sync::sync();
-    const float inv = sh.inv;
     float p[PER], sel[PER];
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
         p[j] = (j * nt + tid) < n_expert ? (float) (ex[j] * inv) : -INFINITY;
         sel[j] = p[j];
     }
-    select_topk<PER, Sync>(sel, p, n_expert, k, tid, nt, sh);
-    if (tid == 0) {
-        double s = 0.0;
-        for (int i = 0; i < k; ++i) s += (double) sh.val[i];
-        const double sc = fmax(s, 6.103515625e-05);   // 2^-14
-        for (int i = 0; i < k; ++i) sh.val[i] = (float) ((double) sh.val[i] / sc);
-    }
+    if constexpr (PER == 1) select_rank<Sync>(p[0], n_expert, k, tid, (unsigned long long*) s_ex, sh);
+    else select_topk<PER, Sync>(sel, p, n_expert, k, tid, nt, sh);
+    // weights renormalised in double by max(their sum in selection order, 2^-14): every thread adds, k threads divide
+    double s = 0.0;
+    for (int i = 0; i < k; ++i) s += (double) sh.val[i];
+    const double sc = fmax(s, 6.103515625e-05);   // 2^-14
+    const float mine = tid < k ? (float) ((double) sh.val[tid] / sc) : 0.0f;
+    Sync::sync();
+    if (tid < k) sh.val[tid] = mine;
     Sync::sync();
 }
 

@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     uint32_t* s_tab = (uint32_t*) s_raw;
     uint8_t* s_cols = s_raw + kRepTabBytes<T>;
     const int nblk_x = n_embd / 32, nblk_h = h_ld / 32;
-    const int cols_blocks = max(nblk_x, (MAYA_MAX_K + 1) * nblk_h);
+    const int cols_blocks = (max(nblk_x, (MAYA_MAX_K + 1) * nblk_h) + 1) & ~1;   // even: the router's scratch is 16-byte aligned
     int4* cq = (int4*) s_cols;
     float* cd = (float*) (s_cols + (size_t) cols_blocks * 32);
     int* cs = (int*) (s_cols + (size_t) cols_blocks * 36);
@@ -211,8 +211,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             int nu = 0;                                          // units of this batch: u0, u0 + grid, ...
             for (int u = u0; u < U && nu < kUnitBatch; u += gridDim.x) ++nu;
             // an item = two FFN rows of a unit: their gate rows and up rows, four weight rows sharing the activation
-            // registers (more field loads in flight per warp than one row pair)
-            for (int it = warp; it < nu * 16; it += NW) {
+            // registers (more field loads in flight per warp than one row pair).  An odd last unit would leave half the
+            // warps idle for a whole item: it is done one FFN row a warp instead (all 32 busy for half as long) - what a
+            // rank with few experts mostly has.
+            static_assert(NW == 32, "a unit's 32 FFN rows map onto the block's 32 warps");
+            const int nu4 = nu & ~1;
+            for (int it = warp; it < nu4 * 16; it += NW) {
                 const int j = it >> 4, u = u0 + j * (int) gridDim.x, ra_in = 2 * (it & 15);
                 float o[4];
                 if (u < units_r) {
@@ -232,6 +236,22 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
                     sh.hbuf[j][ra_in] = swiglu(o[0], o[1], A.limit);
                     sh.hbuf[j][ra_in + 1] = swiglu(o[2], o[3], A.limit);
                 }
+            }
+            if (nu & 1) {
+                const int u = u0 + nu4 * (int) gridDim.x;
+                float o[2];
+                if (u < units_r) {
+                    const int ei = u / ng, ra = (u - ei * ng) * 32 + warp, e = sh.ve[ei];
+                    const uint8_t* blob = (const uint8_t*) sh.ptr[e];
+                    const uint8_t* rows[2] = {blob + (size_t) ra * rb, blob + (size_t) (n_ff + ra) * rb};
+                    rows_dot1<T, 2>(rows, X, n_embd, lane, s_tab, o);
+                } else if constexpr (TS != 0) {
+                    const int ra = A.sh_lo + (u - units_r) * 32 + warp;
+                    const size_t rbs = row_bytes(TS, n_embd);
+                    const uint8_t* rows[2] = {A.shared + (size_t) ra * rbs, A.shared + (size_t) (A.n_ff_sh + ra) * rbs};
+                    rows_dot1<TS, 2>(rows, X, n_embd, lane, nullptr, o);
+                }
+                if (lane == 0) sh.hbuf[nu4][warp] = swiglu(o[0], o[1], A.limit);
             }
             __syncthreads();
             if (warp < nu) {                                     // one warp rounds one unit
@@ -338,7 +358,7 @@ int launch_fused(const FusedArgs& A, cudaStream_t s) {
     int dev = 0;
     cudaGetDevice(&dev);
     const int nblk_x = A.n_embd / 32, nblk_h = (A.n_ff > A.n_ff_sh ? A.n_ff : A.n_ff_sh) / 32;
-    const int cols_blocks = nblk_x > (MAYA_MAX_K + 1) * nblk_h ? nblk_x : (MAYA_MAX_K + 1) * nblk_h;
+    const int cols_blocks = ((nblk_x > (MAYA_MAX_K + 1) * nblk_h ? nblk_x : (MAYA_MAX_K + 1) * nblk_h) + 1) & ~1;
     const size_t smem = (size_t) kRepTabBytes<T> + (size_t) cols_blocks * 40 + (size_t) A.n_expert * sizeof(double);
     if (smem > 220 * 1024) return refuse(MAYA_ERR_LIMIT);
     if (cached_dev != dev) {
