@@ -201,7 +201,10 @@ def reference_arm(args) -> None:
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
-def build_layers(torch, api, n_layers: int, expert_range, shared_range):
+def build_layers(torch, api, n_layers: int, rank: int, world: int, partition: str):
+    """The resident layers of this rank.  N > 1, partition "width": FFN rows [rank * n_ff / N, (rank + 1) * n_ff / N) of
+    every expert (the reference's tensor-parallel split; every rank carries 1 / N of every token); "expert": experts
+    [rank * E / N, (rank + 1) * E / N) whole, the shared expert width-sliced."""
     cfg = CFG
     lc = api.MoeLayerConfig(cfg["n_embd"], cfg["n_ff"], cfg["n_expert"], cfg["k"], cfg["gu_type"], cfg["d_type"],
                             cfg["n_ff_sh"], cfg["sh_gu_type"], cfg["sh_d_type"], cfg["limit"])
@@ -215,6 +218,14 @@ def build_layers(torch, api, n_layers: int, expert_range, shared_range):
     sgu = 2 * cfg["n_ff_sh"] * S.row_bytes(cfg["sh_gu_type"], Hd)
     api.synth_weights(cfg["sh_gu_type"], 100001, 0.02, 2 * cfg["n_ff_sh"], Hd, shared0[:sgu])
     api.synth_weights(cfg["sh_d_type"], 100002, 0.02, Hd, cfg["n_ff_sh"], shared0[sgu:])
+    expert_range = shared_range = None
+    if world > 1 and partition == "width":
+        wid, wid_sh = FF // world, cfg["n_ff_sh"] // world
+        lc, experts0, shared0 = api.width_slice(lc, experts0, shared0, rank * wid, (rank + 1) * wid, rank * wid_sh, (rank + 1) * wid_sh)
+        torch.cuda.empty_cache()
+    elif world > 1:
+        per, wid_sh = E // world, cfg["n_ff_sh"] // world
+        expert_range, shared_range = (rank * per, (rank + 1) * per), (rank * wid_sh, (rank + 1) * wid_sh)
     layers = []
     for i in range(n_layers):
         # further layers are byte copies in their own memory: the values do not change the work, the addresses do
@@ -245,9 +256,7 @@ def gpu_arm(args) -> None:
     cfg = CFG
     Hd, E, k = cfg["n_embd"], cfg["n_expert"], cfg["k"]
     per = E // world
-    wid = cfg["n_ff_sh"] // world            # every rank holds 1 / world of the shared expert's width
-    lc, layers = build_layers(torch, api, args.layers, (rank * per, (rank + 1) * per) if world > 1 else None,
-                              (rank * wid, (rank + 1) * wid) if world > 1 else None)
+    lc, layers = build_layers(torch, api, args.layers, rank, world, args.partition)
 
     logits_h = torch.from_numpy(S.router_logits("C2", N_TOKENS, E, cfg["zipf"])).pin_memory()
     x_h = torch.from_numpy(S.bf16_bits(S.activations("C2", N_TOKENS, Hd, "bf16")).view(np.int16)).view(torch.bfloat16).pin_memory()
@@ -361,12 +370,17 @@ def gpu_arm(args) -> None:
 
     with ClockSampler(local_rank) as clocks:
         ms_dev = timed(run_dev)
+        # block 0's stamps of the timed run's last step (with the cross-rank sum in the kernel when N > 1)
+        step_phases = layers[(K - 1) % len(layers)].phase_ns(stream)
         ms_e2e = timed(run_e2e)
 
     # ---- the dominant kernel alone: gate/up of the routed experts (+ the shared expert's down rows in the same launch)
     roof = None
     if rank == 0:
         roof = dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, min(K, 64), stream, world)
+        if world > 1:
+            names = ["route+quantize", "gate_up", "grid_barrier", "down+combine", "cross_rank_sum"]
+            roof["block0_phase_end_us_last_timed_step"] = {n: step_phases[i + 1] / 1e3 for i, n in enumerate(names)}
 
     if rank == 0:
         bytes_tok = algorithmic_bytes_per_token()
@@ -382,7 +396,10 @@ def gpu_arm(args) -> None:
                        "launch": ("CUDA graph of the K steps" + (", partial outputs summed over peer HBM in the layer kernel's epilogue" if peer is not None else "")),
                        "e2e_pipeline": f"input copies up to {E2E_DEPTH} steps ahead on a copy stream, output copy on a third stream"
                        if use_graph else "eager launches + NCCL all-reduce of the partial outputs (comparison baseline)",
-                       "parallelism": "1 GPU" if world == 1 else f"expert-parallel {world} x {per} experts, shared expert width-sliced {world} x {cfg['n_ff_sh'] // world}"},
+                       "parallelism": "1 GPU" if world == 1 else
+                       (f"width-sliced experts (tensor parallel): every rank holds FFN rows {cfg['n_ff'] // world} of {cfg['n_ff']} of all {E} experts and of the shared one"
+                        if args.partition == "width" else
+                        f"expert-parallel {world} x {per} experts, shared expert width-sliced {world} x {cfg['n_ff_sh'] // world}")},
             "hbm_gbs": bytes_tok * value / 1e9, "hbm_frac_of_%s_peak" % peak_kind: bytes_tok * value / 1e9 / peak,
             "hbm_frac_of_nominal_8TBs": bytes_tok * value / 8e12,
             "e2e": {"value": e2e, "unit": "tok/s/layer", "h2d_bytes_per_step": E * 4 + Hd * 2, "d2h_bytes_per_step": Hd * 4,
@@ -449,6 +466,8 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ar", default="peer", choices=["peer", "nccl"], help="N > 1: how the ranks' partial outputs are summed")
+    ap.add_argument("--partition", default="width", choices=["width", "expert"],
+                    help="N > 1: every rank holds a width slice of every expert (default), or whole experts by id")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
                     help="decode: the headline single-token layer (C2); prefill: the 4096-token prompt chunk (C4), 1 GPU")
     ap.add_argument("--prefill-scale", type=int, default=1,

@@ -302,8 +302,9 @@ MAYA_API size_t maya_moe_layer_scratch_bytes(const maya_moe_layer* L, int n_toke
 /* Reads the sticky barrier-error word of a layer scratch (synchronises the stream first). 0 = no error. */
 MAYA_API int maya_moe_layer_error(const maya_moe_layer* L, int n_tokens, const void* scratch, void* stream);
 /* Diagnostic: block 0's wall-clock stamps (ns, %globaltimer) of the last fused single-token launch on this scratch:
- * start, end of routing/quantizing, end of its gate/up work, past the grid barrier, end.  Synchronises the stream. */
-MAYA_API int maya_moe_layer_phase_ns(const maya_moe_layer* L, const void* scratch, void* stream, unsigned long long* out5);
+ * start, end of routing/quantizing, end of its gate/up work, past the grid barrier, end of down + combine, end of the
+ * cross-rank sum (= the previous stamp without one).  Synchronises the stream. */
+MAYA_API int maya_moe_layer_phase_ns(const maya_moe_layer* L, const void* scratch, void* stream, unsigned long long* out6);
 /* logits [n_tokens, n_expert] f32; x [n_tokens, n_embd] f32 (x_is_bf16 == 0) or bf16 bits; out [n_tokens, n_embd] f32;
  * ids / weights [n_tokens, k] (outputs, may be NULL... then scratch holds them).  n_tokens <= MAYA_MAX_WIN_TOKENS. */
 MAYA_API int maya_moe_layer_decode(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
@@ -322,8 +323,10 @@ typedef struct maya_peer_ar_failure {
 } maya_peer_ar_failure;
 
 /* PeerAr (ds4_kernels.cuh:536-547) for nm ranks.  Every rank owns, in its own HBM, a receive buffer of
- * 2 slots x nm rows x stride floats (maya_peer_ar_recv_bytes) and 2 x nm x MAYA_PEER_AR_BLOCKS flags
- * (maya_peer_ar_flag_bytes), both zeroed (flags start at first_seq - 1 = 0, the first call uses seq 1).
+ * 2 slots x nm rows x stride floats followed by as many 64-bit {seq, value} words - the form the fused layer kernel
+ * exchanges its short rows in, one flagged store per float and no fence - (maya_peer_ar_recv_bytes covers both) and
+ * 2 x nm x MAYA_PEER_AR_BLOCKS flags (maya_peer_ar_flag_bytes), all zeroed (flags start at first_seq - 1 = 0, the
+ * first call uses seq 1).
  * peer_recv / peer_flags are DEVICE arrays of nm pointers: rank m's buffers as mapped into this rank's address space
  * (peer access or IPC; entry mi = this rank's own).  Calls on each rank's single stream must have matching n and seq,
  * with no skipped calls; seq wraps modulo 2^32.  A wait longer than timeout_ns sets *error (sticky: later calls return

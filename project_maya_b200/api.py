@@ -18,6 +18,7 @@ from . import _lib
 from ._lib import ExpertLayout, MmqProduct, MoeLayerDesc, MoePlan, MoeWin
 
 Q8_0, Q4_K, IQ3_S, IQ2_S = 8, 12, 21, 22
+_BLOCK = {Q8_0: 32, Q4_K: 256, IQ3_S: 256, IQ2_S: 256}       # values per GGUF block
 TYPE_NAMES = {Q8_0: "Q8_0", Q4_K: "Q4_K", IQ3_S: "IQ3_S", IQ2_S: "IQ2_S"}
 STATUS = {0: "ok", -1: "bad argument", -2: "unsupported ggml type", -3: "CUDA launch failed", -4: "beyond a limit",
           -5: "no sm_100 device"}
@@ -300,6 +301,47 @@ class MoeLayerConfig:
         return 2 * self.n_ff_sh * row_bytes(self.sh_gu_type, self.n_embd) + self.n_embd * row_bytes(self.sh_d_type, self.n_ff_sh)
 
 
+def width_slice(cfg: MoeLayerConfig, experts, shared, lo: int, hi: int, sh_lo: int | None = None, sh_hi: int | None = None):
+    """(cfg', experts', shared'): FFN rows lo..hi-1 of every routed expert (sh_lo..sh_hi-1 of the shared one) as blobs
+    of their own - each expert's gate and up rows of that range and the same COLUMNS of its down rows.
+
+    A width slice of an expert is an expert of FFN width hi - lo, and the slices' outputs add up to the whole expert's:
+    out = sum over slices of down[:, slice] . SwiGLU(gate[slice] x, up[slice] x).  This is how the reference splits
+    experts under tensor parallelism (its experts are width-sliced, never partitioned by id): every rank then carries
+    1 / N of EVERY token's work whatever the routing, where a partition by expert id gives a rank whatever share of
+    the token's experts it happens to hold.  The partial outputs are summed by the same all-reduce.  lo, hi must be
+    multiples of the down type's block size (256 for the k- and i-quants) so that the column slice is whole blocks; the
+    result is this rank's resident copy (nothing refers to the full blobs afterwards)."""
+    H = cfg.n_embd
+
+    def cut(blob, gu_t, d_t, n_ff, a, b):          # blob: [..., blob_bytes]
+        rb, drb = row_bytes(gu_t, H), row_bytes(d_t, n_ff)
+        gu = n_ff * rb
+        lead = blob.shape[:-1]
+        gate = blob[..., :gu].reshape(*lead, n_ff, rb)[..., a:b, :].reshape(*lead, -1)
+        up = blob[..., gu:2 * gu].reshape(*lead, n_ff, rb)[..., a:b, :].reshape(*lead, -1)
+        down = blob[..., 2 * gu:].reshape(*lead, H, drb)[..., row_bytes(d_t, a):row_bytes(d_t, b)].reshape(*lead, -1)
+        return torch.cat([gate, up, down], dim=-1).contiguous()
+
+    def whole_blocks(t, *vals):
+        for v in vals:
+            if v % _BLOCK[t] != 0:
+                raise ValueError(f"width slice bound {v} is not a multiple of the block size {_BLOCK[t]}")
+
+    whole_blocks(cfg.d_type, lo, hi)
+    ex = cut(experts, cfg.gu_type, cfg.d_type, cfg.n_ff, lo, hi)
+    sh, n_ff_sh = None, 0
+    if shared is not None and cfg.n_ff_sh:
+        sh_lo = lo if sh_lo is None else sh_lo
+        sh_hi = hi if sh_hi is None else sh_hi
+        whole_blocks(cfg.sh_d_type, sh_lo, sh_hi)
+        sh = cut(shared, cfg.sh_gu_type, cfg.sh_d_type, cfg.n_ff_sh, sh_lo, sh_hi)
+        n_ff_sh = sh_hi - sh_lo
+    out = MoeLayerConfig(cfg.n_embd, hi - lo, cfg.n_expert, cfg.k, cfg.gu_type, cfg.d_type, n_ff_sh, cfg.sh_gu_type,
+                         cfg.sh_d_type, cfg.limit)
+    return out, ex, sh
+
+
 class MoeLayer:
     """One resident MoE layer: `experts` uint8 [n_expert, blob_bytes] on the device, optional `shared` blob.
 
@@ -347,9 +389,9 @@ class MoeLayer:
 
     def phase_ns(self, stream=None):
         """Block 0's phase stamps of the last fused single-token launch, as offsets in ns from its start."""
-        buf = (C.c_ulonglong * 5)()
+        buf = (C.c_ulonglong * 6)()
         _check("moe_layer_phase_ns", _lib.load().maya_moe_layer_phase_ns(C.byref(self.desc), _ptr(self.scratch), _stream(stream), buf))
-        return [int(buf[i]) - int(buf[0]) for i in range(5)]
+        return [int(buf[i]) - int(buf[0]) for i in range(6)]
 
     def error(self, stream=None) -> int:
         """The scratch's sticky device-side error word (0 = none); synchronises the stream."""

@@ -36,7 +36,8 @@ using namespace maya;
 
 extern "C" size_t maya_peer_ar_recv_bytes(int nm, size_t stride) {
     if (nm < 1 || nm > MAYA_PEER_AR_MAX_RANKS || stride == 0) return 0;
-    return (size_t) 2 * nm * stride * sizeof(float);
+    // two slots of nm rows, then the same again as 64-bit {seq, value} words (the fused layer kernel's exchange)
+    return (size_t) 2 * nm * stride * (sizeof(float) + sizeof(unsigned long long));
 }
 extern "C" size_t maya_peer_ar_flag_bytes(int nm) {
     if (nm < 1 || nm > MAYA_PEER_AR_MAX_RANKS) return 0;

@@ -141,8 +141,10 @@ template<> struct Dec1<MAYA_IQ3_S> {
     }
 };
 
-// NR rows against the one staged column; out[r] is bit-identical to rows_dot<T, NR, 1>.
-template<int T, int NR>
+// NR rows against the one staged column; out[r] is bit-identical to rows_dot<T, NR, 1>.  UNR > 1 puts UNR passes of
+// the lane loop into one basic block so that the loads of NR x UNR blocks are in flight together (the loop is bound by
+// load latency, not by bytes); every lane still adds its terms in ascending k, so the bits do not change.
+template<int T, int NR, int UNR = 1>
 __device__ __forceinline__ void rows_dot1(const uint8_t* const* rows, const XCols& x, int n_in, int lane,
                                           const uint32_t* tab, float (&out)[NR]) {
     using D = Dec1<T>;
@@ -150,7 +152,7 @@ __device__ __forceinline__ void rows_dot1(const uint8_t* const* rows, const XCol
     float acc[NR];
 #pragma unroll
     for (int r = 0; r < NR; ++r) acc[r] = 0.0f;
-    for (int k = lane; k < ncalls; k += 32) {
+    auto pass = [&](int k) {
         const int kb = k / D::cpb, ci = k - kb * D::cpb;
         const int xb = kb * (Fmt<T>::qk / 32) + ci * D::xblk;
         const XQ a = xq_load1(x, xb);
@@ -162,9 +164,50 @@ __device__ __forceinline__ void rows_dot1(const uint8_t* const* rows, const XCol
             dec.load(rows[r] + (size_t) kb * Fmt<T>::bytes, ci, tab, lane);
             acc[r] = __fadd_rn(acc[r], dec.dot(a, b));
         }
+    };
+    int k = lane;
+    if constexpr (UNR > 1) {
+        for (; k + 32 * (UNR - 1) < ncalls; k += 32 * UNR) {
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) pass(k + 32 * u);
+        }
     }
+    for (; k < ncalls; k += 32) pass(k);
 #pragma unroll
     for (int r = 0; r < NR; ++r) out[r] = warp_sum(acc[r]);
+}
+
+// Calls a row of n_in values takes (one lane makes one call per pass of rows_dot1's loop).
+template<int T>
+__device__ __forceinline__ int calls_per_row(int n_in) { return (n_in / Fmt<T>::qk) * Dec1<T>::cpb; }
+
+// Rows SHORTER than a warp's 32 calls (ncalls = 8 or 16: rows of 256 or 512 values, what a width slice of an expert
+// leaves of its down rows): 32 / ncalls rows are taken side by side, lane group g = lane / ncalls working on its own
+// rows[r] (the caller passes each lane ITS group's row addresses).  out[r] is valid in every lane of the group and is
+// bit-identical to rows_dot1's: there the lanes beyond ncalls add zeros in the first steps of the same shuffle tree.
+template<int T, int NR>
+__device__ __forceinline__ void rows_dot1_short(const uint8_t* const* rows, const XCols& x, int ncalls, int lane,
+                                                const uint32_t* tab, float (&out)[NR]) {
+    using D = Dec1<T>;
+    const int c = lane & (ncalls - 1);
+    const int kb = c / D::cpb, ci = c - kb * D::cpb;
+    const int xb = kb * (Fmt<T>::qk / 32) + ci * D::xblk;
+    const XQ a = xq_load1(x, xb);
+    XQ b = a;
+    if constexpr (D::xblk == 2) b = xq_load1(x, xb + 1);
+    float acc[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        D dec;
+        dec.load(rows[r] + (size_t) kb * Fmt<T>::bytes, ci, tab, lane);
+        acc[r] = __fadd_rn(0.0f, dec.dot(a, b));
+    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        float v = acc[r];
+        for (int o = ncalls >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        out[r] = v;
+    }
 }
 
 }  // namespace maya

@@ -33,10 +33,13 @@ __device__ __forceinline__ bool peer_allreduce_block(float* x, int q0, int q1, c
         float4* dst = (float4*) (a.peer_recv[m] + row);
         for (int q = q0 + tid; q < q1; q += nt) dst[q] = ((const float4*) x)[q];
     }
-    __threadfence_system();          // my stores reach the peers before the flags do
+    // The block's stores reach the peers before the flags do: the barrier orders every thread's stores before the
+    // flag-writing threads' system-scope fence (fences are cumulative), so only those few threads pay for one - a
+    // system fence by all 1024 threads of all blocks cost the layer kernel several microseconds.
     __syncthreads();
     const size_t fslot = (size_t) slot * nm;
     if (tid < nm && tid != mi) {
+        __threadfence_system();
         volatile unsigned* f = a.peer_flags[tid] + ((fslot + mi) * MAYA_PEER_AR_BLOCKS + b) * MAYA_PEER_AR_FLAG_STRIDE;
         *f = seq;
     }
@@ -79,5 +82,64 @@ __device__ __forceinline__ bool peer_allreduce_block(float* x, int q0, int q1, c
     return true;
 }
 
+// The same sum for SHORT vectors (the fused layer kernel: 40-odd floats a block), latency first: every float travels as
+// one 64-bit store {seq, value} into the peers' word area (it follows the rows in the receive buffer: 2 x nm x stride
+// 64-bit words, zeroed at start), and the receiver polls the word itself.  No fence, no separate flag: one NVLink
+// one-way latency, where rows + flags cost a store round trip (the system fence) and then the flag's trip.  64-bit
+// stores are single-copy atomic, the two slots alternate by seq as above (a word is overwritten two calls later, which
+// the writer only reaches after this rank's reads of it), seq is never 0.  Same bounded wait, error word and failure
+// record.  Returns false when the transport is (or becomes) poisoned; x is then undefined.
+__device__ __forceinline__ bool peer_allreduce_block_words(float* x, int q0, int q1, const maya_peer_ar& a, int mi,
+                                                           unsigned seq, int b) {
+    __shared__ int s_ready;
+    const int tid = threadIdx.x, nt = blockDim.x, nm = a.nm;
+    if (tid == 0) s_ready = (*(volatile unsigned*) a.error & 1u) == 0;
+    __syncthreads();
+    if (!s_ready) return false;
+    const size_t slot = seq & 1u, words_off = (size_t) 2 * nm * a.stride;      // floats of row area before the words
+    for (int t = tid; t < 4 * (q1 - q0); t += nt) {
+        const size_t i = (size_t) 4 * q0 + t;
+        const float mine = x[i];
+        const unsigned long long word = ((unsigned long long) seq << 32) | __float_as_uint(mine);
+        for (int m = 0; m < nm; ++m)
+            if (m != mi)
+                *((volatile unsigned long long*) (a.peer_recv[m] + words_off) + (slot * nm + mi) * a.stride + i) = word;
+        const unsigned long long t0 = ar_global_ns();
+        float acc = 0.0f;
+        bool ok = true;
+        for (int m = 0; m < nm && ok; ++m) {
+            float p = mine;
+            if (m != mi) {
+                const volatile unsigned long long* src =
+                    (const volatile unsigned long long*) (a.recv + words_off) + (slot * nm + m) * a.stride + i;
+                unsigned long long w;
+                while ((unsigned) ((w = *src) >> 32) != seq) {
+                    const unsigned long long el = ar_global_ns() - t0;
+                    if (el >= a.timeout_ns) {
+                        if ((atomicOr(a.error, 1u) & 1u) == 0 && a.failure != nullptr) {
+                            a.failure->sequence = seq;
+                            a.failure->observed = (unsigned) (w >> 32);
+                            a.failure->block = (unsigned) b;
+                            a.failure->n4 = (unsigned) (q1 - q0);
+                            a.failure->rank = (unsigned) mi;
+                            a.failure->waited_for = (unsigned) m;
+                            a.failure->elapsed_ns = el;
+                            a.failure->timeout_ns = a.timeout_ns;
+                            a.failure->captured = 1;
+                        }
+                        ok = false;
+                        break;
+                    }
+                }
+                p = __uint_as_float((unsigned) w);
+            }
+            acc = m == 0 ? p : __fadd_rn(acc, p);
+        }
+        if (ok) x[i] = acc;
+        else s_ready = 0;
+    }
+    __syncthreads();
+    return s_ready != 0;
+}
 
 }  // namespace maya

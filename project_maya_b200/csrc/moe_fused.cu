@@ -23,6 +23,8 @@
 #include "maya_dots_t1.cuh"
 #include "maya_internal.cuh"
 #include "maya_peer_ar.cuh"
+#include <type_traits>
+
 #include "maya_router.cuh"
 
 namespace maya {
@@ -244,12 +246,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
                     const int ei = u / ng, ra = (u - ei * ng) * 32 + warp, e = sh.ve[ei];
                     const uint8_t* blob = (const uint8_t*) sh.ptr[e];
                     const uint8_t* rows[2] = {blob + (size_t) ra * rb, blob + (size_t) (n_ff + ra) * rb};
-                    rows_dot1<T, 2>(rows, X, n_embd, lane, s_tab, o);
+                    rows_dot1<T, 2, 2>(rows, X, n_embd, lane, s_tab, o);
                 } else if constexpr (TS != 0) {
                     const int ra = A.sh_lo + (u - units_r) * 32 + warp;
                     const size_t rbs = row_bytes(TS, n_embd);
                     const uint8_t* rows[2] = {A.shared + (size_t) ra * rbs, A.shared + (size_t) (A.n_ff_sh + ra) * rbs};
-                    rows_dot1<TS, 2>(rows, X, n_embd, lane, nullptr, o);
+                    rows_dot1<TS, 2, 2>(rows, X, n_embd, lane, nullptr, o);
                 }
                 if (lane == 0) sh.hbuf[nu4][warp] = swiglu(o[0], o[1], A.limit);
             }
@@ -272,24 +274,24 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     slice(n_embd / gran, gridDim.x, blockIdx.x, o0, o1);
     o0 *= gran;
     o1 *= gran;
-    const int nrows = o1 - o0, npairs = (nrows + 1) / 2;
+    const int nrows = o1 - o0;
     const size_t drb = row_bytes(T, n_ff), down_off = 2 * (size_t) n_ff * row_bytes(T, n_embd);
-    const int nvt = sh.nv + (has_sh ? 1 : 0);
-    auto down_rows = [&](int it, const uint8_t*& base, size_t& pitch, size_t& bytes, int& e, int& ra, int& rb2) {
-        const int ei = it / npairs, pr = it - ei * npairs;
-        e = ei < sh.nv ? sh.ve[ei] : k;
-        ra = o0 + 2 * pr;
-        rb2 = min(ra + 1, o1 - 1);
-        if (e < k) {
-            base = (const uint8_t*) sh.ptr[e] + down_off;
-            pitch = drb;
-            bytes = drb;
-        } else {                                     // this rank's columns [sh_lo, sh_hi) of the shared expert's down rows
-            pitch = row_bytes(TS, A.n_ff_sh);
-            base = A.shared + 2 * (size_t) A.n_ff_sh * row_bytes(TS, n_embd) + row_bytes(TS, A.sh_lo);
-            bytes = row_bytes(TS, A.sh_hi - A.sh_lo);
-        }
+    // A phase-2 item = a few of this block's output rows against one expert's h.  Rows of 64 or more calls (2048
+    // values of an i-quant): two rows, all lanes on each.  Shorter rows - a width slice of an expert - are taken four
+    // at a time per lane group, and 32 / calls lane groups side by side when a row has fewer than 32 calls, so that an
+    // item keeps every lane busy and a block needs 1-3 rounds of its warps instead of 6 ever shorter ones.
+    struct DownShape { int calls, groups, rpi, items; };
+    auto shape = [&](int calls) {
+        DownShape d;
+        d.calls = calls;
+        d.groups = (calls < 32 && (calls & (calls - 1)) == 0) ? 32 / calls : 1;
+        d.rpi = (calls <= 32 ? 4 : 2) * d.groups;
+        d.items = (nrows + d.rpi - 1) / d.rpi;
+        return d;
     };
+    const DownShape dr = shape(calls_per_row<T>(n_ff));
+    DownShape ds = dr;
+    if constexpr (TS != 0) ds = shape(calls_per_row<TS>(has_sh ? A.sh_hi - A.sh_lo : n_ff));
     __syncthreads();
     stamp(A.sync, 2);
     const bool ok = grid_barrier(A.sync, sh.epoch);
@@ -306,28 +308,62 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             for (int i = tid; i < nb; i += kFusedThreads) { cd[i] = __ldcg(gd + i); cs[i] = __ldcg(gs + i); }
         }
         __syncthreads();
-        for (int it = warp; it < npairs * nvt; it += NW) {
-            const uint8_t* base; size_t pitch, bytes; int e, ra, rb2;
-            down_rows(it, base, pitch, bytes, e, ra, rb2);
-            const int pr = (ra - o0) >> 1;
-            float o[2] = {0.0f, 0.0f};
-            {
+        // One loop per (expert class, item shape), chosen outside it: a single loop that branched per item between the
+        // shapes cost the common case 2.6 us.  The item index runs on from the routed class into the shared one, so the
+        // warps stay evenly loaded.
+        const int items_r = sh.nv * dr.items, items_all = items_r + (has_sh ? ds.items : 0);
+        auto run = [&](auto type_c, auto nr_c, auto short_c, auto routed_c, int it, int it_end, const DownShape& d) {
+            constexpr int TY = decltype(type_c)::value, NR = decltype(nr_c)::value;
+            constexpr bool SHORT = decltype(short_c)::value, ROUTED = decltype(routed_c)::value;
+            for (; it < it_end; it += NW) {
+                const int li = ROUTED ? it : it - items_r;
+                const int ei = ROUTED ? li / d.items : 0, grp = li - ei * d.items;
+                const int e = ROUTED ? sh.ve[ei] : k;
+                const int r0 = grp * d.rpi + (SHORT ? lane / d.calls : 0);      // this lane's first row; then + groups
                 XCols H;
                 H.q = cq + (size_t) 2 * e * nblk_h; H.d = cd + (size_t) e * nblk_h; H.isum = cs + (size_t) e * nblk_h;
                 H.nblk = nblk_h;
-                const uint8_t* rows[2] = {base + (size_t) ra * pitch, base + (size_t) rb2 * pitch};
-                if (e < k) {
-                    rows_dot1<T, 2>(rows, H, n_ff, lane, s_tab, o);
-                } else if constexpr (TS != 0) {
+                const uint8_t* base;
+                size_t pitch;
+                int n_in;
+                if constexpr (ROUTED) {
+                    base = (const uint8_t*) sh.ptr[e] + down_off;
+                    pitch = drb;
+                    n_in = n_ff;
+                } else {                             // this rank's columns [sh_lo, sh_hi) of the shared expert's down rows
                     const int b0 = A.sh_lo / 32;
-                    H.q += 2 * b0; H.d += b0; H.isum += b0; H.nblk = (A.sh_hi - A.sh_lo) / 32;
-                    rows_dot1<TS, 2>(rows, H, A.sh_hi - A.sh_lo, lane, nullptr, o);
+                    pitch = row_bytes(TY, A.n_ff_sh);
+                    base = A.shared + 2 * (size_t) A.n_ff_sh * row_bytes(TY, n_embd) + row_bytes(TY, A.sh_lo);
+                    n_in = A.sh_hi - A.sh_lo;
+                    H.q += 2 * b0; H.d += b0; H.isum += b0; H.nblk = n_in / 32;
+                }
+                const uint8_t* rows[NR];
+#pragma unroll
+                for (int r = 0; r < NR; ++r) rows[r] = base + (size_t) (o0 + min(r0 + r * d.groups, nrows - 1)) * pitch;
+                float o[NR];
+                const uint32_t* tab = ROUTED ? s_tab : nullptr;
+                if constexpr (SHORT) rows_dot1_short<TY, NR>(rows, H, d.calls, lane, tab, o);
+                else rows_dot1<TY, NR>(rows, H, n_in, lane, tab, o);
+                if (SHORT ? (lane & (d.calls - 1)) == 0 : lane == 0) {
+#pragma unroll
+                    for (int r = 0; r < NR; ++r)
+                        if (r0 + r * d.groups < nrows) sh.part[r0 + r * d.groups][e] = o[r];
                 }
             }
-            if (lane == 0) {
-                sh.part[2 * pr][e] = o[0];
-                if (2 * pr + 1 < nrows) sh.part[2 * pr + 1][e] = o[1];
-            }
+            return it;
+        };
+        using std::integral_constant;
+        using std::true_type;
+        using std::false_type;
+        int it = warp;
+        if (dr.groups > 1) it = run(integral_constant<int, T>{}, integral_constant<int, 4>{}, true_type{}, true_type{}, it, items_r, dr);
+        else if (dr.rpi == 4) it = run(integral_constant<int, T>{}, integral_constant<int, 4>{}, false_type{}, true_type{}, it, items_r, dr);
+        else it = run(integral_constant<int, T>{}, integral_constant<int, 2>{}, false_type{}, true_type{}, it, items_r, dr);
+        if constexpr (TS != 0) {
+            if (!has_sh) {
+            } else if (ds.groups > 1) run(integral_constant<int, TS>{}, integral_constant<int, 4>{}, true_type{}, false_type{}, it, items_all, ds);
+            else if (ds.rpi == 4) run(integral_constant<int, TS>{}, integral_constant<int, 4>{}, false_type{}, false_type{}, it, items_all, ds);
+            else run(integral_constant<int, TS>{}, integral_constant<int, 2>{}, false_type{}, false_type{}, it, items_all, ds);
         }
         __syncthreads();
         if (tid < nrows) {
@@ -336,15 +372,16 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             A.out[o0 + tid] = __fadd_rn(m, has_sh ? sh.part[tid][k] : 0.0f);
         }
     }
+    stamp(A.sync, 4);
     // ---------------------------------------------------------------- epilogue: the cross-rank sum of this block's rows
     if (A.ar.nm >= 2) {
         __syncthreads();
         int u0, u1;
         slice(n_embd / 4, gridDim.x, blockIdx.x, u0, u1);
-        peer_allreduce_block(A.out, u0, u1, A.ar, A.ar_rank, sh.ar_seq, blockIdx.x);
+        peer_allreduce_block_words(A.out, u0, u1, A.ar, A.ar_rank, sh.ar_seq, blockIdx.x);
     }
     __syncthreads();
-    stamp(A.sync, 4);
+    stamp(A.sync, 5);
     // the launch's last word: the next launch on this scratch (stream-ordered) starts a new epoch
     if (blockIdx.x == 0 && tid == 0) {
         *(volatile unsigned*) &A.sync[1] = sh.epoch + 1u;

@@ -117,11 +117,11 @@ extern "C" int maya_moe_layer_error(const maya_moe_layer* L, int n_tokens, const
     return (int) word;
 }
 
-extern "C" int maya_moe_layer_phase_ns(const maya_moe_layer* L, const void* scratch, void* stream, unsigned long long* out5) {
-    if (check_layer(L) != MAYA_OK || !scratch || !out5) return MAYA_ERR_ARG;
+extern "C" int maya_moe_layer_phase_ns(const maya_moe_layer* L, const void* scratch, void* stream, unsigned long long* out6) {
+    if (check_layer(L) != MAYA_OK || !scratch || !out6) return MAYA_ERR_ARG;
     const Scratch S = carve(*L, 1, (uint8_t*) scratch);
     if (cudaStreamSynchronize(as_stream(stream)) != cudaSuccess) return note_launch("phase_ns sync");
-    if (cudaMemcpy(out5, S.sync + 4, 5 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess)
+    if (cudaMemcpy(out6, S.sync + 4, 6 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess)
         return note_launch("phase_ns copy");
     return MAYA_OK;
 }

@@ -23,7 +23,7 @@ def T(cuda):
 
 
 def buffers(T, r):
-    recv = r.keep[0][r.mi].view(T.float32).view(2, r.nm, r.stride)
+    recv = r.keep[0][r.mi][: 2 * r.nm * r.stride * 4].view(T.float32).view(2, r.nm, r.stride)
     flags = r.keep[1][r.mi].view(T.int32).view(2, r.nm, BLOCKS, FSTRIDE)
     return recv, flags
 

@@ -181,6 +181,37 @@ def test_width_sliced_shared_expert_sums_to_whole(T, api, oracle, n_ranks):
         api.MoeLayer(lc, experts, shared, shared_range=(16, wid)).forward(ld[:1], xd[:1])     # not a multiple of 32
 
 
+@pytest.mark.parametrize("n_ranks", [2, 4, 8])
+def test_width_sliced_experts_sum_to_whole(T, api, oracle, n_ranks):
+    """Tensor-parallel ranks: every rank holds FFN rows [r * n_ff / N, (r + 1) * n_ff / N) of EVERY expert as blobs of
+    their own (api.width_slice) and runs the same layer kernel on them; routing is replicated (same ids on every rank),
+    the rank-ordered sum of the partial outputs is the one-rank output up to the order of the down sums.  At N = 8 a
+    slice is one 256-value block wide."""
+    cfg = dict(H.CONFIGS["C2"], n_expert=16)
+    lc, experts, shared = synth_layer(T, api, cfg, 16, seed=23)
+    logits = H.router_logits("C2", 3, 16, 1.1)
+    x = H.activations("C2", 3, cfg["n_embd"], "bf16")
+    ld, xd = dev(T, logits), dev(T, x, T.bfloat16)
+    wid = cfg["n_ff"] // n_ranks
+    ranks = []
+    for r in range(n_ranks):
+        c, ex, sh = api.width_slice(lc, experts, shared, r * wid, (r + 1) * wid)
+        assert c.n_ff == wid and ex.shape == (16, c.blob_bytes) and sh.numel() == c.shared_bytes
+        ranks.append(api.MoeLayer(c, ex, sh))
+    whole_layer = api.MoeLayer(lc, experts, shared)
+    for t in range(3):
+        ids0, w0, whole = whole_layer.forward(ld[t:t + 1], xd[t:t + 1])
+        parts = []
+        for L in ranks:
+            ids, w, out = L.forward(ld[t:t + 1], xd[t:t + 1])
+            assert T.equal(ids, ids0) and T.equal(w, w0)
+            parts.append(out.cpu().numpy()[0])
+        assert H.rel_err(oracle.allreduce_in_order(np.stack(parts)), whole.cpu().numpy()[0]) <= 1e-5
+        assert min(np.abs(p).max() for p in parts) > 0
+    with pytest.raises(ValueError):
+        api.width_slice(lc, experts, shared, 0, 100)       # not whole blocks
+
+
 @pytest.mark.parametrize("t,shared", [(H.Q4_K, False), (H.Q8_0, False), (H.IQ2_S, True), (H.IQ3_S, True), (H.IQ3_S, False)])
 def test_fused_token_kernel_equals_staged_kernels_bitwise(T, api, oracle, t, shared):
     """One token through the single fused kernel and through the separate launches: the same bits, and the oracle's
@@ -283,3 +314,68 @@ def test_rms_router_and_two_launch_layer(T, api, oracle, router_dtype):
     assert np.array_equal(ids.cpu().numpy(), ids_o)
     want = oracle_token(oracle, cfg, experts, shared, ids_o[0], w_o[0], xg)
     assert H.rel_err(out.cpu().numpy()[0], want) <= TIGHT
+
+
+def _word_area(T, r):
+    """The {seq, value} words of rank r's receive buffer: they follow its 2 x nm x stride floats of rows."""
+    return r.keep[0][r.mi][2 * r.nm * r.stride * 4:].view(T.int64).view(2, r.nm, r.stride)
+
+
+def _words(seq, v):
+    return ((np.uint64(seq) << np.uint64(32)) | v.view(np.uint32).astype(np.uint64)).view(np.int64)
+
+
+def test_fused_layer_exchanges_flagged_words(T, api, oracle):
+    """The cross-rank sum in the fused kernel's epilogue, on one GPU: rank 1 of 3 runs alone with the other ranks'
+    {seq, value} words placed in its receive area beforehand.  Its output is rank 0's + its own + rank 2's vector, added
+    in that order (bit for bit), and its own words land in both peers' areas with the call's sequence number."""
+    from project_maya_b200.peer import PeerGroup
+    cfg = dict(n_embd=1024, n_ff=512, n_expert=8, k=2, gu_type=H.Q8_0, d_type=H.Q8_0)
+    lc, experts, _ = synth_layer(T, api, cfg, 8, seed=31)
+    layer = api.MoeLayer(lc, experts, None)
+    n = cfg["n_embd"]
+    ranks = PeerGroup.on_one_device(3, stride=n, timeout_ms=50.0)
+    logits = H.router_logits("words", 3, 8, 1.1)
+    x = H.activations("words", 3, n, "bf16")
+    ld, xd = dev(T, logits), dev(T, x, T.bfloat16)
+    rng = np.random.default_rng(5)
+    for t, seq in enumerate((1, 2, 3)):
+        local = layer.forward(ld[t:t + 1], xd[t:t + 1])[2].cpu().numpy()[0]
+        others = {m: rng.standard_normal(n).astype(np.float32) for m in (0, 2)}
+        others[0][:4] = [0.0, -0.0, np.float32(1e-38), np.float32(3e38)]
+        area = _word_area(T, ranks[1])
+        for m, v in others.items():
+            area[seq & 1, m, :n] = T.from_numpy(_words(seq, v)).cuda()
+        got = layer.forward(ld[t:t + 1], xd[t:t + 1], peer=ranks[1])[2].cpu().numpy()[0]
+        want = oracle.allreduce_in_order(np.stack([others[0], local, others[2]]))
+        assert got.tobytes() == want.tobytes()
+        for m in (0, 2):
+            pushed = _word_area(T, ranks[m])[seq & 1, 1, :n].cpu().numpy()
+            assert np.array_equal(pushed, _words(seq, local))
+    assert not ranks[1].poisoned()
+
+
+def test_fused_layer_exchange_times_out_and_poisons(T, api):
+    """A peer that never sends: the wait in the fused kernel's epilogue gives up after the time-out, records who it
+    waited for and poisons the transport; later calls return at once and the device still answers."""
+    import time
+    from project_maya_b200.peer import PeerGroup
+    cfg = dict(n_embd=1024, n_ff=512, n_expert=8, k=2, gu_type=H.Q8_0, d_type=H.Q8_0)
+    lc, experts, _ = synth_layer(T, api, cfg, 8, seed=31)
+    layer = api.MoeLayer(lc, experts, None)
+    r = PeerGroup.on_one_device(2, stride=cfg["n_embd"], timeout_ms=20.0)[0]
+    ld, xd = dev(T, H.router_logits("words", 1, 8, 1.1)), dev(T, H.activations("words", 1, cfg["n_embd"], "bf16"), T.bfloat16)
+    t0 = time.time()
+    layer.forward(ld, xd, peer=r)
+    T.cuda.synchronize()
+    assert time.time() - t0 < 2.0
+    assert r.poisoned()
+    f = r.failure_record()
+    assert f.captured == 1 and f.sequence == 1 and f.rank == 0 and f.waited_for == 1 and f.elapsed_ns >= f.timeout_ns
+    t0 = time.time()
+    for _ in range(32):
+        layer.forward(ld, xd, peer=r)
+    T.cuda.synchronize()
+    assert time.time() - t0 < 1.0
+    assert layer.error() == 0                                   # the layer's own barrier is not affected
+    assert bool((T.ones(4, device="cuda") * 2 == 2).all())
