@@ -361,6 +361,27 @@ MAYA_API int maya_allreduce_peer(float* x, int n, const maya_peer_ar* a, int mi,
 MAYA_API int maya_moe_layer_decode_ar(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
                                       int n_tokens, int* ids, float* weights, float* out, void* scratch,
                                       size_t scratch_bytes, const maya_peer_ar* a, int mi, unsigned seq, void* stream);
+/* The consumer behind the block: glmf::hc_post (include/strata/kernels/glm_fast.hpp:124; hc_post_kernel,
+ * src/kernels/cuda/glm_fast.cu:2747-2757).  The residual is a stack of 4 streams of n_embd floats;
+ * R_new[d][e] = block_out[e] * post[d] + sum_s comb[d * 4 + s] * R_old[s][e] (post[4], comb[16] dst-major, device
+ * memory).  R_new must not alias R_old. */
+typedef struct maya_hc_post_args {
+    const float* R_old;   /* [4][n_embd] */
+    const float* post;    /* [4] */
+    const float* comb;    /* [4][4]: comb[d * 4 + s] weighs input stream s in output stream d */
+    float* R_new;         /* [4][n_embd] */
+} maya_hc_post_args;
+MAYA_API int maya_hc_post(const float* block_out, const float* R_old, const float* post, const float* comb, int n_embd,
+                          float* R_new, void* stream);
+/* maya_moe_layer_decode[_ar] followed by that write, one token (n_tokens tokens: hc points to n_tokens structures' worth
+ * of arrays, token t at R_old + t * 4 * n_embd, post + t * 4, comb + t * 16, R_new + t * 4 * n_embd).  `a` may be NULL
+ * (one rank: no cross-rank sum).  One token: the write happens in the fused layer kernel's epilogue, each block on the
+ * output rows it has just combined and summed - what Glm5Model::fast_moe follows the block with
+ * (src/core/glm_fast_path.cu:7309) costs no launch.  `out` still receives the block's output. */
+MAYA_API int maya_moe_layer_decode_hc(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
+                                      int n_tokens, int* ids, float* weights, float* out, void* scratch,
+                                      size_t scratch_bytes, const maya_peer_ar* a, int mi, unsigned seq,
+                                      const maya_hc_post_args* hc, void* stream);
 /* Set-up helpers (startup only, they allocate and synchronise): a zeroed device buffer another process on the same
  * machine can map. */
 MAYA_API int maya_peer_buffer_create(size_t bytes, void** ptr, unsigned char handle[64]);

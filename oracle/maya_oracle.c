@@ -543,6 +543,20 @@ ORC_API void orc_rms_router(const float* h, const float* add, const float* w, fl
     }
 }
 
+/* ------------------------------------------------------------------ hyper-connection write after the FFN block
+ * hc_post_kernel (src/kernels/cuda/glm_fast.cu:2747-2757), the consumer of the MoE output: the residual is a stack of 4
+ * streams R[s][n_embd]; R_new[d][e] = block_out[e] * post[d] + sum_s comb[d * 4 + s] * R_old[s][e], the sum taken in
+ * ascending s as multiply-adds onto the product (the reference's `acc += a * b` compiles to fused multiply-adds). */
+ORC_API void orc_hc_post(const float* block_out, const float* R_old, const float* post, const float* comb, int n_embd,
+                         float* R_new) {
+    for (int d = 0; d < 4; ++d)
+        for (int e = 0; e < n_embd; ++e) {
+            float acc = block_out[e] * post[d];
+            for (int s = 0; s < 4; ++s) acc = fmaf(comb[d * 4 + s], R_old[(size_t) s * n_embd + e], acc);
+            R_new[(size_t) d * n_embd + e] = acc;
+        }
+}
+
 /* ------------------------------------------------------------------ prefill grouping
  * glmb::expert_count / expert_scatter (glm_batch.cu:2102-2133): counts[e]; a stable rank per (token, slot)
  * pair i in ascending i; row = base[id] + rank; row_tok[row] = i / k; pos[i] = row. */

@@ -159,6 +159,15 @@ class Oracle:
                                 _p(router_w, _f32p), E, _p(h_out, _f32p), _p(x, _f32p), _p(logits, _f32p))
         return h_out, x, logits
 
+    def hc_post(self, block_out, R_old, post, comb):
+        """R_new [4, n_embd] = block_out * post[d] + comb[d, :] . R_old[:, e]"""
+        b, R, po, co = _f32(block_out).reshape(-1), _f32(R_old), _f32(post).reshape(-1), _f32(comb).reshape(-1)
+        n = b.size
+        assert R.shape == (4, n) and po.size == 4 and co.size == 16
+        out = np.empty((4, n), np.float32)
+        self.lib.orc_hc_post(_p(b, _f32p), _p(R, _f32p), _p(po, _f32p), _p(co, _f32p), n, _p(out, _f32p))
+        return out
+
     # ---- misc
     def allreduce_in_order(self, parts) -> np.ndarray:
         parts = _f32(parts)

@@ -59,6 +59,10 @@ class PeerArDesc(C.Structure):
                 ("nm", c_int), ("seq_counter", c_void_p)]
 
 
+class HcPostArgs(C.Structure):
+    _fields_ = [("R_old", c_void_p), ("post", c_void_p), ("comb", c_void_p), ("R_new", c_void_p)]
+
+
 _SIGNATURES = {
     "maya_version": (C.c_char_p, []),
     "maya_last_cuda_error": (c_int, []),
@@ -117,6 +121,10 @@ _SIGNATURES = {
     "maya_allreduce_peer": (c_int, [c_void_p, c_int, C.POINTER(PeerArDesc), c_int, C.c_uint, c_void_p]),
     "maya_moe_layer_decode_ar": (c_int, [C.POINTER(MoeLayerDesc), c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_size_t, C.POINTER(PeerArDesc), c_int, C.c_uint, c_void_p]),
+    "maya_hc_post": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "maya_moe_layer_decode_hc": (c_int, [C.POINTER(MoeLayerDesc), c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_size_t, C.POINTER(PeerArDesc), c_int, C.c_uint,
+                                         C.POINTER(HcPostArgs), c_void_p]),
     "maya_peer_buffer_create": (c_int, [c_size_t, C.POINTER(c_void_p), C.c_char_p]),
     "maya_peer_buffer_open": (c_int, [C.c_char_p, C.POINTER(c_void_p)]),
     "maya_peer_buffer_close": (c_int, [c_void_p]),

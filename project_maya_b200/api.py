@@ -15,7 +15,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib
-from ._lib import ExpertLayout, MmqProduct, MoeLayerDesc, MoePlan, MoeWin
+from ._lib import ExpertLayout, HcPostArgs, MmqProduct, MoeLayerDesc, MoePlan, MoeWin
 
 Q8_0, Q4_K, IQ3_S, IQ2_S = 8, 12, 21, 22
 _BLOCK = {Q8_0: 32, Q4_K: 256, IQ3_S: 256, IQ2_S: 256}       # values per GGUF block
@@ -239,6 +239,14 @@ def rms_router(h, add, norm_w, eps: float, router_w, h_out=None, stream=None):
 
 
 # ---------------------------------------------------------------- prompt-path grouped GEMM (tensor cores)
+def hc_post(block_out, R_old, post, comb, R_new=None, stream=None):
+    """glmf::hc_post: R_new [4, n_embd] = block_out * post[d] + comb[d, :] . R_old[:, e] (comb dst-major)."""
+    n = block_out.numel()
+    R_new = R_new if R_new is not None else torch.empty((4, n), dtype=torch.float32, device=block_out.device)
+    _check("hc_post", _lib.load().maya_hc_post(_ptr(block_out), _ptr(R_old), _ptr(post), _ptr(comb), n, _ptr(R_new), _stream(stream)))
+    return R_new
+
+
 def mmq_supported(ggml_type: int) -> bool:
     """mmq::supported (include/strata/prefill/moe_mmq.hpp:16)."""
     return bool(_lib.load().maya_mmq_supported(ggml_type))
@@ -366,13 +374,26 @@ class MoeLayer:
             raise MayaError("moe_layer_scratch_bytes", -1)
         self.scratch = torch.zeros(nbytes, dtype=torch.uint8, device=experts.device)   # zeroed: holds a barrier counter
 
-    def forward(self, logits, x, ids=None, weights=None, out=None, stream=None, peer=None):
+    def forward(self, logits, x, ids=None, weights=None, out=None, stream=None, peer=None, hc=None):
+        """hc = (R_old [T, 4, n_embd], post [T, 4], comb [T, 4, 4], R_new [T, 4, n_embd]): also write the block's output
+        into the residual stack (glmf::hc_post) - in the layer kernel's epilogue for one token."""
         T = logits.shape[0]
         dev = logits.device
         ids = ids if ids is not None else torch.empty((T, self.cfg.k), dtype=torch.int32, device=dev)
         weights = weights if weights is not None else torch.empty((T, self.cfg.k), dtype=torch.float32, device=dev)
         out = out if out is not None else torch.empty((T, self.cfg.n_embd), dtype=torch.float32, device=dev)
         assert x.dtype in (torch.float32, torch.bfloat16)
+        if hc is not None:
+            args = HcPostArgs(*[_ptr(t) for t in hc])
+            seq = 0
+            if peer is not None:
+                seq = 0 if (peer.device_seq and T == 1) else peer.next_seq()
+            _check("moe_layer_decode_hc",
+                   _lib.load().maya_moe_layer_decode_hc(C.byref(self.desc), _ptr(logits), _ptr(x), int(x.dtype == torch.bfloat16),
+                                                        T, _ptr(ids), _ptr(weights), _ptr(out), _ptr(self.scratch),
+                                                        self.scratch.numel(), C.byref(peer.desc) if peer is not None else None,
+                                                        peer.mi if peer is not None else 0, seq, C.byref(args), _stream(stream)))
+            return ids, weights, out
         if peer is not None:     # expert-parallel: `out` becomes the rank-ordered sum over the group (peer.PeerRank)
             _check("moe_layer_decode_ar",
                    _lib.load().maya_moe_layer_decode_ar(C.byref(self.desc), _ptr(logits), _ptr(x), int(x.dtype == torch.bfloat16),

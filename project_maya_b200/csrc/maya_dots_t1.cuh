@@ -141,12 +141,38 @@ template<> struct Dec1<MAYA_IQ3_S> {
     }
 };
 
-// NR rows against the one staged column; out[r] is bit-identical to rows_dot<T, NR, 1>.  UNR > 1 puts UNR passes of
-// the lane loop into one basic block so that the loads of NR x UNR blocks are in flight together (the loop is bound by
-// load latency, not by bytes); every lane still adds its terms in ascending k, so the bits do not change.
-template<int T, int NR, int UNR = 1>
+// NR rows against the one staged column; out[r] is bit-identical to rows_dot<T, NR, 1>.
+template<int T, int NR>
 __device__ __forceinline__ void rows_dot1(const uint8_t* const* rows, const XCols& x, int n_in, int lane,
                                           const uint32_t* tab, float (&out)[NR]) {
+    using D = Dec1<T>;
+    const int ncalls = (n_in / Fmt<T>::qk) * D::cpb;
+    float acc[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) acc[r] = 0.0f;
+    for (int k = lane; k < ncalls; k += 32) {
+        const int kb = k / D::cpb, ci = k - kb * D::cpb;
+        const int xb = kb * (Fmt<T>::qk / 32) + ci * D::xblk;
+        const XQ a = xq_load1(x, xb);
+        XQ b = a;
+        if constexpr (D::xblk == 2) b = xq_load1(x, xb + 1);
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            D dec;
+            dec.load(rows[r] + (size_t) kb * Fmt<T>::bytes, ci, tab, lane);
+            acc[r] = __fadd_rn(acc[r], dec.dot(a, b));
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r) out[r] = warp_sum(acc[r]);
+}
+
+// The same with two passes of the lane loop in one basic block, so that the loads of 2 x NR blocks are in flight
+// together (the loop is bound by load latency, not by bytes); every lane still adds its terms in ascending k, so the
+// bits do not change.  For the two-row items a block with little work runs.
+template<int T, int NR>
+__device__ __forceinline__ void rows_dot1_x2(const uint8_t* const* rows, const XCols& x, int n_in, int lane,
+                                             const uint32_t* tab, float (&out)[NR]) {
     using D = Dec1<T>;
     const int ncalls = (n_in / Fmt<T>::qk) * D::cpb;
     float acc[NR];
@@ -166,11 +192,9 @@ __device__ __forceinline__ void rows_dot1(const uint8_t* const* rows, const XCol
         }
     };
     int k = lane;
-    if constexpr (UNR > 1) {
-        for (; k + 32 * (UNR - 1) < ncalls; k += 32 * UNR) {
-#pragma unroll
-            for (int u = 0; u < UNR; ++u) pass(k + 32 * u);
-        }
+    for (; k + 32 < ncalls; k += 64) {
+        pass(k);
+        pass(k + 32);
     }
     for (; k < ncalls; k += 32) pass(k);
 #pragma unroll

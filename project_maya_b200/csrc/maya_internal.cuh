@@ -34,6 +34,6 @@ int win_combine(const unsigned long long* plan_ptr, const float* plan_w, int T, 
 bool fused_t1_supported(const maya_moe_layer& L);
 int fused_t1(const maya_moe_layer& L, const float* logits, const void* x, int x_is_bf16, int* ids, float* weights,
              float* out, float* h_scratch, unsigned* sync, const maya_peer_ar* ar, int ar_rank, unsigned ar_seq,
-             cudaStream_t s);
+             const maya_hc_post_args* hc, cudaStream_t s);
 
 }  // namespace maya

@@ -25,6 +25,7 @@
 #include "maya_peer_ar.cuh"
 #include <type_traits>
 
+#include "maya_hc_post.cuh"
 #include "maya_router.cuh"
 
 namespace maya {
@@ -55,6 +56,7 @@ struct FusedArgs {
     maya_peer_ar ar;           // ar.nm >= 2: sum `out` over the ranks in the epilogue
     int ar_rank;
     unsigned ar_seq;
+    maya_hc_post_args hc;      // hc.R_new != NULL: the hyper-connection write of `out` into the residual stack, last
     unsigned* sync;            // scratch: [0] arrivals, [1] epoch, [2] error, [4..13] block 0's phase time stamps (ns)
 };
 
@@ -246,12 +248,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
                     const int ei = u / ng, ra = (u - ei * ng) * 32 + warp, e = sh.ve[ei];
                     const uint8_t* blob = (const uint8_t*) sh.ptr[e];
                     const uint8_t* rows[2] = {blob + (size_t) ra * rb, blob + (size_t) (n_ff + ra) * rb};
-                    rows_dot1<T, 2, 2>(rows, X, n_embd, lane, s_tab, o);
+                    rows_dot1_x2<T, 2>(rows, X, n_embd, lane, s_tab, o);
                 } else if constexpr (TS != 0) {
                     const int ra = A.sh_lo + (u - units_r) * 32 + warp;
                     const size_t rbs = row_bytes(TS, n_embd);
                     const uint8_t* rows[2] = {A.shared + (size_t) ra * rbs, A.shared + (size_t) (A.n_ff_sh + ra) * rbs};
-                    rows_dot1<TS, 2, 2>(rows, X, n_embd, lane, nullptr, o);
+                    rows_dot1_x2<TS, 2>(rows, X, n_embd, lane, nullptr, o);
                 }
                 if (lane == 0) sh.hbuf[nu4][warp] = swiglu(o[0], o[1], A.limit);
             }
@@ -381,6 +383,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
         peer_allreduce_block_words(A.out, u0, u1, A.ar, A.ar_rank, sh.ar_seq, blockIdx.x);
     }
     __syncthreads();
+    if (A.hc.R_new != nullptr) {    // the consumer of `out`: this block's rows are final (and the same on every rank)
+        int e0 = o0, e1 = o1;
+        if (A.ar.nm >= 2) { slice(n_embd / 4, gridDim.x, blockIdx.x, e0, e1); e0 *= 4; e1 *= 4; }
+        hc_post_rows(A.out, A.hc, n_embd, e0, e1, tid, kFusedThreads);
+    }
     stamp(A.sync, 5);
     // the launch's last word: the next launch on this scratch (stream-ordered) starts a new epoch
     if (blockIdx.x == 0 && tid == 0) {
@@ -427,8 +434,9 @@ bool fused_t1_supported(const maya_moe_layer& L) {
 
 int fused_t1(const maya_moe_layer& L, const float* logits, const void* x, int x_is_bf16, int* ids, float* weights,
              float* out, float* h_scratch, unsigned* sync, const maya_peer_ar* ar, int ar_rank, unsigned ar_seq,
-             cudaStream_t s) {
+             const maya_hc_post_args* hc, cudaStream_t s) {
     FusedArgs A{};
+    if (hc != nullptr) A.hc = *hc;
     if (ar != nullptr) { A.ar = *ar; A.ar_rank = ar_rank; A.ar_seq = ar_seq; }
     A.logits = logits; A.x = x; A.x_is_bf16 = x_is_bf16;
     A.n_embd = L.n_embd; A.n_ff = L.n_ff; A.n_expert = L.n_expert; A.k = L.k;

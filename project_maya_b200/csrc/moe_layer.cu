@@ -128,7 +128,8 @@ extern "C" int maya_moe_layer_phase_ns(const maya_moe_layer* L, const void* scra
 
 static int layer_decode(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16, int n_tokens, int* ids,
                         float* weights, float* out, void* scratch, size_t scratch_bytes, const maya_peer_ar* ar, int mi,
-                        unsigned seq, void* stream);
+                        unsigned seq, void* stream, const maya_hc_post_args* hc = nullptr);
+static int ar_args_ok(const maya_moe_layer* L, int n_tokens, float* out, const maya_peer_ar* a, int mi, unsigned seq);
 
 extern "C" int maya_moe_layer_decode(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
                                      int n_tokens, int* ids, float* weights, float* out, void* scratch,
@@ -139,19 +140,44 @@ extern "C" int maya_moe_layer_decode(const maya_moe_layer* L, const float* logit
 extern "C" int maya_moe_layer_decode_ar(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
                                         int n_tokens, int* ids, float* weights, float* out, void* scratch,
                                         size_t scratch_bytes, const maya_peer_ar* a, int mi, unsigned seq, void* stream) {
+    if (ar_args_ok(L, n_tokens, out, a, mi, seq) != MAYA_OK) return refuse(MAYA_ERR_ARG);
+    return layer_decode(L, logits, x, x_is_bf16, n_tokens, ids, weights, out, scratch, scratch_bytes, a, mi, seq, stream);
+}
+
+static int ar_args_ok(const maya_moe_layer* L, int n_tokens, float* out, const maya_peer_ar* a, int mi, unsigned seq) {
     if (!a || a->nm < 2 || a->nm > MAYA_PEER_AR_MAX_RANKS || mi < 0 || mi >= a->nm || !a->recv || !a->peer_recv ||
         !a->flags || !a->peer_flags || !a->error || a->timeout_ns == 0 || a->stride % 4)
-        return refuse(MAYA_ERR_ARG);
-    if (L && n_tokens > 0 && (size_t) n_tokens * L->n_embd > a->stride) return refuse(MAYA_ERR_ARG);
-    if (out && !aligned16(out)) return refuse(MAYA_ERR_ARG);
+        return MAYA_ERR_ARG;
+    if (L && n_tokens > 0 && (size_t) n_tokens * L->n_embd > a->stride) return MAYA_ERR_ARG;
+    if (out && !aligned16(out)) return MAYA_ERR_ARG;
     if (seq == 0u && (a->seq_counter == nullptr || n_tokens != 1 || (L && (L->staged || !fused_t1_supported(*L)))))
-        return refuse(MAYA_ERR_ARG);   // the device-side sequence number exists only in the fused single-token kernel
-    return layer_decode(L, logits, x, x_is_bf16, n_tokens, ids, weights, out, scratch, scratch_bytes, a, mi, seq, stream);
+        return MAYA_ERR_ARG;           // the device-side sequence number exists only in the fused single-token kernel
+    return MAYA_OK;
+}
+
+extern "C" int maya_moe_layer_decode_hc(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
+                                        int n_tokens, int* ids, float* weights, float* out, void* scratch,
+                                        size_t scratch_bytes, const maya_peer_ar* a, int mi, unsigned seq,
+                                        const maya_hc_post_args* hc, void* stream) {
+    if (!hc || !hc->R_old || !hc->post || !hc->comb || !hc->R_new || hc->R_new == hc->R_old) return refuse(MAYA_ERR_ARG);
+    if (a != nullptr && ar_args_ok(L, n_tokens, out, a, mi, seq) != MAYA_OK) return refuse(MAYA_ERR_ARG);
+    return layer_decode(L, logits, x, x_is_bf16, n_tokens, ids, weights, out, scratch, scratch_bytes, a, mi, seq, stream, hc);
+}
+
+// The staged paths' consumer: one hc_post launch per token, after `out` is complete.
+static int hc_post_tokens(const maya_hc_post_args* hc, const float* out, int T, int n_embd, void* stream) {
+    if (hc == nullptr) return MAYA_OK;
+    for (int t = 0; t < T; ++t) {
+        const int st = maya_hc_post(out + (size_t) t * n_embd, hc->R_old + (size_t) t * 4 * n_embd, hc->post + t * 4,
+                                    hc->comb + t * 16, n_embd, hc->R_new + (size_t) t * 4 * n_embd, stream);
+        if (st != MAYA_OK) return st;
+    }
+    return MAYA_OK;
 }
 
 static int layer_decode(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16, int n_tokens, int* ids,
                         float* weights, float* out, void* scratch, size_t scratch_bytes, const maya_peer_ar* ar, int mi,
-                        unsigned seq, void* stream) {
+                        unsigned seq, void* stream, const maya_hc_post_args* hc) {
     int st = check_layer(L);
     if (st != MAYA_OK) return refuse(st);
     if (n_tokens < 1 || n_tokens > MAYA_MAX_WIN_TOKENS) return refuse(MAYA_ERR_LIMIT);
@@ -163,7 +189,7 @@ static int layer_decode(const maya_moe_layer* L, const float* logits, const void
     int* d_ids = ids ? ids : S.ids;
     float* d_w = weights ? weights : S.weights;
     if (T == 1 && !L->staged && fused_t1_supported(*L))
-        return fused_t1(*L, logits, x, x_is_bf16, d_ids, d_w, out, S.h, S.sync, ar, mi, seq, s);
+        return fused_t1(*L, logits, x, x_is_bf16, d_ids, d_w, out, S.h, S.sync, ar, mi, seq, hc, s);
     if (L->n_ff_sh > 0 && L->shared_here && (L->sh_lo != 0 || (L->sh_hi != 0 && L->sh_hi != L->n_ff_sh)))
         return refuse(MAYA_ERR_ARG);                 // only the fused kernel slices the shared expert
 
@@ -204,8 +230,8 @@ static int layer_decode(const maya_moe_layer* L, const float* logits, const void
                               shared ? sh_blob + sh_down_off : nullptr, L->sh_d_type, S.sh_hq, L->n_ff_sh, S.sh_out, stream);
         if (st != MAYA_OK) return st;
         st = maya_moe_down(L->d_type, &P, L->k, L->n_embd, L->n_ff, down_off, S.hq, shared ? S.sh_out : nullptr, out, stream);
-        if (st != MAYA_OK || ar == nullptr) return st;
-        return maya_allreduce_peer(out, L->n_embd, ar, mi, seq, stream);
+        if (st == MAYA_OK && ar != nullptr) st = maya_allreduce_peer(out, L->n_embd, ar, mi, seq, stream);
+        return st == MAYA_OK ? hc_post_tokens(hc, out, 1, L->n_embd, stream) : st;
     }
     if (shared) {
         for (int c0 = 0; c0 < T; c0 += MAYA_MAX_COLS) {
@@ -236,6 +262,6 @@ static int layer_decode(const maya_moe_layer* L, const float* logits, const void
     W.limit = L->limit;
     W.down_off = down_off;
     st = maya_moe_win_experts(L->gu_type, L->d_type, &W, stream);
-    if (st != MAYA_OK || ar == nullptr) return st;
-    return maya_allreduce_peer(out, T * L->n_embd, ar, mi, seq, stream);
+    if (st == MAYA_OK && ar != nullptr) st = maya_allreduce_peer(out, T * L->n_embd, ar, mi, seq, stream);
+    return st == MAYA_OK ? hc_post_tokens(hc, out, T, L->n_embd, stream) : st;
 }

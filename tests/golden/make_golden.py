@@ -80,7 +80,9 @@ def glm5_router() -> None:
 def glm5_moe_layer(layer: int = 1) -> None:
     """Layer `layer` of data/glm5-synth.gguf (F32 tensors: 12 experts of 128 x 64, top-3 sigmoid routing, one shared
     expert) read through the package's own loader, with llama.cpp's captured activations of that layer for 8 tokens:
-    the normed hidden state that enters the MoE block, the routing, the routed output, the shared expert's output."""
+    the normed hidden state that enters the MoE block, the routing, the routed output, the shared expert's output; and
+    what follows the block: the residual stack before it (hc_attn_post), the hyper-connection gains (hc_post_ffn,
+    hc_comb_ffn - stored src-major, [src][dst]) and the residual stack after it (l_out)."""
     import gguf
     from project_maya_b200 import gguf_loader
     path = REFERENCE / "data" / "glm5-synth.gguf"
@@ -102,7 +104,9 @@ def glm5_moe_layer(layer: int = 1) -> None:
         ids=d("ffn_moe_topk", np.int32).reshape(n_tok, k), weights=d("ffn_moe_weights").reshape(n_tok, k),
         moe_out=d("ffn_moe_out").reshape(n_tok, L.n_embd), shexp=d("ffn_shexp").reshape(n_tok, L.n_embd),
         out=d("ffn_out").reshape(n_tok, L.n_embd), w_scale=np.float32(meta["expert_weights_scale"]),
-        clamp=np.float32(meta["swiglu_clamp_exp"]), clamp_sh=np.float32(meta["swiglu_clamp_shexp"]))
+        clamp=np.float32(meta["swiglu_clamp_exp"]), clamp_sh=np.float32(meta["swiglu_clamp_shexp"]),
+        hc_R_old=d("hc_attn_post").reshape(n_tok, 4, L.n_embd), hc_post=d("hc_post_ffn").reshape(n_tok, 4),
+        hc_comb_src_major=d("hc_comb_ffn").reshape(n_tok, 4, 4), hc_R_new=d("l_out").reshape(n_tok, 4, L.n_embd))
 
 
 def c1_experts():

@@ -99,6 +99,67 @@ def test_oracle_layer_matches_llama_cpp(g, oracle):
     assert H.rel_err(moe + shx, g["out"]) <= QUANT_TOL
 
 
+def hc_inputs(g, t):
+    """Token t's hyper-connection inputs in the kernels' convention: comb dst-major (llama.cpp stores [src][dst])."""
+    return g["hc_R_old"][t], g["hc_post"][t], np.ascontiguousarray(g["hc_comb_src_major"][t].T)
+
+
+def test_oracle_hc_post_matches_llama_cpp(g, oracle):
+    """What follows the MoE block: llama.cpp's residual stack after the layer (l_out) is the hyper-connection write of
+    its ffn_out into the stack before it - the oracle's hc_post on the captured tensors, to float rounding (llama.cpp
+    sums in another order)."""
+    for t in range(g["x"].shape[0]):
+        R_old, post, comb = hc_inputs(g, t)
+        got = oracle.hc_post(g["out"][t], R_old, post, comb)
+        assert np.abs(got - g["hc_R_new"][t]).max() <= 1e-6
+        wrong = oracle.hc_post(g["out"][t], R_old, post, comb.T.copy())      # the dst/src mix-up must show
+        assert np.abs(wrong - g["hc_R_new"][t]).max() > 1e-2
+
+
+@pytest.mark.gpu
+def test_hc_post_kernel_and_fused_epilogue(g, oracle, cuda):
+    """maya_hc_post is the oracle bit for bit (same product and multiply-add chain), on llama.cpp's captured tensors
+    and on a wide random case; the layer kernel's epilogue (maya_moe_layer_decode_hc) writes the same bits as the layer
+    followed by the stand-alone launch, for one token (fused) and a window (staged)."""
+    import torch as T
+    from project_maya_b200 import api
+    for t in range(g["x"].shape[0]):
+        R_old, post, comb = hc_inputs(g, t)
+        got = api.hc_post(*[T.from_numpy(np.ascontiguousarray(a)).cuda() for a in (g["out"][t], R_old, post, comb)])
+        assert got.cpu().numpy().tobytes() == oracle.hc_post(g["out"][t], R_old, post, comb).tobytes()
+        assert np.abs(got.cpu().numpy() - g["hc_R_new"][t]).max() <= 1e-6
+    rng = np.random.default_rng(3)
+    n = 6144
+    b, R = rng.standard_normal(n).astype(np.float32), rng.standard_normal((4, n)).astype(np.float32)
+    post, comb = rng.standard_normal(4).astype(np.float32), rng.standard_normal((4, 4)).astype(np.float32)
+    got = api.hc_post(*[T.from_numpy(a).cuda() for a in (b, R, post, comb)])
+    assert got.cpu().numpy().tobytes() == oracle.hc_post(b, R, post, comb).tobytes()
+    with pytest.raises(api.MayaError):
+        Rd = T.from_numpy(R).cuda()
+        api.hc_post(T.from_numpy(b).cuda(), Rd, T.from_numpy(post).cuda(), T.from_numpy(comb).cuda(), R_new=Rd)
+
+    cfg = api.MoeLayerConfig(1024, 512, 8, 2, H.Q8_0, H.Q8_0)
+    experts = T.empty((8, cfg.blob_bytes), dtype=T.uint8, device="cuda")
+    gu = 2 * 512 * H.row_bytes(H.Q8_0, 1024)
+    for e in range(8):
+        api.synth_weights(H.Q8_0, 2 * e, 0.02, 2 * 512, 1024, experts[e, :gu])
+        api.synth_weights(H.Q8_0, 2 * e + 1, 0.02, 1024, 512, experts[e, gu:])
+    layer = api.MoeLayer(cfg, experts, None)
+    ld = T.from_numpy(H.router_logits("hc", 5, 8, 1.1)).cuda()
+    xd = T.from_numpy(H.activations("hc", 5, 1024, "bf16")).to(T.bfloat16).cuda()
+    for sl in (slice(0, 1), slice(1, 5)):                      # one token: the fused kernel; four: the staged kernels
+        nt = sl.stop - sl.start
+        R_old = T.from_numpy(rng.standard_normal((nt, 4, 1024)).astype(np.float32)).cuda()
+        post_d = T.from_numpy(rng.standard_normal((nt, 4)).astype(np.float32)).cuda()
+        comb_d = T.from_numpy(rng.standard_normal((nt, 4, 4)).astype(np.float32)).cuda()
+        R_new = T.zeros((nt, 4, 1024), dtype=T.float32, device="cuda")
+        plain = layer.forward(ld[sl], xd[sl])[2].clone()
+        out = layer.forward(ld[sl], xd[sl], hc=(R_old, post_d, comb_d, R_new))[2]
+        assert T.equal(out, plain)
+        for t in range(nt):
+            assert T.equal(R_new[t], api.hc_post(plain[t], R_old[t], post_d[t], comb_d[t]))
+
+
 @pytest.mark.gpu
 def test_kernels_on_gguf_layer_match_llama_cpp(g, oracle, cuda):
     """The CUDA path on the same layer: sigmoid router (ids exact), plan-form gate/up + down with the shared expert's
