@@ -167,40 +167,6 @@ __device__ __forceinline__ void rows_dot1(const uint8_t* const* rows, const XCol
     for (int r = 0; r < NR; ++r) out[r] = warp_sum(acc[r]);
 }
 
-// The same with two passes of the lane loop in one basic block, so that the loads of 2 x NR blocks are in flight
-// together (the loop is bound by load latency, not by bytes); every lane still adds its terms in ascending k, so the
-// bits do not change.  For the two-row items a block with little work runs.
-template<int T, int NR>
-__device__ __forceinline__ void rows_dot1_x2(const uint8_t* const* rows, const XCols& x, int n_in, int lane,
-                                             const uint32_t* tab, float (&out)[NR]) {
-    using D = Dec1<T>;
-    const int ncalls = (n_in / Fmt<T>::qk) * D::cpb;
-    float acc[NR];
-#pragma unroll
-    for (int r = 0; r < NR; ++r) acc[r] = 0.0f;
-    auto pass = [&](int k) {
-        const int kb = k / D::cpb, ci = k - kb * D::cpb;
-        const int xb = kb * (Fmt<T>::qk / 32) + ci * D::xblk;
-        const XQ a = xq_load1(x, xb);
-        XQ b = a;
-        if constexpr (D::xblk == 2) b = xq_load1(x, xb + 1);
-#pragma unroll
-        for (int r = 0; r < NR; ++r) {
-            D dec;
-            dec.load(rows[r] + (size_t) kb * Fmt<T>::bytes, ci, tab, lane);
-            acc[r] = __fadd_rn(acc[r], dec.dot(a, b));
-        }
-    };
-    int k = lane;
-    for (; k + 32 < ncalls; k += 64) {
-        pass(k);
-        pass(k + 32);
-    }
-    for (; k < ncalls; k += 32) pass(k);
-#pragma unroll
-    for (int r = 0; r < NR; ++r) out[r] = warp_sum(acc[r]);
-}
-
 // Calls a row of n_in values takes (one lane makes one call per pass of rows_dot1's loop).
 template<int T>
 __device__ __forceinline__ int calls_per_row(int n_in) { return (n_in / Fmt<T>::qk) * Dec1<T>::cpb; }

@@ -248,12 +248,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
                     const int ei = u / ng, ra = (u - ei * ng) * 32 + warp, e = sh.ve[ei];
                     const uint8_t* blob = (const uint8_t*) sh.ptr[e];
                     const uint8_t* rows[2] = {blob + (size_t) ra * rb, blob + (size_t) (n_ff + ra) * rb};
-                    rows_dot1_x2<T, 2>(rows, X, n_embd, lane, s_tab, o);
+                    rows_dot1<T, 2>(rows, X, n_embd, lane, s_tab, o);
                 } else if constexpr (TS != 0) {
                     const int ra = A.sh_lo + (u - units_r) * 32 + warp;
                     const size_t rbs = row_bytes(TS, n_embd);
                     const uint8_t* rows[2] = {A.shared + (size_t) ra * rbs, A.shared + (size_t) (A.n_ff_sh + ra) * rbs};
-                    rows_dot1_x2<TS, 2>(rows, X, n_embd, lane, nullptr, o);
+                    rows_dot1<TS, 2>(rows, X, n_embd, lane, nullptr, o);
                 }
                 if (lane == 0) sh.hbuf[nu4][warp] = swiglu(o[0], o[1], A.limit);
             }
