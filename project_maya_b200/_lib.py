@@ -5,10 +5,12 @@ There is no fallback: if the library has not been built, importing the compute e
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
-LIB_PATH = PKG / "libmaya_moe.so"
+# MAYA_MOE_LIB: another build of the same library (comparing two builds on one machine); it must export the same ABI
+LIB_PATH = Path(os.environ.get("MAYA_MOE_LIB") or PKG / "libmaya_moe.so")
 
 c_void_p, c_int, c_float, c_size_t, c_int64, c_uint64 = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_int64, C.c_uint64
 
