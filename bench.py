@@ -377,7 +377,8 @@ def gpu_arm(args) -> None:
     # ---- the dominant kernel alone: gate/up of the routed experts (+ the shared expert's down rows in the same launch)
     roof = None
     if rank == 0:
-        roof = dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, min(K, 64), stream, world)
+        roof = dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, min(K, 64), stream, world,
+                                        ms_dev * 1e3 / K, use_graph)
         if world > 1:
             names = ["route+quantize", "gate_up", "grid_barrier", "down+combine", "cross_rank_sum"]
             roof["block0_phase_end_us_last_timed_step"] = {n: step_phases[i + 1] / 1e3 for i, n in enumerate(names)}
@@ -424,12 +425,16 @@ def gpu_arm(args) -> None:
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one moe_layer_t1_kernel launch of this workload on one GPU, from the ncu
 # capture summarised in profiles/moe_layer_t1_kernel_C2.md (the algorithmic bytes are 136.8 MB: no re-reads)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 140.6e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 141.9e6
 
 
-def dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, steps: int, stream, world: int = 1) -> dict:
-    """Times the fused layer kernel alone: one CUDA-event pair per launch on the launching stream, same rotating
-    layers and tokens as the timed loop (so every launch reads its experts from HBM)."""
+def dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, steps: int, stream, world: int, us_step: float,
+                             in_graph: bool) -> dict:
+    """The fused layer kernel against the HBM roofline.  A step of the timed loop IS one launch of this kernel (with the
+    cross-rank sum in its epilogue at N > 1), so its average launch duration is the timed region's CUDA-event time over
+    its K launches (us_step; it includes the gap between two launches of the graph).  A second leg times launches one
+    by one, eagerly, with an event pair each - same rotating layers and tokens - for block 0's phase stamps and as a
+    cross-check (event records and eager launch overhead make it the larger number)."""
     cfg = CFG
     Hd, k = cfg["n_embd"], cfg["k"]
     ids = torch.empty((1, k), dtype=torch.int32, device="cuda")
@@ -444,14 +449,17 @@ def dominant_kernel_roofline(torch, api, lc, layers, logits_d, x_d, steps: int, 
                 layers[s % len(layers)].forward(logits_d[tok:tok + 1], x_d[tok:tok + 1], ids, w, out)
                 evs[s][1].record(stream)
             stream.synchronize()
-    us = float(np.mean([a.elapsed_time(b) for a, b in evs])) * 1e3
+    us_eager = float(np.mean([a.elapsed_time(b) for a, b in evs])) * 1e3
+    us = us_step if in_graph else us_eager
     phases = layers[(steps - 1) % len(layers)].phase_ns(stream)
     peak, kind = measured_peaks()
     alg = algorithmic_bytes_per_token() // world        # N > 1: this rank's mean share (its experts, its slice of the shared one)
     achieved = alg / (us * 1e-6) / 1e9
     return {"bound": "hbm", "kernel": "moe_layer_t1_kernel<IQ2_S, Q8_0> (the whole layer: route, q8_1, gate/up + SwiGLU, down, combine)",
             "achieved": achieved, "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": achieved / peak,
-            "algorithmic_bytes_per_launch": alg, "us_per_launch": us, "launches_timed": steps,
+            "algorithmic_bytes_per_launch": alg, "us_per_launch": us,
+            "us_per_launch_from": "the timed region: CUDA events around the graph of K launches, / K" if in_graph else "one CUDA-event pair per eager launch",
+            "us_per_launch_eager_event_pairs": us_eager, "eager_launches_timed": steps,
             "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
             "block0_phase_end_us": {"route+quantize": phases[1] / 1e3, "gate_up": phases[2] / 1e3, "grid_barrier": phases[3] / 1e3,
                                     "down+combine": phases[4] / 1e3}}
