@@ -23,6 +23,7 @@
 #include "maya_dots_t1.cuh"
 #include "maya_internal.cuh"
 #include "maya_peer_ar.cuh"
+#include <cstdlib>
 #include <type_traits>
 
 #include "maya_hc_post.cuh"
@@ -145,6 +146,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     int* cs = (int*) (s_cols + (size_t) cols_blocks * 36);
     double* s_ex = (double*) (s_cols + (size_t) cols_blocks * 40);
 
+    // Programmatic dependent launch: the next launch on the stream may be set up while this one runs, and this one may
+    // have started before the launch in front of it ended.  Nothing of global memory is read or written before
+    // grid_dependency_wait() (only the codebook, a constant of the library, is copied to shared memory before it);
+    // without the launch attribute both instructions do nothing.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (tid >= kRouteThreads) load_tab_rep<T>(s_tab, tid - kRouteThreads, kFusedThreads - kRouteThreads);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (tid == 0) {
         sh.epoch = *(volatile unsigned*) &A.sync[1];
         sh.ar_seq = A.ar_seq != 0u || A.ar.seq_counter == nullptr ? A.ar_seq : *(volatile unsigned*) A.ar.seq_counter + 1u;
@@ -175,8 +183,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             sh.nv = nv;
         }
     } else {
-        const int t2 = tid - kRouteThreads, n2 = kFusedThreads - kRouteThreads;
-        load_tab_rep<T>(s_tab, t2, n2);
+        const int t2 = tid - kRouteThreads;
         // the token's activations: 8 loads in flight per lane before the first is used (they come from HBM)
         constexpr int NW2 = (kFusedThreads - kRouteThreads) / 32;
         for (int b0 = (t2 >> 5); b0 < nblk_x; b0 += 8 * NW2) {
@@ -358,11 +365,57 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
         using std::true_type;
         using std::false_type;
         int it = warp;
+#ifdef MAYA_EXP_QUADS
+        const bool long_rows = dr.groups == 1 && dr.rpi == 2 && (!has_sh || (ds.groups == 1 && ds.rpi == 2));
+        if (long_rows) {
+            // Long rows (two or more passes of the lane loop): four rows an item keep more loads in flight than two.
+            // Whole rounds of the 32 warps run such quads; a last round of at most 16 quads is split into row pairs so
+            // that it takes every warp half as long instead of half the warps as long.
+            const int Q = (nrows + 3) / 4, nE = sh.nv + (has_sh ? 1 : 0), total4 = nE * Q, full = total4 & ~31, rest = total4 - full;
+            auto item = [&](auto nr_c, int qi, int first_row) {
+                constexpr int NR = decltype(nr_c)::value;
+                const int ei = qi / Q;
+                const int e = ei < sh.nv ? sh.ve[ei] : k;
+                const int r0 = (qi - ei * Q) * 4 + first_row;
+                XCols H;
+                H.q = cq + (size_t) 2 * e * nblk_h; H.d = cd + (size_t) e * nblk_h; H.isum = cs + (size_t) e * nblk_h;
+                H.nblk = nblk_h;
+                float o[NR];
+                const uint8_t* rows[NR];
+                if (e < k) {
+                    const uint8_t* base = (const uint8_t*) sh.ptr[e] + down_off;
+#pragma unroll
+                    for (int r = 0; r < NR; ++r) rows[r] = base + (size_t) (o0 + min(r0 + r, nrows - 1)) * drb;
+                    rows_dot1<T, NR>(rows, H, n_ff, lane, s_tab, o);
+                } else if constexpr (TS != 0) {
+                    const int b0 = A.sh_lo / 32, n_in = A.sh_hi - A.sh_lo;
+                    const size_t pitch = row_bytes(TS, A.n_ff_sh);
+                    const uint8_t* base = A.shared + 2 * (size_t) A.n_ff_sh * row_bytes(TS, n_embd) + row_bytes(TS, A.sh_lo);
+                    H.q += 2 * b0; H.d += b0; H.isum += b0; H.nblk = n_in / 32;
+#pragma unroll
+                    for (int r = 0; r < NR; ++r) rows[r] = base + (size_t) (o0 + min(r0 + r, nrows - 1)) * pitch;
+                    rows_dot1<TS, NR>(rows, H, n_in, lane, nullptr, o);
+                }
+                if (lane == 0) {
+#pragma unroll
+                    for (int r = 0; r < NR; ++r)
+                        if (r0 + r < nrows) sh.part[r0 + r][e] = o[r];
+                }
+            };
+            const int endA = rest > 16 ? total4 : full;
+            for (; it < endA; it += NW) item(integral_constant<int, 4>{}, it, 0);
+            if (rest > 0 && rest <= 16 && warp < 2 * rest) item(integral_constant<int, 2>{}, full + (warp >> 1), 2 * (warp & 1));
+        } else
+#endif
         if (dr.groups > 1) it = run(integral_constant<int, T>{}, integral_constant<int, 4>{}, true_type{}, true_type{}, it, items_r, dr);
         else if (dr.rpi == 4) it = run(integral_constant<int, T>{}, integral_constant<int, 4>{}, false_type{}, true_type{}, it, items_r, dr);
         else it = run(integral_constant<int, T>{}, integral_constant<int, 2>{}, false_type{}, true_type{}, it, items_r, dr);
         if constexpr (TS != 0) {
+#ifdef MAYA_EXP_QUADS
+            if (!has_sh || long_rows) {
+#else
             if (!has_sh) {
+#endif
             } else if (ds.groups > 1) run(integral_constant<int, TS>{}, integral_constant<int, 4>{}, true_type{}, false_type{}, it, items_all, ds);
             else if (ds.rpi == 4) run(integral_constant<int, TS>{}, integral_constant<int, 4>{}, false_type{}, false_type{}, it, items_all, ds);
             else run(integral_constant<int, TS>{}, integral_constant<int, 2>{}, false_type{}, false_type{}, it, items_all, ds);
@@ -418,6 +471,31 @@ int launch_fused(const FusedArgs& A, cudaStream_t s) {
     if (A.ar.nm >= 2 && grid > MAYA_PEER_AR_BLOCKS) return refuse(MAYA_ERR_LIMIT);
     FusedArgs args = A;
     void* params[] = {&args};
+    // Cooperative (the grid barrier needs every block resident) and, when asked for and accepted by the driver,
+    // programmatically serialized after the launch in front of it: its set-up then overlaps that launch's tail.
+    static int pdl = -1;                       // -1: not tried; 0: off or refused; 1: in use
+    if (pdl < 0) {
+        const char* e = std::getenv("MAYA_MOE_PDL");       // "0" turns it off
+        pdl = e != nullptr && e[0] == '0' ? 0 : 1;
+    }
+    if (pdl == 1) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(kFusedThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute at[2];
+        at[0].id = cudaLaunchAttributeCooperative;
+        at[0].val.cooperative = 1;
+        at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 2;
+        if (cudaLaunchKernelExC(&cfg, (const void*) moe_layer_t1_kernel<T, TS>, params) == cudaSuccess)
+            return note_launch("moe_layer_t1");
+        cudaGetLastError();                    // refused in this form: clear, and use the plain cooperative launch from now on
+        pdl = 0;
+    }
     cudaLaunchCooperativeKernel((const void*) moe_layer_t1_kernel<T, TS>, dim3(grid), dim3(kFusedThreads), params, smem, s);
     return note_launch("moe_layer_t1");
 }
