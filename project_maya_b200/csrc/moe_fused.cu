@@ -365,57 +365,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
         using std::true_type;
         using std::false_type;
         int it = warp;
-#ifdef MAYA_EXP_QUADS
-        const bool long_rows = dr.groups == 1 && dr.rpi == 2 && (!has_sh || (ds.groups == 1 && ds.rpi == 2));
-        if (long_rows) {
-            // Long rows (two or more passes of the lane loop): four rows an item keep more loads in flight than two.
-            // Whole rounds of the 32 warps run such quads; a last round of at most 16 quads is split into row pairs so
-            // that it takes every warp half as long instead of half the warps as long.
-            const int Q = (nrows + 3) / 4, nE = sh.nv + (has_sh ? 1 : 0), total4 = nE * Q, full = total4 & ~31, rest = total4 - full;
-            auto item = [&](auto nr_c, int qi, int first_row) {
-                constexpr int NR = decltype(nr_c)::value;
-                const int ei = qi / Q;
-                const int e = ei < sh.nv ? sh.ve[ei] : k;
-                const int r0 = (qi - ei * Q) * 4 + first_row;
-                XCols H;
-                H.q = cq + (size_t) 2 * e * nblk_h; H.d = cd + (size_t) e * nblk_h; H.isum = cs + (size_t) e * nblk_h;
-                H.nblk = nblk_h;
-                float o[NR];
-                const uint8_t* rows[NR];
-                if (e < k) {
-                    const uint8_t* base = (const uint8_t*) sh.ptr[e] + down_off;
-#pragma unroll
-                    for (int r = 0; r < NR; ++r) rows[r] = base + (size_t) (o0 + min(r0 + r, nrows - 1)) * drb;
-                    rows_dot1<T, NR>(rows, H, n_ff, lane, s_tab, o);
-                } else if constexpr (TS != 0) {
-                    const int b0 = A.sh_lo / 32, n_in = A.sh_hi - A.sh_lo;
-                    const size_t pitch = row_bytes(TS, A.n_ff_sh);
-                    const uint8_t* base = A.shared + 2 * (size_t) A.n_ff_sh * row_bytes(TS, n_embd) + row_bytes(TS, A.sh_lo);
-                    H.q += 2 * b0; H.d += b0; H.isum += b0; H.nblk = n_in / 32;
-#pragma unroll
-                    for (int r = 0; r < NR; ++r) rows[r] = base + (size_t) (o0 + min(r0 + r, nrows - 1)) * pitch;
-                    rows_dot1<TS, NR>(rows, H, n_in, lane, nullptr, o);
-                }
-                if (lane == 0) {
-#pragma unroll
-                    for (int r = 0; r < NR; ++r)
-                        if (r0 + r < nrows) sh.part[r0 + r][e] = o[r];
-                }
-            };
-            const int endA = rest > 16 ? total4 : full;
-            for (; it < endA; it += NW) item(integral_constant<int, 4>{}, it, 0);
-            if (rest > 0 && rest <= 16 && warp < 2 * rest) item(integral_constant<int, 2>{}, full + (warp >> 1), 2 * (warp & 1));
-        } else
-#endif
         if (dr.groups > 1) it = run(integral_constant<int, T>{}, integral_constant<int, 4>{}, true_type{}, true_type{}, it, items_r, dr);
         else if (dr.rpi == 4) it = run(integral_constant<int, T>{}, integral_constant<int, 4>{}, false_type{}, true_type{}, it, items_r, dr);
         else it = run(integral_constant<int, T>{}, integral_constant<int, 2>{}, false_type{}, true_type{}, it, items_r, dr);
         if constexpr (TS != 0) {
-#ifdef MAYA_EXP_QUADS
-            if (!has_sh || long_rows) {
-#else
             if (!has_sh) {
-#endif
             } else if (ds.groups > 1) run(integral_constant<int, TS>{}, integral_constant<int, 4>{}, true_type{}, false_type{}, it, items_all, ds);
             else if (ds.rpi == 4) run(integral_constant<int, TS>{}, integral_constant<int, 4>{}, false_type{}, false_type{}, it, items_all, ds);
             else run(integral_constant<int, TS>{}, integral_constant<int, 2>{}, false_type{}, false_type{}, it, items_all, ds);
