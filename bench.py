@@ -391,7 +391,8 @@ def gpu_arm(args) -> None:
         line = {
             "metric": "MoE expert-FFN decode tokens/s per layer", "value": value, "unit": "tok/s/layer", "n_gpus": world,
             "steps": K, "warmup": max(W, 3), "ms_per_step": ms_dev / K, "higher_is_better": True,
-            "scaling": "strong",     # the token stream is the same at every N: the experts (the work) are divided among the ranks "vs_baseline": None, "dtype": "int8 x int8 -> f32", "data": "synthetic",
+            "scaling": "strong",     # the token stream is the same at every N: the experts (the work) are divided among the ranks
+            "vs_baseline": None, "dtype": "int8 x int8 -> f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "layers_resident": len(layers),
                        "l2": "inputs larger than L2: steps rotate over %d resident layers and 256 tokens" % len(layers),
                        "launch": ("CUDA graph of the K steps" + (", partial outputs summed over peer HBM in the layer kernel's epilogue" if peer is not None else "")),
