@@ -261,13 +261,22 @@ def gpu_arm(args) -> None:
     logits_h = torch.from_numpy(S.router_logits("C2", N_TOKENS, E, cfg["zipf"])).pin_memory()
     x_h = torch.from_numpy(S.bf16_bits(S.activations("C2", N_TOKENS, Hd, "bf16")).view(np.int16)).view(torch.bfloat16).pin_memory()
     logits_d, x_d = logits_h.cuda(), x_h.cuda()
+    # a step's inputs as one pinned record [logits f32 | x bf16], the way an engine hands a token over: one copy a step
+    IN_L, IN_BYTES = E * 4, E * 4 + Hd * 2
+    in_h = torch.empty((N_TOKENS, IN_BYTES), dtype=torch.uint8).pin_memory()
+    in_h[:, :IN_L] = logits_h.view(torch.uint8).view(N_TOKENS, IN_L)
+    in_h[:, IN_L:] = x_h.view(torch.uint8).view(N_TOKENS, Hd * 2)
     K, W = args.steps, args.warmup
     out_d = torch.empty((K, Hd), dtype=torch.float32, device="cuda")
     ids_d = torch.empty((K, k), dtype=torch.int32, device="cuda")
     w_d = torch.empty((K, k), dtype=torch.float32, device="cuda")
     out_h = torch.empty((K, Hd), dtype=torch.float32).pin_memory()
-    stage_l = torch.empty((K, E), dtype=torch.float32, device="cuda")
-    stage_x = torch.empty((K, Hd), dtype=torch.bfloat16, device="cuda")
+    stage = torch.empty((K, IN_BYTES), dtype=torch.uint8, device="cuda")
+    stage_l = [None] * K
+    stage_x = [None] * K
+    for s_ in range(K):
+        stage_l[s_] = stage[s_, :IN_L].view(torch.float32).view(1, E)
+        stage_x[s_] = stage[s_, IN_L:].view(torch.bfloat16).view(1, Hd)
 
     peer = None
     if world > 1 and args.ar == "peer":
@@ -300,12 +309,11 @@ def gpu_arm(args) -> None:
             with torch.cuda.stream(s_in):
                 if s >= E2E_DEPTH:
                     s_in.wait_event(done[s - E2E_DEPTH])
-                stage_l[s:s + 1].copy_(logits_h[tok:tok + 1], non_blocking=True)
-                stage_x[s:s + 1].copy_(x_h[tok:tok + 1], non_blocking=True)
+                stage[s].copy_(in_h[tok], non_blocking=True)
                 ready = torch.cuda.Event()
                 ready.record(s_in)
             cur.wait_event(ready)
-            step(s, stage_l[s:s + 1], stage_x[s:s + 1])
+            step(s, stage_l[s], stage_x[s])
             ev = torch.cuda.Event()
             ev.record(cur)
             done.append(ev)
@@ -317,9 +325,8 @@ def gpu_arm(args) -> None:
 
     def step_e2e(s: int):                      # the unpipelined form, for the eager warm-up only
         tok = s % N_TOKENS
-        stage_l[s:s + 1].copy_(logits_h[tok:tok + 1], non_blocking=True)
-        stage_x[s:s + 1].copy_(x_h[tok:tok + 1], non_blocking=True)
-        step(s, stage_l[s:s + 1], stage_x[s:s + 1])
+        stage[s].copy_(in_h[tok], non_blocking=True)
+        step(s, stage_l[s], stage_x[s])
         out_h[s:s + 1].copy_(out_d[s:s + 1], non_blocking=True)
 
     stream = torch.cuda.Stream()
