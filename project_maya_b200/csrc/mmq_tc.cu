@@ -55,10 +55,10 @@ constexpr uint32_t kACol = 2 * TN;      // the A operand's 3 stages from 320: pe
 constexpr int kMaxUnits = 16;
 constexpr int kDone = 16;               // ring of "pair of K steps consumed" barriers (one tcgen05.commit per pair: a commit
                                         // costs the tensor pipe about as much as a product)
-// Raw weight units.  Q8_0 / Q4_K: a row's 256 K-values are 272 / 144 bytes, a multiple of 16, so a unit is one tiled TMA
-// box (64 rows).  IQ2_S / IQ3_S blocks are 82 / 110 bytes: a unit is 64 per-row bulk copies of the 16-byte aligned
-// window around the row's block (96 / 128 bytes), rows 112 / 144 bytes apart in shared memory (an odd number of
-// 16-byte words: a warp's 16-byte reads of 32 rows fall in different banks).
+// Raw weight units, one tiled TMA box of 64 rows each.  Q8_0 / Q4_K: a row's 256 K-values are 272 / 144 bytes, a
+// multiple of 16.  IQ2_S / IQ3_S blocks are 82 / 110 bytes: the box is the 16-byte aligned window around the rows' block
+// (96 / 128 bytes used) taken 112 / 144 bytes wide, so that rows are an odd number of 16-byte words apart in shared
+// memory (a warp's 16-byte reads of 32 rows fall in different banks).
 template<int T> constexpr bool kIq = T == MAYA_IQ2_S || T == MAYA_IQ3_S;
 template<int T> constexpr int kBlkBytes = T == MAYA_IQ2_S ? 82 : T == MAYA_IQ3_S ? 110 : 0;
 template<int T> constexpr int kWin = T == MAYA_IQ2_S ? 96 : 128;
@@ -539,36 +539,6 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             atomicAdd(A.probe + 8, 1ull);
             atomicAdd(A.probe + 9, (unsigned long long) nkt);
         }
-    } else if (warp == kDqWarps && kIq<T>) {
-        // ------------------------------------------------------------ raw weight units of the i-quants: the whole warp,
-        //                                                              a lane copies the windows of rows lane, lane + 32
-        if constexpr (kIq<T>) {
-            const size_t rbw = row_bytes(T, A.w_cols);
-            const uint8_t* wexp = A.w + (size_t) found_e * A.expert_bytes;
-            int issued = 0;
-            bool ok = true;
-            for (int kb = 0; kb < nkb && ok; ++kb) {
-                const size_t koff = ((size_t) kb * kBlkBytes<T>) & ~(size_t) 15;
-                const uint32_t wbytes = (uint32_t) min((size_t) kWin<T>, rbw - koff);     // never past the end of the row
-                for (int sl = 0; sl < 4; ++sl) {
-                    const int u = kb * 4 + sl, slot = u % NU;
-                    if (u >= NU && !wait_or_fail(P, &P.raw_empty[slot], ((u / NU) - 1) & 1)) { ok = false; break; }
-                    const int wrow = GLU ? (sl < 2 ? m0 + 64 * sl : A.w_rows + m0 + 64 * (sl - 2)) : m0 + 64 * sl;
-                    const int valid = max(0, min(kUnitRows, A.mat_rows - wrow));     // rows of the unit that exist
-                    if (lane == 0) {
-                        if (valid > 0) mbar_expect_tx(&P.raw_full[slot], (uint32_t) valid * wbytes);
-                        else mbar_arrive(&P.raw_full[slot]);
-                    }
-                    __syncwarp();
-                    uint8_t* ubase = raw + (size_t) slot * kUnitBytes<T>;
-                    for (int rr = lane; rr < valid; rr += 32)
-                        bulk_load(ubase + rr * kRawRow<T>, wexp + (size_t) (wrow + rr) * rbw + koff, wbytes, &P.raw_full[slot]);
-                    issued = u + 1;
-                }
-            }
-            if (!ok)                                             // let the copies in flight land before the block ends
-                for (int u = max(0, issued - NU); u < issued; ++u) wait_or_fail(P, &P.raw_full[u % NU], (u / NU) & 1);
-        }
     } else if (warp == kDqWarps) {
         // ------------------------------------------------------------ raw weight units (one lane)
         if (lane == 0) {
@@ -580,7 +550,10 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                     if (u >= NU && !wait_or_fail(P, &P.raw_empty[slot], ((u / NU) - 1) & 1)) { ok = false; break; }
                     const int wrow = GLU ? (sl < 2 ? m0 + 64 * sl : A.w_rows + m0 + 64 * (sl - 2)) : m0 + 64 * sl;
                     mbar_expect_tx(&P.raw_full[slot], kUnitBytes<T>);
-                    tma_load_3d(raw + (size_t) slot * kUnitBytes<T>, &tm_w, &P.raw_full[slot], kb * (kRawRow<T> / 4), wrow, found_e);
+                    // x: the block's 32-bit words (k-quants), or the 16-byte aligned byte offset of the window around the
+                    // i-quant block (the box is then 112 / 144 bytes of each row; past the row's end it reads as zeros)
+                    const int x0 = kIq<T> ? (int) (((size_t) kb * kBlkBytes<T>) & ~(size_t) 15) : kb * (kRawRow<T> / 4);
+                    tma_load_3d(raw + (size_t) slot * kUnitBytes<T>, &tm_w, &P.raw_full[slot], x0, wrow, found_e);
                     issued = u + 1;
                 }
             }
@@ -752,6 +725,13 @@ int launch_mmq(const maya_mmq_product* p, const MmqArgs& A, cudaStream_t s) {
         const cuuint64_t st[2] = {(cuuint64_t) rbw, (cuuint64_t) p->expert_bytes};
         const cuuint32_t box[3] = {(cuuint32_t) (kRawRow<T> / 4), kUnitRows, 1};
         if (!make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, p->w, dim, st, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return note_launch("mmq weight tensor map");
+    } else {                   // i-quants as bytes: a box = the 112 / 144 bytes of 64 rows that hold the block's window;
+                               // a row is a multiple of 16 bytes (K a multiple of 2048) and so is every window's start
+        const cuuint64_t dim[3] = {(cuuint64_t) rbw, (cuuint64_t) mat_rows, (cuuint64_t) p->n};
+        const cuuint64_t st[2] = {(cuuint64_t) rbw, (cuuint64_t) p->expert_bytes};
+        const cuuint32_t box[3] = {(cuuint32_t) kRawRow<T>, kUnitRows, 1};
+        if (!make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, p->w, dim, st, box, CU_TENSOR_MAP_SWIZZLE_NONE))
             return note_launch("mmq weight tensor map");
     }
     {   // activations: f16 [row][K]; a box = 64 K-values (128 bytes) of 128 or 32 rows, written with the 128-byte swizzle
