@@ -28,6 +28,7 @@
 
 #include "maya_hc_post.cuh"
 #include "maya_router.cuh"
+#include "maya_fused_args.cuh"
 
 namespace maya {
 namespace {
@@ -37,29 +38,6 @@ constexpr int kRouteThreads = 256;
 constexpr int kMaxSliceRows = 96;          // output rows a block may own (n_embd / grid rounded up)
 constexpr unsigned kSpinLimit = 1u << 22;  // barrier polls before giving up (~ a second)
 
-struct FusedArgs {
-    const float* logits;       // [n_expert]
-    const void* x;             // [n_embd] f32 or bf16
-    int x_is_bf16;
-    int n_embd, n_ff, n_expert, k;
-    const uint8_t* experts;
-    size_t expert_stride;
-    int expert_lo, expert_hi;
-    const uint8_t* shared;     // NULL: none (or not on this rank)
-    int n_ff_sh;
-    int sh_lo, sh_hi;          // this rank's slice of the shared expert's FFN width (multiples of 32): its gate/up rows
-                               // and the same columns of every down row; the ranks' partial outputs add up
-    float limit;
-    int* ids;                  // [k] out
-    float* weights;            // [k] out
-    float* out;                // [n_embd] out
-    float* h;                  // scratch [(k + 1)][max(n_ff, n_ff_sh)] f32
-    maya_peer_ar ar;           // ar.nm >= 2: sum `out` over the ranks in the epilogue
-    int ar_rank;
-    unsigned ar_seq;
-    maya_hc_post_args hc;      // hc.R_new != NULL: the hyper-connection write of `out` into the residual stack, last
-    unsigned* sync;            // scratch: [0] arrivals, [1] epoch, [2] error, [4..13] block 0's phase time stamps (ns)
-};
 
 constexpr int kUnitBatch = 4;   // units of 32 FFN rows a block works on at a time (64 four-row items: two per warp)
 
