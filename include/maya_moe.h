@@ -285,11 +285,8 @@ typedef struct maya_moe_layer {
     float limit;                 /* SwiGLU clamp; INFINITY = none */
     int expert_lo, expert_hi;    /* this rank's experts [lo, hi); others contribute nothing (expert-parallel) */
     int shared_here;             /* non-zero: this rank adds the shared expert */
-    int staged;                  /* which kernels take a single token; the result bits are the same in every case.
-                                    0: the library's choice (the streamed single kernel where it covers the layer, else
-                                    the grid-barrier single kernel, else the staged kernels); 1: the staged kernels
-                                    (router, q8_1, gate/up, down as separate launches); 2: the grid-barrier single
-                                    kernel where it covers the layer, else the staged kernels */
+    int staged;                  /* non-zero: run one token through the staged kernels (router, q8_1, gate/up, down as
+                                    separate launches) instead of the single fused kernel; same bits either way */
     int sh_lo, sh_hi;            /* with shared_here: this rank's slice [sh_lo, sh_hi) of the shared expert's FFN width
                                     (multiples of 32; 0, 0 = all of it): its gate/up rows and the same columns of the down
                                     rows, so that the ranks' partial outputs add up to the shared expert's output (the

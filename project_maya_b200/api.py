@@ -359,14 +359,14 @@ class MoeLayer:
     FFN width instead of all of it (single-token calls only)."""
 
     def __init__(self, cfg: MoeLayerConfig, experts, shared=None, expert_range=None, shared_here=True, max_tokens: int = 16,
-                 staged: int = 0, shared_range=None):
+                 staged: bool = False, shared_range=None):
         self.cfg = cfg
         self.experts = experts
         self.shared = shared
         lo, hi = expert_range if expert_range is not None else (0, cfg.n_expert)
         self.desc = MoeLayerDesc(cfg.n_embd, cfg.n_ff, cfg.n_expert, cfg.k, cfg.gu_type, cfg.d_type, _ptr(experts),
                                  cfg.blob_bytes, cfg.n_ff_sh if shared is not None else 0, cfg.sh_gu_type,
-                                 cfg.sh_d_type, _ptr(shared), cfg.limit, lo, hi, int(bool(shared_here)), int(staged),
+                                 cfg.sh_d_type, _ptr(shared), cfg.limit, lo, hi, int(bool(shared_here)), int(bool(staged)),
                                  *(shared_range if shared_range is not None else (0, 0)))
         self.max_tokens = max_tokens
         nbytes = int(_lib.load().maya_moe_layer_scratch_bytes(C.byref(self.desc), max_tokens))

@@ -24,6 +24,13 @@ __device__ __forceinline__ uint32_t prmt_sign(uint32_t x) {
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(m) : "r"(x), "r"(0u), "r"(0x89ABu));
     return m;
 }
+// prmt.b32 in its default mode with the selector as given: nibble n < 8 picks byte n of {a, b}; n + 8 gives the top bit
+// of that byte replicated (0x00 for a byte below 0x80: how a zero byte is made without a zero operand).
+__device__ __forceinline__ uint32_t prmt_raw(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
 __device__ __forceinline__ uint32_t sign_mask_lo(uint32_t s) { return prmt_sign(s * 0x80402010u); }   // bits 0..3 of s
 __device__ __forceinline__ uint32_t sign_mask_hi(uint32_t s) { return prmt_sign(s * 0x08040201u); }   // bits 4..7 of s
 
@@ -86,9 +93,13 @@ template<> struct Dec1<MAYA_IQ2_S> {
         ls0 = (int) (sc & 0x0F);
         ls1 = (int) (sc >> 4);
         const uint2* grid = (const uint2*) tab + (lane & 15);
+        // byte l of hw = bits 2l, 2l+1 of qh (the entries' high index bits): fields 0 and 2 by one multiply, 1 and 3 by
+        // another; the partial products that miss their byte land on bits the mask drops and none of their sums carries
+        // into a kept bit.  An entry index is then ONE byte permute: {qs byte l, hw byte l, 0, 0}.
+        const uint32_t hw = ((qh & 0x33u) * 0x1001u + (qh & 0xCCu) * 0x40040u) & 0x03030303u;
 #pragma unroll
         for (int l = 0; l < 4; ++l) {
-            const uint32_t idx = byte_of(qs, l) | ((qh << (8 - 2 * l)) & 0x300);
+            const uint32_t idx = prmt_raw(qs, hw, 0xCC00u + ((4 + l) << 4) + l);
             const uint2 g = grid[idx * 16];
             const uint32_t s = byte_of(sg, l);
             mk[2 * l] = sign_mask_lo(s);

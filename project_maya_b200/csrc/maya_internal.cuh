@@ -36,11 +36,4 @@ int fused_t1(const maya_moe_layer& L, const float* logits, const void* x, int x_
              float* out, float* h_scratch, unsigned* sync, const maya_peer_ar* ar, int ar_rank, unsigned ar_seq,
              const maya_hc_post_args* hc, cudaStream_t s);
 
-// The streamed single-token layer kernel (moe_stream.cu): same arguments, same bits.
-bool stream_t1_supported(const maya_moe_layer& L);
-size_t stream_scratch_bytes(int h_ld);
-int stream_t1(const maya_moe_layer& L, const float* logits, const void* x, int x_is_bf16, int* ids, float* weights,
-              float* out, float* h_scratch, unsigned* sync, const maya_peer_ar* ar, int ar_rank, unsigned ar_seq,
-              const maya_hc_post_args* hc, cudaStream_t s);
-
 }  // namespace maya

@@ -40,8 +40,7 @@ Scratch carve(const maya_moe_layer& L, int T, uint8_t* base) {
     s.sync = (unsigned*) take(16 * sizeof(unsigned));
     {
         const int ld = L.n_ff > L.n_ff_sh ? L.n_ff : L.n_ff_sh;
-        const size_t fused = (size_t) (MAYA_MAX_K + 1) * ld * sizeof(float), streamed = stream_scratch_bytes(ld);
-        s.h = (float*) take(fused > streamed ? fused : streamed);
+        s.h = (float*) take((size_t) (MAYA_MAX_K + 1) * ld * sizeof(float));
     }
     s.xq = take((size_t) T * (L.n_embd / 32) * kQ81Bytes);
     s.plan_ptr = (unsigned long long*) take((size_t) T * 8 * sizeof(unsigned long long));
@@ -151,7 +150,7 @@ static int ar_args_ok(const maya_moe_layer* L, int n_tokens, float* out, const m
         return MAYA_ERR_ARG;
     if (L && n_tokens > 0 && (size_t) n_tokens * L->n_embd > a->stride) return MAYA_ERR_ARG;
     if (out && !aligned16(out)) return MAYA_ERR_ARG;
-    if (seq == 0u && (a->seq_counter == nullptr || n_tokens != 1 || (L && (L->staged == 1 || !fused_t1_supported(*L)))))
+    if (seq == 0u && (a->seq_counter == nullptr || n_tokens != 1 || (L && (L->staged || !fused_t1_supported(*L)))))
         return MAYA_ERR_ARG;           // the device-side sequence number exists only in the fused single-token kernel
     return MAYA_OK;
 }
@@ -189,9 +188,7 @@ static int layer_decode(const maya_moe_layer* L, const float* logits, const void
     cudaStream_t s = as_stream(stream);
     int* d_ids = ids ? ids : S.ids;
     float* d_w = weights ? weights : S.weights;
-    if (T == 1 && !L->staged && stream_t1_supported(*L))
-        return stream_t1(*L, logits, x, x_is_bf16, d_ids, d_w, out, S.h, S.sync, ar, mi, seq, hc, s);
-    if (T == 1 && L->staged != 1 && fused_t1_supported(*L))
+    if (T == 1 && !L->staged && fused_t1_supported(*L))
         return fused_t1(*L, logits, x, x_is_bf16, d_ids, d_w, out, S.h, S.sync, ar, mi, seq, hc, s);
     if (L->n_ff_sh > 0 && L->shared_here && (L->sh_lo != 0 || (L->sh_hi != 0 && L->sh_hi != L->n_ff_sh)))
         return refuse(MAYA_ERR_ARG);                 // only the fused kernel slices the shared expert

@@ -251,37 +251,6 @@ def test_fused_token_kernel_equals_staged_kernels_bitwise(T, api, oracle, t, sha
     assert H.rel_err(out.cpu().numpy()[0], want) <= TIGHT
 
 
-@pytest.mark.parametrize("shared,lo_hi", [(True, (0, 17)), (False, (0, 20)), (True, (5, 9))])
-def test_streamed_token_kernel_equals_the_other_kernels_bitwise(T, api, oracle, shared, lo_hi):
-    """The streamed single-token kernel (bulk copies into shared memory, per-slot readiness instead of a grid barrier)
-    against the grid-barrier kernel and the staged kernels: the same ids, weights and output bits, call after call on
-    one scratch, also when part of the experts belong to "another rank"."""
-    n_embd, n_ff, n_expert, k = 2048, 2048, 20, 6
-    cfg = dict(n_embd=n_embd, n_ff=n_ff, n_expert=n_expert, k=k, gu_type=H.IQ2_S, d_type=H.IQ2_S, limit=7.0)
-    if shared:
-        cfg.update(n_ff_sh=1024, sh_gu_type=H.Q8_0, sh_d_type=H.Q8_0)
-    lc, experts, sh = synth_layer(T, api, cfg, n_expert, seed=33)
-    lc.limit = 7.0
-    streamed = api.MoeLayer(lc, experts, sh, expert_range=lo_hi)
-    barrier = api.MoeLayer(lc, experts, sh, expert_range=lo_hi, staged=2)
-    staged = api.MoeLayer(lc, experts, sh, expert_range=lo_hi, staged=1)
-    logits = H.router_logits("streamed", 8, n_expert, 1.1)
-    x = H.activations("streamed", 8, n_embd, "bf16")
-    ids_o, _ = oracle.router_top10(logits, k)
-    for rep in range(3):
-        for i in range(8):
-            ld, xd = dev(T, logits[i:i + 1]), dev(T, x[i:i + 1], T.bfloat16)
-            ids_a, w_a, out_a = streamed.forward(ld, xd)
-            ids_b, w_b, out_b = barrier.forward(ld, xd)
-            assert T.equal(ids_a, ids_b) and T.equal(w_a, w_b)
-            assert np.array_equal(ids_a.cpu().numpy()[0], ids_o[i])
-            assert T.equal(out_a, out_b), f"token {i} (pass {rep}) differs from the grid-barrier kernel"
-            if rep == 0:
-                _, _, out_c = staged.forward(ld, xd)
-                assert T.equal(out_a, out_c), f"token {i} differs from the staged kernels"
-    assert streamed.error() == 0
-
-
 def test_fused_kernel_many_calls_one_scratch(T, api):
     """The grid barrier's counter lives in the scratch: hundreds of calls, single tokens and windows interleaved."""
     cfg = dict(n_embd=512, n_ff=256, n_expert=8, k=4, gu_type=H.Q4_K, d_type=H.Q4_K)
