@@ -6,6 +6,11 @@
   oracle/_ref/libmaya_ref.so       the reference's own CPU code for this path, compiled from the reference tree where it
                                    lies (only when that tree is present; outputs only under oracle/_ref/): the AVX-512 /
                                    AVX2 expert rows, the router test's host reference, the Q8_K quantizer transcription
+  oracle/_ref/libmaya_ref_gpu.so   the reference's own CUDA expert kernels (router_top10.cu, iq_kernels.cu,
+                                   native_mmvq.cu, glm_fast.cu) compiled for sm_100a behind the C ABI of ref_shim_gpu.cu:
+                                   the live parity pin of the GPU tests and the bench's "GPU kernel to beat"
+
+The reference tree is the directory MAYA_REFERENCE_TREE names, else a directory "reference" beside this repository.
 """
 from __future__ import annotations
 
@@ -17,7 +22,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent
 GRIDS = ROOT / "project_maya_b200" / "csrc" / "generated"
-REFERENCE = Path(os.environ.get("MAYA_REFERENCE_TREE", "/root/reference"))
+REFERENCE = Path(os.environ.get("MAYA_REFERENCE_TREE") or ROOT.parent / "reference")
 
 
 def _run(cmd: list[str]) -> None:
@@ -77,6 +82,39 @@ def build_ref() -> Path | None:
     return out
 
 
+def build_ref_gpu() -> Path | None:
+    """Compile the reference's CUDA expert kernels for sm_100a where they lie (no file of it is copied or changed).
+    native_mmvq.cu takes --use_fast_math as in the reference's CMakeLists.txt:578-592.  glm_fast.cu takes over a minute."""
+    out = HERE / "_ref" / "libmaya_ref_gpu.so"
+    if not reference_present():
+        return out if out.exists() else None
+    out.parent.mkdir(exist_ok=True)
+    nvcc = "/usr/local/cuda/bin/nvcc"
+    inc = ["-I", str(REFERENCE / "include"), "-I", str(REFERENCE / "third_party" / "ggml"), "-I", str(REFERENCE / "src" / "kernels" / "cuda")]
+    common = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-w", "-c"]
+    cu = REFERENCE / "src" / "kernels" / "cuda"
+    units = [
+        (cu / "router_top10.cu", []),
+        (cu / "iq_kernels.cu", []),
+        (cu / "native_mmvq.cu", ["--use_fast_math"]),
+        (cu / "glm_fast.cu", []),
+        (HERE / "ref_shim_gpu.cu", ["-Xcompiler", "-fvisibility=hidden"]),
+    ]
+    import concurrent.futures as cf
+    objs, jobs = [], []
+    for src, fl in units:
+        obj = HERE / "_ref" / ("gpu_" + src.stem + ".o")
+        objs.append(obj)
+        if _stale(obj, [src]):
+            jobs.append(common + fl + inc + [str(src), "-o", str(obj)])
+    with cf.ThreadPoolExecutor(max_workers=max(1, len(jobs))) as ex:
+        list(ex.map(_run, jobs))
+    if _stale(out, objs):
+        _run([nvcc, "-shared", "-o", str(out), *map(str, objs)])
+    return out
+
+
 if __name__ == "__main__":
     print(build_oracle())
     print(build_ref())
+    print(build_ref_gpu())
