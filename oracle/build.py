@@ -70,6 +70,7 @@ def build_ref() -> Path | None:
         (HERE / "ref_shim_rows.cpp", []),
         (HERE / "ref_shim_router.cpp", []),
         (HERE / "ref_shim_q8k.cpp", []),
+        (HERE / "ref_shim_layer.cpp", avx2 + ["-O3", "-pthread"]),
     ]
     objs = []
     for src, fl in units:
@@ -78,7 +79,7 @@ def build_ref() -> Path | None:
             _run(common + fl + inc + [str(src), "-o", str(obj)])
         objs.append(obj)
     if _stale(out, objs):
-        _run(["g++", "-shared", "-o", str(out), *map(str, objs)])
+        _run(["g++", "-shared", "-pthread", "-o", str(out), *map(str, objs)])
     return out
 
 

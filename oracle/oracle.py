@@ -271,3 +271,23 @@ class Ref:
         outs = (C.c_void_p * nt)(*[out[i].ctypes.data for i in range(nt)])
         self.lib.ref_rows(int(avx512), t, _p(w, _u8p), C.c_size_t(row_bytes), n, arr, nt, outs, r0, r1)
         return out
+
+    def pool_threads(self, threads: int) -> int:
+        return int(self.lib.ref_pool_threads(int(threads)))
+
+    def layer_tokens(self, gu_type, d_type, gu_row, d_row, n_embd, n_ff, k, blobs, weights, x, shared, n_ff_sh, avx512=True):
+        """n_tok decode tokens of a layer on the host pool (ref_shim_layer.cpp): blobs = n_tok * k uint8 arrays (token t's
+        j-th routed expert), weights [n_tok, k], x [n_tok, n_embd] f32, shared = the Q8_0 shared expert's blob or None.
+        Returns (out [n_tok, n_embd], seconds)."""
+        x = _f32(x)
+        n_tok = x.shape[0]
+        weights = _f32(weights)
+        keep = [_u8(b) for b in blobs]
+        arr = (C.c_void_p * len(keep))(*[b.ctypes.data for b in keep])
+        sh = _u8(shared) if shared is not None else None
+        out = np.zeros((n_tok, n_embd), np.float32)
+        self.lib.ref_layer_tokens.restype = C.c_double
+        dt = self.lib.ref_layer_tokens(int(avx512), gu_type, d_type, C.c_size_t(gu_row), C.c_size_t(d_row), n_embd, n_ff, k, arr,
+                                       _p(weights, _f32p), _p(x, _f32p), _p(sh, _u8p) if sh is not None else None,
+                                       n_ff_sh if sh is not None else 0, n_tok, _p(out, _f32p))
+        return out, float(dt)
