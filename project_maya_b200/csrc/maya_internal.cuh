@@ -17,6 +17,7 @@ struct GroupArgs {
     const int* ent_out;
     const int* skip;
     int tok_from_slot;
+    int cap_entries;      // > 0: the kernels touch no entry at or beyond it
 };
 
 int gate_up_groups(int gu_type, const GroupArgs& A, int n_groups_grid, int n_embd, int n_ff, size_t up_off, float limit,

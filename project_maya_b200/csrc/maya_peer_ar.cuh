@@ -91,11 +91,11 @@ __device__ __forceinline__ bool peer_allreduce_block(float* x, int q0, int q1, c
 // record.  Returns false when the transport is (or becomes) poisoned; x is then undefined.
 __device__ __forceinline__ bool peer_allreduce_block_words(float* x, int q0, int q1, const maya_peer_ar& a, int mi,
                                                            unsigned seq, int b) {
-    __shared__ int s_ready;
+    __shared__ int s_ready, s_failed;
     const int tid = threadIdx.x, nt = blockDim.x, nm = a.nm;
-    if (tid == 0) s_ready = (*(volatile unsigned*) a.error & 1u) == 0;
+    if (tid == 0) { s_ready = (*(volatile unsigned*) a.error & 1u) == 0; s_failed = 0; }
     __syncthreads();
-    if (!s_ready) return false;
+    if (!s_ready) return false;          // s_ready is not written again: every thread reads the same value
     const size_t slot = seq & 1u, words_off = (size_t) 2 * nm * a.stride;      // floats of row area before the words
     for (int t = tid; t < 4 * (q1 - q0); t += nt) {
         const size_t i = (size_t) 4 * q0 + t;
@@ -136,10 +136,10 @@ __device__ __forceinline__ bool peer_allreduce_block_words(float* x, int q0, int
             acc = m == 0 ? p : __fadd_rn(acc, p);
         }
         if (ok) x[i] = acc;
-        else s_ready = 0;
+        else s_failed = 1;
     }
     __syncthreads();
-    return s_ready != 0;
+    return s_failed == 0;
 }
 
 }  // namespace maya

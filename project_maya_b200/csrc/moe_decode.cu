@@ -38,6 +38,7 @@ struct Groups {
     const int* ent_out;              // [entries] the entry's output row (down), or NULL: its slot
     const int* skip;                 // optional "do nothing" flag
     int tok_from_slot;
+    int cap_entries;                 // > 0: entry numbers at or beyond it are not touched (the scratch ends there)
     __device__ __forceinline__ int slot(int e) const { return ent_slot ? ent_slot[e] : e; }
     __device__ __forceinline__ int tok(int e) const { return ent_tok ? ent_tok[e] : (tok_from_slot ? slot(e) >> 3 : 0); }
     __device__ __forceinline__ int out_row(int e) const { return ent_out ? ent_out[e] : slot(e); }
@@ -103,8 +104,10 @@ __global__ void __launch_bounds__(kGuWarps * 32) gate_up_kernel(Groups G, int n_
     if (G.n_groups != nullptr && g >= *G.n_groups) return;
     const unsigned long long ptr = G.ptr[g];
     if (ptr == 0ull) return;
-    const int e0 = G.start ? G.start[g] : g, e1 = G.start ? G.start[g + 1] : g + 1;
-    if (e1 <= e0) return;
+    const int e0 = G.start ? G.start[g] : g;
+    int e1 = G.start ? G.start[g + 1] : g + 1;
+    if (G.cap_entries > 0) e1 = min(e1, G.cap_entries);      // an inconsistent start table must not reach past the scratch
+    if (e1 <= e0 || e0 < 0) return;
 
     __shared__ float s_g[kNC][kGuRows], s_u[kNC][kGuRows];
     uint32_t* s_tab = (uint32_t*) s_raw;
@@ -222,8 +225,10 @@ __global__ void __launch_bounds__(kDownWarps * 32) down_groups_kernel(Groups G, 
     if (G.n_groups != nullptr && g >= *G.n_groups) return;
     const unsigned long long ptr = G.ptr[g];
     if (ptr == 0ull) return;
-    const int e0 = G.start ? G.start[g] : g, e1 = G.start ? G.start[g + 1] : g + 1;
-    if (e1 <= e0) return;
+    const int e0 = G.start ? G.start[g] : g;
+    int e1 = G.start ? G.start[g + 1] : g + 1;
+    if (G.cap_entries > 0) e1 = min(e1, G.cap_entries);      // an inconsistent start table must not reach past the scratch
+    if (e1 <= e0 || e0 < 0) return;
     uint32_t* s_tab = (uint32_t*) s_raw;
     int4* q; float* d; int* is;
     const int nblk = n_ff / 32;
@@ -427,14 +432,14 @@ int check_shapes(int gu_type, int d_type, int k, int n_embd, int n_ff) {
 int gate_up_groups(int gu_type, const GroupArgs& A, int n_groups_grid, int n_embd, int n_ff, size_t up_off, float limit,
                    const void* xq, size_t xq_stride, void* hq, const void* sh_down, int sh_type, const void* sh_hq,
                    int n_ff_sh, float* sh_out, cudaStream_t s) {
-    Groups G{A.ptr, A.start, A.n_groups, A.ent_slot, A.ent_tok, A.ent_out, A.skip, A.tok_from_slot};
+    Groups G{A.ptr, A.start, A.n_groups, A.ent_slot, A.ent_tok, A.ent_out, A.skip, A.tok_from_slot, A.cap_entries};
 #define CALL(TT) launch_gate_up<TT>(G, n_groups_grid, n_embd, n_ff, up_off, limit, xq, xq_stride, hq, sh_down, sh_type, sh_hq, n_ff_sh, sh_out, s)
     MAYA_TYPE_SWITCH(gu_type, CALL)
 #undef CALL
 }
 int down_groups(int d_type, const GroupArgs& A, int n_groups_grid, int n_embd, int n_ff, size_t down_off, const void* hq,
                 float* part, cudaStream_t s) {
-    Groups G{A.ptr, A.start, A.n_groups, A.ent_slot, A.ent_tok, A.ent_out, A.skip, A.tok_from_slot};
+    Groups G{A.ptr, A.start, A.n_groups, A.ent_slot, A.ent_tok, A.ent_out, A.skip, A.tok_from_slot, A.cap_entries};
 #define CALL(TT) launch_down_groups<TT>(G, n_groups_grid, n_embd, n_ff, down_off, hq, part, s)
     MAYA_TYPE_SWITCH(d_type, CALL)
 #undef CALL
@@ -544,6 +549,7 @@ extern "C" int maya_expert_grouped(const maya_expert_layout* L, const unsigned l
     A.n_groups = n_groups;
     A.ent_tok = ent_tok;
     A.ent_out = ent_dst;
+    A.cap_entries = (int) (cap_entries < 0x7fffffff ? cap_entries : 0x7fffffff);   // the scratch (and `out`) hold this many
     int st = gate_up_groups(L->gu_type, A, (int) cap_groups, n_embd, n_ff, L->up_off, swiglu_limit, x_q8_1,
                             (size_t) (n_embd / 32) * kQ81Bytes, scratch, nullptr, 0, nullptr, 0, nullptr, s);
     if (st != MAYA_OK) return st;

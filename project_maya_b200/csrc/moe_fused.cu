@@ -8,13 +8,15 @@
 //
 //   phase 0 (every block, redundantly - no grid-wide dependency): warps 0-7 route the token (the same bits in every
 //            block); warps 8-31 build the replicated codebook in shared memory and quantize x to q8_1 there;
-//   phase 1  block b owns a contiguous slice of the FFN rows; its warps take (row, expert) items - gate row and up row
-//            of one expert, sharing the activation registers - and write h = SwiGLU(gate, up) as f32 to scratch;
-//            the shared expert is expert k;
-//   grid barrier (bounded spin on a counter in the caller's scratch; a time-out sets a sticky error word);
-//   phase 2  every block quantizes all (k + 1) x n_ff values of h to q8_1 in shared memory, then owns a contiguous
-//            slice of the output rows: items are (row pair, expert); the per-expert partials meet in shared memory and
-//            one thread per row runs the combine chain in plan order.
+//   phase 1  a unit = 32 consecutive FFN rows of one expert (the shared expert's units follow the routed ones); block b
+//            takes units b, b + grid, ...; a warp item is two FFN rows (their gate and up rows share the activation
+//            registers); the block that computed a unit rounds its 32 h values to one q8_1 block and writes it to the
+//            scratch;
+//   grid barrier (a wait on a counter in the caller's scratch, bounded by %globaltimer; a time-out sets a sticky error
+//            word, and every thread of the block then skips phase 2, the cross-rank exchange and the residual write);
+//   phase 2  every block copies the q8_1 image of h ((k + 1) x n_ff / 32 blocks) to shared memory, then owns a
+//            contiguous slice of the output rows: items are (row pair, expert); the per-expert partials meet in shared
+//            memory and one thread per row runs the combine chain in plan order.
 //
 // Every (row, expert) dot, the q8_1 of h and the combine chain use the operations and order of the staged kernels
 // (moe_decode.cu), so the output is bit-identical to maya_moe_gate_up + maya_moe_down on the same plan.
@@ -23,7 +25,7 @@
 #include "maya_dots_t1.cuh"
 #include "maya_internal.cuh"
 #include "maya_peer_ar.cuh"
-#include <cstdlib>
+#include <atomic>
 #include <type_traits>
 
 #include "maya_hc_post.cuh"
@@ -36,7 +38,7 @@ namespace {
 constexpr int kFusedThreads = 1024;
 constexpr int kRouteThreads = 256;
 constexpr int kMaxSliceRows = 96;          // output rows a block may own (n_embd / grid rounded up)
-constexpr unsigned kSpinLimit = 1u << 22;  // barrier polls before giving up (~ a second)
+constexpr unsigned long long kBarrierTimeoutNs = 1000000000ull;   // the grid barrier gives up after a second
 
 
 constexpr int kUnitBatch = 4;   // units of 32 FFN rows a block works on at a time (64 four-row items: two per warp)
@@ -51,6 +53,7 @@ struct FusedShared {
     int ve[MAYA_MAX_K];        // the plan entries this rank computes (blob address != 0), in plan order
     int nv;
     float hbuf[kUnitBatch][32];   // the h values of the (expert, 32-row group) units this block is working on
+    int bar_ok;                   // the grid barrier's verdict, for every thread of the block
 };
 
 // balanced contiguous split of n rows over nb blocks
@@ -85,22 +88,25 @@ __device__ __forceinline__ void stamp(unsigned* sync, int i) {
     if (blockIdx.x == 0 && threadIdx.x == 0) *(volatile unsigned long long*) &sync[4 + 2 * i] = global_ns();
 }
 
-__device__ __forceinline__ bool grid_barrier(unsigned* sync, unsigned epoch) {
+// All blocks of the (cooperative) grid meet here.  false in EVERY thread of the block when the wait ran out: thread 0
+// leaves its verdict in shared memory before the closing barrier.
+__device__ __forceinline__ bool grid_barrier(unsigned* sync, unsigned epoch, int* s_ok) {
     __syncthreads();
-    bool ok = true;
     if (threadIdx.x == 0) {
+        int ok = 1;
         __threadfence();
         atomicAdd(&sync[0], 1u);
         const unsigned target = (epoch + 1u) * gridDim.x;
-        unsigned spins = 0;
+        const unsigned long long t0 = global_ns();
         while ((int) (*(volatile unsigned*) &sync[0] - target) < 0) {
-            if (++spins > kSpinLimit) { ok = false; atomicExch(&sync[2], 1u); break; }
+            if (global_ns() - t0 > kBarrierTimeoutNs) { ok = 0; atomicExch(&sync[2], 1u); break; }
             __nanosleep(20);
         }
         __threadfence();
+        *s_ok = ok;
     }
     __syncthreads();
-    return ok;
+    return *s_ok != 0;
 }
 
 template<int T, int TS>
@@ -281,7 +287,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     if constexpr (TS != 0) ds = shape(calls_per_row<TS>(has_sh ? A.sh_hi - A.sh_lo : n_ff));
     __syncthreads();
     stamp(A.sync, 2);
-    const bool ok = grid_barrier(A.sync, sh.epoch);
+    const bool ok = grid_barrier(A.sync, sh.epoch, &sh.bar_ok);
     stamp(A.sync, 3);
 
     // ---------------------------------------------------------------- phase 2: q8_1(h), down, combine
@@ -361,14 +367,18 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     }
     stamp(A.sync, 4);
     // ---------------------------------------------------------------- epilogue: the cross-rank sum of this block's rows
+    // After a barrier time-out `out` was not computed: nothing is sent (the peers' waits run out into their own sticky
+    // error) and the residual is not written.  After a failed exchange `out` is undefined: no residual write either.
+    bool final_ok = ok;
     if (A.ar.nm >= 2) {
         __syncthreads();
         int u0, u1;
         slice(n_embd / 4, gridDim.x, blockIdx.x, u0, u1);
-        peer_allreduce_block_words(A.out, u0, u1, A.ar, A.ar_rank, sh.ar_seq, blockIdx.x);
+        if (ok) final_ok = peer_allreduce_block_words(A.out, u0, u1, A.ar, A.ar_rank, sh.ar_seq, blockIdx.x);
+        else if (tid == 0) atomicOr(A.ar.error, 1u);
     }
     __syncthreads();
-    if (A.hc.R_new != nullptr) {    // the consumer of `out`: this block's rows are final (and the same on every rank)
+    if (A.hc.R_new != nullptr && final_ok) {    // the consumer of `out`: this block's rows are final (and the same on every rank)
         int e0 = o0, e1 = o1;
         if (A.ar.nm >= 2) { slice(n_embd / 4, gridDim.x, blockIdx.x, e0, e1); e0 *= 4; e1 *= 4; }
         hc_post_rows(A.out, A.hc, n_embd, e0, e1, tid, kFusedThreads);
@@ -383,6 +393,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
 
 template<int T, int TS>
 int launch_fused(const FusedArgs& A, cudaStream_t s) {
+    // per instantiation: the device and dynamic shared-memory size the attribute was last set for, and whether the
+    // programmatic-serialization attribute is in use (1), was refused by the driver (0) or has not been tried (-1)
+    static std::atomic<int> attr_dev{-1}, pdl{-1};
+    static std::atomic<size_t> attr_smem{0};
     static thread_local int cached_dev = -1, cached_grid = 0;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -396,21 +410,20 @@ int launch_fused(const FusedArgs& A, cudaStream_t s) {
         cached_grid = sms;
         cached_dev = dev;
     }
-    if (cudaFuncSetAttribute(moe_layer_t1_kernel<T, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess)
-        return note_launch("fused smem attribute");
+    if (attr_dev.load() != dev || attr_smem.load() != smem) {
+        if (cudaFuncSetAttribute(moe_layer_t1_kernel<T, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess)
+            return note_launch("fused smem attribute");
+        attr_dev.store(dev);
+        attr_smem.store(smem);
+    }
     int grid = cached_grid;
     if (4 * ((A.n_embd / 4 + grid - 1) / grid) > kMaxSliceRows || A.n_embd % 4) return refuse(MAYA_ERR_LIMIT);
     if (A.ar.nm >= 2 && grid > MAYA_PEER_AR_BLOCKS) return refuse(MAYA_ERR_LIMIT);
     FusedArgs args = A;
     void* params[] = {&args};
-    // Cooperative (the grid barrier needs every block resident) and, when asked for and accepted by the driver,
+    // Cooperative (the grid barrier needs every block resident) and, where the driver accepts the attribute,
     // programmatically serialized after the launch in front of it: its set-up then overlaps that launch's tail.
-    static int pdl = -1;                       // -1: not tried; 0: off or refused; 1: in use
-    if (pdl < 0) {
-        const char* e = std::getenv("MAYA_MOE_PDL");       // "0" turns it off
-        pdl = e != nullptr && e[0] == '0' ? 0 : 1;
-    }
-    if (pdl == 1) {
+    if (pdl.load() != 0) {
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(grid);
         cfg.blockDim = dim3(kFusedThreads);
@@ -423,10 +436,12 @@ int launch_fused(const FusedArgs& A, cudaStream_t s) {
         at[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = at;
         cfg.numAttrs = 2;
-        if (cudaLaunchKernelExC(&cfg, (const void*) moe_layer_t1_kernel<T, TS>, params) == cudaSuccess)
-            return note_launch("moe_layer_t1");
-        cudaGetLastError();                    // refused in this form: clear, and use the plain cooperative launch from now on
-        pdl = 0;
+        const cudaError_t e = cudaLaunchKernelExC(&cfg, (const void*) moe_layer_t1_kernel<T, TS>, params);
+        if (e == cudaSuccess) { pdl.store(1); return note_launch("moe_layer_t1"); }
+        // only "this attribute / combination is not supported" turns the attribute off; any other failure is the launch's
+        if (e != cudaErrorNotSupported && e != cudaErrorInvalidValue) return note_launch("moe_layer_t1");
+        cudaGetLastError();
+        pdl.store(0);
     }
     cudaLaunchCooperativeKernel((const void*) moe_layer_t1_kernel<T, TS>, dim3(grid), dim3(kFusedThreads), params, smem, s);
     return note_launch("moe_layer_t1");

@@ -268,6 +268,25 @@ def test_fused_kernel_many_calls_one_scratch(T, api):
     assert layer.error() == 0
 
 
+def test_fused_layer_barrier_times_out_and_reports(T, api):
+    """The fused kernel's one wait on other blocks is bounded: with the scratch's epoch word set ahead of its arrival
+    counter (a state no launch leaves behind) the grid barrier can never be satisfied; the call still returns after the
+    time limit, every block having skipped the second phase, and the sticky error word says so."""
+    cfg = dict(n_embd=512, n_ff=256, n_expert=8, k=4, gu_type=H.Q4_K, d_type=H.Q4_K)
+    lc, experts, _ = synth_layer(T, api, cfg, 8, seed=3)
+    layer = api.MoeLayer(lc, experts)
+    logits = dev(T, H.router_logits("timeout", 1, 8, None))
+    x = dev(T, H.activations("timeout", 1, 512, "f32"))
+    layer.forward(logits, x)
+    T.cuda.synchronize()
+    assert layer.error() == 0
+    words = layer.scratch[:16].view(T.int32)
+    words[1] += 7                                  # the epoch word: the barrier now waits for arrivals that never come
+    layer.forward(logits, x)
+    T.cuda.synchronize()                           # returns: the wait gave up after its second
+    assert layer.error() != 0
+
+
 def test_layer_refusals(T, api):
     cfg = H.CONFIGS["C1"]
     lc = layer_cfg(api, cfg)

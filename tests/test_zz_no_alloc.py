@@ -59,3 +59,30 @@ def test_static_scratch_limit_is_refused(cuda):
     with pytest.raises(api.MayaError) as e:
         api.native_expert_grouped_static(L, dummy, dummy, dummy, dummy, dummy, 1, too_many, dummy, dummy.float())
     assert e.value.status == -4
+
+
+def test_entry_cap_holds_on_the_device(cuda):
+    """A start table that claims more entries than cap_entries (inconsistent device data) must not make the kernels
+    write past the scratch - here the library's own array - or past `out`: entries at and beyond the cap are left alone."""
+    import torch as T
+    from project_maya_b200 import api
+    t, n_embd, n_ff, cap, claimed = H.Q4_K, 512, 256, 4, 9
+    rng = H.rng_for("cap")
+    blob = T.from_numpy(H.constructed_expert(t, t, n_embd, n_ff, rng)).cuda()
+    x = T.from_numpy(rng.standard_normal((claimed, n_embd)).astype(np.float32)).cuda()
+    xq = api.native_quantize_q8_1(x)
+    grp_ptr = T.tensor([blob.data_ptr()], dtype=T.int64, device="cuda")
+    ent = T.arange(claimed, dtype=T.int32, device="cuda")
+    n_groups = T.tensor([1], dtype=T.int32, device="cuda")
+    L = api.native_expert_layout(t, t, n_embd, n_ff)
+    outs = []
+    for n_claim in (cap, claimed):
+        grp_start = T.tensor([0, n_claim], dtype=T.int32, device="cuda")
+        out = T.full((claimed, n_embd), 5.0, dtype=T.float32, device="cuda")
+        api.native_expert_grouped_static(L, grp_ptr, grp_start, n_groups, ent, ent, 1, cap, xq, out, 7.0)
+        T.cuda.synchronize()
+        assert bool((out[cap:] == 5.0).all()), "rows beyond cap_entries were written"
+        outs.append(out)
+    assert T.equal(outs[0], outs[1])
+    assert bool((outs[0][:cap] != 5.0).any())
+
