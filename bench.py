@@ -530,7 +530,7 @@ def main() -> None:
                     help="prefill only: divide experts and tokens by this (a reduced case for profiler captures)")
     args = ap.parse_args()
     if args.workload == "prefill" and args.impl == "ours":
-        from project_maya_b200 import bench_prefill
+        import bench_prefill
         steps = args.steps if args.steps != 256 else 8
         sampler = ClockSampler(0)
         line = bench_prefill.run(steps, args.warmup if args.warmup != 8 else 3, min(args.layers, 2), sampler, args.prefill_scale)

@@ -16,9 +16,9 @@ from pathlib import Path
 
 import numpy as np
 
-from . import synthetic as S
+from project_maya_b200 import synthetic as S
 
-ROOT = Path(__file__).resolve().parent.parent
+ROOT = Path(__file__).resolve().parent
 CFG = S.CONFIGS["C4"]
 
 
@@ -50,7 +50,7 @@ def run(steps: int, warmup: int, layers: int, clock_sampler=None, scale: int = 1
     reduced case of the same kernels for profiler captures; the headline configuration is scale = 1."""
     import torch
 
-    from . import _lib, api
+    from project_maya_b200 import _lib, api
 
     lib = _lib.load()
     Hd, FF, E, k, T = CFG["n_embd"], CFG["n_ff"], CFG["n_expert"] // scale, CFG["k"], CFG["T"] // scale

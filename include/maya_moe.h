@@ -256,13 +256,6 @@ MAYA_API int maya_mmq_run(const maya_mmq_product* p, void* stream);
  * bit for bit to maya_mmq_run followed by maya_swiglu_rows.  n_ff % 128 == 0. */
 MAYA_API int maya_mmq_run_glu(const maya_mmq_product* p, float limit, void* stream);
 
-/* Development aid without a counterpart in the reference: when `counters` (device, 10 zeroed 64-bit words) is not NULL,
- * every block of the following grouped-GEMM launches adds SM clock cycles to it: [0] expansion warp 0 waiting for raw
- * weight units, [1] waiting for a free operand stage, [2] its whole K loop; [3] the issuing lane waiting for
- * activation tiles, [4] for expanded weights, [5] its whole loop; [6] epilogue wait for the last product, [7] epilogue;
- * [8] blocks; [9] K steps.  NULL switches it off. */
-MAYA_API void maya_mmq_set_probe(unsigned long long* counters);
-
 /* The producer in front of the layer: glmf::rms_q8 (glm_fast.hpp:534: h += add; x = rms(h) * norm_w, eps inside the
  * square root) and the router job of the GEMV batch Glm5Model::fast_moe issues next (glm_fast_path.cu:6925:
  * logits = router_w . x, router_w [n_expert][n_embd] F32 or BF16 bits) in ONE launch, so that a decode layer is this call

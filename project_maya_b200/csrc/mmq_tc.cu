@@ -89,10 +89,7 @@ struct MmqArgs {
     __half* xq_out;              // fused form, optional: q8_1-rounded h as f16, [sorted row][w_rows]
     float limit;
     unsigned* error;             // optional sticky error word
-    unsigned long long* probe;   // optional: cycle counters summed over the blocks (maya_mmq_set_probe)
 };
-
-unsigned long long* g_probe = nullptr;
 
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *(uint32_t*) &h; }
 __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *(__half2*) &u; }
@@ -299,9 +296,6 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
         }
     }
     if (found_e < 0) return;                        // beyond the last group: uniform for the whole block
-    const long long t_start = clock64();
-    const bool probing = A.probe != nullptr;
-    long long c_wait0 = 0, c_wait1 = 0;
     const int be = A.expert_map ? A.expert_map[found_e] : found_e;
     const int row0 = A.bounds[be] + found_g * TN;
     const int nrows = min(TN, A.bounds[be + 1] - row0);
@@ -362,7 +356,6 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
         // kt % 2 == t, so that a step's latency (shared-memory reads, the packed-half chain, the tensor-memory store
         // and its wait) overlaps the other team's step.
         const int team = warp >> 3, row = tid & 255, w8 = warp & 7;
-        const bool timing = probing && warp == 0;
         const int slab = row >> 6;
         const uint8_t* const rbase = raw + (size_t) (row & 63) * kRawRow<T>;
         // rows 0..127 feed accumulator 0, rows 128..255 accumulator 1; a warp reaches the 32 lanes of its quadrant
@@ -370,19 +363,13 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
         bool ok = true;
         for (int kb = 0; kb < nkb && ok; ++kb) {
             const int u = kb * 4 + slab, slot = u % NU;
-            {
-                const long long t0 = timing ? clock64() : 0;
-                if (!wait_or_fail(P, &P.raw_full[slot], (u / NU) & 1)) { ok = false; break; }
-                if (timing) c_wait0 += clock64() - t0;
-            }
+            if (!wait_or_fail(P, &P.raw_full[slot], (u / NU) & 1)) { ok = false; break; }
             const uint8_t* rrow = rbase + (size_t) slot * kUnitBytes<T>;
             auto put = [&](int kp, const uint32_t (&o)[32]) -> bool {   // the row's 64 values of pair kp -> its lane
                 const int s = kp % kSt;
                 if (kp >= kSt) {                     // the stage was last read by pair kp - kSt
                     const int pp = kp - kSt;
-                    const long long t0 = timing ? clock64() : 0;
                     if (!wait_or_fail(P, &P.done[pp & (kDone - 1)], (pp / kDone) & 1)) return false;
-                    if (timing) c_wait1 += clock64() - t0;
                     tc_fence_after();
                 }
                 tmem_st32(a_lane + s * 64, o);
@@ -455,12 +442,10 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             if (lane == 0) mbar_arrive(&P.raw_empty[slot]);      // 4 warps read a unit; after the 4th it may be overwritten
         }
         // ------------------------------------------------------------ epilogue
-        const long long t_loop = clock64();
         if (ok && !wait_or_fail(P, &P.final, 0)) ok = false;
         tc_fence_after();
         named_bar_sync(3, kDqWarps * 32);            // every expansion warp gets here (all waits are bounded) ...
         ok = !failed(P);                             // ... and they agree: the epilogue's barriers need all of them
-        const long long t_epi = clock64();
         if (ok) {
             // The tile leaves through shared memory (both rings are free now: every load was consumed): the warps drop
             // their lanes' values into [activation row][weight row] order, then one bulk copy per activation row
@@ -530,15 +515,6 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             }
             if (tid < nrows) bulk_wait_read<0>();                        // the copies have read shared memory: the block may end
         }
-        if (probing && tid == 0) {
-            atomicAdd(A.probe + 0, (unsigned long long) c_wait0);
-            atomicAdd(A.probe + 1, (unsigned long long) c_wait1);
-            atomicAdd(A.probe + 2, (unsigned long long) (t_loop - t_start));
-            atomicAdd(A.probe + 6, (unsigned long long) (t_epi - t_loop));
-            atomicAdd(A.probe + 7, (unsigned long long) (clock64() - t_epi));
-            atomicAdd(A.probe + 8, 1ull);
-            atomicAdd(A.probe + 9, (unsigned long long) nkt);
-        }
     } else if (warp == kDqWarps) {
         // ------------------------------------------------------------ raw weight units (one lane)
         if (lane == 0) {
@@ -585,16 +561,8 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                 const uint64_t d0b = hi | b_lo, d1b = hi | (b_lo + 2), d2b = hi | (b_lo + 4), d3b = hi | (b_lo + 6);
                 const uint32_t done_bar = done0 + ((kp & (kDone - 1)) << 3);
                 const bool rb = mbar_test_wait_addr(bfull, ph_b), ra = mbar_test_wait_addr(afull, ph_a);
-                if (!rb) {                                       // not there yet: the bounded wait (timed when probing)
-                    const long long t0 = probing ? clock64() : 0;
-                    if (!wait_or_fail(P, &P.b_full[(bfull - bfull0) >> 3], ph_b)) { ok = false; break; }
-                    if (probing) c_wait0 += clock64() - t0;
-                }
-                if (!ra) {
-                    const long long t0 = probing ? clock64() : 0;
-                    if (!wait_or_fail(P, &P.a_full[(afull - afull0) >> 3], ph_a)) { ok = false; break; }
-                    if (probing) c_wait1 += clock64() - t0;
-                }
+                if (!rb && !wait_or_fail(P, &P.b_full[(bfull - bfull0) >> 3], ph_b)) { ok = false; break; }   // not there yet: the bounded wait
+                if (!ra && !wait_or_fail(P, &P.a_full[(afull - afull0) >> 3], ph_a)) { ok = false; break; }
                 tc_fence_after();
                 mma_f16_ts_x4_commit(d0, at, d0b, d1b, d2b, d3b, idesc, first, done_bar);
                 first = 1;
@@ -604,11 +572,6 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                 if (b_lo == b_lo_end) { b_lo = b_lo0; bfull = bfull0; ph_b ^= 1; }
             }
             if (ok) mma_commit(&P.final);
-            if (probing && my == 0) {
-                atomicAdd(A.probe + 3, (unsigned long long) c_wait0);
-                atomicAdd(A.probe + 4, (unsigned long long) c_wait1);
-                atomicAdd(A.probe + 5, (unsigned long long) (clock64() - t_start));
-            }
         }
     } else if (warp == kDqWarps + 2) {
         // ------------------------------------------------------------ activation tiles (one lane)
@@ -772,7 +735,7 @@ int run_product(const maya_mmq_product* p, bool glu, float limit, cudaStream_t s
     A.w = (const uint8_t*) p->w; A.expert_bytes = p->expert_bytes; A.mat_rows = (int) p->w_rows;
     A.w_rows = (int) out_rows; A.w_cols = (int) p->w_cols; A.n = p->n; A.expert_map = p->expert_map; A.bounds = p->bounds;
     A.ids = p->ids; A.dst = p->dst; A.ld_dst = p->ld_dst; A.xq_out = glu ? (__half*) p->xq_out : nullptr; A.limit = limit;
-    A.error = p->error; A.probe = g_probe;
+    A.error = p->error;
     switch (p->type) {
         case MAYA_Q4_K: return glu ? launch_mmq<MAYA_Q4_K, true>(p, A, s) : launch_mmq<MAYA_Q4_K, false>(p, A, s);
         case MAYA_Q8_0: return glu ? launch_mmq<MAYA_Q8_0, true>(p, A, s) : launch_mmq<MAYA_Q8_0, false>(p, A, s);
@@ -801,7 +764,6 @@ extern "C" int maya_mmq_quantize_bf16(const uint16_t* x, const int32_t* ids, voi
                                       int64_t rows, void* stream) {
     return launch_quantize<uint16_t>(x, ids, xq, type, cols, ld, rows, stream);
 }
-extern "C" void maya_mmq_set_probe(unsigned long long* counters) { g_probe = counters; }
 extern "C" int maya_mmq_run(const maya_mmq_product* p, void* stream) { return run_product(p, false, 0.0f, as_stream(stream)); }
 extern "C" int maya_mmq_run_glu(const maya_mmq_product* p, float limit, void* stream) {
     return run_product(p, true, limit, as_stream(stream));

@@ -35,7 +35,7 @@ sys.path.insert(0, str(ROOT / "tests"))
 import helpers as H  # noqa: E402
 from oracle.oracle import Oracle, Ref  # noqa: E402
 
-REFERENCE = Path(os.environ.get("MAYA_REFERENCE_TREE", "/root/reference"))
+from oracle.build import REFERENCE  # noqa: E402  (MAYA_REFERENCE_TREE, else a "reference" directory beside this repository)
 
 
 def router_cases(ref: Ref) -> None:

@@ -32,7 +32,8 @@ def test_generated_codebooks_match_reference_header_when_present():
     """The generated IQ2_S / IQ3_S tables are the GGUF format's: compared with the header the reference vendors."""
     import re
     import os
-    hdr = Path(os.environ.get("MAYA_REFERENCE_TREE", "/root/reference")) / "third_party" / "ggml" / "ggml-common.h"
+    from oracle.build import REFERENCE
+    hdr = REFERENCE / "third_party" / "ggml" / "ggml-common.h"
     if not hdr.exists():
         pytest.skip("reference tree not on this machine")
     import sys
