@@ -348,12 +348,21 @@ MAYA_API int maya_peer_ar_preload(void* stream);
 MAYA_API int maya_allreduce_peer(float* x, int n, const maya_peer_ar* a, int mi, unsigned seq, void* stream);
 /* maya_moe_layer_decode followed by that sum of `out` over the ranks.  One token: the sum runs in the epilogue of the
  * fused layer kernel (each block pushes the output rows it just combined to every peer, then adds the peers' rows in rank
- * order) - no separate launch.  2..16 tokens: the window kernels, then maya_allreduce_peer on out[n_tokens * n_embd].
+ * order) - no separate launch.  2..16 tokens: the window kernels, the sum inside their last launch: the combine kernel's
+ * blocks exchange the rows they have just combined (the reference runs a separate allreduce over out[T * n_embd] after
+ * win_experts, src/ds4/ds4_model.cu:22822-22828).
  * seq == 0 (single token only): the kernel uses *a->seq_counter + 1 and stores it back when it ends, so every rank's
  * n-th call carries n without the host counting - the form to capture in a CUDA graph. */
 MAYA_API int maya_moe_layer_decode_ar(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
                                       int n_tokens, int* ids, float* weights, float* out, void* scratch,
                                       size_t scratch_bytes, const maya_peer_ar* a, int mi, unsigned seq, void* stream);
+/* The prompt path's last step on an expert-parallel rank, with the cross-rank sum in the same launch:
+ * maya_moe_combine_rows_local into ffn [T][n_embd] (contiguous, 16-byte aligned, T * n_embd <= a->stride), each block then
+ * exchanging the rows it has combined - ffn ends as the rank-ordered sum over the nm ranks, the same bits on every rank.
+ * No counterpart (the reference's prompt path is single-GPU; its decode path sums with a separate allreduce launch). */
+MAYA_API int maya_moe_combine_rows_local_ar(const float* out, const int* pos, const float* w, const int* ids, int e_lo,
+                                            int e_hi, const float* sh, int T, int k, int n_embd, float* ffn,
+                                            const maya_peer_ar* a, int mi, unsigned seq, void* stream);
 /* The consumer behind the block: glmf::hc_post (include/strata/kernels/glm_fast.hpp:124; hc_post_kernel,
  * src/kernels/cuda/glm_fast.cu:2747-2757).  The residual is a stack of 4 streams of n_embd floats;
  * R_new[d][e] = block_out[e] * post[d] + sum_s comb[d * 4 + s] * R_old[s][e] (post[4], comb[16] dst-major, device

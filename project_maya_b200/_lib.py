@@ -110,6 +110,8 @@ _SIGNATURES = {
     "maya_mmq_run_glu": (c_int, [C.POINTER(MmqProduct), c_float, c_void_p]),
     "maya_moe_combine_rows_local": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,
                                             c_void_p, c_void_p]),
+    "maya_moe_combine_rows_local_ar": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,
+                                               c_void_p, c_void_p, c_int, C.c_uint, c_void_p]),
     "maya_moe_combine_add": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "maya_moe_layer_scratch_bytes": (c_size_t, [C.POINTER(MoeLayerDesc), c_int]),
     "maya_moe_layer_error": (c_int, [C.POINTER(MoeLayerDesc), c_int, c_void_p, c_void_p]),

@@ -486,7 +486,9 @@ class MoePrefill:
             self.sh_out = torch.empty((T, H), **f32)
             self.sh_down_off = 2 * FS * row_bytes(cfg.sh_gu_type, H)
 
-    def forward(self, logits, x, stream=None):
+    def forward(self, logits, x, stream=None, peer=None):
+        """peer (a peer.PeerRank whose stride holds T * n_embd floats), on an expert-parallel rank: the returned ffn is the
+        rank-ordered sum over the group, exchanged inside the combine launch."""
         cfg, lib, s = self.cfg, _lib.load(), _stream(stream)
         T, k, H, FF, E = logits.shape[0], cfg.k, cfg.n_embd, cfg.n_ff, cfg.n_expert
         assert T <= self.max_tokens and x.shape == (T, H) and x.dtype in (torch.float32, torch.bfloat16)
@@ -525,6 +527,11 @@ class MoePrefill:
         if self.expert_range is None:
             _check("moe_combine_rows", lib.maya_moe_combine_rows(_ptr(self.out), _ptr(self.pos), _ptr(w), _ptr(sh_out), T, k, H,
                                                                 _ptr(ffn), s))
+        elif peer is not None:
+            _check("moe_combine_rows_local_ar",
+                   lib.maya_moe_combine_rows_local_ar(_ptr(self.out), _ptr(self.pos), _ptr(w), _ptr(ids), self.expert_range[0],
+                                                      self.expert_range[1], _ptr(sh_out), T, k, H, _ptr(ffn), C.byref(peer.desc),
+                                                      peer.mi, peer.next_seq(), s))
         else:
             _check("moe_combine_rows_local",
                    lib.maya_moe_combine_rows_local(_ptr(self.out), _ptr(self.pos), _ptr(w), _ptr(ids), self.expert_range[0],

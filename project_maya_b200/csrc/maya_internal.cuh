@@ -31,6 +31,8 @@ int win_combine(const unsigned long long* plan_ptr, const float* plan_w, int T, 
                 const float* cpu_part, const int* cpu_flag, const float* sh_out, float* out, size_t out_stride,
                 cudaStream_t s);
 
+int win_experts(int gu_type, int d_type, const maya_moe_win* w, const maya_peer_ar* ar, int mi, unsigned seq, cudaStream_t s);
+
 // The fused single-token layer kernel (moe_fused.cu).
 bool fused_t1_supported(const maya_moe_layer& L);
 int fused_t1(const maya_moe_layer& L, const float* logits, const void* x, int x_is_bf16, int* ids, float* weights,

@@ -17,6 +17,7 @@
 
 #include "maya_dots.cuh"
 #include "maya_internal.cuh"
+#include "maya_peer_ar.cuh"
 
 namespace maya {
 namespace {
@@ -346,6 +347,41 @@ __global__ void __launch_bounds__(256) win_combine_kernel(const unsigned long lo
     out[(size_t) t * out_stride + r] = __fadd_rn(m, sh_out != nullptr ? sh_out[(size_t) t * n_embd + r] : 0.0f);
 }
 
+// win_combine_kernel and the cross-rank sum in one launch (the reference follows win_experts with a separate allreduce
+// over out[T * n_embd], src/ds4/ds4_model.cu:22822-22828): block b combines its share [q0, q1) (float4 units of the
+// contiguous [T][n_embd] output), then runs the rows + flags exchange on it (peer_allreduce_block).
+__global__ void __launch_bounds__(256) win_combine_ar_kernel(const unsigned long long* __restrict__ plan_ptr,
+                                                             const float* __restrict__ plan_w, int k, int n_embd,
+                                                             const float* __restrict__ part,
+                                                             const float* __restrict__ cpu_part,
+                                                             const int* __restrict__ cpu_flag,
+                                                             const float* __restrict__ sh_out, float* out, int n4,
+                                                             maya_peer_ar a, int mi, unsigned seq) {
+    const int nb = gridDim.x, b = blockIdx.x;
+    const int base = n4 / nb, rem = n4 % nb;
+    const int q0 = b * base + min(b, rem), q1 = q0 + base + (b < rem ? 1 : 0);
+    for (int q = q0 + threadIdx.x; q < q1; q += blockDim.x) {
+        const int t = (int) (((size_t) q * 4) / n_embd), r = (int) ((size_t) q * 4 - (size_t) t * n_embd);
+        float4 m = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int j = 0; j < k; ++j) {
+            float4 pv = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (plan_ptr[t * 8 + j] != 0ull) pv = *(const float4*) (part + ((size_t) t * 8 + j) * n_embd + r);
+            const float wj = plan_w[t * 8 + j];
+            m.x = __fmaf_rn(wj, pv.x, m.x); m.y = __fmaf_rn(wj, pv.y, m.y); m.z = __fmaf_rn(wj, pv.z, m.z); m.w = __fmaf_rn(wj, pv.w, m.w);
+        }
+        if (cpu_flag != nullptr && cpu_flag[t]) {
+            const float4 c = *(const float4*) (cpu_part + (size_t) t * n_embd + r);
+            m.x = __fadd_rn(m.x, c.x); m.y = __fadd_rn(m.y, c.y); m.z = __fadd_rn(m.z, c.z); m.w = __fadd_rn(m.w, c.w);
+        }
+        float4 s4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (sh_out != nullptr) s4 = *(const float4*) (sh_out + (size_t) t * n_embd + r);
+        m.x = __fadd_rn(m.x, s4.x); m.y = __fadd_rn(m.y, s4.y); m.z = __fadd_rn(m.z, s4.z); m.w = __fadd_rn(m.w, s4.w);
+        ((float4*) out)[q] = m;
+    }
+    __syncthreads();
+    peer_allreduce_block(out, q0, q1, a, mi, seq, b);
+}
+
 // native_moe combine: s = parts[0] * w[0]; s = fma(parts[i], w[i], s); + shared (native_moe.cu:42-47).
 __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ parts, const float* __restrict__ w,
                                                       const float* __restrict__ shared, float* __restrict__ y,
@@ -458,6 +494,48 @@ int win_combine(const unsigned long long* plan_ptr, const float* plan_w, int T, 
     return note_launch("moe_win_combine");
 }
 
+int win_combine_ar(const unsigned long long* plan_ptr, const float* plan_w, int T, int k, int n_embd, const float* part,
+                   const float* cpu_part, const int* cpu_flag, const float* sh_out, float* out, const maya_peer_ar& a, int mi,
+                   unsigned seq, cudaStream_t s) {
+    const int n4 = (int) ((size_t) T * n_embd / 4);
+    int blocks = (n4 + 255) / 256;
+    if (blocks > MAYA_PEER_AR_BLOCKS) blocks = MAYA_PEER_AR_BLOCKS;
+    win_combine_ar_kernel<<<blocks, 256, 0, s>>>(plan_ptr, plan_w, k, n_embd, part, cpu_part, cpu_flag, sh_out, out, n4, a, mi, seq);
+    return note_launch("moe_win_combine_ar");
+}
+
+// moe_win_experts; with `ar` the cross-rank sum of out[T][n_embd] (contiguous) runs inside the combine launch.
+int win_experts(int gu_type, int d_type, const maya_moe_win* w, const maya_peer_ar* ar, int mi, unsigned seq, cudaStream_t s) {
+    if (!w || !w->plan_w || !w->xq || !w->hq || !w->part || !w->out) return refuse(MAYA_ERR_ARG);
+    if (w->cpu_flag != nullptr && w->cpu_part == nullptr) return refuse(MAYA_ERR_ARG);
+    int st = check_shapes(gu_type, d_type, w->k, w->n_embd, w->n_ff);
+    if (st != MAYA_OK) return refuse(st);
+    if (ar != nullptr && (w->out_stride != (size_t) w->n_embd || w->n_embd % 4 || !aligned16(w->out) || !aligned16(w->part) ||
+                          (w->sh_out && !aligned16(w->sh_out)) || (w->cpu_part && !aligned16(w->cpu_part))))
+        return refuse(MAYA_ERR_ARG);
+    st = maya_moe_win_group(w, s);
+    if (st != MAYA_OK) return st;
+    const int cap = w->T * 8;
+    const size_t up_off = row_bytes(gu_type, w->n_embd) * (size_t) w->n_ff;
+    // entry id i = t * 8 + j: token t's column (xq_stride apart), h / partial slot i
+    GroupArgs A{};
+    A.ptr = w->grp_ptr;
+    A.start = w->grp_start;
+    A.n_groups = w->n_groups;
+    A.ent_slot = w->grp_ent;
+    A.tok_from_slot = 1;
+    st = gate_up_groups(gu_type, A, cap, w->n_embd, w->n_ff, up_off, w->limit, w->xq, w->xq_stride, w->hq, nullptr, 0,
+                        nullptr, 0, nullptr, s);
+    if (st != MAYA_OK) return st;
+    st = down_groups(d_type, A, cap, w->n_embd, w->n_ff, w->down_off, w->hq, w->part, s);
+    if (st != MAYA_OK) return st;
+    if (ar != nullptr)
+        return win_combine_ar(w->plan_ptr, w->plan_w, w->T, w->k, w->n_embd, w->part, w->cpu_part, w->cpu_flag, w->sh_out, w->out,
+                              *ar, mi, seq, s);
+    return win_combine(w->plan_ptr, w->plan_w, w->T, w->k, w->n_embd, w->part, w->cpu_part, w->cpu_flag, w->sh_out, w->out,
+                       w->out_stride, s);
+}
+
 }  // namespace maya
 
 using namespace maya;
@@ -498,29 +576,7 @@ extern "C" int maya_moe_win_group(const maya_moe_win* w, void* stream) {
 }
 
 extern "C" int maya_moe_win_experts(int gu_type, int d_type, const maya_moe_win* w, void* stream) {
-    if (!w || !w->plan_w || !w->xq || !w->hq || !w->part || !w->out) return refuse(MAYA_ERR_ARG);
-    if (w->cpu_flag != nullptr && w->cpu_part == nullptr) return refuse(MAYA_ERR_ARG);
-    int st = check_shapes(gu_type, d_type, w->k, w->n_embd, w->n_ff);
-    if (st != MAYA_OK) return refuse(st);
-    st = maya_moe_win_group(w, stream);
-    if (st != MAYA_OK) return st;
-    cudaStream_t s = as_stream(stream);
-    const int cap = w->T * 8;
-    const size_t up_off = row_bytes(gu_type, w->n_embd) * (size_t) w->n_ff;
-    // entry id i = t * 8 + j: token t's column (xq_stride apart), h / partial slot i
-    GroupArgs A{};
-    A.ptr = w->grp_ptr;
-    A.start = w->grp_start;
-    A.n_groups = w->n_groups;
-    A.ent_slot = w->grp_ent;
-    A.tok_from_slot = 1;
-    st = gate_up_groups(gu_type, A, cap, w->n_embd, w->n_ff, up_off, w->limit, w->xq, w->xq_stride, w->hq, nullptr, 0,
-                        nullptr, 0, nullptr, s);
-    if (st != MAYA_OK) return st;
-    st = down_groups(d_type, A, cap, w->n_embd, w->n_ff, w->down_off, w->hq, w->part, s);
-    if (st != MAYA_OK) return st;
-    return win_combine(w->plan_ptr, w->plan_w, w->T, w->k, w->n_embd, w->part, w->cpu_part, w->cpu_flag, w->sh_out, w->out,
-                       w->out_stride, s);
+    return win_experts(gu_type, d_type, w, nullptr, 0, 0u, as_stream(stream));
 }
 
 extern "C" size_t maya_expert_scratch_bytes(int64_t cap_entries, int64_t n_ff) {

@@ -261,7 +261,6 @@ static int layer_decode(const maya_moe_layer* L, const float* logits, const void
     W.n_ff = L->n_ff;
     W.limit = L->limit;
     W.down_off = down_off;
-    st = maya_moe_win_experts(L->gu_type, L->d_type, &W, stream);
-    if (st == MAYA_OK && ar != nullptr) st = maya_allreduce_peer(out, T * L->n_embd, ar, mi, seq, stream);
+    st = win_experts(L->gu_type, L->d_type, &W, ar, mi, seq, s);       // with `ar`: the sum runs in the combine launch
     return st == MAYA_OK ? hc_post_tokens(hc, out, T, L->n_embd, stream) : st;
 }

@@ -8,6 +8,7 @@
 #include <math.h>
 
 #include "maya_common.cuh"
+#include "maya_peer_ar.cuh"
 
 namespace maya {
 namespace {
@@ -112,6 +113,37 @@ __global__ void __launch_bounds__(256) combine_rows_local_kernel(const float* __
     ffn[(size_t) t * n_embd + e] = __fadd_rn(m, sh ? sh[(size_t) t * n_embd + e] : 0.0f);
 }
 
+// combine_rows_local_kernel and the cross-rank sum in one launch: block b combines its share [q0, q1) (float4 units of
+// the flat [T][n_embd] result) into ffn, then pushes it to every peer's receive slot, raises its flag there, waits
+// (bounded) for the peers' flags and adds the nm rows in rank order (peer_allreduce_block: the rows + flags form).
+__global__ void __launch_bounds__(256) combine_rows_local_ar_kernel(const float* __restrict__ out, const int* __restrict__ pos,
+                                                                    const float* __restrict__ w, const int* __restrict__ ids,
+                                                                    int e_lo, int e_hi, const float* __restrict__ sh, int k,
+                                                                    int n_embd, float* ffn, int n4, maya_peer_ar a, int mi,
+                                                                    unsigned seq) {
+    const int nb = gridDim.x, b = blockIdx.x;
+    const int base = n4 / nb, rem = n4 % nb;
+    const int q0 = b * base + min(b, rem), q1 = q0 + base + (b < rem ? 1 : 0);
+    for (int q = q0 + threadIdx.x; q < q1; q += blockDim.x) {
+        const int t = (int) (((size_t) q * 4) / n_embd), e = (int) ((size_t) q * 4 - (size_t) t * n_embd);
+        float4 m = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int j = 0; j < k; ++j) {
+            const int id = ids[t * k + j];
+            if (id >= e_lo && id < e_hi) {
+                const float wj = w[t * k + j];
+                const float4 o = *(const float4*) (out + (size_t) pos[t * k + j] * n_embd + e);
+                m.x = __fmaf_rn(wj, o.x, m.x); m.y = __fmaf_rn(wj, o.y, m.y); m.z = __fmaf_rn(wj, o.z, m.z); m.w = __fmaf_rn(wj, o.w, m.w);
+            }
+        }
+        float4 s4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (sh) s4 = *(const float4*) (sh + (size_t) t * n_embd + e);
+        m.x = __fadd_rn(m.x, s4.x); m.y = __fadd_rn(m.y, s4.y); m.z = __fadd_rn(m.z, s4.z); m.w = __fadd_rn(m.w, s4.w);
+        ((float4*) ffn)[q] = m;
+    }
+    __syncthreads();
+    peer_allreduce_block(ffn, q0, q1, a, mi, seq, b);
+}
+
 // ffn[t] += sum over t's routes whose sorted row lies in [lo, hi) of w * out[row - base]
 __global__ void __launch_bounds__(256) combine_add_kernel(const float* __restrict__ out, int base, int lo, int hi,
                                                           const int* __restrict__ pos, const float* __restrict__ w, int k,
@@ -173,6 +205,21 @@ extern "C" int maya_moe_combine_rows_local(const float* out, const int* pos, con
     const dim3 grid((unsigned) ((n_embd + 255) / 256), (unsigned) T);
     combine_rows_local_kernel<<<grid, 256, 0, as_stream(stream)>>>(out, pos, w, ids, e_lo, e_hi, sh, k, n_embd, ffn);
     return note_launch("moe_combine_rows_local");
+}
+extern "C" int maya_moe_combine_rows_local_ar(const float* out, const int* pos, const float* w, const int* ids, int e_lo,
+                                              int e_hi, const float* sh, int T, int k, int n_embd, float* ffn,
+                                              const maya_peer_ar* a, int mi, unsigned seq, void* stream) {
+    if (T <= 0) return MAYA_OK;
+    if (!out || !pos || !w || !ids || !ffn || k <= 0 || n_embd <= 0 || n_embd % 4 || e_lo > e_hi) return refuse(MAYA_ERR_ARG);
+    if (!a || !a->recv || !a->peer_recv || !a->flags || !a->peer_flags || !a->error || a->timeout_ns == 0) return refuse(MAYA_ERR_ARG);
+    if (a->nm < 2 || a->nm > MAYA_PEER_AR_MAX_RANKS || mi < 0 || mi >= a->nm || a->stride % 4) return refuse(MAYA_ERR_ARG);
+    if ((size_t) T * n_embd > a->stride || !aligned16(ffn) || !aligned16(out) || (sh && !aligned16(sh))) return refuse(MAYA_ERR_ARG);
+    const int n4 = (int) ((size_t) T * n_embd / 4);
+    int blocks = (n4 + 255) / 256;
+    if (blocks > MAYA_PEER_AR_BLOCKS) blocks = MAYA_PEER_AR_BLOCKS;
+    combine_rows_local_ar_kernel<<<blocks, 256, 0, as_stream(stream)>>>(out, pos, w, ids, e_lo, e_hi, sh, k, n_embd, ffn, n4, *a,
+                                                                        mi, seq);
+    return note_launch("moe_combine_rows_local_ar");
 }
 extern "C" int maya_moe_combine_add(const float* out, int base, int lo, int hi, const int* pos, const float* w, int T,
                                     int k, int n_embd, float* ffn, void* stream) {

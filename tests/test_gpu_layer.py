@@ -268,6 +268,34 @@ def test_fused_kernel_many_calls_one_scratch(T, api):
     assert layer.error() == 0
 
 
+def test_window_combine_carries_the_cross_rank_sum(T, api, oracle):
+    """2..16 tokens on an expert-parallel rank: the rank-ordered sum of out[T][n_embd] runs inside the window's combine
+    launch.  Three ranks on this GPU, one after another; what the ranks still to run would push is placed beforehand."""
+    from project_maya_b200.peer import PeerGroup
+    from test_gpu_allreduce import place_peer_pushes
+    n_embd, n_ff, n_expert, k, nm, n_tok = 1024, 512, 12, 4, 3, 5
+    cfg = dict(n_embd=n_embd, n_ff=n_ff, n_expert=n_expert, k=k, gu_type=H.Q4_K, d_type=H.Q4_K, n_ff_sh=256,
+               sh_gu_type=H.Q8_0, sh_d_type=H.Q8_0)
+    lc, experts, sh = synth_layer(T, api, cfg, n_expert, seed=9)
+    logits = dev(T, H.router_logits("winar", n_tok, n_expert, 1.1))
+    x = dev(T, H.activations("winar", n_tok, n_embd, "bf16"), T.bfloat16)
+    per = n_expert // nm
+    layers = [api.MoeLayer(lc, experts, sh, expert_range=(r * per, (r + 1) * per), shared_here=(r == 0)) for r in range(nm)]
+    partial = [l.forward(logits, x)[2].clone() for l in layers]                     # each rank's own terms
+    want = np.stack([oracle.allreduce_in_order(np.stack([p[t].cpu().numpy() for p in partial])) for t in range(n_tok)])
+    ranks = PeerGroup.on_one_device(nm, stride=16 * n_embd, timeout_ms=200.0)
+    for r in ranks:
+        r.device_seq = False
+    vecs = [p.reshape(-1) for p in partial]
+    for mi in range(nm):
+        place_peer_pushes(T, ranks, mi, 1, vecs, later_only=True)
+    for r in range(nm):
+        out = layers[r].forward(logits, x, peer=ranks[r])[2]
+        T.cuda.synchronize()
+        assert not ranks[r].poisoned()
+        assert out.cpu().numpy().tobytes() == want.tobytes(), f"rank {r}"
+
+
 def test_fused_layer_barrier_times_out_and_reports(T, api):
     """The fused kernel's one wait on other blocks is bounded: with the scratch's epoch word set ahead of its arrival
     counter (a state no launch leaves behind) the grid barrier can never be satisfied; the call still returns after the

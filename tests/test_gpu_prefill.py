@@ -348,3 +348,17 @@ def test_c5_batch64_through_prompt_path_and_expert_parallel_partition(T, api, or
     summed = np.stack([oracle.allreduce_in_order(np.stack([p[tk] for p in partial])) for tk in range(n_tok)])
     assert H.rel_err(summed, got) <= 1e-5
     assert all(np.abs(p).max() > 0 for p in partial)
+    # the same partition with the cross-rank sum inside the combine launch: the four ranks run one after another on
+    # this GPU, the pushes of the ranks that have not run yet placed into a rank's receive buffers beforehand
+    from project_maya_b200.peer import PeerGroup
+    from test_gpu_allreduce import place_peer_pushes
+    ranks = PeerGroup.on_one_device(n_ranks, stride=n_tok * Hd, timeout_ms=200.0)
+    vecs = [T.from_numpy(p.reshape(-1)).cuda() for p in partial]
+    for mi in range(n_ranks):
+        place_peer_pushes(T, ranks, mi, 1, vecs, later_only=True)
+    for r in range(n_ranks):
+        rank = api.MoePrefill(lc, experts, max_tokens=n_tok, expert_range=(r * per, (r + 1) * per))
+        fused = rank.forward(ld, xd, peer=ranks[r])[2]
+        T.cuda.synchronize()
+        assert not ranks[r].poisoned()
+        assert fused.cpu().numpy().tobytes() == summed.tobytes(), f"rank {r}: not the rank-ordered sum"
