@@ -260,7 +260,7 @@ def gpu_arm(args) -> None:
     if world > 1 and args.ar == "peer":
         from project_maya_b200.peer import PeerGroup
         peer = PeerGroup.over_processes(rank, world, Hd, timeout_ms=5000.0)
-        peer.device_seq = True      # sequence numbers counted on the device: the K steps can be captured in a graph
+        peer.set_device_seq(True)   # sequence numbers counted on the device: the K steps can be captured in a graph
 
     def step(s: int, l_row, x_row):
         layers[s % len(layers)].forward(l_row, x_row, ids_d[s:s + 1], w_d[s:s + 1], out_d[s:s + 1], peer=peer)
@@ -376,6 +376,17 @@ def gpu_arm(args) -> None:
             names = ["route+quantize", "gate_up", "grid_barrier", "down+combine", "cross_rank_sum"]
             roof["block0_phase_end_us_last_timed_step"] = {n: step_phases[i + 1] / 1e3 for i, n in enumerate(names)}
 
+    # ---- configuration C5 (IQ3_S, experts partitioned by id, batch 1 and 64; peer exchange against NCCL) on every rank
+    c5 = None
+    if not args.no_c5:
+        import bench_c5
+        peer1 = peer64 = None
+        if world > 1:
+            from project_maya_b200.peer import PeerGroup
+            peer1 = PeerGroup.over_processes(rank, world, Hd, timeout_ms=5000.0)
+            peer64 = PeerGroup.over_processes(rank, world, 64 * Hd, timeout_ms=5000.0)
+        c5 = bench_c5.run(torch, api, dist if world > 1 else None, rank, world, peer1, peer64)
+
     if rank == 0:
         bytes_tok = algorithmic_bytes_per_token()
         value = K / (ms_dev * 1e-3)
@@ -410,6 +421,8 @@ def gpu_arm(args) -> None:
                        "us_per_step_x_median_sm_mhz": (ms_dev / K * 1e3) * (clocks.summary()["sm_mhz"] or 0.0)},
             "roofline": roof,
         }
+        if c5 is not None:
+            line["extra"] = {"c5": c5}
         if world == 1:
             line["gpu_baseline"] = reference_gpu_leg(torch, layers, logits_d, x_d, K)
         if world == 1 and not args.no_cpu_baseline:
@@ -521,6 +534,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-c5", action="store_true", help="skip the extra.c5 leg (IQ3_S expert-parallel layer, batch 1 and 64)")
     ap.add_argument("--ar", default="peer", choices=["peer", "nccl"], help="N > 1: how the ranks' partial outputs are summed")
     ap.add_argument("--partition", default="width", choices=["width", "expert"],
                     help="N > 1: every rank holds a width slice of every expert (default), or whole experts by id")

@@ -335,8 +335,10 @@ typedef struct maya_peer_ar {
     size_t stride;                   /* floats per row, a multiple of 4, >= n */
     unsigned long long timeout_ns;
     int nm;
-    unsigned* seq_counter;           /* optional device word (zeroed): lets maya_moe_layer_decode_ar take its sequence
-                                        number from the device (seq argument 0), so a captured CUDA graph can be replayed */
+    unsigned* seq_counter;           /* optional, TWO device words (zeroed): [0] lets maya_moe_layer_decode_ar and
+                                        maya_moe_combine_rows_local_ar take their sequence number from the device (seq
+                                        argument 0), so a captured CUDA graph can be replayed; [1] is scratch of those
+                                        launches (zero between them) */
 } maya_peer_ar;
 
 MAYA_API size_t maya_peer_ar_recv_bytes(int nm, size_t stride);
@@ -351,8 +353,8 @@ MAYA_API int maya_allreduce_peer(float* x, int n, const maya_peer_ar* a, int mi,
  * order) - no separate launch.  2..16 tokens: the window kernels, the sum inside their last launch: the combine kernel's
  * blocks exchange the rows they have just combined (the reference runs a separate allreduce over out[T * n_embd] after
  * win_experts, src/ds4/ds4_model.cu:22822-22828).
- * seq == 0 (single token only): the kernel uses *a->seq_counter + 1 and stores it back when it ends, so every rank's
- * n-th call carries n without the host counting - the form to capture in a CUDA graph. */
+ * seq == 0: the kernel uses *a->seq_counter + 1 and stores it back when it ends, so every rank's n-th call carries n
+ * without the host counting - the form to capture in a CUDA graph (a single token through the staged kernels excepted). */
 MAYA_API int maya_moe_layer_decode_ar(const maya_moe_layer* L, const float* logits, const void* x, int x_is_bf16,
                                       int n_tokens, int* ids, float* weights, float* out, void* scratch,
                                       size_t scratch_bytes, const maya_peer_ar* a, int mi, unsigned seq, void* stream);

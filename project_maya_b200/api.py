@@ -387,7 +387,7 @@ class MoeLayer:
             args = HcPostArgs(*[_ptr(t) for t in hc])
             seq = 0
             if peer is not None:
-                seq = 0 if (peer.device_seq and T == 1) else peer.next_seq()
+                seq = 0 if peer.device_seq else peer.next_seq()
             _check("moe_layer_decode_hc",
                    _lib.load().maya_moe_layer_decode_hc(C.byref(self.desc), _ptr(logits), _ptr(x), int(x.dtype == torch.bfloat16),
                                                         T, _ptr(ids), _ptr(weights), _ptr(out), _ptr(self.scratch),
@@ -399,7 +399,7 @@ class MoeLayer:
                    _lib.load().maya_moe_layer_decode_ar(C.byref(self.desc), _ptr(logits), _ptr(x), int(x.dtype == torch.bfloat16),
                                                         T, _ptr(ids), _ptr(weights), _ptr(out), _ptr(self.scratch),
                                                         self.scratch.numel(), C.byref(peer.desc), peer.mi,
-                                                        0 if (peer.device_seq and T == 1) else peer.next_seq(),
+                                                        0 if peer.device_seq else peer.next_seq(),
                                                         _stream(stream)))
             return ids, weights, out
         _check("moe_layer_decode",
@@ -531,7 +531,7 @@ class MoePrefill:
             _check("moe_combine_rows_local_ar",
                    lib.maya_moe_combine_rows_local_ar(_ptr(self.out), _ptr(self.pos), _ptr(w), _ptr(ids), self.expert_range[0],
                                                       self.expert_range[1], _ptr(sh_out), T, k, H, _ptr(ffn), C.byref(peer.desc),
-                                                      peer.mi, peer.next_seq(), s))
+                                                      peer.mi, 0 if peer.device_seq else peer.next_seq(), s))
         else:
             _check("moe_combine_rows_local",
                    lib.maya_moe_combine_rows_local(_ptr(self.out), _ptr(self.pos), _ptr(w), _ptr(ids), self.expert_range[0],

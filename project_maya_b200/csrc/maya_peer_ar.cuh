@@ -17,6 +17,29 @@ __device__ __forceinline__ float4 ld_fresh4(const float4* p) {   // bypass L1: t
     return v;
 }
 
+// Sequence numbers counted on the device (so that a captured CUDA graph can be replayed): a call made with seq == 0
+// uses seq_counter[0] + 1, and the LAST block of the launch to finish stores it back - by then every block has read
+// the counter.  seq_counter[1] is the launch's finishing ticket (zero between launches).
+// The count skips 0 when it wraps (a zeroed word or flag would match it) by going from 0xffffffff to 2, which also keeps
+// the two receive slots alternating (slot = seq & 1).
+__device__ __forceinline__ unsigned ar_seq_next(unsigned c) { return c == 0xffffffffu ? 2u : c + 1u; }
+__device__ __forceinline__ unsigned ar_seq_begin(const maya_peer_ar& a, unsigned seq) {
+    return seq != 0u || a.seq_counter == nullptr ? seq : ar_seq_next(*(volatile unsigned*) a.seq_counter);
+}
+// every thread of the block calls this after the block's exchange
+__device__ __forceinline__ void ar_seq_end(const maya_peer_ar& a, unsigned seq_arg, unsigned used) {
+    if (seq_arg != 0u || a.seq_counter == nullptr) return;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&a.seq_counter[1], 1u) == gridDim.x - 1u) {
+            a.seq_counter[1] = 0u;
+            *(volatile unsigned*) a.seq_counter = used;
+            __threadfence();
+        }
+    }
+}
+
 // Device-side protocol for one block's share [q0, q1) (in float4 units) of the vector; block index `b` picks the flag
 // word.  Callable from the stand-alone kernel and from the fused layer kernel's epilogue.  Returns false when the
 // transport is (or becomes) poisoned; x is then left as the local partial.
@@ -87,7 +110,8 @@ __device__ __forceinline__ bool peer_allreduce_block(float* x, int q0, int q1, c
 // 64-bit words, zeroed at start), and the receiver polls the word itself.  No fence, no separate flag: one NVLink
 // one-way latency, where rows + flags cost a store round trip (the system fence) and then the flag's trip.  64-bit
 // stores are single-copy atomic, the two slots alternate by seq as above (a word is overwritten two calls later, which
-// the writer only reaches after this rank's reads of it), seq is never 0.  Same bounded wait, error word and failure
+// the writer only reaches after this rank's reads of it); seq is never 0 (the device count skips it when it wraps,
+// ar_seq_next; a host that counts must do the same).  Same bounded wait, error word and failure
 // record.  Returns false when the transport is (or becomes) poisoned; x is then undefined.
 __device__ __forceinline__ bool peer_allreduce_block_words(float* x, int q0, int q1, const maya_peer_ar& a, int mi,
                                                            unsigned seq, int b) {

@@ -379,7 +379,9 @@ __global__ void __launch_bounds__(256) win_combine_ar_kernel(const unsigned long
         ((float4*) out)[q] = m;
     }
     __syncthreads();
-    peer_allreduce_block(out, q0, q1, a, mi, seq, b);
+    const unsigned sq = ar_seq_begin(a, seq);
+    peer_allreduce_block(out, q0, q1, a, mi, sq, b);
+    ar_seq_end(a, seq, sq);
 }
 
 // native_moe combine: s = parts[0] * w[0]; s = fma(parts[i], w[i], s); + shared (native_moe.cu:42-47).

@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (tid == 0) {
         sh.epoch = *(volatile unsigned*) &A.sync[1];
-        sh.ar_seq = A.ar_seq != 0u || A.ar.seq_counter == nullptr ? A.ar_seq : *(volatile unsigned*) A.ar.seq_counter + 1u;
+        sh.ar_seq = ar_seq_begin(A.ar, A.ar_seq);
     }
     stamp(A.sync, 0);
 

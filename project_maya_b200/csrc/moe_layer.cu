@@ -150,8 +150,9 @@ static int ar_args_ok(const maya_moe_layer* L, int n_tokens, float* out, const m
         return MAYA_ERR_ARG;
     if (L && n_tokens > 0 && (size_t) n_tokens * L->n_embd > a->stride) return MAYA_ERR_ARG;
     if (out && !aligned16(out)) return MAYA_ERR_ARG;
-    if (seq == 0u && (a->seq_counter == nullptr || n_tokens != 1 || (L && (L->staged || !fused_t1_supported(*L)))))
-        return MAYA_ERR_ARG;           // the device-side sequence number exists only in the fused single-token kernel
+    // the device-side sequence number lives in the fused single-token kernel and in the window's combine launch
+    if (seq == 0u && (a->seq_counter == nullptr || (n_tokens == 1 && L && (L->staged || !fused_t1_supported(*L)))))
+        return MAYA_ERR_ARG;
     return MAYA_OK;
 }
 

@@ -141,7 +141,9 @@ __global__ void __launch_bounds__(256) combine_rows_local_ar_kernel(const float*
         ((float4*) ffn)[q] = m;
     }
     __syncthreads();
-    peer_allreduce_block(ffn, q0, q1, a, mi, seq, b);
+    const unsigned sq = ar_seq_begin(a, seq);
+    peer_allreduce_block(ffn, q0, q1, a, mi, sq, b);
+    ar_seq_end(a, seq, sq);
 }
 
 // ffn[t] += sum over t's routes whose sorted row lies in [lo, hi) of w * out[row - base]
@@ -213,6 +215,7 @@ extern "C" int maya_moe_combine_rows_local_ar(const float* out, const int* pos, 
     if (!out || !pos || !w || !ids || !ffn || k <= 0 || n_embd <= 0 || n_embd % 4 || e_lo > e_hi) return refuse(MAYA_ERR_ARG);
     if (!a || !a->recv || !a->peer_recv || !a->flags || !a->peer_flags || !a->error || a->timeout_ns == 0) return refuse(MAYA_ERR_ARG);
     if (a->nm < 2 || a->nm > MAYA_PEER_AR_MAX_RANKS || mi < 0 || mi >= a->nm || a->stride % 4) return refuse(MAYA_ERR_ARG);
+    if (seq == 0u && a->seq_counter == nullptr) return refuse(MAYA_ERR_ARG);
     if ((size_t) T * n_embd > a->stride || !aligned16(ffn) || !aligned16(out) || (sh && !aligned16(sh))) return refuse(MAYA_ERR_ARG);
     const int n4 = (int) ((size_t) T * n_embd / 4);
     int blocks = (n4 + 255) / 256;

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes as C
 
+import numpy as np
 import torch
 
 from . import _lib
@@ -27,17 +28,29 @@ class PeerRank:
         self.failure = torch.zeros(C.sizeof(PeerArFailure), dtype=torch.uint8, device="cuda")
         self.recv_tab = torch.tensor(peer_recv, dtype=torch.int64, device="cuda")
         self.flag_tab = torch.tensor(peer_flags, dtype=torch.int64, device="cuda")
-        self.seq_counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.seq_counter = torch.zeros(2, dtype=torch.int32, device="cuda")   # [0] the count, [1] scratch of the launches
         self.desc = PeerArDesc(recv_ptr, self.recv_tab.data_ptr(), flags_ptr, self.flag_tab.data_ptr(),
                                self.error.data_ptr(), self.failure.data_ptr(), stride, int(timeout_ms * 1e6), nm,
                                self.seq_counter.data_ptr())
-        self.device_seq = False     # True: single-token layer calls take their sequence number from seq_counter
+        self.device_seq = False     # True: layer and prompt-path calls take their sequence number from seq_counter
         self.seq = 0
         self.keep = keep
 
     def next_seq(self) -> int:
-        self.seq = (self.seq + 1) & 0xFFFFFFFF
+        """The next sequence number: modulo 2^32, never 0 (0xffffffff is followed by 2, which keeps the two receive
+        slots alternating), as the device-side count does."""
+        self.seq = 2 if self.seq == 0xFFFFFFFF else self.seq + 1
         return self.seq
+
+    def set_device_seq(self, on: bool) -> None:
+        """Hand the count to the device (calls then pass seq 0 and can be captured in a CUDA graph) or take it back."""
+        if on:
+            self.seq_counter[0] = int(np.array(self.seq, np.uint32).view(np.int32))
+            self.seq_counter[1] = 0
+        else:
+            torch.cuda.synchronize()
+            self.seq = int(np.array(int(self.seq_counter[0].item()), np.int32).view(np.uint32))
+        self.device_seq = on
 
     def allreduce(self, x, seq: int | None = None, stream=None):
         """allreduce_peer: x (f32, numel % 4 == 0) becomes the rank-ordered sum over the group, in place."""

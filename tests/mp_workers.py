@@ -107,8 +107,7 @@ def layer_ep_worker(rank: int, world: int, port: int, q):
             if got.cpu().numpy().tobytes() != want.tobytes():
                 bad += 1
         # sequence numbers counted on the device: three single-token calls captured in a CUDA graph, replayed twice
-        peer.seq_counter.fill_(peer.seq)
-        peer.device_seq = True
+        peer.set_device_seq(True)
         ids_g = torch.empty((3, 1, k), dtype=torch.int32, device="cuda")
         w_g = torch.empty((3, 1, k), dtype=torch.float32, device="cuda")
         out_g = torch.zeros((3, 1, n_embd), dtype=torch.float32, device="cuda")

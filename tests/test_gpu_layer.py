@@ -402,6 +402,39 @@ def test_fused_layer_exchanges_flagged_words(T, api, oracle):
     assert not ranks[1].poisoned()
 
 
+def test_fused_layer_word_exchange_sequence_wraps(T, api, oracle):
+    """The device-side sequence count across 2^32 (the reference's own transport test starts at 0xffffffe0,
+    tests/ds4_peer_allreduce_test.cu:143): preset to 0xfffffff8, 24 single-token calls on rank 1 of 2 with rank 0's words
+    placed beforehand under the number each call will use.  The count never takes the value 0 (a zeroed word would
+    match it): 0xffffffff is followed by 2, which also keeps the two receive slots alternating."""
+    from project_maya_b200.peer import PeerGroup
+    cfg = dict(n_embd=1024, n_ff=512, n_expert=8, k=2, gu_type=H.Q8_0, d_type=H.Q8_0)
+    lc, experts, _ = synth_layer(T, api, cfg, 8, seed=31)
+    layer = api.MoeLayer(lc, experts, None)
+    n = cfg["n_embd"]
+    ranks = PeerGroup.on_one_device(2, stride=n, timeout_ms=50.0)
+    r = ranks[1]
+    r.seq = 0xFFFFFFF8
+    r.set_device_seq(True)
+    ld, xd = dev(T, H.router_logits("wrap", 1, 8, 1.1)), dev(T, H.activations("wrap", 1, n, "bf16"), T.bfloat16)
+    local = layer.forward(ld, xd)[2].cpu().numpy()[0]
+    rng = np.random.default_rng(9)
+    seq, seen = 0xFFFFFFF8, []
+    for _ in range(24):
+        seq = 2 if seq == 0xFFFFFFFF else seq + 1
+        seen.append(seq)
+        other = rng.standard_normal(n).astype(np.float32)
+        _word_area(T, r)[seq & 1, 0, :n] = T.from_numpy(_words(seq, other)).cuda()
+        got = layer.forward(ld, xd, peer=r)[2].cpu().numpy()[0]
+        assert got.tobytes() == oracle.allreduce_in_order(np.stack([other, local])).tobytes(), hex(seq)
+        pushed = _word_area(T, ranks[0])[seq & 1, 1, :n].cpu().numpy()
+        assert np.array_equal(pushed, _words(seq, local))
+    assert 0 not in seen and 0xFFFFFFFF in seen and 2 in seen
+    assert all((a & 1) != (b & 1) for a, b in zip(seen, seen[1:]))         # the slots alternate across the wrap too
+    r.set_device_seq(False)
+    assert r.seq == seen[-1] and not r.poisoned()
+
+
 def test_fused_layer_exchange_times_out_and_poisons(T, api):
     """A peer that never sends: the wait in the fused kernel's epilogue gives up after the time-out, records who it
     waited for and poisons the transport; later calls return at once and the device still answers."""
