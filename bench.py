@@ -421,8 +421,21 @@ def gpu_arm(args) -> None:
                        "us_per_step_x_median_sm_mhz": (ms_dev / K * 1e3) * (clocks.summary()["sm_mhz"] or 0.0)},
             "roofline": roof,
         }
+        extra = {}
         if c5 is not None:
-            line["extra"] = {"c5": c5}
+            extra["c5"] = c5
+        if world == 1 and not args.no_extra:
+            del layers[1:]                      # the other workloads bring their own expert tables: make room
+            torch.cuda.empty_cache()
+            import bench_c3
+            import bench_prefill
+            extra["c3"] = bench_c3.run(torch, api)
+            torch.cuda.empty_cache()
+            pf = bench_prefill.run(4, 3, 1)
+            extra["prefill_c4"] = {"workload": pf["config"]["workload"], "tok_s_layer": pf["value"], "ms_per_4096_token_chunk": pf["ms_per_step"],
+                                   "e2e_tok_s_layer": pf["e2e"]["value"], "roofline": pf["roofline"], "gpu_launches": pf["gpu_launches"]}
+        if extra:
+            line["extra"] = extra
         if world == 1:
             line["gpu_baseline"] = reference_gpu_leg(torch, layers, logits_d, x_d, K)
         if world == 1 and not args.no_cpu_baseline:
@@ -534,12 +547,14 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip extra.c3 and extra.prefill_c4 (1 GPU)")
     ap.add_argument("--no-c5", action="store_true", help="skip the extra.c5 leg (IQ3_S expert-parallel layer, batch 1 and 64)")
     ap.add_argument("--ar", default="peer", choices=["peer", "nccl"], help="N > 1: how the ranks' partial outputs are summed")
     ap.add_argument("--partition", default="width", choices=["width", "expert"],
                     help="N > 1: every rank holds a width slice of every expert (default), or whole experts by id")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
-                    help="decode: the headline single-token layer (C2); prefill: the 4096-token prompt chunk (C4), 1 GPU")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "c3"],
+                    help="decode: the headline single-token layer (C2); prefill: the 4096-token prompt chunk (C4), 1 GPU; "
+                         "c3: the 8-token decode window (C3), 1 GPU")
     ap.add_argument("--prefill-scale", type=int, default=1,
                     help="prefill only: divide experts and tokens by this (a reduced case for profiler captures)")
     args = ap.parse_args()
@@ -550,6 +565,12 @@ def main() -> None:
         line = bench_prefill.run(steps, args.warmup if args.warmup != 8 else 3, min(args.layers, 2), sampler, args.prefill_scale)
         line["clocks"] = sampler.summary()
         print(json.dumps(line))
+        return
+    if args.workload == "c3" and args.impl == "ours":
+        import torch
+        import bench_c3
+        from project_maya_b200 import api
+        print(json.dumps(bench_c3.run(torch, api)))
         return
     if args.impl == "reference":
         reference_arm(args)
