@@ -286,6 +286,15 @@ typedef struct maya_moe_layer {
                                     width-sliced placement; summed in another order than on one rank, so equal to it
                                     only to rounding).  A proper slice needs the single fused kernel (one token, Q8_0
                                     shared expert): otherwise the call is refused */
+    int router;                  /* 0: softmax routing (router_top10); 1: sigmoid routing (router_sigmoid.hpp:27,
+                                    glmf::moe_route's arithmetic, glm_fast.hpp:426) with the three fields below */
+    const float* router_bias;    /* sigmoid: [n_expert] added to the scores for the SELECTION only; NULL: none */
+    float router_w_scale;        /* sigmoid: the weights are multiplied by it */
+    int router_norm_w;           /* sigmoid: non-zero divides the weights by max(their sum, 2^-14) first */
+    const float* cpu_part;       /* the tier hooks of MoeDev (glm_fast.hpp:299-300): [n_tokens][n_embd] - what a host lane */
+    const int* cpu_flag;         /* computed for experts that are not resident - added to token t's output when
+                                    cpu_flag[t] != 0 (after the routed terms, before the shared expert, moe_down's order);
+                                    NULL: no host contribution.  With several ranks give it to one rank only. */
 } maya_moe_layer;
 /* Bytes of scratch maya_moe_layer_decode needs for n_tokens tokens.  The scratch must be 256-byte aligned and ZEROED
  * once before its first use (it holds the fused kernel's grid-barrier counter); one scratch serves one stream at a

@@ -39,7 +39,8 @@ class MoeLayerDesc(C.Structure):
                 ("d_type", c_int), ("experts", c_void_p), ("expert_stride", c_size_t), ("n_ff_sh", c_int),
                 ("sh_gu_type", c_int), ("sh_d_type", c_int), ("shared", c_void_p), ("limit", c_float),
                 ("expert_lo", c_int), ("expert_hi", c_int), ("shared_here", c_int), ("staged", c_int), ("sh_lo", c_int),
-                ("sh_hi", c_int)]
+                ("sh_hi", c_int), ("router", c_int), ("router_bias", c_void_p), ("router_w_scale", c_float),
+                ("router_norm_w", c_int), ("cpu_part", c_void_p), ("cpu_flag", c_void_p)]
 
 
 class MmqProduct(C.Structure):

@@ -356,10 +356,12 @@ class MoeLayer:
     forward(logits, x) runs route -> experts -> combine for up to 16 tokens and returns (ids, weights, out).
     expert_range = (lo, hi) restricts this rank to experts lo..hi-1 (expert-parallel partition); the others' terms are
     left out of `out` (another rank adds them).  shared_range = (lo, hi) gives this rank a slice of the shared expert's
-    FFN width instead of all of it (single-token calls only)."""
+    FFN width instead of all of it (single-token calls only).  sigmoid = (bias [n_expert] or None, w_scale, norm_w):
+    sigmoid routing with a selection bias instead of softmax.  cpu_part [T, n_embd] f32 / cpu_flag [T] i32: a host lane's
+    contribution, added to token t's output when cpu_flag[t] != 0 (the tier hooks of the reference's MoeDev)."""
 
     def __init__(self, cfg: MoeLayerConfig, experts, shared=None, expert_range=None, shared_here=True, max_tokens: int = 16,
-                 staged: bool = False, shared_range=None):
+                 staged: bool = False, shared_range=None, sigmoid=None, cpu_part=None, cpu_flag=None):
         self.cfg = cfg
         self.experts = experts
         self.shared = shared
@@ -367,7 +369,10 @@ class MoeLayer:
         self.desc = MoeLayerDesc(cfg.n_embd, cfg.n_ff, cfg.n_expert, cfg.k, cfg.gu_type, cfg.d_type, _ptr(experts),
                                  cfg.blob_bytes, cfg.n_ff_sh if shared is not None else 0, cfg.sh_gu_type,
                                  cfg.sh_d_type, _ptr(shared), cfg.limit, lo, hi, int(bool(shared_here)), int(bool(staged)),
-                                 *(shared_range if shared_range is not None else (0, 0)))
+                                 *(shared_range if shared_range is not None else (0, 0)),
+                                 *((1, _ptr(sigmoid[0]), float(sigmoid[1]), int(bool(sigmoid[2]))) if sigmoid is not None else (0, None, 1.0, 0)),
+                                 _ptr(cpu_part), _ptr(cpu_flag))
+        self._keep = (sigmoid, cpu_part, cpu_flag)
         self.max_tokens = max_tokens
         nbytes = int(_lib.load().maya_moe_layer_scratch_bytes(C.byref(self.desc), max_tokens))
         if nbytes == 0:

@@ -7,6 +7,12 @@ namespace maya {
 
 struct FusedArgs {
     const float* logits;       // [n_expert]
+    int router;                // 0 softmax, 1 sigmoid (+ bias for the selection, weight scale, optional normalisation)
+    const float* router_bias;
+    float router_w_scale;
+    int router_norm_w;
+    const float* cpu_part;     // [n_embd] the host lane's contribution, added when *cpu_flag != 0 (NULL: none)
+    const int* cpu_flag;
     const void* x;             // [n_embd] f32 or bf16
     int x_is_bf16;
     int n_embd, n_ff, n_expert, k;

@@ -173,4 +173,36 @@ __device__ __forceinline__ void route_softmax(const float* __restrict__ l, int n
     Sync::sync();
 }
 
+// One token's sigmoid routing (router_sigmoid.cu:29-74, glm_batch.cu:2063-2100): p = sigmoid(logit) in FP32, selection on
+// p + bias (bias NULL: none), the stable descending top-k, weights from the unbiased p - divided in double by
+// max(their sum, 2^-14) when norm_w - times w_scale.  On return sh.ids[0..k) / sh.val[0..k) hold ids and final weights.
+template<int PER, class Sync>
+__device__ __forceinline__ void route_sigmoid(const float* __restrict__ l, const float* __restrict__ bias, int n_expert, int k,
+                                              float w_scale, int norm_w, int tid, int nt, RouterShared& sh) {
+    float p[PER], sel[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int e = j * nt + tid;
+        if (e < n_expert) {
+            p[j] = __fdiv_rn(1.0f, 1.0f + expf(-l[e]));
+            sel[j] = bias ? p[j] + bias[e] : p[j];
+        } else {
+            p[j] = 0.0f;
+            sel[j] = -INFINITY;
+        }
+    }
+    select_topk<PER, Sync>(sel, p, n_expert, k, tid, nt, sh);
+    if (tid == 0) {
+        double s = 0.0;
+        for (int i = 0; i < k; ++i) s += (double) sh.val[i];
+        const double sc = fmax(s, 6.103515625e-05);
+        for (int i = 0; i < k; ++i) {
+            float w = sh.val[i];
+            if (norm_w) w = (float) ((double) w / sc);
+            sh.val[i] = w * w_scale;
+        }
+    }
+    Sync::sync();
+}
+
 }  // namespace maya

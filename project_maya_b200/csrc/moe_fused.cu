@@ -147,7 +147,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     if (tid < kRouteThreads) {
         using RS = NamedSync<1, kRouteThreads>;
         const int per = (A.n_expert + kRouteThreads - 1) / kRouteThreads;
-        if (per <= 1) route_softmax<1, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
+        if (A.router == 1) {
+            if (per <= 1) route_sigmoid<1, RS>(A.logits, A.router_bias, A.n_expert, k, A.router_w_scale, A.router_norm_w, tid, kRouteThreads, sh.route);
+            else if (per <= 2) route_sigmoid<2, RS>(A.logits, A.router_bias, A.n_expert, k, A.router_w_scale, A.router_norm_w, tid, kRouteThreads, sh.route);
+            else if (per <= 4) route_sigmoid<4, RS>(A.logits, A.router_bias, A.n_expert, k, A.router_w_scale, A.router_norm_w, tid, kRouteThreads, sh.route);
+            else route_sigmoid<8, RS>(A.logits, A.router_bias, A.n_expert, k, A.router_w_scale, A.router_norm_w, tid, kRouteThreads, sh.route);
+        } else if (per <= 1) route_softmax<1, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
         else if (per <= 2) route_softmax<2, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
         else if (per <= 4) route_softmax<4, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
         else route_softmax<8, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
@@ -362,6 +367,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
         if (tid < nrows) {
             float m = 0.0f;
             for (int i = 0; i < k; ++i) m = __fmaf_rn(sh.w[i], sh.ptr[i] != 0ull ? sh.part[tid][i] : 0.0f, m);
+            if (A.cpu_flag != nullptr && *A.cpu_flag) m = __fadd_rn(m, A.cpu_part[o0 + tid]);    // the host lane's answer (moe_down's order)
             A.out[o0 + tid] = __fadd_rn(m, has_sh ? sh.part[tid][k] : 0.0f);
         }
     }
@@ -464,6 +470,8 @@ int fused_t1(const maya_moe_layer& L, const float* logits, const void* x, int x_
     if (hc != nullptr) A.hc = *hc;
     if (ar != nullptr) { A.ar = *ar; A.ar_rank = ar_rank; A.ar_seq = ar_seq; }
     A.logits = logits; A.x = x; A.x_is_bf16 = x_is_bf16;
+    A.router = L.router; A.router_bias = L.router_bias; A.router_w_scale = L.router_w_scale; A.router_norm_w = L.router_norm_w;
+    A.cpu_part = L.cpu_flag != nullptr ? L.cpu_part : nullptr; A.cpu_flag = L.cpu_flag;
     A.n_embd = L.n_embd; A.n_ff = L.n_ff; A.n_expert = L.n_expert; A.k = L.k;
     A.experts = (const uint8_t*) L.experts; A.expert_stride = L.expert_stride;
     A.expert_lo = L.expert_lo; A.expert_hi = L.expert_hi;

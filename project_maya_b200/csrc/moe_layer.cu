@@ -92,6 +92,8 @@ int check_layer(const maya_moe_layer* L) {
         if (L->n_embd % type_qk(L->sh_gu_type) || L->n_ff_sh % type_qk(L->sh_d_type) || L->n_ff_sh % 32) return MAYA_ERR_ARG;
     }
     if (L->expert_lo < 0 || L->expert_hi > L->n_expert || L->expert_lo > L->expert_hi) return MAYA_ERR_ARG;
+    if (L->router != 0 && L->router != 1) return MAYA_ERR_ARG;
+    if (L->cpu_flag != nullptr && L->cpu_part == nullptr) return MAYA_ERR_ARG;
     if (L->sh_lo != 0 || L->sh_hi != 0) {            // a slice of the shared expert's width
         if (L->sh_lo < 0 || L->sh_hi > L->n_ff_sh || L->sh_lo > L->sh_hi || L->sh_lo % 32 || L->sh_hi % 32) return MAYA_ERR_ARG;
     }
@@ -194,7 +196,9 @@ static int layer_decode(const maya_moe_layer* L, const float* logits, const void
     if (L->n_ff_sh > 0 && L->shared_here && (L->sh_lo != 0 || (L->sh_hi != 0 && L->sh_hi != L->n_ff_sh)))
         return refuse(MAYA_ERR_ARG);                 // only the fused kernel slices the shared expert
 
-    st = maya_router_top10(logits, T, L->n_expert, L->k, d_ids, d_w, stream);
+    st = L->router == 1 ? maya_router_sigmoid(logits, L->router_bias, T, L->n_expert, L->k, L->router_w_scale, L->router_norm_w,
+                                              d_ids, d_w, stream)
+                        : maya_router_top10(logits, T, L->n_expert, L->k, d_ids, d_w, stream);
     if (st != MAYA_OK) return st;
     st = x_is_bf16 ? maya_quantize_q8_1_bf16((const uint16_t*) x, S.xq, L->n_embd, T, stream)
                    : maya_quantize_q8_1((const float*) x, S.xq, L->n_embd, T, stream);
@@ -226,7 +230,7 @@ static int layer_decode(const maya_moe_layer* L, const float* logits, const void
     const size_t up_off = row_bytes(L->gu_type, L->n_embd) * (size_t) L->n_ff;
     const size_t down_off = 2 * up_off;
     if (T == 1) {
-        maya_moe_plan P{S.plan_ptr, S.plan_w, nullptr, nullptr, nullptr};
+        maya_moe_plan P{S.plan_ptr, S.plan_w, L->cpu_flag ? L->cpu_part : nullptr, L->cpu_flag, nullptr};
         st = maya_moe_gate_up(L->gu_type, &P, L->k, L->n_embd, L->n_ff, L->limit, S.xq, S.hq,
                               shared ? sh_blob + sh_down_off : nullptr, L->sh_d_type, S.sh_hq, L->n_ff_sh, S.sh_out, stream);
         if (st != MAYA_OK) return st;
@@ -249,6 +253,8 @@ static int layer_decode(const maya_moe_layer* L, const float* logits, const void
     W.xq_stride = (size_t) (L->n_embd / 32) * kQ81Bytes;
     W.hq = S.hq;
     W.part = S.part;
+    W.cpu_part = L->cpu_flag ? L->cpu_part : nullptr;
+    W.cpu_flag = L->cpu_flag;
     W.sh_out = shared ? S.sh_out : nullptr;
     W.out = out;
     W.out_stride = (size_t) L->n_embd;

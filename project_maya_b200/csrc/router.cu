@@ -30,30 +30,10 @@ __global__ void __launch_bounds__(kRouterThreads) router_sigmoid_kernel(const fl
                                                                         float* __restrict__ weights) {
     __shared__ RouterShared sh;
     const int t = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
-    const float* l = logits + (size_t) t * n_expert;
-    float p[PER], sel[PER];
-#pragma unroll
-    for (int j = 0; j < PER; ++j) {
-        const int e = j * nt + tid;
-        if (e < n_expert) {
-            p[j] = __fdiv_rn(1.0f, 1.0f + expf(-l[e]));
-            sel[j] = bias ? p[j] + bias[e] : p[j];
-        } else {
-            p[j] = 0.0f;
-            sel[j] = -INFINITY;
-        }
-    }
-    select_topk<PER, BlockSync>(sel, p, n_expert, k, tid, nt, sh);
-    if (tid == 0) {
-        double s = 0.0;
-        for (int i = 0; i < k; ++i) s += (double) sh.val[i];
-        const double sc = fmax(s, 6.103515625e-05);
-        for (int i = 0; i < k; ++i) {
-            float w = sh.val[i];
-            if (norm_w) w = (float) ((double) w / sc);
-            ids[(size_t) t * k + i] = sh.ids[i];
-            weights[(size_t) t * k + i] = w * w_scale;
-        }
+    route_sigmoid<PER, BlockSync>(logits + (size_t) t * n_expert, bias, n_expert, k, w_scale, norm_w, tid, nt, sh);
+    if (tid < k) {
+        ids[(size_t) t * k + tid] = sh.ids[tid];
+        weights[(size_t) t * k + tid] = sh.val[tid];
     }
 }
 

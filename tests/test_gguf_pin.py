@@ -199,3 +199,18 @@ def test_kernels_on_gguf_layer_match_llama_cpp(g, oracle, cuda):
         want_oracle[t] = oracle.combine_down(parts, g["weights"][t], sho)
     assert H.rel_err(got, want_oracle) <= 2e-4
     assert H.rel_err(got, g["out"]) <= QUANT_TOL
+    # the same layer through ONE call: maya_moe_layer_decode with its sigmoid-router option (selection bias, weight scale,
+    # normalised weights) - the fused single-token kernel and the window path - gives the staged sequence's bits
+    if float(g["clamp"]) == float(g["clamp_sh"]):
+        lc = api.MoeLayerConfig(L.n_embd, L.n_ff, blobs.shape[0], k, H.Q8_0, H.Q8_0, n_ff_sh, H.Q8_0, H.Q8_0, lim)
+        bias = T.from_numpy(g["router_bias"]).cuda()
+        layer = api.MoeLayer(lc, blobs, sh, sigmoid=(bias, float(g["w_scale"]), True))
+        xs = T.from_numpy(g["x"]).cuda()
+        for t in range(g["x"].shape[0]):
+            ids1, w1, out1 = layer.forward(logits[t:t + 1], xs[t:t + 1])
+            assert np.array_equal(ids1.cpu().numpy()[0], g["ids"][t])
+            assert out1.cpu().numpy()[0].tobytes() == got[t].tobytes()
+        nwin = min(g["x"].shape[0], 16)
+        ids_w, _, out_w = layer.forward(logits[:nwin], xs[:nwin])
+        assert np.array_equal(ids_w.cpu().numpy(), g["ids"][:nwin])
+        assert out_w.cpu().numpy().tobytes() == got[:nwin].tobytes()

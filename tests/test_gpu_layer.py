@@ -268,6 +268,51 @@ def test_fused_kernel_many_calls_one_scratch(T, api):
     assert layer.error() == 0
 
 
+@pytest.mark.parametrize("t", [H.IQ2_S, H.Q4_K])
+def test_layer_sigmoid_router_and_host_lane_hooks(T, api, oracle, t):
+    """maya_moe_layer's options: sigmoid routing (selection bias, weight scale, normalisation: router_sigmoid's
+    arithmetic) and the tier hooks cpu_part / cpu_flag (MoeDev's, glm_fast.hpp:299-300).  The fused single-token kernel,
+    the staged kernels and the window path agree bit for bit; the ids are the oracle's sigmoid router's; the host lane's
+    vector enters after the routed terms and before the shared expert (moe_down's order), only when its flag is set."""
+    n_embd, n_ff, E, k = 1024, 512, 24, 4
+    cfg = dict(n_embd=n_embd, n_ff=n_ff, n_expert=E, k=k, gu_type=t, d_type=t, n_ff_sh=256, sh_gu_type=H.Q8_0, sh_d_type=H.Q8_0)
+    lc, experts, sh = synth_layer(T, api, cfg, E, seed=17)
+    rng = H.rng_for("sigmoid-layer", t)
+    bias = (0.3 * rng.standard_normal(E)).astype(np.float32)
+    logits = H.router_logits("sigmoid-layer", 6, E, None)
+    x = H.activations("sigmoid-layer", 6, n_embd, "bf16")
+    cpu_part = rng.standard_normal((6, n_embd)).astype(np.float32)
+    flags = np.array([1, 0, 1, 1, 0, 1], np.int32)
+    ld, xd, bd = dev(T, logits), dev(T, x, T.bfloat16), dev(T, bias)
+    cp, cf = dev(T, cpu_part), dev(T, flags)
+    ids_o, w_o = oracle.router_sigmoid(logits, bias, k, 2.5, True)
+    plain = api.MoeLayer(lc, experts, sh, sigmoid=(bd, 2.5, True))
+    staged_plain = api.MoeLayer(lc, experts, sh, sigmoid=(bd, 2.5, True), staged=True)
+    for i in range(6):
+        hooked = api.MoeLayer(lc, experts, sh, sigmoid=(bd, 2.5, True), cpu_part=cp[i:i + 1], cpu_flag=cf[i:i + 1])
+        hooked_staged = api.MoeLayer(lc, experts, sh, sigmoid=(bd, 2.5, True), cpu_part=cp[i:i + 1], cpu_flag=cf[i:i + 1], staged=True)
+        ids_f, w_f, out_f = hooked.forward(ld[i:i + 1], xd[i:i + 1])
+        ids_s, w_s, out_s = hooked_staged.forward(ld[i:i + 1], xd[i:i + 1])
+        assert np.array_equal(ids_f.cpu().numpy()[0], ids_o[i]) and T.equal(ids_f, ids_s)
+        assert np.abs(w_f.cpu().numpy()[0] - w_o[i]).max() <= 1e-6 and T.equal(w_f, w_s)
+        assert T.equal(out_f, out_s), f"token {i}: fused and staged kernels differ"
+        base = plain.forward(ld[i:i + 1], xd[i:i + 1])[2]
+        assert T.equal(base, staged_plain.forward(ld[i:i + 1], xd[i:i + 1])[2])
+        if flags[i]:
+            assert not T.equal(out_f, base)
+            assert H.rel_err((out_f - base).cpu().numpy()[0], cpu_part[i]) <= 1e-5
+        else:
+            assert T.equal(out_f, base)
+    win = api.MoeLayer(lc, experts, sh, sigmoid=(bd, 2.5, True), cpu_part=cp, cpu_flag=cf)
+    ids_w, _, out_w = win.forward(ld, xd)
+    assert np.array_equal(ids_w.cpu().numpy(), ids_o)
+    for i in range(6):
+        one = api.MoeLayer(lc, experts, sh, sigmoid=(bd, 2.5, True), cpu_part=cp[i:i + 1], cpu_flag=cf[i:i + 1])
+        assert T.equal(out_w[i], one.forward(ld[i:i + 1], xd[i:i + 1])[2][0]), f"window row {i}"
+    with pytest.raises(api.MayaError):
+        api.MoeLayer(lc, experts, sh, cpu_flag=cf[:1]).forward(ld[:1], xd[:1])        # a flag without the vector
+
+
 def test_window_combine_carries_the_cross_rank_sum(T, api, oracle):
     """2..16 tokens on an expert-parallel rank: the rank-ordered sum of out[T][n_embd] runs inside the window's combine
     launch.  Three ranks on this GPU, one after another; what the ranks still to run would push is placed beforehand."""
