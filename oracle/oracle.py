@@ -99,6 +99,18 @@ class Oracle:
         assert rc == 0
         return (part, hq) if want_hq else part
 
+    def expert_q8_1_mixed(self, g_type, u_type, d_type, blob, n_embd, n_ff, limit, xq) -> np.ndarray:
+        """A layer whose up rows have their own type (native_expert_layout(gu_type, up_type, d_type, ...),
+        iq_kernels.hpp:73-77): gate rows, then up rows, then down rows in the blob; the same three GEMVs, SwiGLU and
+        q8_1 image of h as expert_q8_1, composed from the single steps.  With g_type == u_type it is expert_q8_1."""
+        blob = _u8(blob)
+        up_off = n_ff * self.row_bytes(g_type, n_embd)
+        down_off = up_off + n_ff * self.row_bytes(u_type, n_embd)
+        g = self.mmvq(g_type, blob[:up_off], xq, n_embd, n_ff)[0]
+        u = self.mmvq(u_type, blob[up_off:down_off], xq, n_embd, n_ff)[0]
+        hq = self.quantize_q8_1(self.swiglu(g, u, limit))
+        return self.mmvq(d_type, blob[down_off:], hq, n_ff, n_embd)[0]
+
     def expert_f64(self, gu_type, d_type, blob, n_embd, n_ff, x) -> np.ndarray:
         blob, x = _u8(blob), _f32(x).reshape(-1)
         out = np.empty(n_embd, np.float32)

@@ -161,6 +161,78 @@ __global__ void __launch_bounds__(kGuWarps * 32) gate_up_kernel(Groups G, int n_
     }
 }
 
+// A layer whose up rows have their own type (NativeExpertLayout::u_type, iq_kernels.hpp:73-77; the native grouped path
+// only): the gate rows and the up rows of a warp are dotted by two calls of their own decoder.  A row's result does not
+// depend on which rows share a call, so with TG == TU this is gate_up_kernel's arithmetic bit for bit.
+template<int TG, int TU>
+__global__ void __launch_bounds__(kGuWarps * 32) gate_up_mixed_kernel(Groups G, int n_embd, int n_ff, size_t up_off, float limit,
+                                                                      const uint8_t* __restrict__ xq, size_t xq_stride,
+                                                                      uint8_t* __restrict__ hq) {
+    extern __shared__ __align__(16) uint8_t s_raw[];
+    if (G.skip != nullptr && *G.skip) return;
+    const int g = blockIdx.y, chunk = blockIdx.x;
+    if (G.n_groups != nullptr && g >= *G.n_groups) return;
+    const unsigned long long ptr = G.ptr[g];
+    if (ptr == 0ull) return;
+    const int e0 = G.start ? G.start[g] : g;
+    int e1 = G.start ? G.start[g + 1] : g + 1;
+    if (G.cap_entries > 0) e1 = min(e1, G.cap_entries);
+    if (e1 <= e0 || e0 < 0) return;
+
+    __shared__ float s_g[kNC][kGuRows], s_u[kNC][kGuRows];
+    uint32_t* s_tab_g = (uint32_t*) s_raw;
+    uint32_t* s_tab_u = s_tab_g + Fmt<TG>::tab_words;
+    int4* q; float* d; int* is;
+    const int nblk = n_embd / 32;
+    const XCols x = xcols_carve((uint8_t*) (s_tab_u + Fmt<TU>::tab_words), nblk, kNC, &q, &d, &is);
+    load_tab<TG>(s_tab_g);
+    load_tab<TU>(s_tab_u);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t rbg = row_bytes(TG, n_embd), rbu = row_bytes(TU, n_embd);
+    const uint8_t* blob = (const uint8_t*) ptr;
+    constexpr int RPW = kGuRows / kGuWarps;   // 2
+    const uint8_t* grow[RPW];
+    const uint8_t* urow[RPW];
+#pragma unroll
+    for (int j = 0; j < RPW; ++j) {
+        const int r = chunk * kGuRows + warp * RPW + j;
+        grow[j] = blob + (size_t) r * rbg;
+        urow[j] = blob + up_off + (size_t) r * rbu;
+    }
+    for (int eb = e0; eb < e1; eb += kNC) {
+        const int nc = min(kNC, e1 - eb);
+        __syncthreads();
+        for (int c = 0; c < nc; ++c)
+            xcols_stage(xq + (size_t) G.tok(eb + c) * xq_stride, 0, nblk, 1, q + (size_t) 2 * c * nblk, d + (size_t) c * nblk,
+                        is + (size_t) c * nblk);
+        __syncthreads();
+        float og[RPW][kNC], ou[RPW][kNC];
+        if (nc == 1) {
+            float a[RPW][1], b[RPW][1];
+            rows_dot<TG, RPW, 1>(grow, x, 1, n_embd, lane, s_tab_g, a);
+            rows_dot<TU, RPW, 1>(urow, x, 1, n_embd, lane, s_tab_u, b);
+#pragma unroll
+            for (int j = 0; j < RPW; ++j) { og[j][0] = a[j][0]; ou[j][0] = b[j][0]; }
+        } else {
+            rows_dot<TG, RPW, kNC>(grow, x, nc, n_embd, lane, s_tab_g, og);
+            rows_dot<TU, RPW, kNC>(urow, x, nc, n_embd, lane, s_tab_u, ou);
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < RPW; ++j)
+#pragma unroll
+                for (int c = 0; c < kNC; ++c)
+                    if (c < nc) { s_g[c][warp * RPW + j] = og[j][c]; s_u[c][warp * RPW + j] = ou[j][c]; }
+        }
+        __syncthreads();
+        if (warp < nc) {
+            const int dst = G.slot(eb + warp);
+            q8_1_store_warp(swiglu(s_g[warp][lane], s_u[warp][lane], limit),
+                            hq + ((size_t) dst * (n_ff / 32) + chunk) * kQ81Bytes, lane);
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ down, plan form
 // One token: block = kDownRows output rows; warp w computes 4 of them for every plan entry in turn, then combines in
 // plan order: m = 0; m = fma(w_i, part_i, m); out = m [+ cpu_part] + sh_out (the reference's chain, glm_fast.cu:4999-5005).
@@ -445,6 +517,31 @@ int launch_down_groups(const Groups& G, int n_groups_grid, int n_embd, int n_ff,
     return note_launch("down_groups");
 }
 
+template<int TG, int TU>
+int launch_gate_up_mixed(const Groups& G, int n_groups_grid, int n_embd, int n_ff, size_t up_off, float limit, const void* xq,
+                         size_t xq_stride, void* hq, cudaStream_t s) {
+    const size_t smem = (size_t) (Fmt<TG>::tab_words + Fmt<TU>::tab_words) * 4 + xcols_bytes(n_embd / 32, kNC);
+    if (smem > 200 * 1024) return refuse(MAYA_ERR_LIMIT);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(gate_up_mixed_kernel<TG, TU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess)
+        return note_launch("gate_up_mixed smem attribute");
+    const dim3 grid((unsigned) (n_ff / kGuRows), (unsigned) n_groups_grid);
+    gate_up_mixed_kernel<TG, TU><<<grid, kGuWarps * 32, smem, s>>>(G, n_embd, n_ff, up_off, limit, (const uint8_t*) xq, xq_stride,
+                                                                  (uint8_t*) hq);
+    return note_launch("moe_gate_up_mixed");
+}
+template<int TG>
+int launch_gate_up_mixed_u(int u_type, const Groups& G, int n_groups_grid, int n_embd, int n_ff, size_t up_off, float limit,
+                           const void* xq, size_t xq_stride, void* hq, cudaStream_t s) {
+    switch (u_type) {
+        case MAYA_Q8_0: return launch_gate_up_mixed<TG, MAYA_Q8_0>(G, n_groups_grid, n_embd, n_ff, up_off, limit, xq, xq_stride, hq, s);
+        case MAYA_Q4_K: return launch_gate_up_mixed<TG, MAYA_Q4_K>(G, n_groups_grid, n_embd, n_ff, up_off, limit, xq, xq_stride, hq, s);
+        case MAYA_IQ2_S: return launch_gate_up_mixed<TG, MAYA_IQ2_S>(G, n_groups_grid, n_embd, n_ff, up_off, limit, xq, xq_stride, hq, s);
+        case MAYA_IQ3_S: return launch_gate_up_mixed<TG, MAYA_IQ3_S>(G, n_groups_grid, n_embd, n_ff, up_off, limit, xq, xq_stride, hq, s);
+        default: return refuse(MAYA_ERR_TYPE);
+    }
+}
+
 #define MAYA_TYPE_SWITCH(type, CALL)                      \
     switch (type) {                                       \
         case MAYA_Q8_0: return CALL(MAYA_Q8_0);           \
@@ -474,6 +571,19 @@ int gate_up_groups(int gu_type, const GroupArgs& A, int n_groups_grid, int n_emb
 #define CALL(TT) launch_gate_up<TT>(G, n_groups_grid, n_embd, n_ff, up_off, limit, xq, xq_stride, hq, sh_down, sh_type, sh_hq, n_ff_sh, sh_out, s)
     MAYA_TYPE_SWITCH(gu_type, CALL)
 #undef CALL
+}
+
+// gate_up_groups for a layer whose up rows are of another type than its gate rows (no shared-expert rows in the launch).
+int gate_up_groups_mixed(int g_type, int u_type, const GroupArgs& A, int n_groups_grid, int n_embd, int n_ff, size_t up_off,
+                         float limit, const void* xq, size_t xq_stride, void* hq, cudaStream_t s) {
+    Groups G{A.ptr, A.start, A.n_groups, A.ent_slot, A.ent_tok, A.ent_out, A.skip, A.tok_from_slot, A.cap_entries};
+    switch (g_type) {
+        case MAYA_Q8_0: return launch_gate_up_mixed_u<MAYA_Q8_0>(u_type, G, n_groups_grid, n_embd, n_ff, up_off, limit, xq, xq_stride, hq, s);
+        case MAYA_Q4_K: return launch_gate_up_mixed_u<MAYA_Q4_K>(u_type, G, n_groups_grid, n_embd, n_ff, up_off, limit, xq, xq_stride, hq, s);
+        case MAYA_IQ2_S: return launch_gate_up_mixed_u<MAYA_IQ2_S>(u_type, G, n_groups_grid, n_embd, n_ff, up_off, limit, xq, xq_stride, hq, s);
+        case MAYA_IQ3_S: return launch_gate_up_mixed_u<MAYA_IQ3_S>(u_type, G, n_groups_grid, n_embd, n_ff, up_off, limit, xq, xq_stride, hq, s);
+        default: return refuse(MAYA_ERR_TYPE);
+    }
 }
 int down_groups(int d_type, const GroupArgs& A, int n_groups_grid, int n_embd, int n_ff, size_t down_off, const void* hq,
                 float* part, cudaStream_t s) {
@@ -594,7 +704,6 @@ extern "C" int maya_expert_grouped(const maya_expert_layout* L, const unsigned l
         return refuse(MAYA_ERR_ARG);
     if (cap_groups <= 0 || cap_entries <= 0) return MAYA_OK;
     if (cap_groups > 65535) return refuse(MAYA_ERR_LIMIT);
-    if (L->u_type != L->gu_type) return refuse(MAYA_ERR_TYPE);   // mixed gate/up layers are not covered
     if (!type_qk(L->gu_type) || !type_qk(L->d_type)) return refuse(MAYA_ERR_TYPE);
     if (L->n_embd <= 0 || L->n_ff <= 0 || L->n_ff % 32 || L->n_embd % type_qk(L->gu_type) || L->n_ff % type_qk(L->d_type))
         return refuse(MAYA_ERR_ARG);
@@ -608,8 +717,13 @@ extern "C" int maya_expert_grouped(const maya_expert_layout* L, const unsigned l
     A.ent_tok = ent_tok;
     A.ent_out = ent_dst;
     A.cap_entries = (int) (cap_entries < 0x7fffffff ? cap_entries : 0x7fffffff);   // the scratch (and `out`) hold this many
-    int st = gate_up_groups(L->gu_type, A, (int) cap_groups, n_embd, n_ff, L->up_off, swiglu_limit, x_q8_1,
-                            (size_t) (n_embd / 32) * kQ81Bytes, scratch, nullptr, 0, nullptr, 0, nullptr, s);
+    const int u_type = L->u_type;                                      // a mixed layer: the up rows' own type (iq_kernels.hpp:73-77)
+    if (!type_qk(u_type) || L->n_embd % type_qk(u_type)) return refuse(MAYA_ERR_TYPE);
+    int st = u_type == L->gu_type
+                 ? gate_up_groups(L->gu_type, A, (int) cap_groups, n_embd, n_ff, L->up_off, swiglu_limit, x_q8_1,
+                                  (size_t) (n_embd / 32) * kQ81Bytes, scratch, nullptr, 0, nullptr, 0, nullptr, s)
+                 : gate_up_groups_mixed(L->gu_type, u_type, A, (int) cap_groups, n_embd, n_ff, L->up_off, swiglu_limit, x_q8_1,
+                                        (size_t) (n_embd / 32) * kQ81Bytes, scratch, s);
     if (st != MAYA_OK) return st;
     return down_groups(L->d_type, A, (int) cap_groups, n_embd, n_ff, L->down_off, scratch, out, s);
 }

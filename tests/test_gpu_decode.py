@@ -346,6 +346,38 @@ def test_expert_grouped(T, api, oracle, t):
     assert (got[6:] == 9.0).all()
 
 
+@pytest.mark.parametrize("tg,tu,td", [(H.IQ2_S, H.IQ3_S, H.Q4_K), (H.Q4_K, H.Q8_0, H.IQ2_S), (H.Q8_0, H.IQ2_S, H.Q8_0),
+                                      (H.IQ3_S, H.Q4_K, H.IQ3_S)])
+def test_expert_grouped_mixed_gate_up_types(T, api, oracle, tg, tu, td):
+    """native_expert_layout(gu_type, up_type, d_type, ...) with up rows of their own type (iq_kernels.hpp:73-77)."""
+    n_embd, n_ff, n_tok = 512, 256, 6
+    rng = H.rng_for("grp-mixed", tg, tu, td)
+    blobs = [np.concatenate([H.constructed_blocks(tg, n_ff, n_embd, rng).reshape(-1),
+                             H.constructed_blocks(tu, n_ff, n_embd, rng).reshape(-1),
+                             H.constructed_blocks(td, n_embd, n_ff, rng).reshape(-1)]) for _ in range(2)]
+    L = api.native_expert_layout(tg, td, n_embd, n_ff, up_type=tu)
+    assert L.bytes == blobs[0].size and L.up_off == n_ff * H.row_bytes(tg, n_embd)
+    store = dev(T, np.stack(blobs))
+    x = rng.standard_normal((n_tok, n_embd)).astype(np.float32)
+    grp_ptr = T.tensor([store[0].data_ptr(), store[1].data_ptr()], dtype=T.int64, device="cuda")
+    grp_start = T.tensor([0, 5, 6], dtype=T.int32, device="cuda")          # five entries (two passes of columns), then one
+    ent_tok = T.tensor([0, 3, 5, 1, 2, 4], dtype=T.int32, device="cuda")
+    ent_dst = T.tensor([5, 4, 3, 2, 1, 0], dtype=T.int32, device="cuda")
+    n_groups = T.tensor([2], dtype=T.int32, device="cuda")
+    xq = api.native_quantize_q8_1(dev(T, x))
+    scratch = T.zeros(api.native_expert_scratch_bytes(6, n_ff), dtype=T.uint8, device="cuda")
+    out = T.full((6, n_embd), 9.0, dtype=T.float32, device="cuda")
+    api.native_expert_grouped(L, grp_ptr, grp_start, n_groups, ent_dst, ent_tok, 2, 6, xq, scratch, out)
+    got = out.cpu().numpy()
+    for g, tok, dst in [(0, 0, 5), (0, 3, 4), (0, 5, 3), (0, 1, 2), (0, 2, 1), (1, 4, 0)]:
+        want = oracle.expert_q8_1_mixed(tg, tu, td, blobs[g], n_embd, n_ff, H.INF, oracle.quantize_q8_1(x[tok]))
+        assert H.rel_err(got[dst], want) <= TIGHT
+    # the static-scratch entry point runs the same launches
+    out2 = T.full((6, n_embd), 9.0, dtype=T.float32, device="cuda")
+    api.native_expert_grouped_static(L, grp_ptr, grp_start, n_groups, ent_dst, ent_tok, 2, 6, xq, out2)
+    assert T.equal(out, out2)
+
+
 def test_combine_bitwise(T, api, oracle):
     rng = H.rng_for("cmb")
     parts = rng.standard_normal((3, 8, 2048)).astype(np.float32)

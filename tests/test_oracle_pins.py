@@ -141,6 +141,18 @@ def test_quantized_expert_against_float_expert(oracle, t):
     assert np.abs(yq - yf).sum() / np.abs(yf).sum() < 3e-2
 
 
+@pytest.mark.parametrize("t", TYPES)
+def test_mixed_type_expert_is_the_plain_expert_when_the_types_agree(oracle, t):
+    """oracle.expert_q8_1_mixed (the up rows' own type, iq_kernels.hpp:73-77) composes the single steps; with one type
+    for gate and up it must be expert_q8_1 bit for bit, which pins the composition the mixed-type GPU test checks against."""
+    n_embd, n_ff = 512, 256
+    blob = H.constructed_expert(t, t, n_embd, n_ff, H.rng_for("mixed-pin", t))
+    xq = oracle.quantize_q8_1(H.rng_for("mixed-pin-x", t).standard_normal(n_embd).astype(np.float32))
+    for limit in (H.INF, 7.0):
+        assert np.array_equal(oracle.expert_q8_1_mixed(t, t, t, blob, n_embd, n_ff, limit, xq),
+                              oracle.expert_q8_1(t, t, blob, n_embd, n_ff, limit, xq))
+
+
 @pytest.mark.parametrize("t", [H.Q4_K, H.IQ2_S, H.IQ3_S])
 @pytest.mark.parametrize("avx512", [True, False])
 def test_oracle_against_reference_cpu_rows(oracle, ref, t, avx512):
