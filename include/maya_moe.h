@@ -219,7 +219,11 @@ MAYA_API int maya_moe_combine_add(const float* out, int base, int lo, int hi, co
 MAYA_API int maya_mmq_supported(int type);
 /* mmq::q8_bytes (moe_mmq.hpp:20): bytes of `rows` quantized activation rows of `cols` values.  The rows are stored as
  * f16: each value is d * q of the row's q8_1 image (d = f16(amax / 127) per 32 values, q = round(x / d)), the
- * operand the f16 tensor-core product reads; cols * 2 bytes a row, no padding.  0 for cols % 32 != 0. */
+ * operand the f16 tensor-core product reads, followed by one f16 per 32 values - f16(sum of the unquantized values)
+ * minus the sum of the stored ones, what llama.cpp's MMQ keeps as the "ds4" layout's sum (mmq.cuh:27-46) - padded with
+ * zeros to a multiple of 64: (cols + roundup(cols / 32, 64)) * 2 bytes a row.  A Q4_K product multiplies a group's
+ * constant term -dmin * m by that sum, as the reference's prompt path does (its decode kernels take the sum of the
+ * rounded values instead).  0 for cols % 32 != 0. */
 MAYA_API size_t maya_mmq_q8_bytes(int64_t rows, int64_t cols);
 /* mmq::quantize (moe_mmq.hpp:34): output row i = the q8_1 image of row ids[i] of x (row i when ids is NULL); x has
  * ld floats a row.  `type` is the weight type the product will use (checked with maya_mmq_supported; the layout is
@@ -244,7 +248,7 @@ typedef struct maya_mmq_product {
     int64_t ld_dst;
     const int32_t* expert_map;   /* NULL, or device table: matrix i of w uses bounds[expert_map[i]] (a staged group) */
     unsigned* error;             /* NULL, or device word set to 1 when a bounded wait inside the kernel ran out */
-    void* xq_out;                /* maya_mmq_run_glu only, NULL or [total_rows][n_ff] f16: h already quantized as
+    void* xq_out;                /* maya_mmq_run_glu only, NULL or maya_mmq_q8_bytes(total_rows, n_ff) bytes: h already quantized as
                                     maya_mmq_quantize(h, NULL, ...) would, row = the sorted row (ids not applied);
                                     with it dst may be NULL */
 } maya_mmq_product;

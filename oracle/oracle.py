@@ -111,6 +111,61 @@ class Oracle:
         hq = self.quantize_q8_1(self.swiglu(g, u, limit))
         return self.mmvq(d_type, blob[down_off:], hq, n_ff, n_embd)[0]
 
+    # ---- the prompt path's arithmetic as the reference models it on the host
+    def mmq_host_model(self, t: int, w, n_rows: int, K: int, x) -> np.ndarray:
+        """The reference's host model of what its prompt-path GEMM (llama.cpp's MMQ behind mmq::Context::run) computes,
+        restated from tests/glm_dsa/glmd_mmq_ids_test.cu:92-244,288-347 (the dp4a form its CUDA builds keep):
+          activations per 32 values: d_inv = 127 / amax, u = round(x d_inv) (half away from zero), d = 1 / d_inv in float,
+            kept as float for the "d4" layout (Q8_0, IQ2_S, IQ3_S) and rounded to f16 for "ds4" (Q4_K); xr = u d;
+          weights: to_float's values;
+          "plain" (d4 types): y = sum_k w_k xr_k;
+          "offset" (Q4_K): y = sum over 32-value groups b of [sum_{k in b} w_k xr_k + c_b (S_b - sum_{k in b} xr_k)] with
+            c_b = -(dmin m_b), the group's constant term, and S_b the f16-rounded sum of the UNQUANTIZED values, added in
+            the order of quantize_mmq_q8_1 (4 values per thread left to right, then a shuffle tree);
+          every sum in double, in k order.  w: n_rows rows of K quantized values; x [n, K] f32.  Returns [n, n_rows] f64."""
+        x = _f32(x).reshape(-1, K)
+        n = x.shape[0]
+        wf = self.dequantize(t, w, n_rows * K).reshape(n_rows, K).astype(np.float64)
+        xb = x.reshape(n, K // 32, 32)
+        am = np.abs(xb).max(axis=2, keepdims=True).astype(np.float32)
+        with np.errstate(divide="ignore", invalid="ignore"):
+            d_inv = (np.float32(127.0) / am).astype(np.float32)
+            d = (np.float32(1.0) / d_inv).astype(np.float32)
+            v = (xb * d_inv).astype(np.float32)
+        u = np.where(am > 0, np.sign(v) * np.floor(np.abs(v) + np.float32(0.5)), 0.0).astype(np.float32)
+        offset = t == 12                                                   # Q4_K: the ds4 layout
+        ds = d.astype(np.float16).astype(np.float32) if offset else d
+        xr = np.where(am > 0, u * ds, 0.0).astype(np.float32).reshape(n, K).astype(np.float64)
+        y = xr @ wf.T
+        if offset:
+            blk = _u8(w).reshape(n_rows, K // 256, 144)
+            dmin = blk[:, :, 2:4].copy().view(np.float16).astype(np.float32)[:, :, 0]
+            sc8 = blk[:, :, 4:16].astype(np.int32)
+            mn = np.stack([(sc8[:, :, sb + 4] & 63) if sb < 4 else ((sc8[:, :, sb + 4] >> 4) | ((sc8[:, :, sb] >> 6) << 4))
+                           for sb in range(8)], axis=-1)                   # [rows, nb, 8]
+            c = -(dmin[:, :, None] * mn.astype(np.float32)).astype(np.float32).reshape(n_rows, K // 32).astype(np.float64)
+            pt = xb.reshape(n, K // 32, 8, 4)
+            part = ((pt[..., 0] + pt[..., 1]).astype(np.float32) + pt[..., 2]).astype(np.float32)
+            part = (part + pt[..., 3]).astype(np.float32)                  # each thread: its 4 values left to right
+            for off in (4, 2, 1):
+                part = (part[..., :off] + part[..., off:2 * off]).astype(np.float32)
+            S = part[..., 0].astype(np.float16).astype(np.float64)         # [n, K / 32]
+            xa = S - xr.reshape(n, K // 32, 32).sum(axis=2)
+            y = y + xa @ c.T
+        return y
+
+    def expert_mmq(self, gu_type, d_type, blob, n_embd, n_ff, limit, x) -> np.ndarray:
+        """One expert as the reference's PROMPT path computes it (src/core/glm_prefill.cu:3230-3420: mmq::quantize,
+        run_glu, mmq::quantize of h, run): both products by mmq_host_model, SwiGLU on f32 values between them.  Differs
+        from expert_q8_1 (the decode kernels) where a type has a constant term per group: Q4_K's decode dot multiplies
+        -dmin * m by the sum of the ROUNDED activations (dp4a with 0x01010101, native_mmvq.cu:170), MMQ by the stored
+        sum of the unquantized ones - about 1e-2 apart in rel-L2 on N(0, 0.02) weights."""
+        blob = _u8(blob)
+        gu = 2 * n_ff * self.row_bytes(gu_type, n_embd)
+        y = self.mmq_host_model(gu_type, blob[:gu], 2 * n_ff, n_embd, x)[0]
+        h = self.swiglu(y[:n_ff].astype(np.float32), y[n_ff:].astype(np.float32), limit)
+        return self.mmq_host_model(d_type, blob[gu:], n_embd, n_ff, h)[0].astype(np.float32)
+
     def expert_f64(self, gu_type, d_type, blob, n_embd, n_ff, x) -> np.ndarray:
         blob, x = _u8(blob), _f32(x).reshape(-1)
         out = np.empty(n_embd, np.float32)

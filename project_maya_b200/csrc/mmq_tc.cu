@@ -75,6 +75,14 @@ template<int T> constexpr size_t kSmemBytes = (size_t) kTabOff<T> + kTabBytes<T>
 static_assert(kUnits<MAYA_Q4_K> <= kMaxUnits && kUnits<MAYA_Q8_0> <= kMaxUnits && kUnits<MAYA_IQ2_S> <= kMaxUnits &&
               kUnits<MAYA_IQ3_S> <= kMaxUnits, "one mbarrier pair per raw unit");
 
+// The activation image: a row is its w_cols f16 values d * q, then one f16 per 32 values - the group's SUM CORRECTION
+// xa = f16(sum of the unquantized values) - sum of the row's stored d * q values - padded with zeros to a multiple of 64.  llama.cpp's
+// MMQ keeps that unquantized sum beside the block (the "ds4" q8_1 layout) and a type with a constant term per group
+// (Q4_K: -dmin * m) multiplies the term by it, not by the sum of the rounded values; here the same result comes from
+// extra K steps at the end of a Q4_K product: A = -dmin * m of a row's groups, B = xa.  Other types do not read the tail.
+__host__ __device__ constexpr int64_t xq_tail(int64_t cols) { return ((cols / 32) + 63) & ~(int64_t) 63; }
+__host__ __device__ constexpr int64_t xq_ld(int64_t cols) { return cols + xq_tail(cols); }
+
 struct MmqArgs {
     const uint8_t* w;            // the matrices (the i-quant path copies row windows itself; the others go through tm_w)
     size_t expert_bytes;
@@ -99,11 +107,25 @@ __device__ __forceinline__ __half2 bytes23_plus1024(uint32_t x) { return bits_h2
 
 // The one-value-per-lane q8_1 rounding of maya_mmq_quantize: d = min(amax / 127, 65504) kept as f16, q = round(v / d)
 // clamped to +-127, result f16(d) * q.
-__device__ __forceinline__ __half q8_1_round_warp(float v) {
+// `xa` (valid in lane 0): the group's sum correction, f16(S) - sum of the stored f16(d * q), with S added in quantize_mmq_q8_1's order - four
+// consecutive values left to right, then a tree over the eight partial sums at distances 4, 2, 1.
+__device__ __forceinline__ __half q8_1_round_warp(float v, float& xa) {
     const float amax = __uint_as_float(__reduce_max_sync(0xFFFFFFFFu, __float_as_uint(fabsf(v))));
     const float d = fminf(__fdiv_rn(amax, 127.0f), 65504.0f);
     const float q = amax == 0.0f ? 0.0f : fmaxf(-127.0f, fminf(127.0f, roundf(__fdiv_rn(v, d))));
-    return __float2half_rn(__half2float(__float2half_rn(d)) * q);
+    const float dh = __half2float(__float2half_rn(d));
+    float s = __fadd_rn(v, __shfl_down_sync(0xFFFFFFFFu, v, 1));
+    s = __fadd_rn(s, __shfl_down_sync(0xFFFFFFFFu, v, 2));
+    s = __fadd_rn(s, __shfl_down_sync(0xFFFFFFFFu, v, 3));               // lanes 0, 4, ..., 28: their four values
+    s = __fadd_rn(s, __shfl_xor_sync(0xFFFFFFFFu, s, 16));
+    s = __fadd_rn(s, __shfl_xor_sync(0xFFFFFFFFu, s, 8));
+    s = __fadd_rn(s, __shfl_xor_sync(0xFFFFFFFFu, s, 4));
+    const __half r = __float2half_rn(dh * q);
+    float b = __half2float(r);               // the sum of the 32 STORED values: multiples of one power of two, 24 bits in all -
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) b += __shfl_xor_sync(0xFFFFFFFFu, b, o);   // exact in f32 in any order
+    xa = __half2float(__float2half_rn(s)) - b;
+    return r;
 }
 
 // ---- Q4_K: the 16-byte header of a 144-byte block -> d * sc and -(dmin * m) of its 8 sub-blocks, as half2 pairs
@@ -302,6 +324,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
     const bool big = nrows > 128;                   // the activation tile is a 128-row box and a 32-row box
     const int m0 = (int) blockIdx.x * (GLU ? 128 : TM);
     const int nkt = A.w_cols / BK, nkb = A.w_cols / 256;
+    const int ntp = T == MAYA_Q4_K ? (nkb * 8 + 63) / 64 : 0;   // 64-value steps of the sum correction after the K loop
 
     uint8_t* const raw = smem + kBRing<T>;
     if (tid == 0) {
@@ -361,24 +384,24 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
         // rows 0..127 feed accumulator 0, rows 128..255 accumulator 1; a warp reaches the 32 lanes of its quadrant
         const uint32_t a_lane = tmem + ((uint32_t) (32 * (w8 & 3)) << 16) + kACol + (w8 >> 2) * 32;
         bool ok = true;
+        auto put = [&](int kp, const uint32_t (&o)[32]) -> bool {   // the row's 64 values of pair kp -> its lane
+            const int s = kp % kSt;
+            if (kp >= kSt) {                     // the stage was last read by pair kp - kSt
+                const int pp = kp - kSt;
+                if (!wait_or_fail(P, &P.done[pp & (kDone - 1)], (pp / kDone) & 1)) return false;
+                tc_fence_after();
+            }
+            tmem_st32(a_lane + s * 64, o);
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&P.a_full[s]);
+            return true;
+        };
         for (int kb = 0; kb < nkb && ok; ++kb) {
             const int u = kb * 4 + slab, slot = u % NU;
             if (!wait_or_fail(P, &P.raw_full[slot], (u / NU) & 1)) { ok = false; break; }
             const uint8_t* rrow = rbase + (size_t) slot * kUnitBytes<T>;
-            auto put = [&](int kp, const uint32_t (&o)[32]) -> bool {   // the row's 64 values of pair kp -> its lane
-                const int s = kp % kSt;
-                if (kp >= kSt) {                     // the stage was last read by pair kp - kSt
-                    const int pp = kp - kSt;
-                    if (!wait_or_fail(P, &P.done[pp & (kDone - 1)], (pp / kDone) & 1)) return false;
-                    tc_fence_after();
-                }
-                tmem_st32(a_lane + s * 64, o);
-                tmem_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&P.a_full[s]);
-                return true;
-            };
             uint32_t o[32];
             if constexpr (kIq<T>) {
                 constexpr int NWD = kWin<T> / 4;
@@ -441,6 +464,31 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             __syncwarp();
             if (lane == 0) mbar_arrive(&P.raw_empty[slot]);      // 4 warps read a unit; after the 4th it may be overwritten
         }
+        if constexpr (T == MAYA_Q4_K) {
+            // The sum-correction steps: pair j of the tail multiplies the constant terms -dmin * m of the row's groups
+            // [64 j, 64 j + 64) (blocks 8 j .. 8 j + 7, read from global memory: 16 bytes a block, L2-warm) by the
+            // activation rows' corrections.  Teams alternate pairs as in the main loop (the main loop ends on an even pair).
+            const int wrow = (GLU ? (slab < 2 ? m0 + 64 * slab : A.w_rows + m0 + 64 * (slab - 2)) : m0 + 64 * slab) + (row & 63);
+            const bool live = wrow < A.mat_rows;
+            const uint8_t* const grow = A.w + (size_t) found_e * A.expert_bytes + (size_t) wrow * ((size_t) nkb * 144);
+            for (int j = team; j < ntp && ok; j += 2) {
+                uint32_t o[32];
+#pragma unroll
+                for (int b = 0; b < 8; ++b) {
+                    const int kb = 8 * j + b;
+                    if (live && kb < nkb) {
+                        Q4Scales S;
+                        q4k_scales(__ldg((const uint4*) (grow + (size_t) kb * 144)), S);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) o[4 * b + i] = h2_bits(__lows2half2(S.nml[2 * i], S.nml[2 * i + 1]));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) o[4 * b + i] = 0u;
+                    }
+                }
+                ok = put(nkb * 4 + j, o);
+            }
+        }
         // ------------------------------------------------------------ epilogue
         if (ok && !wait_or_fail(P, &P.final, 0)) ok = false;
         tc_fence_after();
@@ -469,9 +517,14 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
 #pragma unroll
                     for (int j = 0; j < 8; ++j) v[j] = swiglu(v[j], up[j], A.limit);
                     if (A.xq_out) {
+                        const int64_t ldq = xq_ld(A.w_rows);
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
-                            if (col0 + j < nrows) b16[(col0 + j) * 128 + mcol] = q8_1_round_warp(v[j]);      // uniform in the warp
+                            if (col0 + j < nrows) {                                                          // uniform in the warp
+                                float xa;
+                                b16[(col0 + j) * 128 + mcol] = q8_1_round_warp(v[j], xa);
+                                if (lane == 0) A.xq_out[(int64_t) (row0 + col0 + j) * ldq + A.w_rows + (m0 >> 5) + q] = __float2half_rn(xa);
+                            }
                     }
                     if (A.dst) {
 #pragma unroll
@@ -482,8 +535,13 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                 fence_proxy_async();
                 named_bar_sync(1, kThreadsEpi);
                 if (tid < nrows) {                                       // one activation row each
-                    const int row_g = row0 + tid;
-                    if (A.xq_out) bulk_store(A.xq_out + (int64_t) row_g * A.w_rows + m0, b16 + tid * 128, 128 * 2);
+                    const int64_t row_g = row0 + tid;
+                    if (A.xq_out) {
+                        const int64_t ldq = xq_ld(A.w_rows);
+                        bulk_store(A.xq_out + row_g * ldq + m0, b16 + tid * 128, 128 * 2);
+                        if (blockIdx.x == 0)                             // the zero padding behind the row's corrections
+                            for (int64_t c = A.w_rows + A.w_rows / 32; c < ldq; ++c) A.xq_out[row_g * ldq + c] = __float2half_rn(0.0f);
+                    }
                     if (A.dst) bulk_store(A.dst + (int64_t) (A.ids ? A.ids[row_g] : row_g) * A.ld_dst + m0, b32 + tid * 128, 128 * 4);
                     bulk_commit();
                 }
@@ -553,7 +611,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             const uint32_t bfull0 = smem_u32(&P.b_full[0]), afull0 = smem_u32(&P.a_full[0]), done0 = smem_u32(&P.done[0]);
             uint32_t b_lo = b_lo0, at = a0, bfull = bfull0, afull = afull0;   // of the next pair of K steps
             uint32_t ph_a = 0, ph_b = 0, first = 0;  // the barriers' phases; first = 0: the first product overwrites
-            const int npairs = nkt / 2;
+            const int npairs = nkt / 2 + ntp;
             bool ok = true;
             for (int kp = 0; kp < npairs; ++kp) {
                 // everything the products need, before the waits
@@ -579,7 +637,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             int issued = 0;
             bool ok = true;
             const uint32_t tx_bytes = big ? kBStage : kBBox;
-            for (int kb2 = 0; kb2 < nkt / 2; ++kb2) {
+            for (int kb2 = 0; kb2 < nkt / 2 + ntp; ++kb2) {     // the image's tail follows its K values
                 const int sb = kb2 % NB;
                 if (kb2 >= NB) {                             // the slot was last read by pair kb2 - NB
                     const int pp = kb2 - NB;
@@ -633,6 +691,7 @@ __global__ void __launch_bounds__(256) mmq_quantize_kernel(const X* __restrict__
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
     const float d = fminf(__fdiv_rn(amax, 127.0f), 65504.0f), dh = __half2float(__float2half_rn(d));
     uint32_t o[4];
+    float bsum = 0.0f;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         float q0 = 0.0f, q1 = 0.0f;
@@ -640,9 +699,27 @@ __global__ void __launch_bounds__(256) mmq_quantize_kernel(const X* __restrict__
             q0 = fmaxf(-127.0f, fminf(127.0f, roundf(__fdiv_rn(v[2 * k], d))));
             q1 = fmaxf(-127.0f, fminf(127.0f, roundf(__fdiv_rn(v[2 * k + 1], d))));
         }
-        o[k] = h2_bits(__floats2half2_rn(dh * q0, dh * q1));
+        const __half2 r = __floats2half2_rn(dh * q0, dh * q1);
+        o[k] = h2_bits(r);
+        bsum += __low2float(r) + __high2float(r);     // the stored values: multiples of one power of two, 24 bits in all - exact
     }
-    if (live) *(uint4*) (xq + row * cols + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    // The group's sum correction (see xq_tail): S in quantize_mmq_q8_1's order - each 4 consecutive values left to right
+    // (this thread holds partial sums 2j and 2j + 1 of the group's eight), then the tree at distances 4, 2, 1.
+    float s0 = __fadd_rn(__fadd_rn(__fadd_rn(v[0], v[1]), v[2]), v[3]), s1 = __fadd_rn(__fadd_rn(__fadd_rn(v[4], v[5]), v[6]), v[7]);
+    s0 = __fadd_rn(s0, __shfl_xor_sync(0xFFFFFFFFu, s0, 2));
+    s1 = __fadd_rn(s1, __shfl_xor_sync(0xFFFFFFFFu, s1, 2));
+    s0 = __fadd_rn(s0, __shfl_xor_sync(0xFFFFFFFFu, s0, 1));
+    s1 = __fadd_rn(s1, __shfl_xor_sync(0xFFFFFFFFu, s1, 1));
+    bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 1);
+    bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 2);
+    const float xa = __half2float(__float2half_rn(__fadd_rn(s0, s1))) - bsum;
+    if (live) {
+        const int64_t ldq = xq_ld(cols);
+        *(uint4*) (xq + row * ldq + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+        if ((c & 3) == 0) xq[row * ldq + cols + (c >> 2)] = __float2half_rn(xa);
+        if (c == 0)                                   // the zero padding behind the row's corrections
+            for (int64_t t = cols + cols / 32; t < ldq; ++t) xq[row * ldq + t] = __float2half_rn(0.0f);
+    }
 }
 
 template<typename X>
@@ -697,9 +774,9 @@ int launch_mmq(const maya_mmq_product* p, const MmqArgs& A, cudaStream_t s) {
         if (!make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, p->w, dim, st, box, CU_TENSOR_MAP_SWIZZLE_NONE))
             return note_launch("mmq weight tensor map");
     }
-    {   // activations: f16 [row][K]; a box = 64 K-values (128 bytes) of 128 or 32 rows, written with the 128-byte swizzle
-        const cuuint64_t dim[2] = {(cuuint64_t) K, (cuuint64_t) p->total_rows};
-        const cuuint64_t st[1] = {(cuuint64_t) K * 2};
+    {   // activations: f16 [row][K + tail] (xq_ld); a box = 64 K-values (128 bytes) of 128 or 32 rows, written with the 128-byte swizzle
+        const cuuint64_t dim[2] = {(cuuint64_t) xq_ld(K), (cuuint64_t) p->total_rows};
+        const cuuint64_t st[1] = {(cuuint64_t) xq_ld(K) * 2};
         const cuuint32_t box[2] = {64, 128}, box32[2] = {64, 32};
         if (!make_map(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xq, dim, st, box, CU_TENSOR_MAP_SWIZZLE_128B) ||
             !make_map(&tx32, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p->xq, dim, st, box32, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -754,7 +831,7 @@ extern "C" int maya_mmq_supported(int type) {
 }
 extern "C" size_t maya_mmq_q8_bytes(int64_t rows, int64_t cols) {
     if (rows <= 0 || cols <= 0 || cols % 32) return 0;
-    return (size_t) rows * (size_t) cols * sizeof(__half);
+    return (size_t) rows * (size_t) xq_ld(cols) * sizeof(__half);
 }
 extern "C" int maya_mmq_quantize(const float* x, const int32_t* ids, void* xq, int type, int64_t cols, int64_t ld,
                                  int64_t rows, void* stream) {

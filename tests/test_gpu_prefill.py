@@ -13,6 +13,7 @@ import helpers as H
 
 pytestmark = pytest.mark.gpu
 TOL, PIN = 1e-2, 2e-5
+MODEL = 1e-3   # rel-L2 from the reference's host model of its MMQ arithmetic (f16 scales and weights cost ~3e-4)
 
 
 @pytest.fixture(scope="module")
@@ -60,6 +61,36 @@ def q4k_f16_weights(raw, rows, cols):
         q = ((q >> 4) if sb & 1 else (q & 0x0F)).astype(np.float64)
         out[:, :, sb, :] = (q * dl[:, :, None] - ml[:, :, None]).astype(np.float16).astype(np.float64)
     return out.reshape(rows, cols)
+
+
+def xq_ld(cols):
+    """Values in a row of the activation image: the cols f16 values d * q, then one sum correction per 32 values, padded
+    with zeros to a multiple of 64."""
+    return cols + ((cols // 32 + 63) // 64) * 64
+
+
+def sum_corrections(x_rows, image):
+    """xa of every 32-value group: f16(S) - sum(d * q), S the f32 sum of the unquantized values in the order of llama.cpp's
+    quantize_mmq_q8_1 (4 consecutive values left to right, then a tree at distances 4, 2, 1); stored as f16."""
+    rows, cols = x_rows.shape
+    pt = x_rows.astype(np.float32).reshape(rows, cols // 32, 8, 4)
+    part = ((pt[..., 0] + pt[..., 1]).astype(np.float32) + pt[..., 2]).astype(np.float32)
+    part = (part + pt[..., 3]).astype(np.float32)
+    for off in (4, 2, 1):
+        part = (part[..., :off] + part[..., off:2 * off]).astype(np.float32)
+    S = part[..., 0].astype(np.float16).astype(np.float32)
+    sxr = image.astype(np.float32).reshape(rows, cols // 32, 32).astype(np.float64).sum(axis=2).astype(np.float32)   # exact
+    return (S - sxr).astype(np.float32).astype(np.float16)
+
+
+def q4k_constant_terms(raw, rows, cols):
+    """-f16(dmin * m) of every 32-value group of Q4_K rows: the A operand of the sum-correction steps."""
+    blk = np.ascontiguousarray(raw).reshape(rows, cols // 256, 144)
+    dmin = blk[:, :, 2:4].copy().view(np.float16).astype(np.float32)[:, :, 0]
+    sc8 = blk[:, :, 4:16].astype(np.int32)
+    mn = np.stack([(sc8[:, :, sb + 4] & 63) if sb < 4 else ((sc8[:, :, sb + 4] >> 4) | ((sc8[:, :, sb] >> 6) << 4))
+                   for sb in range(8)], axis=-1)
+    return -(dmin[:, :, None] * mn.astype(np.float32)).astype(np.float16).astype(np.float64).reshape(rows, cols // 32)
 
 
 def q8_1_image(oracle, x_rows):
@@ -122,8 +153,11 @@ def test_grouped_product_ragged_groups(T, api, oracle, t):
     row_tok = rng.integers(0, n_tok, total).astype(np.int32)
     dst_row = rng.permutation(total + 5)[:total].astype(np.int32)            # scattered, with holes
     xq = api.mmq_quantize(dev(T, x), dev(T, row_tok), t)
-    xq_host = xq.cpu().numpy().view(np.float16).reshape(total, cols)
+    xq_full = xq.cpu().numpy().view(np.float16).reshape(total, xq_ld(cols))
+    xq_host, xa_host = xq_full[:, :cols], xq_full[:, cols:cols + cols // 32]
     assert np.array_equal(xq_host, q8_1_image(oracle, x[row_tok])), "mmq_quantize differs from the q8_1 oracle's d * q"
+    assert np.array_equal(xa_host, sum_corrections(x[row_tok], xq_host)), "the groups' sum corrections"
+    assert not xq_full[:, cols + cols // 32:].any(), "the padding behind the corrections"
     xq_blocks = [oracle.quantize_q8_1(x[r]) for r in row_tok]
 
     ld = rows + 64
@@ -142,11 +176,21 @@ def test_grouped_product_ragged_groups(T, api, oracle, t):
             continue
         wf, xf = f16_weights(oracle, t, w_host[e], rows, cols), xq_host[a:b].astype(np.float64)
         pin = xf @ wf.T
+        if t == H.Q4_K:       # the constant term of a group times the group's unquantized sum, as the reference's MMQ forms it
+            pin = pin + xa_host[a:b].astype(np.float64) @ q4k_constant_terms(w_host[e], rows, cols).T
         g = got[dst_row[a:b], :rows]
         assert H.rel_err(g, pin) <= PIN, f"expert {e}: not the product of its f16 operands"
-        for r in (a, b - 1):                                                  # the q8_1 oracle on the group's edge rows
+        # the decode kernels' q8_1 dot on the group's edge rows.  Q4_K: the reference's two paths differ from each other
+        # there (the decode dot takes the sum of the ROUNDED activations for the constant term, its MMQ - and this path -
+        # the stored sum of the unquantized ones: ~1.1e-2 in rel-L2 on these weights), hence the wider bound
+        for r in (a, b - 1):
             want = oracle.mmvq(t, w_host[e], xq_blocks[r], cols, rows)[0]
-            assert H.rel_err(got[dst_row[r], :rows], want) <= TOL and H.rel_l2(got[dst_row[r], :rows], want) <= TOL
+            tol = 3e-2 if t == H.Q4_K else TOL
+            assert H.rel_err(got[dst_row[r], :rows], want) <= tol and H.rel_l2(got[dst_row[r], :rows], want) <= tol
+        # the reference's own host model of its prompt-path GEMM (tests/glm_dsa/glmd_mmq_ids_test.cu; its gate for its
+        # MMQ kernels is rel-L2 < 1e-4): this path rounds the activation scale and the expanded weights to f16 on top
+        model = oracle.mmq_host_model(t, w_host[e], rows, cols, x[row_tok[a:b]])
+        assert H.rel_l2(g, model) <= MODEL, f"expert {e}: {H.rel_l2(g, model):.3g} from the reference's MMQ host model"
         hit[dst_row[a:b]] = True
     assert np.all(got[:, rows:] == 7.0), "wrote past w_rows"
     assert np.all(got[~hit] == 7.0), "wrote a row no group owns"
@@ -214,15 +258,16 @@ def test_refusals(T, api):
             api.mmq_run(ok(**bad))
     with pytest.raises(api.MayaError):
         api.mmq_run_glu(ok(w_rows=128), H.INF)            # n_ff = 64 is not a multiple of 128
-    assert api.mmq_q8_bytes(3, 100) == 0 and api.mmq_q8_bytes(3, 256) == 3 * 256 * 2
+    assert api.mmq_q8_bytes(3, 100) == 0 and api.mmq_q8_bytes(3, 256) == 3 * xq_ld(256) * 2
     assert all(api.mmq_supported(x) for x in (H.Q8_0, H.Q4_K, H.IQ2_S, H.IQ3_S)) and not api.mmq_supported(2)
 
 
 # ------------------------------------------------------------------------------------------------ the whole layer
 def oracle_prefill_token(oracle, cfg, experts, ids, w, x):
+    """A token as the reference's prompt path computes it: every expert by oracle.expert_mmq (the host model of the
+    reference's MMQ arithmetic), combined in glmb::moe_combine's order."""
     H_, FF = cfg["n_embd"], cfg["n_ff"]
-    xq = oracle.quantize_q8_1(x)
-    parts = np.stack([oracle.expert_q8_1(cfg["gu_type"], cfg["d_type"], experts[int(e)].cpu().numpy(), H_, FF, H.INF, xq)
+    parts = np.stack([oracle.expert_mmq(cfg["gu_type"], cfg["d_type"], experts[int(e)].cpu().numpy(), H_, FF, H.INF, x)
                       for e in ids])
     out = np.zeros(H_, np.float32)
     for j in range(len(ids)):                               # glmb::moe_combine's order: m = fma(w, o, m) from 0
@@ -249,9 +294,12 @@ def test_prefill_layer_small(T, api, oracle, t, n_tok, E):
     ids_o, w_o = oracle.router_top10(logits, cfg["k"])
     assert np.array_equal(ids.cpu().numpy(), ids_o)
     got = ffn.cpu().numpy()
+    # Down rows of 256 values: the q8_1 rounding of h alone is ~2e-2 from the exact product there, and two evaluations whose
+    # h differ by 1e-3 (f16 operands against the model's floats) land ~1e-2 apart through flipped roundings - hence the
+    # wide bound on this small shape; each product by itself is pinned to 1e-3 in test_grouped_product_ragged_groups.
     for tok in (0, n_tok // 2, n_tok - 1):
         want = oracle_prefill_token(oracle, cfg, experts, ids_o[tok], w_o[tok], x[tok])
-        assert H.rel_err(got[tok], want) <= TOL and H.rel_l2(got[tok], want) <= TOL
+        assert H.rel_err(got[tok], want) <= 2.5e-2 and H.rel_l2(got[tok], want) <= 2.5e-2
 
 
 def build_pools(T, api, cfg, types, seed, sigma=0.02):
@@ -273,7 +321,8 @@ def build_pools(T, api, cfg, types, seed, sigma=0.02):
 
 def test_prefill_c4_shape(T, api, oracle):
     """Configuration C4 at its full shape: 4096 tokens x top-8 over 256 experts = 32768 routed rows, bf16 activations,
-    half of the experts stored as Q8_0 and half as Q4_K (seeded assignment).  Three tokens against the oracle; row
+    half of the experts stored as Q8_0 and half as Q4_K (seeded assignment).  Six tokens against the oracle's model of the
+    reference's prompt-path arithmetic (oracle.expert_mmq); every token's expert ids; row
     conservation (every routed pair has exactly one sorted row); and a chunk's results do not depend on what else is in
     the chunk - the first 512 tokens alone give the same bits."""
     c = H.CONFIGS["C4"]
@@ -294,16 +343,15 @@ def test_prefill_c4_shape(T, api, oracle):
     pos = pf.pos.cpu().numpy()
     assert np.array_equal(np.sort(pos), np.arange(n_tok * cfg["k"]))
     assert int(pf.bounds[-1].item()) == n_tok * cfg["k"]
-    ids_o, w_o = oracle.router_top10(logits[:4], cfg["k"])
-    assert np.array_equal(ids.cpu().numpy()[:4], ids_o)
-    for tok in (0, 1, 3):
-        xq = oracle.quantize_q8_1(x[tok])
+    ids_o, w_o = oracle.router_top10(logits, cfg["k"])
+    assert np.array_equal(ids.cpu().numpy(), ids_o)
+    for tok in (0, 1, 3, 1000, 2047, 4095):
         want = np.zeros(cfg["n_embd"], np.float32)
         seen = set()
         for j, e in enumerate(ids_o[tok]):
             t, blobs, i = where[int(e)]
             seen.add(t)
-            part = oracle.expert_q8_1(t, t, blobs[i].cpu().numpy(), cfg["n_embd"], cfg["n_ff"], H.INF, xq)
+            part = oracle.expert_mmq(t, t, blobs[i].cpu().numpy(), cfg["n_embd"], cfg["n_ff"], H.INF, x[tok])
             want = (np.float32(w_o[tok][j]) * part + want).astype(np.float32)
         assert H.rel_err(got[tok], want) <= TOL and H.rel_l2(got[tok], want) <= TOL
     _, _, ffn2 = pf.forward(dev(T, logits[:512]), x_dev[:512])

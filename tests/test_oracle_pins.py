@@ -142,6 +142,26 @@ def test_quantized_expert_against_float_expert(oracle, t):
 
 
 @pytest.mark.parametrize("t", TYPES)
+def test_q8_1_dot_against_the_reference_mmq_host_model(oracle, t):
+    """oracle.mmq_host_model restates the reference's host model of its prompt-path GEMM
+    (tests/glm_dsa/glmd_mmq_ids_test.cu:92-347; that test gates the reference's kernels at rel-L2 < 1e-4 from it).  The
+    decode oracle's q8_1 dots round the activation scale to f16 where the model's d4 layout keeps a float, nothing else:
+    both must agree to a few 1e-4, outlier included, and both sit ~1e-3 from the unquantized-activation product."""
+    rows, K = 48, 1024
+    rng = H.rng_for("mmq-model", t)
+    w = H.constructed_blocks(t, rows, K, rng)
+    x = rng.standard_normal((6, K)).astype(np.float32)
+    x[0, 5] = 3000.0                                                      # the reference test's outlier
+    x[1, 64:96] = 0.0                                                     # an all-zero group
+    model = oracle.mmq_host_model(t, w, rows, K, x)
+    q81 = np.stack([oracle.mmvq(t, w, oracle.quantize_q8_1(x[i]), K, rows)[0] for i in range(6)])
+    assert np.isfinite(model).all()
+    assert H.rel_l2(q81, model) <= 5e-4
+    exact = x.astype(np.float64) @ oracle.dequantize(t, w, rows * K).reshape(rows, K).astype(np.float64).T
+    assert H.rel_l2(model, exact) <= 2e-2
+
+
+@pytest.mark.parametrize("t", TYPES)
 def test_mixed_type_expert_is_the_plain_expert_when_the_types_agree(oracle, t):
     """oracle.expert_q8_1_mixed (the up rows' own type, iq_kernels.hpp:73-77) composes the single steps; with one type
     for gate and up it must be expert_q8_1 bit for bit, which pins the composition the mixed-type GPU test checks against."""
