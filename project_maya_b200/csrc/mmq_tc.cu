@@ -79,7 +79,7 @@ static_assert(kUnits<MAYA_Q4_K> <= kMaxUnits && kUnits<MAYA_Q8_0> <= kMaxUnits &
 // xa = f16(sum of the unquantized values) - sum of the row's stored d * q values - padded with zeros to a multiple of 64.  llama.cpp's
 // MMQ keeps that unquantized sum beside the block (the "ds4" q8_1 layout) and a type with a constant term per group
 // (Q4_K: -dmin * m) multiplies the term by it, not by the sum of the rounded values; here the same result comes from
-// extra K steps at the end of a Q4_K product: A = -dmin * m of a row's groups, B = xa.  Other types do not read the tail.
+// extra K steps inside a Q4_K product: A = -dmin * m of a row's groups, B = xa.  Other types do not read the tail.
 __host__ __device__ constexpr int64_t xq_tail(int64_t cols) { return ((cols / 32) + 63) & ~(int64_t) 63; }
 __host__ __device__ constexpr int64_t xq_ld(int64_t cols) { return cols + xq_tail(cols); }
 
@@ -324,7 +324,10 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
     const bool big = nrows > 128;                   // the activation tile is a 128-row box and a 32-row box
     const int m0 = (int) blockIdx.x * (GLU ? 128 : TM);
     const int nkt = A.w_cols / BK, nkb = A.w_cols / 256;
-    const int ntp = T == MAYA_Q4_K ? (nkb * 8 + 63) / 64 : 0;   // 64-value steps of the sum correction after the K loop
+    // Q4_K: after every 8 blocks of K (32 pairs of K steps) one more pair carries the sum correction of those blocks' 64
+    // groups - A = the groups' constant terms -dmin * m, B = the tail of the activation image (see xq_tail); the last pair
+    // of a K that is not a multiple of 2048 is padded with zeros.  ntp = how many such pairs.
+    const int ntp = T == MAYA_Q4_K ? (nkb + 7) / 8 : 0;
 
     uint8_t* const raw = smem + kBRing<T>;
     if (tid == 0) {
@@ -398,6 +401,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             if (lane == 0) mbar_arrive(&P.a_full[s]);
             return true;
         };
+        [[maybe_unused]] uint4 corr[8];      // Q4_K: the constant terms of the current 8-block chunk (indexed by kb: local memory)
         for (int kb = 0; kb < nkb && ok; ++kb) {
             const int u = kb * 4 + slab, slot = u % NU;
             if (!wait_or_fail(P, &P.raw_full[slot], (u / NU) & 1)) { ok = false; break; }
@@ -441,6 +445,10 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             } else if constexpr (T == MAYA_Q4_K) {
                 Q4Scales S;
                 q4k_scales(*(const uint4*) rrow, S);
+                const int chunk = kb >> 3;           // the team that owns the chunk's correction pair keeps the constant terms
+                if ((chunk & 1) == team)
+                    corr[kb & 7] = make_uint4(h2_bits(__lows2half2(S.nml[0], S.nml[1])), h2_bits(__lows2half2(S.nml[2], S.nml[3])),
+                                              h2_bits(__lows2half2(S.nml[4], S.nml[5])), h2_bits(__lows2half2(S.nml[6], S.nml[7])));
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {        // the 64 values of quant pair p: low nibbles, then high nibbles
                     const int p = 2 * i + team;
@@ -452,7 +460,15 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                         q4k_stage(qa, qb, 0, S.dl[4 * i + 2], S.nml[4 * i + 2], o);
                         q4k_stage(qa, qb, 1, S.dl[4 * i + 3], S.nml[4 * i + 3], o + 16);
                     }
-                    if (!put(kb * 4 + p, o)) { ok = false; break; }
+                    if (!put(kb * 4 + chunk + p, o)) { ok = false; break; }
+                }
+                if (ok && (chunk & 1) == team && ((kb & 7) == 7 || kb == nkb - 1)) {      // the chunk's correction pair
+#pragma unroll
+                    for (int b = 0; b < 8; ++b) {
+                        const uint4 c = b <= (kb & 7) ? corr[b] : make_uint4(0u, 0u, 0u, 0u);
+                        o[4 * b] = c.x; o[4 * b + 1] = c.y; o[4 * b + 2] = c.z; o[4 * b + 3] = c.w;
+                    }
+                    ok = put(kb * 4 + chunk + 4, o);
                 }
             } else {
 #define MAYA_Q80_PAIR(PP) if (ok) { q80_stage<2 * (PP)>(rrow, o); q80_stage<2 * (PP) + 1>(rrow, o + 16); ok = put(kb * 4 + (PP), o); }
@@ -463,31 +479,6 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             if (!ok) break;
             __syncwarp();
             if (lane == 0) mbar_arrive(&P.raw_empty[slot]);      // 4 warps read a unit; after the 4th it may be overwritten
-        }
-        if constexpr (T == MAYA_Q4_K) {
-            // The sum-correction steps: pair j of the tail multiplies the constant terms -dmin * m of the row's groups
-            // [64 j, 64 j + 64) (blocks 8 j .. 8 j + 7, read from global memory: 16 bytes a block, L2-warm) by the
-            // activation rows' corrections.  Teams alternate pairs as in the main loop (the main loop ends on an even pair).
-            const int wrow = (GLU ? (slab < 2 ? m0 + 64 * slab : A.w_rows + m0 + 64 * (slab - 2)) : m0 + 64 * slab) + (row & 63);
-            const bool live = wrow < A.mat_rows;
-            const uint8_t* const grow = A.w + (size_t) found_e * A.expert_bytes + (size_t) wrow * ((size_t) nkb * 144);
-            for (int j = team; j < ntp && ok; j += 2) {
-                uint32_t o[32];
-#pragma unroll
-                for (int b = 0; b < 8; ++b) {
-                    const int kb = 8 * j + b;
-                    if (live && kb < nkb) {
-                        Q4Scales S;
-                        q4k_scales(__ldg((const uint4*) (grow + (size_t) kb * 144)), S);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) o[4 * b + i] = h2_bits(__lows2half2(S.nml[2 * i], S.nml[2 * i + 1]));
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) o[4 * b + i] = 0u;
-                    }
-                }
-                ok = put(nkb * 4 + j, o);
-            }
         }
         // ------------------------------------------------------------ epilogue
         if (ok && !wait_or_fail(P, &P.final, 0)) ok = false;
@@ -507,6 +498,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                 // groups stay balanced whatever the row count.  One pass: the whole tile fits in shared memory.
                 __half* b16 = (__half*) stg;                             // [rows][128] f16 image of h
                 float* b32 = (float*) (stg + TN * 128 * 2);              // [rows][128] h
+                __half* bxa = (__half*) (stg + TN * 128 * 6);            // [rows][4] sum corrections of the row's four 32-value groups
                 const int nchunk = (nrows + 7) >> 3;
                 const int mcol = 32 * q + lane;
                 for (int c = hs; c < nchunk; c += 4) {
@@ -517,13 +509,12 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
 #pragma unroll
                     for (int j = 0; j < 8; ++j) v[j] = swiglu(v[j], up[j], A.limit);
                     if (A.xq_out) {
-                        const int64_t ldq = xq_ld(A.w_rows);
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
                             if (col0 + j < nrows) {                                                          // uniform in the warp
                                 float xa;
                                 b16[(col0 + j) * 128 + mcol] = q8_1_round_warp(v[j], xa);
-                                if (lane == 0) A.xq_out[(int64_t) (row0 + col0 + j) * ldq + A.w_rows + (m0 >> 5) + q] = __float2half_rn(xa);
+                                if (lane == 0) bxa[(col0 + j) * 4 + q] = __float2half_rn(xa);
                             }
                     }
                     if (A.dst) {
@@ -539,6 +530,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                     if (A.xq_out) {
                         const int64_t ldq = xq_ld(A.w_rows);
                         bulk_store(A.xq_out + row_g * ldq + m0, b16 + tid * 128, 128 * 2);
+                        *(uint2*) (A.xq_out + row_g * ldq + A.w_rows + (m0 >> 5)) = *(const uint2*) (bxa + tid * 4);
                         if (blockIdx.x == 0)                             // the zero padding behind the row's corrections
                             for (int64_t c = A.w_rows + A.w_rows / 32; c < ldq; ++c) A.xq_out[row_g * ldq + c] = __float2half_rn(0.0f);
                     }
@@ -637,16 +629,26 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             int issued = 0;
             bool ok = true;
             const uint32_t tx_bytes = big ? kBStage : kBBox;
-            for (int kb2 = 0; kb2 < nkt / 2 + ntp; ++kb2) {     // the image's tail follows its K values
+            const int nmain = nkt / 2;
+            for (int kb2 = 0; kb2 < nmain + ntp; ++kb2) {
                 const int sb = kb2 % NB;
+                // the pair's 64 K-values in the image: K values in order, and after every 32 pairs (or at the end) the
+                // chunk's 64 corrections from the tail behind the row's K values
+                int xcol;
+                if (ntp == 0) xcol = kb2 * 64;
+                else {
+                    const int c = kb2 / 33, r = kb2 - c * 33;
+                    const bool is_corr = r == 32 || kb2 == nmain + ntp - 1;
+                    xcol = is_corr ? A.w_cols + 64 * c : (kb2 - c) * 64;
+                }
                 if (kb2 >= NB) {                             // the slot was last read by pair kb2 - NB
                     const int pp = kb2 - NB;
                     if (!wait_or_fail(P, &P.done[pp % kDone], (pp / kDone) & 1)) { ok = false; break; }
                 }
                 uint8_t* bt = smem + (size_t) sb * kBStage;
                 mbar_expect_tx(&P.b_full[sb], tx_bytes);
-                tma_load_2d(bt, &tm_x, &P.b_full[sb], kb2 * 64, row0);
-                if (big) tma_load_2d(bt + kBBox, &tm_x32, &P.b_full[sb], kb2 * 64, row0 + 128);
+                tma_load_2d(bt, &tm_x, &P.b_full[sb], xcol, row0);
+                if (big) tma_load_2d(bt + kBBox, &tm_x32, &P.b_full[sb], xcol, row0 + 128);
                 issued = kb2 + 1;
             }
             if (!ok)
@@ -713,10 +715,18 @@ __global__ void __launch_bounds__(256) mmq_quantize_kernel(const X* __restrict__
     bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 1);
     bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 2);
     const float xa = __half2float(__float2half_rn(__fadd_rn(s0, s1))) - bsum;
+    // a warp's eight groups: their corrections leave as one 16-byte store when a row is a whole number of warps
+    const bool packed = (cols & 255) == 0;
+    if (packed) {
+        const uint32_t mine = (uint32_t) __half_as_ushort(__float2half_rn(xa));
+        const uint32_t pair = mine | (__shfl_down_sync(0xFFFFFFFFu, mine, 4) << 16);        // lanes 0, 8, 16, 24: groups (2i, 2i + 1)
+        const uint32_t p1 = __shfl_sync(0xFFFFFFFFu, pair, 8), p2 = __shfl_sync(0xFFFFFFFFu, pair, 16), p3 = __shfl_sync(0xFFFFFFFFu, pair, 24);
+        if (live && (threadIdx.x & 31) == 0) *(uint4*) (xq + row * xq_ld(cols) + cols + (c >> 2)) = make_uint4(pair, p1, p2, p3);
+    }
     if (live) {
         const int64_t ldq = xq_ld(cols);
         *(uint4*) (xq + row * ldq + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
-        if ((c & 3) == 0) xq[row * ldq + cols + (c >> 2)] = __float2half_rn(xa);
+        if (!packed && (c & 3) == 0) xq[row * ldq + cols + (c >> 2)] = __float2half_rn(xa);
         if (c == 0)                                   // the zero padding behind the row's corrections
             for (int64_t t = cols + cols / 32; t < ldq; ++t) xq[row * ldq + t] = __float2half_rn(0.0f);
     }
