@@ -35,7 +35,14 @@ enum maya_status {
     MAYA_ERR_DEVICE = -5       /* not an sm_100 device / no CUDA device */
 };
 
-enum maya_ggml_type { MAYA_Q8_0 = 8, MAYA_Q4_K = 12, MAYA_IQ3_S = 21, MAYA_IQ2_S = 22 };
+/* ggml type ids.  The first four run on every path (fused single-token kernel, staged decode kernels, window, grouped,
+ * prompt-path GEMM).  The others - the rest of glmf::moe_supported's table (glm_fast.cu:5798-5801) that the reference's
+ * models use - run on the staged decode paths: maya_mmvq, the plan / window / grouped expert kernels and
+ * maya_moe_layer_decode (which then takes its staged kernels); the prompt-path GEMM refuses them. */
+enum maya_ggml_type {
+    MAYA_Q8_0 = 8, MAYA_Q4_K = 12, MAYA_IQ3_S = 21, MAYA_IQ2_S = 22,
+    MAYA_Q5_K = 13, MAYA_Q6_K = 14, MAYA_IQ2_XXS = 16, MAYA_IQ3_XXS = 18, MAYA_IQ4_XS = 23
+};
 
 #define MAYA_MAX_K 8            /* plan entries per token (glm_fast.hpp:341) */
 #define MAYA_MAX_WIN_TOKENS 16  /* tokens of a window (glm_fast.hpp:459) */

@@ -24,11 +24,13 @@
 #include <string.h>
 
 #define MAYA_GRID_QUAL static const
+#define MAYA_IQ2XXS_GRID MAYA_IQ2XXS_GRID
+#define MAYA_IQ3XXS_GRID MAYA_IQ3XXS_GRID
 #include "maya_iq_grids.inc"
 
 #define ORC_API __attribute__((visibility("default")))
 
-enum { T_Q8_0 = 8, T_Q4_K = 12, T_IQ3_S = 21, T_IQ2_S = 22 };
+enum { T_Q8_0 = 8, T_Q4_K = 12, T_IQ3_S = 21, T_IQ2_S = 22, T_Q5_K = 13, T_Q6_K = 14, T_IQ2_XXS = 16, T_IQ3_XXS = 18, T_IQ4_XS = 23 };
 
 /* ------------------------------------------------------------------ small helpers */
 static inline float h2f(uint16_t h) { _Float16 v; memcpy(&v, &h, 2); return (float) v; }
@@ -55,11 +57,15 @@ static float warp_tree_sum(const float* lane) {
     return v[0];
 }
 
-ORC_API int orc_type_block_values(int type) { return type == T_Q8_0 ? 32 : (type == T_Q4_K || type == T_IQ3_S || type == T_IQ2_S) ? 256 : 0; }
 ORC_API int orc_type_block_bytes(int type) {
-    switch (type) { case T_Q8_0: return 34; case T_Q4_K: return 144; case T_IQ3_S: return 110; case T_IQ2_S: return 82; default: return 0; }
+    switch (type) {
+        case T_Q8_0: return 34; case T_Q4_K: return 144; case T_IQ3_S: return 110; case T_IQ2_S: return 82;
+        case T_Q5_K: return 176; case T_Q6_K: return 210; case T_IQ4_XS: return 136; case T_IQ3_XXS: return 98; case T_IQ2_XXS: return 66;
+        default: return 0;
+    }
 }
-/* iq_row_bytes (iq_kernels.cu:984-1006) / native_mmvq_weight_bytes (native_mmvq.cu) for the four types. */
+ORC_API int orc_type_block_values(int type) { return type == T_Q8_0 ? 32 : orc_type_block_bytes(type) ? 256 : 0; }
+/* iq_row_bytes (iq_kernels.cu:984-1006) / native_mmvq_weight_bytes (native_mmvq.cu). */
 ORC_API size_t orc_row_bytes(int type, int64_t n) {
     const int bv = orc_type_block_values(type);
     return bv ? (size_t) (n / bv) * (size_t) orc_type_block_bytes(type) : 0;
@@ -139,6 +145,83 @@ static void dequant_block(int type, const uint8_t* b, float* y) {
                 for (int j = 0; j < 4; ++j) {
                     const float v = db * (float) ((g >> (8 * j)) & 0xFF);
                     y[32 * ib + 4 * l + j] = ((s >> (4 * (l & 1) + j)) & 1) ? -v : v;
+                }
+            }
+        }
+    } else if (type == T_Q5_K) {
+        /* dequantize_row_q5_K (ggml-quants.c): Q4_K's layout with qh[32] between the scales and qs; bit sb of qh[l] is
+         * the fifth bit of value l of sub-block sb. */
+        const float d = h2f(rd16(b)), dmin = h2f(rd16(b + 2));
+        const uint8_t *qh = b + 16, *qs = b + 48;
+        for (int j = 0; j < 8; ++j) {
+            int sc, mn;
+            q4k_scale_min(b + 4, j, &sc, &mn);
+            const float dl = d * (float) sc, ml = dmin * (float) mn;
+            for (int i = 0; i < 32; ++i) {
+                const int q4 = (j & 1) ? (qs[32 * (j / 2) + i] >> 4) : (qs[32 * (j / 2) + i] & 0x0F);
+                const int q = q4 | (((qh[i] >> j) & 1) << 4);
+                y[32 * j + i] = dl * (float) q - ml;
+            }
+        }
+    } else if (type == T_Q6_K) {
+        /* dequantize_row_q6_K: ql[128] | qh[64] | int8 scales[16] | f16 d; run r = 4 h + k of 32 values. */
+        const float d = h2f(rd16(b + 208));
+        const int8_t* sc = (const int8_t*) (b + 192);
+        for (int r = 0; r < 8; ++r) {
+            const int h = r >> 2, k = r & 3;
+            const uint8_t *ql = b + 64 * h + 32 * (k & 1), *qh = b + 128 + 32 * h;
+            for (int l = 0; l < 32; ++l) {
+                const int q = (((k >> 1) ? (ql[l] >> 4) : (ql[l] & 0x0F)) | (((qh[l] >> (2 * k)) & 3) << 4)) - 32;
+                y[32 * r + l] = (d * (float) sc[8 * h + 2 * k + l / 16]) * (float) q;
+            }
+        }
+    } else if (type == T_IQ4_XS) {
+        /* dequantize_row_iq4_xs: f16 d | u16 scales_h | u8 scales_l[4] | qs[128]; y = d (ls - 32) kvalues[q]. */
+        static const int8_t kv[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+        const float d = h2f(rd16(b));
+        const int sh = rd16(b + 2);
+        for (int ib = 0; ib < 8; ++ib) {
+            const int ls = ((b[4 + ib / 2] >> (4 * (ib & 1))) & 0x0F) | (((sh >> (2 * ib)) & 3) << 4);
+            const float dl = d * (float) (ls - 32);
+            const uint8_t* qs = b + 8 + 16 * ib;
+            for (int j = 0; j < 16; ++j) {
+                y[32 * ib + j] = dl * (float) kv[qs[j] & 0x0F];
+                y[32 * ib + 16 + j] = dl * (float) kv[qs[j] >> 4];
+            }
+        }
+    } else if (type == T_IQ3_XXS) {
+        /* dequantize_row_iq3_xxs: f16 d | qs[64] | u32 gas[8]: db = d (0.5 + (gas >> 28)) 0.5; 7 sign bits per 8 values, the
+         * eighth from their parity (ksigns_iq2xs). */
+        const float d = h2f(rd16(b));
+        for (int ib = 0; ib < 8; ++ib) {
+            const uint32_t aux = (uint32_t) rd32(b + 66 + 4 * ib);
+            const float db = d * (0.5f + (float) (aux >> 28)) * 0.5f;
+            for (int l = 0; l < 4; ++l) {
+                const uint32_t s7 = (aux >> (7 * l)) & 127u;
+                const uint32_t s8 = s7 | ((uint32_t) (__builtin_popcount(s7) & 1) << 7);
+                for (int e = 0; e < 2; ++e) {
+                    const uint32_t g = MAYA_IQ3XXS_GRID[b[2 + 8 * ib + 2 * l + e]];
+                    for (int j = 0; j < 4; ++j) {
+                        const float v = db * (float) ((g >> (8 * j)) & 0xFF);
+                        y[32 * ib + 8 * l + 4 * e + j] = ((s8 >> (4 * e + j)) & 1) ? -v : v;
+                    }
+                }
+            }
+        }
+    } else if (type == T_IQ2_XXS) {
+        /* dequantize_row_iq2_xxs: f16 d | per 32 values { u8 idx[4] | u32 aux }: db = d (0.5 + (aux >> 28)) 0.25. */
+        const float d = h2f(rd16(b));
+        for (int ib = 0; ib < 8; ++ib) {
+            const uint8_t* q = b + 2 + 8 * ib;
+            const uint32_t aux = (uint32_t) rd32(q + 4);
+            const float db = d * (0.5f + (float) (aux >> 28)) * 0.25f;
+            for (int l = 0; l < 4; ++l) {
+                const uint32_t s7 = (aux >> (7 * l)) & 127u;
+                const uint32_t s8 = s7 | ((uint32_t) (__builtin_popcount(s7) & 1) << 7);
+                const uint64_t g = MAYA_IQ2XXS_GRID[q[l]];
+                for (int j = 0; j < 8; ++j) {
+                    const float v = db * (float) ((g >> (8 * j)) & 0xFF);
+                    y[32 * ib + 8 * l + j] = ((s8 >> j) & 1) ? -v : v;
                 }
             }
         }
@@ -231,8 +314,87 @@ static float call_iq3_s(const uint8_t* b, const uint8_t* xq, int c) {
     return h2f(rd16(b)) * h2f(rd16(q8)) * (float) sumi;
 }
 
+/* The other block types of glmf::moe_supported (glm_fast.cu:5798-5801), one 32-weight sub-block a call.  The integer
+ * sums are llama.cpp's vec_dot_*_q8_1 as glm_fast.cu transcribes them (dot_q5_K :246-290, dot_q6_K :310-335, dot_iq2_xxs
+ * :536-559, dot_iq3_xxs :560-583, dot_iq4_xs :605-621): exact int8 dots, Q5_K's scale and min terms with the sum of the
+ * activation quants, Q6_K's two int8 scales per 32 values, IQ4_XS's (ls - 32) * sum, IQ3_XXS's (ls * s + s / 2) / 2 and
+ * IQ2_XXS's s * (2 ls + 1) / 8 with truncating division. */
+static int signed_dot8(uint64_t g, uint32_t s8, const uint8_t* q8) {
+    int part = 0;
+    for (int j = 0; j < 8; ++j) {
+        const int w = (int) ((g >> (8 * j)) & 0xFF);
+        part += (((s8 >> j) & 1) ? -w : w) * (int) (int8_t) q8[j];
+    }
+    return part;
+}
+static float call_q5_K(const uint8_t* b, const uint8_t* xq, int sb) {
+    const uint8_t *qh = b + 16, *qs = b + 48 + 32 * (sb / 2), *q8 = xq + 36 * sb;
+    int sc, mn, dot1 = 0, dot2 = 0;
+    q4k_scale_min(b + 4, sb, &sc, &mn);
+    for (int i = 0; i < 32; ++i) {
+        const int q = ((sb & 1) ? (qs[i] >> 4) : (qs[i] & 0x0F)) | (((qh[i] >> sb) & 1) << 4);
+        dot1 += q * (int) (int8_t) q8[4 + i];
+        dot2 += (int) (int8_t) q8[4 + i];
+    }
+    const float d8 = h2f(rd16(q8));
+    return h2f(rd16(b)) * (d8 * (float) (dot1 * sc)) - h2f(rd16(b + 2)) * (d8 * (float) (dot2 * mn));
+}
+static float call_q6_K(const uint8_t* b, const uint8_t* xq, int r) {
+    const int h = r >> 2, k = r & 3;
+    const uint8_t *ql = b + 64 * h + 32 * (k & 1), *qh = b + 128 + 32 * h, *q8 = xq + 36 * r;
+    const int8_t* sc = (const int8_t*) (b + 192) + 8 * h + 2 * k;
+    int s[2] = {0, 0};
+    for (int l = 0; l < 32; ++l) {
+        const int q = (((k >> 1) ? (ql[l] >> 4) : (ql[l] & 0x0F)) | (((qh[l] >> (2 * k)) & 3) << 4)) - 32;
+        s[l / 16] += q * (int) (int8_t) q8[4 + l];
+    }
+    return h2f(rd16(b + 208)) * h2f(rd16(q8)) * (float) (s[0] * sc[0] + s[1] * sc[1]);
+}
+static float call_iq4_xs(const uint8_t* b, const uint8_t* xq, int ib) {
+    static const int8_t kv[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+    const int sh = rd16(b + 2);
+    const int ls = (((b[4 + ib / 2] >> (4 * (ib & 1))) & 0x0F) | (((sh >> (2 * ib)) & 3) << 4)) - 32;
+    const uint8_t *qs = b + 8 + 16 * ib, *q8 = xq + 36 * ib;
+    int sumi = 0;
+    for (int j = 0; j < 16; ++j)
+        sumi += kv[qs[j] & 0x0F] * (int) (int8_t) q8[4 + j] + kv[qs[j] >> 4] * (int) (int8_t) q8[4 + 16 + j];
+    return h2f(rd16(b)) * h2f(rd16(q8)) * (float) (sumi * ls);
+}
+static float call_iq3_xxs(const uint8_t* b, const uint8_t* xq, int ib) {
+    const uint32_t aux = (uint32_t) rd32(b + 66 + 4 * ib);
+    const uint8_t* q8 = xq + 36 * ib;
+    int sumi = 0;
+    for (int l = 0; l < 4; ++l) {
+        const uint32_t s7 = (aux >> (7 * l)) & 127u;
+        const uint32_t s8 = s7 | ((uint32_t) (__builtin_popcount(s7) & 1) << 7);
+        const uint64_t g = (uint64_t) MAYA_IQ3XXS_GRID[b[2 + 8 * ib + 2 * l]] | ((uint64_t) MAYA_IQ3XXS_GRID[b[2 + 8 * ib + 2 * l + 1]] << 32);
+        sumi += signed_dot8(g, s8, q8 + 4 + 8 * l);
+    }
+    const int ls = (int) (aux >> 28);
+    sumi = (ls * sumi + sumi / 2) / 2;
+    return h2f(rd16(b)) * h2f(rd16(q8)) * (float) sumi;
+}
+static float call_iq2_xxs(const uint8_t* b, const uint8_t* xq, int ib) {
+    const uint8_t *q = b + 2 + 8 * ib, *q8 = xq + 36 * ib;
+    const uint32_t aux = (uint32_t) rd32(q + 4);
+    int sumi = 0;
+    for (int l = 0; l < 4; ++l) {
+        const uint32_t s7 = (aux >> (7 * l)) & 127u;
+        const uint32_t s8 = s7 | ((uint32_t) (__builtin_popcount(s7) & 1) << 7);
+        sumi += signed_dot8(MAYA_IQ2XXS_GRID[q[l]], s8, q8 + 4 + 8 * l);
+    }
+    const int ls = (int) (aux >> 27) | 1;                 /* 2 * scale + 1 (dot_iq2_xxs, glm_fast.cu:555-556) */
+    sumi = sumi * ls / 8;
+    return h2f(rd16(b)) * h2f(rd16(q8)) * (float) sumi;
+}
+
 static float call_dot(int type, const uint8_t* blk, const uint8_t* xq, int c) {
     switch (type) {
+        case T_Q5_K: return call_q5_K(blk, xq, c);
+        case T_Q6_K: return call_q6_K(blk, xq, c);
+        case T_IQ4_XS: return call_iq4_xs(blk, xq, c);
+        case T_IQ3_XXS: return call_iq3_xxs(blk, xq, c);
+        case T_IQ2_XXS: return call_iq2_xxs(blk, xq, c);
         case T_Q8_0: return call_q8_0(blk, xq, c);
         case T_Q4_K: return call_q4_K(blk, xq, c);
         case T_IQ2_S: return call_iq2_s(blk, xq, c);

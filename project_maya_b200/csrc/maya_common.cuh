@@ -26,9 +26,34 @@ template<> struct Fmt<MAYA_Q8_0> { static constexpr int qk = 32, bytes = 34, tab
 template<> struct Fmt<MAYA_Q4_K> { static constexpr int qk = 256, bytes = 144, tab_words = 0; };
 template<> struct Fmt<MAYA_IQ2_S> { static constexpr int qk = 256, bytes = 82, tab_words = 2048; };
 template<> struct Fmt<MAYA_IQ3_S> { static constexpr int qk = 256, bytes = 110, tab_words = 512; };
+// Q5_K  176 B/256: f16 d | f16 dmin | u8 scales[12] | u8 qh[32] | u8 qs[128]
+// Q6_K  210 B/256: u8 ql[128] | u8 qh[64] | i8 scales[16] | f16 d
+// IQ4_XS 136 B/256: f16 d | u16 scales_h | u8 scales_l[4] | u8 qs[128]
+// IQ3_XXS 98 B/256: f16 d | u8 qs[64] | u32 scales_and_signs[8]
+// IQ2_XXS 66 B/256: f16 d | per 32 values { u8 qs[4] | u32 scale_and_signs }
+template<> struct Fmt<MAYA_Q5_K> { static constexpr int qk = 256, bytes = 176, tab_words = 0; };
+template<> struct Fmt<MAYA_Q6_K> { static constexpr int qk = 256, bytes = 210, tab_words = 0; };
+template<> struct Fmt<MAYA_IQ4_XS> { static constexpr int qk = 256, bytes = 136, tab_words = 0; };
+template<> struct Fmt<MAYA_IQ3_XXS> { static constexpr int qk = 256, bytes = 98, tab_words = 256; };
+template<> struct Fmt<MAYA_IQ2_XXS> { static constexpr int qk = 256, bytes = 66, tab_words = 512; };
 
-__host__ __device__ inline int type_qk(int t) { return t == MAYA_Q8_0 ? 32 : (t == MAYA_Q4_K || t == MAYA_IQ3_S || t == MAYA_IQ2_S) ? 256 : 0; }
-__host__ __device__ inline int type_bytes(int t) { return t == MAYA_Q8_0 ? 34 : t == MAYA_Q4_K ? 144 : t == MAYA_IQ3_S ? 110 : t == MAYA_IQ2_S ? 82 : 0; }
+__host__ __device__ inline int type_bytes(int t) {
+    switch (t) {
+        case MAYA_Q8_0: return 34;
+        case MAYA_Q4_K: return 144;
+        case MAYA_IQ3_S: return 110;
+        case MAYA_IQ2_S: return 82;
+        case MAYA_Q5_K: return 176;
+        case MAYA_Q6_K: return 210;
+        case MAYA_IQ4_XS: return 136;
+        case MAYA_IQ3_XXS: return 98;
+        case MAYA_IQ2_XXS: return 66;
+        default: return 0;
+    }
+}
+__host__ __device__ inline int type_qk(int t) { return t == MAYA_Q8_0 ? 32 : type_bytes(t) ? 256 : 0; }
+// The four types every path covers (fused single-token kernel, prompt-path GEMM, device-side weight synthesis).
+__host__ __device__ inline bool type_is_core(int t) { return t == MAYA_Q8_0 || t == MAYA_Q4_K || t == MAYA_IQ3_S || t == MAYA_IQ2_S; }
 __host__ __device__ inline size_t row_bytes(int t, int64_t n) { const int q = type_qk(t); return q ? (size_t) (n / q) * (size_t) type_bytes(t) : 0; }
 
 constexpr int kQ81Bytes = 36;

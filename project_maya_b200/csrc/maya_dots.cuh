@@ -1,4 +1,5 @@
-// maya_dots.cuh - the quantized dot products: GGUF weight blocks (Q8_0, Q4_K, IQ2_S, IQ3_S) against q8_1 activations.
+// maya_dots.cuh - the quantized dot products: GGUF weight blocks (Q8_0, Q4_K, IQ2_S, IQ3_S; Q5_K, Q6_K, IQ4_XS, IQ3_XXS,
+// IQ2_XXS) against q8_1 activations.
 //
 // Integer semantics follow llama.cpp's vec_dot_*_q8_1 as the reference transcribes them (per 32-value sub-block:
 // exact int8 dot, IQ2_S's (s0*l0 + s1*l1 + (s0+s1)/2)/4 with truncating division, IQ3_S's sum * (1 + 2*scale), Q4_K's
@@ -213,19 +214,191 @@ template<> struct Dec<MAYA_IQ3_S> {
     }
 };
 
+// Q5_K: Q4_K's layout with a fifth bit per value (qh bit sb of byte l belongs to value l of sub-block sb).
+template<> struct Dec<MAYA_Q5_K> {
+    static constexpr int cpb = 4, xblk = 2;
+    int lo[8], hi[8];
+    int sc0, sc1, m0, m1;
+    float d, dmin;
+    __device__ __forceinline__ void load(const uint8_t* blk, int j, const uint32_t*) {
+        const uint32_t dm = ld_u32(blk);
+        d = __half2float(__ushort_as_half((uint16_t) (dm & 0xFFFF)));
+        dmin = __half2float(__ushort_as_half((uint16_t) (dm >> 16)));
+        const uint8_t* s12 = blk + 4;
+        const int a = 2 * j;
+        if (j < 2) {
+            sc0 = s12[a] & 63; m0 = s12[a + 4] & 63;
+            sc1 = s12[a + 1] & 63; m1 = s12[a + 5] & 63;
+        } else {
+            sc0 = (s12[a + 4] & 0x0F) | ((s12[a - 4] >> 6) << 4); m0 = (s12[a + 4] >> 4) | ((s12[a] >> 6) << 4);
+            sc1 = (s12[a + 5] & 0x0F) | ((s12[a - 3] >> 6) << 4); m1 = (s12[a + 5] >> 4) | ((s12[a + 1] >> 6) << 4);
+        }
+        const int4* h = (const int4*) (blk + 16);
+        const int4* q = (const int4*) (blk + 48 + 32 * j);
+        const int4 h0 = h[0], h1 = h[1], q0 = q[0], q1 = q[1];
+        const int hh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+        const int qq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            lo[i] = (qq[i] & 0x0F0F0F0F) | (((hh[i] >> (2 * j)) & 0x01010101) << 4);
+            hi[i] = ((qq[i] >> 4) & 0x0F0F0F0F) | (((hh[i] >> (2 * j + 1)) & 0x01010101) << 4);
+        }
+    }
+    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
+        const XQ a = xq_load(x, col, xb), b = xq_load(x, col, xb + 1);
+        int s0 = 0, s1 = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { s0 = __dp4a(lo[i], a.u[i], s0); s1 = __dp4a(hi[i], b.u[i], s1); }
+        const float sd = __fadd_rn(__fmul_rn(a.d, (float) (s0 * sc0)), __fmul_rn(b.d, (float) (s1 * sc1)));
+        const float sm = __fadd_rn(__fmul_rn(a.d, (float) (a.isum * m0)), __fmul_rn(b.d, (float) (b.isum * m1)));
+        return __fsub_rn(__fmul_rn(d, sd), __fmul_rn(dmin, sm));
+    }
+};
+
+// Q6_K: a call = one run of 32 values (run r = 4 h + k of half h: ql bytes [64 h + 32 (k & 1), +32), low nibble for
+// k < 2 else high; qh bytes [32 h, +32) bits 2k, 2k + 1; value = 6-bit q - 32), two int8 scales (16 values each).
+// Blocks of 210 bytes are only 2-byte aligned.
+template<> struct Dec<MAYA_Q6_K> {
+    static constexpr int cpb = 8, xblk = 1;
+    int w[8];
+    int sa, sb;
+    float d;
+    __device__ __forceinline__ void load(const uint8_t* blk, int r, const uint32_t*) {
+        const int h = r >> 2, k = r & 3;
+        const uint8_t* ql = blk + 64 * h + 32 * (k & 1);
+        const uint8_t* qh = blk + 128 + 32 * h;
+        const uint32_t sc = ld_u16(blk + 192 + 8 * h + 2 * k);
+        sa = (int) (int8_t) (sc & 0xFF);
+        sb = (int) (int8_t) (sc >> 8);
+        d = ld_f16(blk + 208);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t l4 = (ld_u32_a2(ql + 4 * i) >> (4 * (k >> 1))) & 0x0F0F0F0Fu;
+            const uint32_t h2 = ((ld_u32_a2(qh + 4 * i) >> (2 * k)) & 0x03030303u) << 4;
+            // q - 32 per byte, q in 0..63: with bit 7 set no byte borrows, and flipping it back leaves the two's complement
+            w[i] = (int) ((((l4 | h2) | 0x80808080u) - 0x20202020u) ^ 0x80808080u);
+        }
+    }
+    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
+        const XQ v = xq_load(x, col, xb);
+        int s0 = 0, s1 = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { s0 = __dp4a(w[i], v.u[i], s0); s1 = __dp4a(w[4 + i], v.u[4 + i], s1); }
+        return __fmul_rn(__fmul_rn(d, v.d), (float) (s0 * sa + s1 * sb));
+    }
+};
+
+// IQ4_XS: a call = sub-block ib of 32 values: 16 bytes of 4-bit indices into the 16-entry non-linear value table (first
+// the 16 low nibbles, then the 16 high ones), one 6-bit scale ls - 32.  The table sits in four registers and a lookup
+// of four indices is three byte permutes: the low three index bits select within each half of the table, bit 3 picks
+// the half (__byte_perm reads three bits of a selector nibble).
+template<> struct Dec<MAYA_IQ4_XS> {
+    static constexpr int cpb = 8, xblk = 1;
+    int w[8];
+    int ls;
+    float d;
+    __device__ __forceinline__ static uint32_t lut4(uint32_t sel16) {      // four 4-bit indices in bits 0..15 -> four table bytes
+        constexpr uint32_t t0 = 0xBFAD9881u, t1 = 0xF6EADDCFu, t2 = 0x26190D01u, t3 = 0x71594535u;   // -127 .. 113, little-endian
+        const uint32_t lo = __byte_perm(t0, t1, sel16), hi = __byte_perm(t2, t3, sel16);
+        return __byte_perm(lo, hi, 0x3210u | ((sel16 & 0x8888u) >> 1));
+    }
+    __device__ __forceinline__ void load(const uint8_t* blk, int ib, const uint32_t*) {
+        d = ld_f16(blk);
+        const uint32_t sh = ld_u16(blk + 2), sl = blk[4 + (ib >> 1)];
+        ls = (int) (((sl >> (4 * (ib & 1))) & 0x0F) | (((sh >> (2 * ib)) & 3) << 4)) - 32;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t q = ld_u32_a2(blk + 8 + 16 * ib + 4 * i);       // bytes 4i .. 4i + 3: nibbles (b0 lo, b0 hi, b1 lo, ...)
+            const uint32_t a = lut4(q & 0xFFFFu), b = lut4(q >> 16);
+            w[i] = (int) __byte_perm(a, b, 0x6420);                        // the four low nibbles' values: values 4i .. 4i + 3
+            w[4 + i] = (int) __byte_perm(a, b, 0x7531);                    // the high nibbles': values 16 + 4i ..
+        }
+    }
+    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
+        const XQ v = xq_load(x, col, xb);
+        int s = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s = __dp4a(w[i], v.u[i], s);
+        return __fmul_rn(__fmul_rn(d, v.d), (float) (s * ls));
+    }
+};
+
+// The 8 sign bits of 8 values from their 7-bit code: the eighth makes the number of set bits even (ksigns_iq2xs).
+__device__ __forceinline__ uint32_t ksign8(uint32_t s7) { return s7 | ((__popc(s7) & 1u) << 7); }
+
+// IQ3_XXS: a call = sub-block ib: 8 codebook indices (4 values each) and one 32-bit word of 4 x 7 sign bits + 4-bit scale.
+template<> struct Dec<MAYA_IQ3_XXS> {
+    static constexpr int cpb = 8, xblk = 1;
+    int w[8];
+    int ls;
+    float d;
+    __device__ __forceinline__ void load(const uint8_t* blk, int c, const uint32_t* tab) {
+        d = ld_f16(blk);
+        const uint32_t q0 = ld_u32_a2(blk + 2 + 8 * c), q1 = ld_u32_a2(blk + 6 + 8 * c), aux = ld_u32_a2(blk + 66 + 4 * c);
+        ls = (int) (aux >> 28);
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const uint32_t s8 = ksign8((aux >> (7 * l)) & 127u);
+            const uint32_t qa = ((l < 2 ? q0 : q1) >> (16 * (l & 1))) & 0xFFFFu;
+            w[2 * l] = apply_sign4(tab[qa & 0xFF], sign_mask4(s8 & 0x0F));
+            w[2 * l + 1] = apply_sign4(tab[qa >> 8], sign_mask4(s8 >> 4));
+        }
+    }
+    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
+        const XQ v = xq_load(x, col, xb);
+        int s = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s = __dp4a(w[i], v.u[i], s);
+        return __fmul_rn(__fmul_rn(d, v.d), (float) ((ls * s + s / 2) / 2));
+    }
+};
+
+// IQ2_XXS: a call = sub-block ib: 4 codebook indices (8 values each), then 4 x 7 sign bits + 4-bit scale.
+template<> struct Dec<MAYA_IQ2_XXS> {
+    static constexpr int cpb = 8, xblk = 1;
+    int w[8];
+    int ls;
+    float d;
+    __device__ __forceinline__ void load(const uint8_t* blk, int c, const uint32_t* tab) {
+        d = ld_f16(blk);
+        const uint32_t qi = ld_u32_a2(blk + 2 + 8 * c), aux = ld_u32_a2(blk + 6 + 8 * c);
+        ls = (int) (aux >> 27) | 1;                  // 2 * scale + 1
+        const uint2* grid = (const uint2*) tab;
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const uint2 g = grid[(qi >> (8 * l)) & 0xFF];
+            const uint32_t s8 = ksign8((aux >> (7 * l)) & 127u);
+            w[2 * l] = apply_sign4(g.x, sign_mask4(s8 & 0x0F));
+            w[2 * l + 1] = apply_sign4(g.y, sign_mask4(s8 >> 4));
+        }
+    }
+    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
+        const XQ v = xq_load(x, col, xb);
+        int s = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s = __dp4a(w[i], v.u[i], s);
+        return __fmul_rn(__fmul_rn(d, v.d), (float) (s * ls / 8));
+    }
+};
+
 // ---------------------------------------------------------------- codebooks
 // One device copy per translation unit (no relocatable device code needed); generated at build time.
 #define MAYA_GRID_QUAL static __device__ const
 #define MAYA_IQ2S_GRID g_iq2s_grid
 #define MAYA_IQ3S_GRID g_iq3s_grid
+#define MAYA_IQ2XXS_GRID g_iq2xxs_grid
+#define MAYA_IQ3XXS_GRID g_iq3xxs_grid
 #include "generated/maya_iq_grids.inc"
 #undef MAYA_IQ2S_GRID
 #undef MAYA_IQ3S_GRID
+#undef MAYA_IQ2XXS_GRID
+#undef MAYA_IQ3XXS_GRID
 #undef MAYA_GRID_QUAL
 
 template<int T> __device__ __forceinline__ void load_tab(uint32_t* s_tab) {
     if constexpr (Fmt<T>::tab_words > 0) {
-        const uint32_t* src = T == MAYA_IQ2_S ? (const uint32_t*) g_iq2s_grid : (const uint32_t*) g_iq3s_grid;
+        const uint32_t* src = T == MAYA_IQ2_S ? (const uint32_t*) g_iq2s_grid : T == MAYA_IQ3_S ? (const uint32_t*) g_iq3s_grid
+                              : T == MAYA_IQ2_XXS ? (const uint32_t*) g_iq2xxs_grid : (const uint32_t*) g_iq3xxs_grid;
         for (int i = threadIdx.x; i < Fmt<T>::tab_words; i += blockDim.x) s_tab[i] = src[i];
     }
 }

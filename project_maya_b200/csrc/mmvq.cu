@@ -79,6 +79,11 @@ extern "C" int maya_mmvq(int type, const void* w, const void* xq, float* y, int 
         case MAYA_Q8_0: return launch_mmvq_cols<MAYA_Q8_0>(w, xq, y, n_in, n_out, ncols, s);
         case MAYA_Q4_K: return launch_mmvq_cols<MAYA_Q4_K>(w, xq, y, n_in, n_out, ncols, s);
         case MAYA_IQ2_S: return launch_mmvq_cols<MAYA_IQ2_S>(w, xq, y, n_in, n_out, ncols, s);
-        default: return launch_mmvq_cols<MAYA_IQ3_S>(w, xq, y, n_in, n_out, ncols, s);
+        case MAYA_IQ3_S: return launch_mmvq_cols<MAYA_IQ3_S>(w, xq, y, n_in, n_out, ncols, s);
+        case MAYA_Q5_K: return launch_mmvq_cols<MAYA_Q5_K>(w, xq, y, n_in, n_out, ncols, s);
+        case MAYA_Q6_K: return launch_mmvq_cols<MAYA_Q6_K>(w, xq, y, n_in, n_out, ncols, s);
+        case MAYA_IQ4_XS: return launch_mmvq_cols<MAYA_IQ4_XS>(w, xq, y, n_in, n_out, ncols, s);
+        case MAYA_IQ3_XXS: return launch_mmvq_cols<MAYA_IQ3_XXS>(w, xq, y, n_in, n_out, ncols, s);
+        default: return launch_mmvq_cols<MAYA_IQ2_XXS>(w, xq, y, n_in, n_out, ncols, s);
     }
 }

@@ -548,6 +548,11 @@ int launch_gate_up_mixed_u(int u_type, const Groups& G, int n_groups_grid, int n
         case MAYA_Q4_K: return CALL(MAYA_Q4_K);           \
         case MAYA_IQ2_S: return CALL(MAYA_IQ2_S);         \
         case MAYA_IQ3_S: return CALL(MAYA_IQ3_S);         \
+        case MAYA_Q5_K: return CALL(MAYA_Q5_K);           \
+        case MAYA_Q6_K: return CALL(MAYA_Q6_K);           \
+        case MAYA_IQ4_XS: return CALL(MAYA_IQ4_XS);       \
+        case MAYA_IQ3_XXS: return CALL(MAYA_IQ3_XXS);     \
+        case MAYA_IQ2_XXS: return CALL(MAYA_IQ2_XXS);     \
         default: return refuse(MAYA_ERR_TYPE);            \
     }
 
@@ -659,7 +664,7 @@ extern "C" int maya_moe_gate_up(int gu_type, const maya_moe_plan* plan, int k, i
     const int st = check_shapes(gu_type, -1, k, n_embd, n_ff);
     if (st != MAYA_OK) return refuse(st);
     if (sh_down != nullptr) {
-        if (!type_qk(sh_type)) return refuse(MAYA_ERR_TYPE);
+        if (!type_is_core(sh_type)) return refuse(MAYA_ERR_TYPE);      // the shared expert's rows: Q8_0, Q4_K, IQ2_S, IQ3_S
         if (!sh_hq || !sh_out || n_ff_sh <= 0 || n_ff_sh % type_qk(sh_type) || n_ff_sh % 32) return refuse(MAYA_ERR_ARG);
     }
     GroupArgs A{};

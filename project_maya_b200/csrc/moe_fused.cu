@@ -457,7 +457,7 @@ int launch_fused(const FusedArgs& A, cudaStream_t s) {
 
 // Whether the fused single-token kernel covers this layer (else the staged kernels run).
 bool fused_t1_supported(const maya_moe_layer& L) {
-    if (L.gu_type != L.d_type) return false;
+    if (L.gu_type != L.d_type || !type_is_core(L.gu_type)) return false;
     if (L.n_ff_sh > 0 && (L.sh_gu_type != MAYA_Q8_0 || L.sh_d_type != MAYA_Q8_0)) return false;
     if (L.n_expert > kRouteThreads * kRouterMaxPerThread) return false;
     return true;

@@ -88,7 +88,7 @@ int check_layer(const maya_moe_layer* L) {
         return MAYA_ERR_ARG;
     if (L->n_ff_sh > 0) {
         if (!L->shared) return MAYA_ERR_ARG;
-        if (!type_qk(L->sh_gu_type) || !type_qk(L->sh_d_type)) return MAYA_ERR_TYPE;
+        if (!type_is_core(L->sh_gu_type) || !type_is_core(L->sh_d_type)) return MAYA_ERR_TYPE;
         if (L->n_embd % type_qk(L->sh_gu_type) || L->n_ff_sh % type_qk(L->sh_d_type) || L->n_ff_sh % 32) return MAYA_ERR_ARG;
     }
     if (L->expert_lo < 0 || L->expert_hi > L->n_expert || L->expert_lo > L->expert_hi) return MAYA_ERR_ARG;

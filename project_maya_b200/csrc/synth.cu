@@ -346,7 +346,7 @@ using namespace maya;
 
 extern "C" int maya_quantize_weights_host(int type, const float* w, int64_t n_rows, int64_t n_cols, void* out) {
     const int qk = type_qk(type);
-    if (!qk) return MAYA_ERR_TYPE;
+    if (!type_is_core(type)) return MAYA_ERR_TYPE;      // quantizers exist for Q8_0, Q4_K, IQ2_S, IQ3_S only
     if (!w || !out || n_rows <= 0 || n_cols <= 0 || n_cols % qk) return MAYA_ERR_ARG;
     const int64_t nb = n_rows * (n_cols / qk);
     const int bb = type_bytes(type);
@@ -365,7 +365,7 @@ extern "C" int maya_quantize_weights_host(int type, const float* w, int64_t n_ro
 
 extern "C" int maya_synth_weights(int type, uint64_t seed, float sigma, int64_t n_rows, int64_t n_cols, void* out,
                                   void* stream) {
-    if (!type_qk(type)) return refuse(MAYA_ERR_TYPE);
+    if (!type_is_core(type)) return refuse(MAYA_ERR_TYPE);
     if (!out || n_rows <= 0 || n_cols <= 0 || n_cols % 256) return refuse(MAYA_ERR_ARG);
     const int64_t n_super = n_rows * (n_cols / 256);
     if (n_super > (int64_t) 0x7fffffff * 8) return refuse(MAYA_ERR_LIMIT);

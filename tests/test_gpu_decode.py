@@ -16,6 +16,7 @@ pytestmark = pytest.mark.gpu
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 TYPES = [H.Q8_0, H.Q4_K, H.IQ2_S, H.IQ3_S]
+MORE = list(H.MORE_TYPES)          # Q5_K, Q6_K, IQ4_XS, IQ3_XXS, IQ2_XXS: the staged decode paths
 TOL = 1e-2      # the path's stated tolerance
 TIGHT = 2e-4    # what an implementation with the oracle's integer arithmetic actually reaches
 
@@ -121,7 +122,7 @@ def test_swiglu_q8_1(T, api, oracle):
 
 
 # ------------------------------------------------------------------------------------------------ GEMV
-@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("t", TYPES + MORE)
 @pytest.mark.parametrize("n_in,n_out", [(2048, 1024), (6144, 515), (256, 7)])
 def test_mmvq_matches_oracle(T, api, oracle, t, n_in, n_out):
     w = H.constructed_blocks(t, n_out, n_in, H.rng_for("mv", t, n_in))
@@ -133,7 +134,7 @@ def test_mmvq_matches_oracle(T, api, oracle, t, n_in, n_out):
     assert H.rel_err(y, want) <= TIGHT
 
 
-@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("t", TYPES + MORE)
 def test_mmvq_multi_column_is_single_column_bitwise(T, api, t):
     n_in, n_out = 2048, 300
     w = dev(T, H.constructed_blocks(t, n_out, n_in, H.rng_for("mc", t)))
@@ -224,6 +225,21 @@ def test_gate_up_down_plan(T, api, oracle, t, quantized):
     assert H.rel_err(got, want) <= TIGHT
 
 
+@pytest.mark.parametrize("t", MORE)
+def test_gate_up_down_plan_further_types(T, api, oracle, t):
+    """The plan kernels on the rest of glmf::moe_supported's types (glm_fast.cu:5798-5801): random valid blocks, k = 8,
+    clamped and plain SwiGLU, a skipped entry."""
+    n_embd, n_ff, k = 1024, 512, 8
+    blobs = [expert_blob(t, n_embd, n_ff, i, False) for i in range(k)]
+    w = H.rng_for("pw-more", t).random(k).astype(np.float32)
+    w /= w.sum()
+    x = H.rng_for("px-more", t).standard_normal(n_embd).astype(np.float32)
+    for limit, skip in ((H.INF, ()), (7.0, (2,))):
+        got, _ = run_plan(T, api, t, n_embd, n_ff, blobs, w, x, limit, skip_entries=skip)
+        want = oracle_plan(oracle, t, n_embd, n_ff, blobs, w, x, limit, skip_entries=skip)
+        assert H.rel_err(got, want) <= TIGHT
+
+
 def test_plan_edge_cases(T, api, oracle):
     t, n_embd, n_ff = H.IQ3_S, 512, 256
     blobs = [expert_blob(t, n_embd, n_ff, i, False) for i in range(5)]          # k = 5 < 8
@@ -293,8 +309,7 @@ def run_window(T, api, t, n_embd, n_ff, store, ids, w, x, limit):
     return keep["out"].reshape(n_tok, n_embd), plan_ptr, plan_w, xq, keep
 
 
-@pytest.mark.parametrize("t", TYPES)
-@pytest.mark.parametrize("n_tok", [1, 3, 8, 16])
+@pytest.mark.parametrize("t,n_tok", [(t, n) for t in TYPES for n in (1, 3, 8, 16)] + [(t, n) for t in MORE for n in (3, 8)])
 def test_window_equals_token_by_token_bitwise(T, api, oracle, t, n_tok):
     n_embd, n_ff, E, k = 512, 256, 12, 4
     store = dev(T, np.stack([expert_blob(t, n_embd, n_ff, e, False) for e in range(E)]))
@@ -321,7 +336,7 @@ def test_window_equals_token_by_token_bitwise(T, api, oracle, t, n_tok):
 
 
 # ------------------------------------------------------------------------------------------------ grouped (native) form
-@pytest.mark.parametrize("t", [H.Q4_K, H.IQ2_S])
+@pytest.mark.parametrize("t", [H.Q4_K, H.IQ2_S, H.Q6_K, H.IQ4_XS, H.IQ3_XXS])
 def test_expert_grouped(T, api, oracle, t):
     n_embd, n_ff, n_tok = 512, 256, 6
     blobs = [expert_blob(t, n_embd, n_ff, e, False) for e in range(3)]

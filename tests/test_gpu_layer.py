@@ -504,3 +504,32 @@ def test_fused_layer_exchange_times_out_and_poisons(T, api):
     assert time.time() - t0 < 1.0
     assert layer.error() == 0                                   # the layer's own barrier is not affected
     assert bool((T.ones(4, device="cuda") * 2 == 2).all())
+
+
+@pytest.mark.parametrize("t", list(H.MORE_TYPES))
+def test_layer_with_further_block_types(T, api, oracle, t):
+    """maya_moe_layer_decode on routed experts stored as Q5_K, Q6_K, IQ4_XS, IQ3_XXS or IQ2_XXS (the rest of
+    glmf::moe_supported's table): the staged kernels run, with a Q8_0 shared expert beside them; single tokens against the
+    oracle, and a 5-token window equal to its tokens bit for bit."""
+    n_embd, n_ff, E, k, n_sh = 1024, 512, 12, 4, 256
+    cfg = dict(n_embd=n_embd, n_ff=n_ff, n_expert=E, k=k, gu_type=t, d_type=t, n_ff_sh=n_sh, sh_gu_type=H.Q8_0, sh_d_type=H.Q8_0)
+    rng = H.rng_for("layer-more", t)
+    experts_np = np.stack([H.constructed_expert(t, t, n_embd, n_ff, rng) for _ in range(E)])
+    shared_np = H.constructed_expert(H.Q8_0, H.Q8_0, n_embd, n_sh, rng)
+    experts, shared = dev(T, experts_np), dev(T, shared_np)
+    lc = api.MoeLayerConfig(n_embd, n_ff, E, k, t, t, n_sh, H.Q8_0, H.Q8_0, 7.0)
+    layer = api.MoeLayer(lc, experts, shared)
+    logits = rng.standard_normal((5, E)).astype(np.float32)
+    x = rng.standard_normal((5, n_embd)).astype(np.float32)
+    ids_o, w_o = oracle.router_top10(logits, k)
+    singles = []
+    for i in range(5):
+        ids, w, out = layer.forward(dev(T, logits[i:i + 1]), dev(T, x[i:i + 1]))
+        assert np.array_equal(ids.cpu().numpy()[0], ids_o[i])
+        want = oracle_token(oracle, cfg, experts, shared, ids_o[i], w_o[i], x[i], 7.0)
+        assert H.rel_err(out.cpu().numpy()[0], want) <= 2e-4
+        singles.append(out[0].clone())
+    _, _, win = layer.forward(dev(T, logits), dev(T, x))
+    for i in range(5):
+        assert T.equal(win[i], singles[i])
+    assert layer.error() == 0

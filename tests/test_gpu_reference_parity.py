@@ -247,3 +247,26 @@ def test_prompt_path_c4_full_shape_matches_reference_decode_kernels(T, api, refg
             worst = max(worst, rel(T, ffn[t], want))
     print(f"C4, prompt path vs reference decode kernels on 64 of 4096 tokens: worst {worst:.3g}")
     assert worst <= 5e-2, worst
+
+
+@pytest.mark.parametrize("t", list(H.MORE_TYPES))
+def test_further_block_types_match_reference_kernels(T, api, refgpu, t):
+    """Q5_K, Q6_K, IQ4_XS, IQ3_XXS, IQ2_XXS experts (random valid blocks) through glmf::moe_gate_up / moe_down and through
+    maya_moe_layer_decode's staged kernels, 16 tokens; and the 8-token window against glmf::moe_win_experts."""
+    n_embd, n_ff, E, k = 2048, 1024, 16, 8
+    rng = H.rng_for("ref-more", t)
+    experts = dev(T, np.stack([H.constructed_expert(t, t, n_embd, n_ff, rng) for _ in range(E)]))
+    lc = api.MoeLayerConfig(n_embd, n_ff, E, k, t, t)
+    ours = api.MoeLayer(lc, experts, None)
+    ref = refgpu.RefLayer(refgpu.RefGpu(), n_embd, n_ff, E, k, t, t, H.row_bytes, experts)
+    logits = dev(T, rng.standard_normal((16, E)).astype(np.float32))
+    x = dev(T, rng.standard_normal((16, n_embd)).astype(np.float32))
+    worst = 0.0
+    with T.cuda.stream(T.cuda.Stream()):
+        for i in range(16):
+            ids, w, out = ours.forward(logits[i:i + 1], x[i:i + 1])
+            ids_r, w_r, out_r = ref.forward(logits[i:i + 1], x[i:i + 1])
+            assert T.equal(ids, ids_r)
+            worst = max(worst, rel(T, out[0], out_r))
+    print(f"type {t}: worst relative difference from the reference kernels over 16 tokens: {worst:.3g}")
+    assert worst <= TIGHT, worst

@@ -16,10 +16,32 @@ import helpers as H
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 TYPES = [H.Q8_0, H.Q4_K, H.IQ2_S, H.IQ3_S]
-GGUF_NAME = {H.Q8_0: "Q8_0", H.Q4_K: "Q4_K", H.IQ2_S: "IQ2_S", H.IQ3_S: "IQ3_S"}
+ALL_TYPES = TYPES + list(H.MORE_TYPES)
+GGUF_NAME = {H.Q8_0: "Q8_0", H.Q4_K: "Q4_K", H.IQ2_S: "IQ2_S", H.IQ3_S: "IQ3_S", H.Q5_K: "Q5_K", H.Q6_K: "Q6_K",
+             H.IQ4_XS: "IQ4_XS", H.IQ3_XXS: "IQ3_XXS", H.IQ2_XXS: "IQ2_XXS"}
 
 
-@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("t", H.MORE_TYPES)
+def test_q8_1_dot_of_the_further_types_against_the_float_product(oracle, t):
+    """The q8_1 dots of Q5_K, Q6_K, IQ4_XS, IQ3_XXS, IQ2_XXS decode the same blocks as the dequantizer above (pinned to
+    gguf-py bit for bit), so W . x from the integer path must sit within q8_1's rounding of the float product - a wrong
+    field, sign or scale would show as O(1).  Also: the Python block sizes are the C ones."""
+    rows, K = 32, 2048
+    rng = H.rng_for("more-dot", t)
+    w = H.constructed_blocks(t, rows, K, rng)
+    assert w.shape[1] == oracle.row_bytes(t, K)
+    x = rng.standard_normal((3, K)).astype(np.float32)
+    wf = oracle.dequantize(t, w, rows * K).reshape(rows, K).astype(np.float64)
+    for i in range(3):
+        got = oracle.mmvq(t, w, oracle.quantize_q8_1(x[i]), K, rows)[0]
+        assert H.rel_l2(got, wf @ x[i].astype(np.float64)) <= 2e-2
+    # linear in the activations' block scales: doubling x doubles every dot exactly (powers of two)
+    a = oracle.mmvq(t, w, oracle.quantize_q8_1(x[0]), K, rows)[0]
+    b = oracle.mmvq(t, w, oracle.quantize_q8_1(2.0 * x[0]), K, rows)[0]
+    assert np.array_equal(2.0 * a, b)
+
+
+@pytest.mark.parametrize("t", ALL_TYPES)
 def test_dequantize_matches_gguf_py(oracle, t):
     from gguf import GGMLQuantizationType, quants
     blocks = H.constructed_blocks(t, 16, 1024, H.rng_for("deq", t))
