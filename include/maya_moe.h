@@ -41,7 +41,7 @@ enum maya_status {
  * maya_moe_layer_decode (which then takes its staged kernels); the prompt-path GEMM refuses them. */
 enum maya_ggml_type {
     MAYA_Q8_0 = 8, MAYA_Q4_K = 12, MAYA_IQ3_S = 21, MAYA_IQ2_S = 22,
-    MAYA_Q5_K = 13, MAYA_Q6_K = 14, MAYA_IQ2_XXS = 16, MAYA_IQ3_XXS = 18, MAYA_IQ4_XS = 23
+    MAYA_Q5_K = 13, MAYA_Q6_K = 14, MAYA_IQ2_XXS = 16, MAYA_IQ3_XXS = 18, MAYA_IQ1_S = 19, MAYA_IQ4_XS = 23
 };
 
 #define MAYA_MAX_K 8            /* plan entries per token (glm_fast.hpp:341) */

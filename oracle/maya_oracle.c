@@ -26,11 +26,12 @@
 #define MAYA_GRID_QUAL static const
 #define MAYA_IQ2XXS_GRID MAYA_IQ2XXS_GRID
 #define MAYA_IQ3XXS_GRID MAYA_IQ3XXS_GRID
+#define MAYA_IQ1S_GRID MAYA_IQ1S_GRID
 #include "maya_iq_grids.inc"
 
 #define ORC_API __attribute__((visibility("default")))
 
-enum { T_Q8_0 = 8, T_Q4_K = 12, T_IQ3_S = 21, T_IQ2_S = 22, T_Q5_K = 13, T_Q6_K = 14, T_IQ2_XXS = 16, T_IQ3_XXS = 18, T_IQ4_XS = 23 };
+enum { T_Q8_0 = 8, T_Q4_K = 12, T_IQ3_S = 21, T_IQ2_S = 22, T_Q5_K = 13, T_Q6_K = 14, T_IQ2_XXS = 16, T_IQ3_XXS = 18, T_IQ1_S = 19, T_IQ4_XS = 23 };
 
 /* ------------------------------------------------------------------ small helpers */
 static inline float h2f(uint16_t h) { _Float16 v; memcpy(&v, &h, 2); return (float) v; }
@@ -60,7 +61,7 @@ static float warp_tree_sum(const float* lane) {
 ORC_API int orc_type_block_bytes(int type) {
     switch (type) {
         case T_Q8_0: return 34; case T_Q4_K: return 144; case T_IQ3_S: return 110; case T_IQ2_S: return 82;
-        case T_Q5_K: return 176; case T_Q6_K: return 210; case T_IQ4_XS: return 136; case T_IQ3_XXS: return 98; case T_IQ2_XXS: return 66;
+        case T_Q5_K: return 176; case T_Q6_K: return 210; case T_IQ4_XS: return 136; case T_IQ3_XXS: return 98; case T_IQ2_XXS: return 66; case T_IQ1_S: return 50;
         default: return 0;
     }
 }
@@ -222,6 +223,22 @@ static void dequant_block(int type, const uint8_t* b, float* y) {
                 for (int j = 0; j < 8; ++j) {
                     const float v = db * (float) ((g >> (8 * j)) & 0xFF);
                     y[32 * ib + 8 * l + j] = ((s8 >> j) & 1) ? -v : v;
+                }
+            }
+        }
+    } else if (type == T_IQ1_S) {
+        /* dequantize_row_iq1_s: f16 d | qs[32] | u16 qh[8]: dl = d (2 ((qh >> 12) & 7) + 1), delta = +-0.125 by qh bit 15,
+         * index = qs | ((qh >> 3l) & 7) << 8, y = dl (g + delta) with g in {-1, 0, 1} (the table holds g + 1 in nibbles:
+         * byte j low = value j, high = value j + 4). */
+        const float d = h2f(rd16(b));
+        for (int ib = 0; ib < 8; ++ib) {
+            const int qh = rd16(b + 34 + 2 * ib);
+            const float dl = d * (float) (2 * ((qh >> 12) & 7) + 1), delta = (qh & 0x8000) ? -0.125f : 0.125f;
+            for (int l = 0; l < 4; ++l) {
+                const uint32_t g = MAYA_IQ1S_GRID[b[2 + 4 * ib + l] | (((qh >> (3 * l)) & 7) << 8)];
+                for (int j = 0; j < 8; ++j) {
+                    const int v = (int) ((g >> (8 * (j & 3) + 4 * (j >> 2))) & 0x0F) - 1;
+                    y[32 * ib + 8 * l + j] = dl * ((float) v + delta);
                 }
             }
         }
@@ -388,8 +405,25 @@ static float call_iq2_xxs(const uint8_t* b, const uint8_t* xq, int ib) {
     return h2f(rd16(b)) * h2f(rd16(q8)) * (float) sumi;
 }
 
+/* dot_iq1_s (glm_fast.cu:584-604): sum over the sub-block of (g + 1) q, then d1q (d8 sumi + S8 delta) with S8 the q8_1
+ * block's stored sum of the unquantized activations and delta = -1 + 1/8 (- 1/4 when qh bit 15 is set). */
+static float call_iq1_s(const uint8_t* b, const uint8_t* xq, int ib) {
+    const int qh = rd16(b + 34 + 2 * ib);
+    const uint8_t* q8 = xq + 36 * ib;
+    int sumi = 0;
+    for (int l = 0; l < 4; ++l) {
+        const uint32_t g = MAYA_IQ1S_GRID[b[2 + 4 * ib + l] | (((qh >> (3 * l)) & 7) << 8)];
+        for (int j = 0; j < 8; ++j)
+            sumi += (int) ((g >> (8 * (j & 3) + 4 * (j >> 2))) & 0x0F) * (int) (int8_t) q8[4 + 8 * l + j];
+    }
+    const float d1q = h2f(rd16(b)) * (float) (2 * ((qh >> 12) & 7) + 1);
+    const float delta = (qh & 0x8000) ? -1.125f : -0.875f;
+    return d1q * (h2f(rd16(q8)) * (float) sumi + h2f(rd16(q8 + 2)) * delta);
+}
+
 static float call_dot(int type, const uint8_t* blk, const uint8_t* xq, int c) {
     switch (type) {
+        case T_IQ1_S: return call_iq1_s(blk, xq, c);
         case T_Q5_K: return call_q5_K(blk, xq, c);
         case T_Q6_K: return call_q6_K(blk, xq, c);
         case T_IQ4_XS: return call_iq4_xs(blk, xq, c);

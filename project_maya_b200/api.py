@@ -18,10 +18,10 @@ from . import _lib
 from ._lib import ExpertLayout, HcPostArgs, MmqProduct, MoeLayerDesc, MoePlan, MoeWin
 
 Q8_0, Q4_K, IQ3_S, IQ2_S = 8, 12, 21, 22
-Q5_K, Q6_K, IQ2_XXS, IQ3_XXS, IQ4_XS = 13, 14, 16, 18, 23      # staged decode paths only (see maya_ggml_type in the header)
-_BLOCK = {Q8_0: 32, Q4_K: 256, IQ3_S: 256, IQ2_S: 256, Q5_K: 256, Q6_K: 256, IQ2_XXS: 256, IQ3_XXS: 256, IQ4_XS: 256}   # values per GGUF block
+Q5_K, Q6_K, IQ2_XXS, IQ3_XXS, IQ1_S, IQ4_XS = 13, 14, 16, 18, 19, 23      # staged decode paths only (see maya_ggml_type in the header)
+_BLOCK = {Q8_0: 32, Q4_K: 256, IQ3_S: 256, IQ2_S: 256, Q5_K: 256, Q6_K: 256, IQ2_XXS: 256, IQ3_XXS: 256, IQ4_XS: 256, IQ1_S: 256}   # values per GGUF block
 TYPE_NAMES = {Q8_0: "Q8_0", Q4_K: "Q4_K", IQ3_S: "IQ3_S", IQ2_S: "IQ2_S", Q5_K: "Q5_K", Q6_K: "Q6_K", IQ2_XXS: "IQ2_XXS",
-              IQ3_XXS: "IQ3_XXS", IQ4_XS: "IQ4_XS"}
+              IQ3_XXS: "IQ3_XXS", IQ4_XS: "IQ4_XS", IQ1_S: "IQ1_S"}
 STATUS = {0: "ok", -1: "bad argument", -2: "unsupported ggml type", -3: "CUDA launch failed", -4: "beyond a limit",
           -5: "no sm_100 device"}
 INF = float("inf")

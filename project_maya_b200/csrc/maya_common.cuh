@@ -36,6 +36,8 @@ template<> struct Fmt<MAYA_Q6_K> { static constexpr int qk = 256, bytes = 210, t
 template<> struct Fmt<MAYA_IQ4_XS> { static constexpr int qk = 256, bytes = 136, tab_words = 0; };
 template<> struct Fmt<MAYA_IQ3_XXS> { static constexpr int qk = 256, bytes = 98, tab_words = 256; };
 template<> struct Fmt<MAYA_IQ2_XXS> { static constexpr int qk = 256, bytes = 66, tab_words = 512; };
+// IQ1_S  50 B/256: f16 d | u8 qs[32] | u16 qh[8]
+template<> struct Fmt<MAYA_IQ1_S> { static constexpr int qk = 256, bytes = 50, tab_words = 2048; };
 
 __host__ __device__ inline int type_bytes(int t) {
     switch (t) {
@@ -48,6 +50,7 @@ __host__ __device__ inline int type_bytes(int t) {
         case MAYA_IQ4_XS: return 136;
         case MAYA_IQ3_XXS: return 98;
         case MAYA_IQ2_XXS: return 66;
+        case MAYA_IQ1_S: return 50;
         default: return 0;
     }
 }

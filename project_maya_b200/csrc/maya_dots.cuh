@@ -1,5 +1,5 @@
 // maya_dots.cuh - the quantized dot products: GGUF weight blocks (Q8_0, Q4_K, IQ2_S, IQ3_S; Q5_K, Q6_K, IQ4_XS, IQ3_XXS,
-// IQ2_XXS) against q8_1 activations.
+// IQ2_XXS, IQ1_S) against q8_1 activations.
 //
 // Integer semantics follow llama.cpp's vec_dot_*_q8_1 as the reference transcribes them (per 32-value sub-block:
 // exact int8 dot, IQ2_S's (s0*l0 + s1*l1 + (s0+s1)/2)/4 with truncating division, IQ3_S's sum * (1 + 2*scale), Q4_K's
@@ -42,6 +42,9 @@ __device__ __forceinline__ XCols xcols_carve(uint8_t* smem, int nblk, int ncols,
 }
 
 // Stage `ncols` q8_1 columns (col_stride bytes apart in global memory) into the SoA form.  All threads of the block.
+// SUM_F16: the `isum` slot takes the block's stored f16 sum of the unquantized values (as float bits) instead of the integer
+// sum of its quants - what IQ1_S's dot needs (its constant term multiplies that sum) and no other type of a launch reads.
+template<bool SUM_F16 = false>
 __device__ __forceinline__ void xcols_stage(const uint8_t* xq, size_t col_stride, int nblk, int ncols, int4* q, float* d,
                                             int* isum) {
     const int total = nblk * ncols;
@@ -53,10 +56,14 @@ __device__ __forceinline__ void xcols_stage(const uint8_t* xq, size_t col_stride
         const int c = b / nblk, kb = b - c * nblk;
         const uint8_t* src = xq + (size_t) c * col_stride + (size_t) kb * kQ81Bytes;
         d[b] = ld_f16(src);
-        int s = 0;
+        if constexpr (SUM_F16) {
+            isum[b] = __float_as_int(ld_f16(src + 2));
+        } else {
+            int s = 0;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) s = __dp4a(*(const int*) (src + 4 + 4 * w), 0x01010101, s);
-        isum[b] = s;
+            for (int w = 0; w < 8; ++w) s = __dp4a(*(const int*) (src + 4 + 4 * w), 0x01010101, s);
+            isum[b] = s;
+        }
     }
 }
 
@@ -381,6 +388,33 @@ template<> struct Dec<MAYA_IQ2_XXS> {
     }
 };
 
+// IQ1_S: a call = sub-block ib: four 11-bit codebook indices (8 values in {-1, 0, 1} each, kept as value + 1 in nibbles),
+// one 3-bit scale and the sign of the +-1/8 shift.  sum((g + delta) x) = sum((g + 1) q) d8 + (delta - 1) * S with S the
+// q8_1 block's stored sum of the unquantized activations (staged into the isum slot: xcols_stage<true>).
+template<> struct Dec<MAYA_IQ1_S> {
+    static constexpr int cpb = 8, xblk = 1;
+    int w[8];
+    float d1q, delta;
+    __device__ __forceinline__ void load(const uint8_t* blk, int c, const uint32_t* tab) {
+        const uint32_t qs = ld_u32_a2(blk + 2 + 4 * c), qh = ld_u16(blk + 34 + 2 * c);
+        d1q = ld_f16(blk) * (float) (2 * ((qh >> 12) & 7) + 1);
+        delta = (qh & 0x8000u) ? -1.125f : -0.875f;
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const uint32_t g = tab[((qs >> (8 * l)) & 0xFF) | (((qh >> (3 * l)) & 7) << 8)];
+            w[2 * l] = (int) (g & 0x0F0F0F0Fu);
+            w[2 * l + 1] = (int) ((g >> 4) & 0x0F0F0F0Fu);
+        }
+    }
+    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
+        const XQ v = xq_load(x, col, xb);
+        int s = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s = __dp4a(w[i], v.u[i], s);
+        return __fmul_rn(d1q, __fadd_rn(__fmul_rn(v.d, (float) s), __fmul_rn(__int_as_float(v.isum), delta)));
+    }
+};
+
 // ---------------------------------------------------------------- codebooks
 // One device copy per translation unit (no relocatable device code needed); generated at build time.
 #define MAYA_GRID_QUAL static __device__ const
@@ -388,7 +422,9 @@ template<> struct Dec<MAYA_IQ2_XXS> {
 #define MAYA_IQ3S_GRID g_iq3s_grid
 #define MAYA_IQ2XXS_GRID g_iq2xxs_grid
 #define MAYA_IQ3XXS_GRID g_iq3xxs_grid
+#define MAYA_IQ1S_GRID g_iq1s_grid
 #include "generated/maya_iq_grids.inc"
+#undef MAYA_IQ1S_GRID
 #undef MAYA_IQ2S_GRID
 #undef MAYA_IQ3S_GRID
 #undef MAYA_IQ2XXS_GRID
@@ -398,7 +434,8 @@ template<> struct Dec<MAYA_IQ2_XXS> {
 template<int T> __device__ __forceinline__ void load_tab(uint32_t* s_tab) {
     if constexpr (Fmt<T>::tab_words > 0) {
         const uint32_t* src = T == MAYA_IQ2_S ? (const uint32_t*) g_iq2s_grid : T == MAYA_IQ3_S ? (const uint32_t*) g_iq3s_grid
-                              : T == MAYA_IQ2_XXS ? (const uint32_t*) g_iq2xxs_grid : (const uint32_t*) g_iq3xxs_grid;
+                              : T == MAYA_IQ2_XXS ? (const uint32_t*) g_iq2xxs_grid : T == MAYA_IQ1_S ? (const uint32_t*) g_iq1s_grid
+                              : (const uint32_t*) g_iq3xxs_grid;
         for (int i = threadIdx.x; i < Fmt<T>::tab_words; i += blockDim.x) s_tab[i] = src[i];
     }
 }

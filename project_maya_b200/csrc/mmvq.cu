@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(kMvWarps * 32) mmvq_kernel(const uint8_t* __re
     const int nblk = n_in / 32;
     const XCols x = xcols_carve(s_raw + Fmt<T>::tab_words * 4, nblk, ncols, &xq_q, &xq_d, &xq_s);
     load_tab<T>(s_tab);
-    xcols_stage(xq, (size_t) nblk * kQ81Bytes, nblk, ncols, xq_q, xq_d, xq_s);
+    xcols_stage<T == MAYA_IQ1_S>(xq, (size_t) nblk * kQ81Bytes, nblk, ncols, xq_q, xq_d, xq_s);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t rb = row_bytes(T, n_in);
@@ -84,6 +84,7 @@ extern "C" int maya_mmvq(int type, const void* w, const void* xq, float* y, int 
         case MAYA_Q6_K: return launch_mmvq_cols<MAYA_Q6_K>(w, xq, y, n_in, n_out, ncols, s);
         case MAYA_IQ4_XS: return launch_mmvq_cols<MAYA_IQ4_XS>(w, xq, y, n_in, n_out, ncols, s);
         case MAYA_IQ3_XXS: return launch_mmvq_cols<MAYA_IQ3_XXS>(w, xq, y, n_in, n_out, ncols, s);
-        default: return launch_mmvq_cols<MAYA_IQ2_XXS>(w, xq, y, n_in, n_out, ncols, s);
+        case MAYA_IQ2_XXS: return launch_mmvq_cols<MAYA_IQ2_XXS>(w, xq, y, n_in, n_out, ncols, s);
+        default: return launch_mmvq_cols<MAYA_IQ1_S>(w, xq, y, n_in, n_out, ncols, s);
     }
 }

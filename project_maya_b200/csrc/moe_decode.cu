@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(kGuWarps * 32) gate_up_kernel(Groups G, int n_
         __syncthreads();   // the previous pass is done with the staged columns and s_g / s_u
         for (int c = 0; c < nc; ++c) {
             const int tok = G.tok(eb + c);
-            xcols_stage(xq + (size_t) tok * xq_stride, 0, nblk, 1, q + (size_t) 2 * c * nblk, d + (size_t) c * nblk,
+            xcols_stage<T == MAYA_IQ1_S>(xq + (size_t) tok * xq_stride, 0, nblk, 1, q + (size_t) 2 * c * nblk, d + (size_t) c * nblk,
                         is + (size_t) c * nblk);
         }
         __syncthreads();
@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(kDownWarps * 32) down_plan_kernel(maya_moe_pla
     const int nblk = n_ff / 32;
     const XCols x = xcols_carve(s_raw + Fmt<T>::tab_words * 4, nblk, k, &q, &d, &is);
     load_tab<T>(s_tab);
-    xcols_stage(hq, (size_t) nblk * kQ81Bytes, nblk, k, q, d, is);
+    xcols_stage<T == MAYA_IQ1_S>(hq, (size_t) nblk * kQ81Bytes, nblk, k, q, d, is);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int r0 = (int) blockIdx.x * kDownRows + warp * kDownRowsPerWarp;
@@ -319,7 +319,7 @@ __global__ void __launch_bounds__(kDownWarps * 32) down_groups_kernel(Groups G, 
         __syncthreads();
         for (int c = 0; c < nc; ++c) {
             const int dst = G.slot(eb + c);
-            xcols_stage(hq + (size_t) dst * nblk * kQ81Bytes, 0, nblk, 1, q + (size_t) 2 * c * nblk, d + (size_t) c * nblk,
+            xcols_stage<T == MAYA_IQ1_S>(hq + (size_t) dst * nblk * kQ81Bytes, 0, nblk, 1, q + (size_t) 2 * c * nblk, d + (size_t) c * nblk,
                         is + (size_t) c * nblk);
         }
         __syncthreads();
@@ -553,6 +553,7 @@ int launch_gate_up_mixed_u(int u_type, const Groups& G, int n_groups_grid, int n
         case MAYA_IQ4_XS: return CALL(MAYA_IQ4_XS);       \
         case MAYA_IQ3_XXS: return CALL(MAYA_IQ3_XXS);     \
         case MAYA_IQ2_XXS: return CALL(MAYA_IQ2_XXS);     \
+        case MAYA_IQ1_S: return CALL(MAYA_IQ1_S);         \
         default: return refuse(MAYA_ERR_TYPE);            \
     }
 

@@ -4,11 +4,11 @@ from __future__ import annotations
 import numpy as np
 
 Q8_0, Q4_K, IQ3_S, IQ2_S = 8, 12, 21, 22
-Q5_K, Q6_K, IQ2_XXS, IQ3_XXS, IQ4_XS = 13, 14, 16, 18, 23            # staged decode paths only
+Q5_K, Q6_K, IQ2_XXS, IQ3_XXS, IQ1_S, IQ4_XS = 13, 14, 16, 18, 19, 23   # staged decode paths only
 BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), IQ3_S: (256, 110), IQ2_S: (256, 82),
-         Q5_K: (256, 176), Q6_K: (256, 210), IQ2_XXS: (256, 66), IQ3_XXS: (256, 98), IQ4_XS: (256, 136)}
+         Q5_K: (256, 176), Q6_K: (256, 210), IQ2_XXS: (256, 66), IQ3_XXS: (256, 98), IQ4_XS: (256, 136), IQ1_S: (256, 50)}
 CORE_TYPES = (Q8_0, Q4_K, IQ2_S, IQ3_S)
-MORE_TYPES = (Q5_K, Q6_K, IQ4_XS, IQ3_XXS, IQ2_XXS)
+MORE_TYPES = (Q5_K, Q6_K, IQ4_XS, IQ3_XXS, IQ2_XXS, IQ1_S)
 INF = float("inf")
 
 # name -> (n_embd, n_ff, n_expert, k, gu/d type, shared (n_ff_sh, type) or None, activation dtype, tokens per step)
@@ -93,7 +93,7 @@ def constructed_blocks(t: int, n_rows: int, n_cols: int, rng: np.random.Generato
     nb = n_rows * (n_cols // qk)
     b = rng.integers(0, 256, size=(nb, bb), dtype=np.uint8)
     lo, hi = {Q8_0: (2e-4, 6e-4), Q4_K: (1e-4, 4e-4), IQ2_S: (2e-3, 6e-3), IQ3_S: (2e-3, 6e-3), Q5_K: (5e-5, 2e-4),
-              Q6_K: (1e-5, 3e-5), IQ4_XS: (1e-5, 3e-5), IQ3_XXS: (2e-4, 6e-4), IQ2_XXS: (2e-4, 6e-4)}[t]
+              Q6_K: (1e-5, 3e-5), IQ4_XS: (1e-5, 3e-5), IQ3_XXS: (2e-4, 6e-4), IQ2_XXS: (2e-4, 6e-4), IQ1_S: (2e-3, 6e-3)}[t]
     d_at = 208 if t == Q6_K else 0                        # Q6_K keeps its super-scale at the end of the block
     b[:, d_at:d_at + 2] = rng.uniform(lo, hi, size=nb).astype(np.float16).view(np.uint8).reshape(nb, 2)
     if t in (Q4_K, Q5_K):

@@ -18,7 +18,7 @@ GOLDEN = Path(__file__).resolve().parent / "golden"
 TYPES = [H.Q8_0, H.Q4_K, H.IQ2_S, H.IQ3_S]
 ALL_TYPES = TYPES + list(H.MORE_TYPES)
 GGUF_NAME = {H.Q8_0: "Q8_0", H.Q4_K: "Q4_K", H.IQ2_S: "IQ2_S", H.IQ3_S: "IQ3_S", H.Q5_K: "Q5_K", H.Q6_K: "Q6_K",
-             H.IQ4_XS: "IQ4_XS", H.IQ3_XXS: "IQ3_XXS", H.IQ2_XXS: "IQ2_XXS"}
+             H.IQ4_XS: "IQ4_XS", H.IQ3_XXS: "IQ3_XXS", H.IQ2_XXS: "IQ2_XXS", H.IQ1_S: "IQ1_S"}
 
 
 @pytest.mark.parametrize("t", H.MORE_TYPES)
