@@ -109,7 +109,10 @@ __device__ __forceinline__ bool grid_barrier(unsigned* sync, unsigned epoch, int
     return *s_ok != 0;
 }
 
-template<int T, int TS>
+// RT: the router - 0 softmax, 1 sigmoid.  A template parameter, not a branch on A.router: with both routers compiled into
+// one kernel the softmax layer's routing phase ran 2 us longer (the 64-register cap of a 1024-thread block is shared by
+// everything the phase may call).
+template<int T, int TS, int RT>
 __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArgs A) {
     extern __shared__ __align__(16) uint8_t s_raw[];
     __shared__ FusedShared sh;
@@ -147,15 +150,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     if (tid < kRouteThreads) {
         using RS = NamedSync<1, kRouteThreads>;
         const int per = (A.n_expert + kRouteThreads - 1) / kRouteThreads;
-        if (A.router == 1) {
+        if constexpr (RT == 1) {
             if (per <= 1) route_sigmoid<1, RS>(A.logits, A.router_bias, A.n_expert, k, A.router_w_scale, A.router_norm_w, tid, kRouteThreads, sh.route);
             else if (per <= 2) route_sigmoid<2, RS>(A.logits, A.router_bias, A.n_expert, k, A.router_w_scale, A.router_norm_w, tid, kRouteThreads, sh.route);
             else if (per <= 4) route_sigmoid<4, RS>(A.logits, A.router_bias, A.n_expert, k, A.router_w_scale, A.router_norm_w, tid, kRouteThreads, sh.route);
             else route_sigmoid<8, RS>(A.logits, A.router_bias, A.n_expert, k, A.router_w_scale, A.router_norm_w, tid, kRouteThreads, sh.route);
-        } else if (per <= 1) route_softmax<1, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
-        else if (per <= 2) route_softmax<2, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
-        else if (per <= 4) route_softmax<4, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
-        else route_softmax<8, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
+        } else {
+            if (per <= 1) route_softmax<1, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
+            else if (per <= 2) route_softmax<2, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
+            else if (per <= 4) route_softmax<4, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
+            else route_softmax<8, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
+        }
         if (tid < k) {
             const int e = sh.route.ids[tid];
             sh.w[tid] = sh.route.val[tid];
@@ -397,8 +402,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     }
 }
 
-template<int T, int TS>
-int launch_fused(const FusedArgs& A, cudaStream_t s) {
+template<int T, int TS, int RT>
+int launch_fused_rt(const FusedArgs& A, cudaStream_t s) {
     // per instantiation: the device and dynamic shared-memory size the attribute was last set for, and whether the
     // programmatic-serialization attribute is in use (1), was refused by the driver (0) or has not been tried (-1)
     static std::atomic<int> attr_dev{-1}, pdl{-1};
@@ -417,7 +422,7 @@ int launch_fused(const FusedArgs& A, cudaStream_t s) {
         cached_dev = dev;
     }
     if (attr_dev.load() != dev || attr_smem.load() != smem) {
-        if (cudaFuncSetAttribute(moe_layer_t1_kernel<T, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(moe_layer_t1_kernel<T, TS, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess)
             return note_launch("fused smem attribute");
         attr_dev.store(dev);
         attr_smem.store(smem);
@@ -442,15 +447,20 @@ int launch_fused(const FusedArgs& A, cudaStream_t s) {
         at[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = at;
         cfg.numAttrs = 2;
-        const cudaError_t e = cudaLaunchKernelExC(&cfg, (const void*) moe_layer_t1_kernel<T, TS>, params);
+        const cudaError_t e = cudaLaunchKernelExC(&cfg, (const void*) moe_layer_t1_kernel<T, TS, RT>, params);
         if (e == cudaSuccess) { pdl.store(1); return note_launch("moe_layer_t1"); }
         // only "this attribute / combination is not supported" turns the attribute off; any other failure is the launch's
         if (e != cudaErrorNotSupported && e != cudaErrorInvalidValue) return note_launch("moe_layer_t1");
         cudaGetLastError();
         pdl.store(0);
     }
-    cudaLaunchCooperativeKernel((const void*) moe_layer_t1_kernel<T, TS>, dim3(grid), dim3(kFusedThreads), params, smem, s);
+    cudaLaunchCooperativeKernel((const void*) moe_layer_t1_kernel<T, TS, RT>, dim3(grid), dim3(kFusedThreads), params, smem, s);
     return note_launch("moe_layer_t1");
+}
+
+template<int T, int TS>
+int launch_fused(const FusedArgs& A, cudaStream_t s) {
+    return A.router == 1 ? launch_fused_rt<T, TS, 1>(A, s) : launch_fused_rt<T, TS, 0>(A, s);
 }
 
 }  // namespace
