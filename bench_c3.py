@@ -88,6 +88,28 @@ def run(torch, api) -> dict:
                         "kernels": "win_group + gate_up_kernel + down_groups_kernel + win_combine_kernel per window"},
            "error": layer.error()}
 
+    # ---- the same windows through the prompt path (tensor-core grouped product over f16 operands: within 1e-2 of the
+    #      window kernels, not bit-identical to them) - where the crossover between the two paths lies at this batch
+    pf = api.MoePrefill(lc, experts, max_tokens=T)
+    pf_out = torch.empty((N_WIN * T, Hd), dtype=torch.float32, device="cuda")
+
+    def prompt_path():
+        for i in range(N_WIN):
+            sl = slice(i * T, (i + 1) * T)
+            pf_out[sl].copy_(pf.forward(logits[sl], x[sl])[2])
+
+    with torch.cuda.stream(stream):
+        prompt_path()
+    stream.synchronize()
+    g1 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g1, stream=stream):
+        prompt_path()
+    us_pf = _median_ms(torch, stream, g1.replay) * 1e3 / N_WIN
+    res["prompt_path"] = {"us_per_step": us_pf, "tok_s_layer": T * 1e6 / us_pf, "hbm_gbs": bytes_step / us_pf / 1e3,
+                          "frac": bytes_step / us_pf / 1e3 / peak, "launch": f"CUDA graph of {N_WIN} x api.MoePrefill.forward",
+                          "max_rel_diff_from_window_kernels": float((pf_out.double() - out.double()).abs().max() / out.double().abs().max()),
+                          "error": pf.error()}
+
     # ---- the reference's window kernel on the same table and tokens
     from oracle import ref_gpu
     if not ref_gpu.available():

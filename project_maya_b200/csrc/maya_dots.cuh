@@ -119,8 +119,7 @@ template<> struct Dec<MAYA_Q8_0> {
 #pragma unroll
         for (int i = 0; i < 8; ++i) w[i] = (int) __byte_perm(W[i], W[i + 1], sel);
     }
-    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
-        const XQ v = xq_load(x, col, xb);
+    __device__ __forceinline__ float dot(const XQ& v, const XQ&) const {
         int s = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) s = __dp4a(w[i], v.u[i], s);
@@ -153,8 +152,7 @@ template<> struct Dec<MAYA_Q4_K> {
 #pragma unroll
         for (int i = 0; i < 8; ++i) { lo[i] = qq[i] & 0x0F0F0F0F; hi[i] = (qq[i] >> 4) & 0x0F0F0F0F; }
     }
-    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
-        const XQ a = xq_load(x, col, xb), b = xq_load(x, col, xb + 1);
+    __device__ __forceinline__ float dot(const XQ& a, const XQ& b) const {
         int s0 = 0, s1 = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) { s0 = __dp4a(lo[i], a.u[i], s0); s1 = __dp4a(hi[i], b.u[i], s1); }
@@ -185,8 +183,7 @@ template<> struct Dec<MAYA_IQ2_S> {
             w[2 * l + 1] = apply_sign4(g.y, sign_mask4(s >> 4));
         }
     }
-    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
-        const XQ v = xq_load(x, col, xb);
+    __device__ __forceinline__ float dot(const XQ& v, const XQ&) const {
         int s0 = 0, s1 = 0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) { s0 = __dp4a(w[i], v.u[i], s0); s1 = __dp4a(w[4 + i], v.u[4 + i], s1); }
@@ -212,8 +209,7 @@ template<> struct Dec<MAYA_IQ3_S> {
             w[l] = apply_sign4(tab[idx], sign_mask4((sg >> (4 * l)) & 0x0F));
         }
     }
-    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
-        const XQ v = xq_load(x, col, xb);
+    __device__ __forceinline__ float dot(const XQ& v, const XQ&) const {
         int s = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) s = __dp4a(w[i], v.u[i], s);
@@ -251,8 +247,7 @@ template<> struct Dec<MAYA_Q5_K> {
             hi[i] = ((qq[i] >> 4) & 0x0F0F0F0F) | (((hh[i] >> (2 * j + 1)) & 0x01010101) << 4);
         }
     }
-    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
-        const XQ a = xq_load(x, col, xb), b = xq_load(x, col, xb + 1);
+    __device__ __forceinline__ float dot(const XQ& a, const XQ& b) const {
         int s0 = 0, s1 = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) { s0 = __dp4a(lo[i], a.u[i], s0); s1 = __dp4a(hi[i], b.u[i], s1); }
@@ -286,8 +281,7 @@ template<> struct Dec<MAYA_Q6_K> {
             w[i] = (int) ((((l4 | h2) | 0x80808080u) - 0x20202020u) ^ 0x80808080u);
         }
     }
-    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
-        const XQ v = xq_load(x, col, xb);
+    __device__ __forceinline__ float dot(const XQ& v, const XQ&) const {
         int s0 = 0, s1 = 0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) { s0 = __dp4a(w[i], v.u[i], s0); s1 = __dp4a(w[4 + i], v.u[4 + i], s1); }
@@ -321,8 +315,7 @@ template<> struct Dec<MAYA_IQ4_XS> {
             w[4 + i] = (int) __byte_perm(a, b, 0x7531);                    // the high nibbles': values 16 + 4i ..
         }
     }
-    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
-        const XQ v = xq_load(x, col, xb);
+    __device__ __forceinline__ float dot(const XQ& v, const XQ&) const {
         int s = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) s = __dp4a(w[i], v.u[i], s);
@@ -351,8 +344,7 @@ template<> struct Dec<MAYA_IQ3_XXS> {
             w[2 * l + 1] = apply_sign4(tab[qa >> 8], sign_mask4(s8 >> 4));
         }
     }
-    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
-        const XQ v = xq_load(x, col, xb);
+    __device__ __forceinline__ float dot(const XQ& v, const XQ&) const {
         int s = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) s = __dp4a(w[i], v.u[i], s);
@@ -379,8 +371,7 @@ template<> struct Dec<MAYA_IQ2_XXS> {
             w[2 * l + 1] = apply_sign4(g.y, sign_mask4(s8 >> 4));
         }
     }
-    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
-        const XQ v = xq_load(x, col, xb);
+    __device__ __forceinline__ float dot(const XQ& v, const XQ&) const {
         int s = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) s = __dp4a(w[i], v.u[i], s);
@@ -406,8 +397,7 @@ template<> struct Dec<MAYA_IQ1_S> {
             w[2 * l + 1] = (int) ((g >> 4) & 0x0F0F0F0Fu);
         }
     }
-    __device__ __forceinline__ float dot(const XCols& x, int col, int xb) const {
-        const XQ v = xq_load(x, col, xb);
+    __device__ __forceinline__ float dot(const XQ& v, const XQ&) const {
         int s = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) s = __dp4a(w[i], v.u[i], s);
@@ -454,16 +444,29 @@ __device__ __forceinline__ void rows_dot(const uint8_t* const* rows, const XCols
     for (int r = 0; r < NR; ++r)
 #pragma unroll
         for (int c = 0; c < NC; ++c) acc[r][c] = 0.0f;
+    // The decoded rows of a pass stay in registers and a column's activation blocks are read from shared memory ONCE for
+    // all of them (the dots were bound by shared-memory wavefronts when every row re-read them);
+    // RP rows a pass: all NR, two for the types whose call spans two q8_1 blocks (twice the registers a row).
+    constexpr int RP = D::xblk == 2 ? (NR < 2 ? NR : 2) : NR;
     for (int k = lane; k < ncalls; k += 32) {
         const int kb = k / D::cpb, ci = k - kb * D::cpb;
         const int xb = kb * (Fmt<T>::qk / 32) + ci * D::xblk;
 #pragma unroll
-        for (int r = 0; r < NR; ++r) {
-            D dec;
-            dec.load(rows[r] + (size_t) kb * Fmt<T>::bytes, ci, tab);
+        for (int r0 = 0; r0 < NR; r0 += RP) {
+            D dec[RP];
+#pragma unroll
+            for (int j = 0; j < RP; ++j)
+                if (r0 + j < NR) dec[j].load(rows[r0 + j] + (size_t) kb * Fmt<T>::bytes, ci, tab);
 #pragma unroll
             for (int c = 0; c < NC; ++c)
-                if (c < ncols) acc[r][c] = __fadd_rn(acc[r][c], dec.dot(x, c, xb));
+                if (c < ncols) {
+                    const XQ a = xq_load(x, c, xb);
+                    XQ b = a;
+                    if constexpr (D::xblk == 2) b = xq_load(x, c, xb + 1);
+#pragma unroll
+                    for (int j = 0; j < RP; ++j)
+                        if (r0 + j < NR) acc[r0 + j][c] = __fadd_rn(acc[r0 + j][c], dec[j].dot(a, b));
+                }
         }
     }
 #pragma unroll

@@ -48,7 +48,7 @@ struct Groups {
 // ------------------------------------------------------------------------------------------------ gate / up
 // grid (n_ff / 32, groups [+ 1 shared-down row of blocks]); block 512.
 template<int T>
-__global__ void __launch_bounds__(kGuWarps * 32) gate_up_kernel(Groups G, int n_groups_grid, int n_embd, int n_ff,
+__global__ void __launch_bounds__(kGuWarps * 32, 2) gate_up_kernel(Groups G, int n_groups_grid, int n_embd, int n_ff,
                                                                 size_t up_off, float limit,
                                                                 const uint8_t* __restrict__ xq, size_t xq_stride,
                                                                 uint8_t* __restrict__ hq,
@@ -83,7 +83,7 @@ __device__ __forceinline__ void shared_down_rows(const uint8_t* sh_down, const u
 }
 
 template<int T>
-__global__ void __launch_bounds__(kGuWarps * 32) gate_up_kernel(Groups G, int n_groups_grid, int n_embd, int n_ff,
+__global__ void __launch_bounds__(kGuWarps * 32, 2) gate_up_kernel(Groups G, int n_groups_grid, int n_embd, int n_ff,
                                                                 size_t up_off, float limit,
                                                                 const uint8_t* __restrict__ xq, size_t xq_stride,
                                                                 uint8_t* __restrict__ hq,
@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(kDownWarps * 32) down_plan_kernel(maya_moe_pla
 // ------------------------------------------------------------------------------------------------ down, group form
 // grid (n_embd / kDownRows, groups): part[dst][row] = down[row] . hq[dst] for every entry of the group (unweighted).
 template<int T>
-__global__ void __launch_bounds__(kDownWarps * 32) down_groups_kernel(Groups G, int n_embd, int n_ff, size_t down_off,
+__global__ void __launch_bounds__(kDownWarps * 32, 4) down_groups_kernel(Groups G, int n_embd, int n_ff, size_t down_off,
                                                                       const uint8_t* __restrict__ hq,
                                                                       float* __restrict__ part) {
     extern __shared__ __align__(16) uint8_t s_raw[];

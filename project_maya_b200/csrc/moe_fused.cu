@@ -135,10 +135,19 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
 
     // Programmatic dependent launch: the next launch on the stream may be set up while this one runs, and this one may
     // have started before the launch in front of it ended.  Nothing of global memory is read or written before
-    // grid_dependency_wait() (only the codebook, a constant of the library, is copied to shared memory before it);
+    // grid_dependency_wait() (only the codebook, a constant of the library, is copied to shared memory before it ...);
     // without the launch attribute both instructions do nothing.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (tid >= kRouteThreads) load_tab_rep<T>(s_tab, tid - kRouteThreads, kFusedThreads - kRouteThreads);
+    // ... and the token's logits and activations are asked into L2 (a prefetch reads nothing into the SM: whatever the
+    // launch in front still writes there is read after the wait, from L2, the point of coherence)
+    if (tid < kRouteThreads) {
+        if (tid * 32 < A.n_expert) asm volatile("prefetch.global.L2 [%0];" ::"l"(A.logits + tid * 32));
+    } else {
+        const int t2 = tid - kRouteThreads;
+        const size_t xb = (size_t) n_embd * (A.x_is_bf16 ? 2 : 4);
+        if ((size_t) t2 * 128 < xb) asm volatile("prefetch.global.L2 [%0];" ::"l"((const uint8_t*) A.x + (size_t) t2 * 128));
+        load_tab_rep<T>(s_tab, t2, kFusedThreads - kRouteThreads);
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (tid == 0) {
         sh.epoch = *(volatile unsigned*) &A.sync[1];
