@@ -256,7 +256,7 @@ struct Pipe {                       // static shared memory of a block
     uint64_t final;
     uint32_t tmem;
     int fail;
-    int scan[kMmqThreads];
+    int scan[2];                     // the block's (matrix, row group), found by warp 0
 };
 
 __device__ __forceinline__ bool failed(const Pipe& P) { return *(volatile const int*) &P.fail != 0; }
@@ -282,41 +282,48 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int NU = kUnits<T>, NB = kBStages<T>;
 
-    // ---- which (matrix, 160-row group) is blockIdx.y: inclusive scan of the per-matrix group counts, kMmqThreads
-    //      matrices at a time; `base` carries the groups of the matrices before
-    int found_e = -1, found_g = 0;
-    {
-        int base = 0;
-        for (int e0 = 0; e0 < A.n && found_e < 0; e0 += kMmqThreads) {
-            const int e = e0 + tid;
-            int cnt = 0;
-            if (e < A.n) {
+    // ---- which (matrix, 160-row group) is blockIdx.y: ONE warp scans the per-matrix group counts (each lane the counts
+    //      of a run of consecutive matrices, an exclusive warp scan of the runs' sums, then the lane whose run holds the
+    //      wanted group walks it), 1024 matrices a round, and leaves the answer in shared memory - one block barrier
+    //      instead of the twenty a block-wide scan needs, on a path every tile and every surplus block of the grid takes
+    if (warp == 0) {
+        int found_e = -1, found_g = 0, base = 0;
+        const int want_all = (int) blockIdx.y;
+        for (int e0 = 0; e0 < A.n && found_e < 0; e0 += 1024) {
+            const int per = (min(A.n - e0, 1024) + 31) >> 5;          // matrices a lane (<= 32)
+            const int lo = e0 + lane * per, hi = min(lo + per, min(A.n, e0 + 1024));
+            int mine = 0;
+            for (int e = lo; e < hi; ++e) {
                 const int be = A.expert_map ? A.expert_map[e] : e;
-                cnt = (A.bounds[be + 1] - A.bounds[be] + TN - 1) / TN;
+                mine += (A.bounds[be + 1] - A.bounds[be] + TN - 1) / TN;
             }
-            P.scan[tid] = cnt;
-            __syncthreads();
-            for (int o = 1; o < kMmqThreads; o <<= 1) {
-                const int v = tid >= o ? P.scan[tid - o] : 0;
-                __syncthreads();
-                P.scan[tid] += v;
-                __syncthreads();
+            int incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += v;
             }
-            const int total = P.scan[kMmqThreads - 1];
-            const int want = (int) blockIdx.y - base;
-            if (want < total) {
-                int lo = 0, hi = kMmqThreads - 1;       // the first entry whose inclusive sum exceeds `want`
-                while (lo < hi) {
-                    const int mid = (lo + hi) >> 1;
-                    if (P.scan[mid] > want) hi = mid; else lo = mid + 1;
+            const int total = __shfl_sync(0xFFFFFFFFu, incl, 31);
+            const int want = want_all - base;
+            const unsigned holds = __ballot_sync(0xFFFFFFFFu, want >= incl - mine && want < incl);
+            if (want < total && holds != 0u && lane == __ffs(holds) - 1) {
+                int g = want - (incl - mine);
+                for (int e = lo; e < hi; ++e) {
+                    const int be = A.expert_map ? A.expert_map[e] : e;
+                    const int cnt = (A.bounds[be + 1] - A.bounds[be] + TN - 1) / TN;
+                    if (g < cnt) { found_e = e; found_g = g; break; }
+                    g -= cnt;
                 }
-                found_e = e0 + lo;
-                found_g = want - (lo > 0 ? P.scan[lo - 1] : 0);
+                P.scan[0] = found_e;
+                P.scan[1] = found_g;
             }
+            found_e = __shfl_sync(0xFFFFFFFFu, found_e, holds != 0u && want < total ? __ffs(holds) - 1 : 0);
             base += total;
-            __syncthreads();
         }
+        if (found_e < 0 && lane == 0) P.scan[0] = -1;
     }
+    __syncthreads();
+    const int found_e = P.scan[0], found_g = P.scan[1];
     if (found_e < 0) return;                        // beyond the last group: uniform for the whole block
     const int be = A.expert_map ? A.expert_map[found_e] : found_e;
     const int row0 = A.bounds[be] + found_g * TN;
