@@ -53,7 +53,7 @@ struct FusedShared {
     int ve[MAYA_MAX_K];        // the plan entries this rank computes (blob address != 0), in plan order
     int nv;
     float hbuf[kUnitBatch][32];   // the h values of the (expert, 32-row group) units this block is working on
-    int bar_ok;                   // the grid barrier's verdict, for every thread of the block
+    int bar_ok;                   // the grid barrier's outcome, for every thread of the block
 };
 
 // balanced contiguous split of n rows over nb blocks
@@ -89,7 +89,7 @@ __device__ __forceinline__ void stamp(unsigned* sync, int i) {
 }
 
 // All blocks of the (cooperative) grid meet here.  false in EVERY thread of the block when the wait ran out: thread 0
-// leaves its verdict in shared memory before the closing barrier.
+// leaves the outcome in shared memory before the closing barrier.
 __device__ __forceinline__ bool grid_barrier(unsigned* sync, unsigned epoch, int* s_ok) {
     __syncthreads();
     if (threadIdx.x == 0) {
