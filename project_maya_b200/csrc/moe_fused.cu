@@ -112,7 +112,9 @@ __device__ __forceinline__ bool grid_barrier(unsigned* sync, unsigned epoch, int
 // RT: the router - 0 softmax, 1 sigmoid.  A template parameter, not a branch on A.router: with both routers compiled into
 // one kernel the softmax layer's routing phase ran 2 us longer (the 64-register cap of a 1024-thread block is shared by
 // everything the phase may call).
-template<int T, int TS, int RT>
+// HV: the kernel may cut phase-1 units in halves (decided per launch on the device; the code for it is compiled in only
+// where a rank's units can be that few - in the one-GPU kernel it cost 1 us by its mere presence).
+template<int T, int TS, int RT, bool HV>
 __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArgs A) {
     extern __shared__ __align__(16) uint8_t s_raw[];
     __shared__ FusedShared sh;
@@ -221,6 +223,50 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     {
         const int ng = n_ff / 32, units_r = sh.nv * ng, ng_sh = has_sh ? (A.sh_hi - A.sh_lo) / 32 : 0, U = units_r + ng_sh;
         const size_t rb = row_bytes(T, n_embd);
+        // Fewer units than half the grid (a rank's share at 8 GPUs): a unit is cut into two halves of 16 FFN rows for two
+        // blocks - one weight row a warp - so that twice as many SMs pull rows.  A half leaves its 16 h values as f32 in
+        // the scratch; the block that brings the unit's counter to an odd value found the other half there already and
+        // rounds the 32 values to the unit's q8_1 block (the same 32 values, the same rounding: the same bits).
+        const bool halves = HV && U > 0 && 2 * U <= (int) gridDim.x;
+        if (HV && halves) {
+            float* const hst = (float*) ((uint8_t*) A.h + (size_t) (MAYA_MAX_K + 1) * nblk_h * 40);
+            unsigned* const hcnt = (unsigned*) (hst + (size_t) (MAYA_MAX_K + 1) * nblk_h * 32);
+            if ((int) blockIdx.x < 2 * U) {
+                const int u = (int) blockIdx.x >> 1, half = (int) blockIdx.x & 1;
+                const int fr = 16 * half + (warp >> 1), mat = warp & 1;         // FFN row in the unit; gate (0) or up (1)
+                int e, g;
+                float o[1] = {0.0f};
+                if (u < units_r) {
+                    const int ei = u / ng;
+                    e = sh.ve[ei];
+                    g = u - ei * ng;
+                    const uint8_t* rows[1] = {(const uint8_t*) sh.ptr[e] + (size_t) (mat * n_ff + g * 32 + fr) * rb};
+                    rows_dot1<T, 1>(rows, X, n_embd, lane, s_tab, o);
+                } else {
+                    e = k;
+                    g = A.sh_lo / 32 + (u - units_r);
+                    if constexpr (TS != 0) {
+                        const uint8_t* rows[1] = {A.shared + (size_t) (mat * A.n_ff_sh + g * 32 + fr) * row_bytes(TS, n_embd)};
+                        rows_dot1<TS, 1>(rows, X, n_embd, lane, nullptr, o);
+                    }
+                }
+                if (lane == 0) sh.hbuf[0][warp] = o[0];
+                __syncthreads();
+                if (warp == 0) {
+                    const int slot = e * nblk_h + g;
+                    if (lane < 16) __stcg(&hst[(size_t) slot * 32 + 16 * half + lane], swiglu(sh.hbuf[0][2 * lane], sh.hbuf[0][2 * lane + 1], A.limit));
+                    __threadfence();
+                    __syncwarp();
+                    unsigned old = 0u;
+                    if (lane == 0) old = atomicAdd(&hcnt[slot], 1u);
+                    old = __shfl_sync(0xffffffffu, old, 0);
+                    if (old & 1u) {                                              // the other half is in place
+                        __threadfence();
+                        q8_1_to_smem(__ldcg(&hst[(size_t) slot * 32 + lane]), (int4*) gq, gd, gs, slot, lane);
+                    }
+                }
+            }
+        } else
         for (int u0 = blockIdx.x; u0 < U; u0 += gridDim.x * kUnitBatch) {
             int nu = 0;                                          // units of this batch: u0, u0 + grid, ...
             for (int u = u0; u < U && nu < kUnitBatch; u += gridDim.x) ++nu;
@@ -411,7 +457,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     }
 }
 
-template<int T, int TS, int RT>
+template<int T, int TS, int RT, bool HV>
 int launch_fused_rt(const FusedArgs& A, cudaStream_t s) {
     // per instantiation: the device and dynamic shared-memory size the attribute was last set for, and whether the
     // programmatic-serialization attribute is in use (1), was refused by the driver (0) or has not been tried (-1)
@@ -431,7 +477,7 @@ int launch_fused_rt(const FusedArgs& A, cudaStream_t s) {
         cached_dev = dev;
     }
     if (attr_dev.load() != dev || attr_smem.load() != smem) {
-        if (cudaFuncSetAttribute(moe_layer_t1_kernel<T, TS, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(moe_layer_t1_kernel<T, TS, RT, HV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess)
             return note_launch("fused smem attribute");
         attr_dev.store(dev);
         attr_smem.store(smem);
@@ -456,20 +502,28 @@ int launch_fused_rt(const FusedArgs& A, cudaStream_t s) {
         at[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = at;
         cfg.numAttrs = 2;
-        const cudaError_t e = cudaLaunchKernelExC(&cfg, (const void*) moe_layer_t1_kernel<T, TS, RT>, params);
+        const cudaError_t e = cudaLaunchKernelExC(&cfg, (const void*) moe_layer_t1_kernel<T, TS, RT, HV>, params);
         if (e == cudaSuccess) { pdl.store(1); return note_launch("moe_layer_t1"); }
         // only "this attribute / combination is not supported" turns the attribute off; any other failure is the launch's
         if (e != cudaErrorNotSupported && e != cudaErrorInvalidValue) return note_launch("moe_layer_t1");
         cudaGetLastError();
         pdl.store(0);
     }
-    cudaLaunchCooperativeKernel((const void*) moe_layer_t1_kernel<T, TS, RT>, dim3(grid), dim3(kFusedThreads), params, smem, s);
+    cudaLaunchCooperativeKernel((const void*) moe_layer_t1_kernel<T, TS, RT, HV>, dim3(grid), dim3(kFusedThreads), params, smem, s);
     return note_launch("moe_layer_t1");
 }
 
 template<int T, int TS>
 int launch_fused(const FusedArgs& A, cudaStream_t s) {
-    return A.router == 1 ? launch_fused_rt<T, TS, 1>(A, s) : launch_fused_rt<T, TS, 0>(A, s);
+    if (A.router == 1) return launch_fused_rt<T, TS, 1, false>(A, s);
+    // units of one routed expert + the shared expert's: when even twice that many fit the grid, a rank with few local
+    // experts (or a narrow width slice) may have fewer units than half the blocks
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    static thread_local int c_dev = -1, c_sms = 0;
+    if (c_dev != dev) { cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); c_dev = dev; c_sms = sms; }
+    const int units_min = A.n_ff / 32 + (A.shared != nullptr ? (A.sh_hi - A.sh_lo) / 32 : 0);
+    return 2 * units_min <= c_sms ? launch_fused_rt<T, TS, 0, true>(A, s) : launch_fused_rt<T, TS, 0, false>(A, s);
 }
 
 }  // namespace

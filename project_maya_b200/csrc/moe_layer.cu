@@ -24,7 +24,7 @@ struct Scratch {
     float* sh_gu;                // [T][2 * n_ff_sh]
     uint8_t* sh_hq;              // [T][n_ff_sh/32] q8_1
     float* sh_out;               // [T][n_embd]
-    float* h;                    // [(k + 1)][max(n_ff, n_ff_sh)] f32: the fused single-token kernel's h
+    float* h;                    // the fused single-token kernel's h: q8_1 image, shared-unit halves, counters
     unsigned* sync;              // [16]: the fused kernel's barrier counter, epoch, error word (zero before first use)
     size_t bytes;
 };
@@ -40,7 +40,9 @@ Scratch carve(const maya_moe_layer& L, int T, uint8_t* base) {
     s.sync = (unsigned*) take(16 * sizeof(unsigned));
     {
         const int ld = L.n_ff > L.n_ff_sh ? L.n_ff : L.n_ff_sh;
-        s.h = (float*) take((size_t) (MAYA_MAX_K + 1) * ld * sizeof(float));
+        // per expert and 32-value group of h: the q8_1 image (40 bytes), the f32 halves two blocks leave when a unit is
+        // shared between them (128 bytes) and that unit's arrival counter
+        s.h = (float*) take((size_t) (MAYA_MAX_K + 1) * (ld / 32) * (40 + 128 + 4));
     }
     s.xq = take((size_t) T * (L.n_embd / 32) * kQ81Bytes);
     s.plan_ptr = (unsigned long long*) take((size_t) T * 8 * sizeof(unsigned long long));

@@ -213,10 +213,12 @@ def test_width_sliced_experts_sum_to_whole(T, api, oracle, n_ranks):
 
 
 @pytest.mark.parametrize("t,shared", [(H.Q4_K, False), (H.Q8_0, False), (H.IQ2_S, True), (H.IQ3_S, True), (H.IQ3_S, False)])
-def test_fused_token_kernel_equals_staged_kernels_bitwise(T, api, oracle, t, shared):
+@pytest.mark.parametrize("n_ff", [768, 256])
+def test_fused_token_kernel_equals_staged_kernels_bitwise(T, api, oracle, t, shared, n_ff):
     """One token through the single fused kernel and through the separate launches: the same bits, and the oracle's
-    values.  Odd sizes on purpose: the FFN and output rows do not divide evenly over the blocks."""
-    n_embd, n_ff, n_expert, k = 1024, 768, 20, 6
+    values.  Odd sizes on purpose: the FFN and output rows do not divide evenly over the blocks.  FFN width 256 leaves
+    fewer 32-row units than half the grid: the kernel then cuts every unit in two for two blocks."""
+    n_embd, n_expert, k = 1024, 20, 6
     cfg = dict(n_embd=n_embd, n_ff=n_ff, n_expert=n_expert, k=k, gu_type=t, d_type=t, limit=7.0)
     if shared:
         cfg.update(n_ff_sh=512, sh_gu_type=H.Q8_0, sh_d_type=H.Q8_0)
