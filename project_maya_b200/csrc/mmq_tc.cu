@@ -409,6 +409,25 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             return true;
         };
         [[maybe_unused]] uint4 corr[8];      // Q4_K: the constant terms of the current 8-block chunk (indexed by kb: local memory)
+        // The same in two halves of 32 K-values: the first half's tensor-memory store is under way while the second half
+        // is expanded (the store, its wait and the hand-off were a serial tail of every pair).
+        auto acquire = [&](int kp) -> bool {
+            if (kp >= kSt) {
+                const int pp = kp - kSt;
+                if (!wait_or_fail(P, &P.done[pp & (kDone - 1)], (pp / kDone) & 1)) return false;
+                tc_fence_after();
+            }
+            return true;
+        };
+        auto st_half = [&](int kp, int h, const uint32_t* o16) {
+            tmem_st16(a_lane + (kp % kSt) * 64 + 16 * h, *(const uint32_t(*)[16]) o16);
+        };
+        auto release = [&](int kp) {
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&P.a_full[kp % kSt]);
+        };
         for (int kb = 0; kb < nkb && ok; ++kb) {
             const int u = kb * 4 + slab, slot = u % NU;
             if (!wait_or_fail(P, &P.raw_full[slot], (u / NU) & 1)) { ok = false; break; }
@@ -460,14 +479,13 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                 for (int i = 0; i < 2; ++i) {        // the 64 values of quant pair p: low nibbles, then high nibbles
                     const int p = 2 * i + team;
                     const uint4 qa = *(const uint4*) (rrow + 16 + 32 * p), qb = *(const uint4*) (rrow + 32 + 32 * p);
-                    if (team == 0) {
-                        q4k_stage(qa, qb, 0, S.dl[4 * i], S.nml[4 * i], o);
-                        q4k_stage(qa, qb, 1, S.dl[4 * i + 1], S.nml[4 * i + 1], o + 16);
-                    } else {
-                        q4k_stage(qa, qb, 0, S.dl[4 * i + 2], S.nml[4 * i + 2], o);
-                        q4k_stage(qa, qb, 1, S.dl[4 * i + 3], S.nml[4 * i + 3], o + 16);
-                    }
-                    if (!put(kb * 4 + chunk + p, o)) { ok = false; break; }
+                    const int kp = kb * 4 + chunk + p, sb0 = 4 * i + 2 * team;
+                    q4k_stage(qa, qb, 0, S.dl[sb0], S.nml[sb0], o);
+                    if (!acquire(kp)) { ok = false; break; }
+                    st_half(kp, 0, o);
+                    q4k_stage(qa, qb, 1, S.dl[sb0 + 1], S.nml[sb0 + 1], o + 16);
+                    st_half(kp, 1, o + 16);
+                    release(kp);
                 }
                 if (ok && (chunk & 1) == team && ((kb & 7) == 7 || kb == nkb - 1)) {      // the chunk's correction pair
 #pragma unroll
@@ -478,7 +496,17 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                     ok = put(kb * 4 + chunk + 4, o);
                 }
             } else {
-#define MAYA_Q80_PAIR(PP) if (ok) { q80_stage<2 * (PP)>(rrow, o); q80_stage<2 * (PP) + 1>(rrow, o + 16); ok = put(kb * 4 + (PP), o); }
+#define MAYA_Q80_PAIR(PP)                                                                      \
+    if (ok) {                                                                                  \
+        q80_stage<2 * (PP)>(rrow, o);                                                          \
+        ok = acquire(kb * 4 + (PP));                                                           \
+        if (ok) {                                                                              \
+            st_half(kb * 4 + (PP), 0, o);                                                      \
+            q80_stage<2 * (PP) + 1>(rrow, o + 16);                                             \
+            st_half(kb * 4 + (PP), 1, o + 16);                                                 \
+            release(kb * 4 + (PP));                                                            \
+        }                                                                                      \
+    }
                 if (team == 0) { MAYA_Q80_PAIR(0) MAYA_Q80_PAIR(2) }
                 else { MAYA_Q80_PAIR(1) MAYA_Q80_PAIR(3) }
 #undef MAYA_Q80_PAIR
