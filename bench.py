@@ -427,8 +427,11 @@ def gpu_arm(args) -> None:
         if world == 1 and not args.no_extra:
             del layers[1:]                      # the other workloads bring their own expert tables: make room
             torch.cuda.empty_cache()
+            import bench_c1
             import bench_c3
             import bench_prefill
+            extra["c1"] = bench_c1.run(torch, api)
+            torch.cuda.empty_cache()
             extra["c3"] = bench_c3.run(torch, api)
             torch.cuda.empty_cache()
             pf = bench_prefill.run(4, 3, 1)
@@ -547,7 +550,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-extra", action="store_true", help="skip extra.c3 and extra.prefill_c4 (1 GPU)")
+    ap.add_argument("--no-extra", action="store_true", help="skip extra.c1, extra.c3 and extra.prefill_c4 (1 GPU)")
     ap.add_argument("--no-c5", action="store_true", help="skip the extra.c5 leg (IQ3_S expert-parallel layer, batch 1 and 64)")
     ap.add_argument("--ar", default="peer", choices=["peer", "nccl"], help="N > 1: how the ranks' partial outputs are summed")
     ap.add_argument("--partition", default="width", choices=["width", "expert"],
