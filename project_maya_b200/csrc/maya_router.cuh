@@ -42,6 +42,7 @@ struct RouterShared {
     float val[64];
     float inv;
     double rd[kRouterMaxWarps];
+    alignas(16) unsigned long long cand[kRouterMaxWarps * 8];   // select_rank: every warp's k best keys (k <= 8)
 };
 
 // k rounds of arg-max over `sel` (expert e = j * nt + tid), "greater value, or equal value and lower index" - the
@@ -91,6 +92,49 @@ __device__ __forceinline__ void select_rank(float p, int n_expert, int k, int ti
                                             RouterShared& sh) {
     const unsigned long long mine = ((unsigned long long) __float_as_uint(p) << 32) | (unsigned) (0xffffffffu - (unsigned) tid);
     if (tid < n_expert) keys[tid] = mine;
+    if (k <= 8) {
+        // Two levels: a key's rank among its own warp's 32 keys first; the k best of every warp are the only candidates
+        // for the global k best (whatever beats a global winner is itself a global winner, hence among its warp's k
+        // best), and a candidate's rank among the candidates is its global rank whenever that is below k.  16 + 32
+        // shared-memory reads a thread instead of 128; the ids and their order are the same.
+        for (int i = tid; i < kRouterMaxWarps * 8; i += 32) sh.cand[i] = 0ull;   // (every warp writes all: no assumption on the
+                                                                                 // group's size) a key is never 0: its low word is not
+        Sync::sync();
+        int lr = 0;
+        if (tid < n_expert) {
+            const int w0 = tid & ~31;
+            if (w0 + 32 <= n_expert) {                        // the whole warp's keys exist: eight reads in flight at a time
+                const ulonglong2* k2 = (const ulonglong2*) (keys + w0);
+#pragma unroll
+                for (int j0 = 0; j0 < 16; j0 += 8) {
+                    ulonglong2 o[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o[j] = k2[j0 + j];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) lr += (o[j].x > mine) + (o[j].y > mine);
+                }
+            } else {
+                for (int a = w0; a < n_expert; ++a) lr += keys[a] > mine;
+            }
+            if (lr < k) sh.cand[(tid >> 5) * 8 + lr] = mine;
+        }
+        Sync::sync();
+        if (tid < n_expert && lr < k) {
+            int rank = 0;
+            const ulonglong2* c2 = (const ulonglong2*) sh.cand;
+#pragma unroll
+            for (int j0 = 0; j0 < kRouterMaxWarps * 4; j0 += 8) {
+                ulonglong2 o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = c2[j0 + j];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) rank += (o[j].x > mine) + (o[j].y > mine);
+            }
+            if (rank < k) { sh.ids[rank] = tid; sh.val[rank] = p; }
+        }
+        Sync::sync();
+        return;
+    }
     Sync::sync();
     if (tid < n_expert) {
         int rank = 0;

@@ -112,6 +112,26 @@ __device__ __forceinline__ bool grid_barrier(unsigned* sync, unsigned epoch, int
 // RT: the router - 0 softmax, 1 sigmoid.  A template parameter, not a branch on A.router: with both routers compiled into
 // one kernel the softmax layer's routing phase ran 2 us longer (the 64-register cap of a 1024-thread block is shared by
 // everything the phase may call).
+// The token's routing by the block's first kRouteThreads threads, as a function of its own: run once a launch, it is
+// kept out of the kernel's register allocation and instruction scheduling (which proved sensitive to what phase 0 holds).
+template<int RT>
+__device__ __noinline__ void route_token(const float* logits, const float* bias, int n_expert, int k, float w_scale, int norm_w,
+                                         int tid, double* s_ex, RouterShared* route) {
+    using RS = NamedSync<1, kRouteThreads>;
+    const int per = (n_expert + kRouteThreads - 1) / kRouteThreads;
+    if constexpr (RT == 1) {
+        if (per <= 1) route_sigmoid<1, RS>(logits, bias, n_expert, k, w_scale, norm_w, tid, kRouteThreads, *route);
+        else if (per <= 2) route_sigmoid<2, RS>(logits, bias, n_expert, k, w_scale, norm_w, tid, kRouteThreads, *route);
+        else if (per <= 4) route_sigmoid<4, RS>(logits, bias, n_expert, k, w_scale, norm_w, tid, kRouteThreads, *route);
+        else route_sigmoid<8, RS>(logits, bias, n_expert, k, w_scale, norm_w, tid, kRouteThreads, *route);
+    } else {
+        if (per <= 1) route_softmax<1, RS>(logits, n_expert, k, tid, kRouteThreads, s_ex, *route);
+        else if (per <= 2) route_softmax<2, RS>(logits, n_expert, k, tid, kRouteThreads, s_ex, *route);
+        else if (per <= 4) route_softmax<4, RS>(logits, n_expert, k, tid, kRouteThreads, s_ex, *route);
+        else route_softmax<8, RS>(logits, n_expert, k, tid, kRouteThreads, s_ex, *route);
+    }
+}
+
 // HV: the kernel may cut phase-1 units in halves (decided per launch on the device; the code for it is compiled in only
 // where a rank's units can be that few - in the one-GPU kernel it cost 1 us by its mere presence).
 template<int T, int TS, int RT, bool HV>
@@ -159,19 +179,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
 
     // ---------------------------------------------------------------- phase 0
     if (tid < kRouteThreads) {
-        using RS = NamedSync<1, kRouteThreads>;
-        const int per = (A.n_expert + kRouteThreads - 1) / kRouteThreads;
-        if constexpr (RT == 1) {
-            if (per <= 1) route_sigmoid<1, RS>(A.logits, A.router_bias, A.n_expert, k, A.router_w_scale, A.router_norm_w, tid, kRouteThreads, sh.route);
-            else if (per <= 2) route_sigmoid<2, RS>(A.logits, A.router_bias, A.n_expert, k, A.router_w_scale, A.router_norm_w, tid, kRouteThreads, sh.route);
-            else if (per <= 4) route_sigmoid<4, RS>(A.logits, A.router_bias, A.n_expert, k, A.router_w_scale, A.router_norm_w, tid, kRouteThreads, sh.route);
-            else route_sigmoid<8, RS>(A.logits, A.router_bias, A.n_expert, k, A.router_w_scale, A.router_norm_w, tid, kRouteThreads, sh.route);
-        } else {
-            if (per <= 1) route_softmax<1, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
-            else if (per <= 2) route_softmax<2, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
-            else if (per <= 4) route_softmax<4, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
-            else route_softmax<8, RS>(A.logits, A.n_expert, k, tid, kRouteThreads, s_ex, sh.route);
-        }
+        route_token<RT>(A.logits, A.router_bias, A.n_expert, k, A.router_w_scale, A.router_norm_w, tid, s_ex, &sh.route);
         if (tid < k) {
             const int e = sh.route.ids[tid];
             sh.w[tid] = sh.route.val[tid];
@@ -223,6 +231,18 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
     {
         const int ng = n_ff / 32, units_r = sh.nv * ng, ng_sh = has_sh ? (A.sh_hi - A.sh_lo) / 32 : 0, U = units_r + ng_sh;
         const size_t rb = row_bytes(T, n_embd);
+        // Unit SLOTS are handed to the blocks in order; which unit sits in a slot spreads the shared expert's units
+        // evenly among the routed ones (slot s holds a shared unit where floor(s * ng_sh / U) steps).  Numbered after
+        // the routed units they all fell into the blocks' last round, 27 MB of Q8_0 rows wanted at once by 64 SMs - an
+        // HBM-bound tail behind an issue-bound phase.  Below, u is a unit in the old numbering: routed [0, units_r), shared after.
+        // (Only with more than two rounds of units a block: with two or fewer - a width slice at 2 or more GPUs - the
+        // spread measured slower, 43.4 against 40.7 us on the half-width slice.)
+        const bool spread = !HV && ng_sh > 0 && U > 2 * (int) gridDim.x;    // (HV kernels serve ranks with few units)
+        auto unit_of = [&](int slot) -> int {
+            if (!spread) return slot;
+            const int c0 = slot * ng_sh / U, c1 = (slot + 1) * ng_sh / U;
+            return c1 > c0 ? units_r + c0 : slot - c0;
+        };
         // Fewer units than half the grid (a rank's share at 8 GPUs): a unit is cut into two halves of 16 FFN rows for two
         // blocks - one weight row a warp - so that twice as many SMs pull rows.  A half leaves its 16 h values as f32 in
         // the scratch; the block that brings the unit's counter to an odd value found the other half there already and
@@ -232,7 +252,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             float* const hst = (float*) ((uint8_t*) A.h + (size_t) (MAYA_MAX_K + 1) * nblk_h * 40);
             unsigned* const hcnt = (unsigned*) (hst + (size_t) (MAYA_MAX_K + 1) * nblk_h * 32);
             if ((int) blockIdx.x < 2 * U) {
-                const int u = (int) blockIdx.x >> 1, half = (int) blockIdx.x & 1;
+                const int u = unit_of((int) blockIdx.x >> 1), half = (int) blockIdx.x & 1;
                 const int fr = 16 * half + (warp >> 1), mat = warp & 1;         // FFN row in the unit; gate (0) or up (1)
                 int e, g;
                 float o[1] = {0.0f};
@@ -277,7 +297,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             static_assert(NW == 32, "a unit's 32 FFN rows map onto the block's 32 warps");
             const int nu4 = nu & ~1;
             for (int it = warp; it < nu4 * 16; it += NW) {
-                const int j = it >> 4, u = u0 + j * (int) gridDim.x, ra_in = 2 * (it & 15);
+                const int j = it >> 4, u = unit_of(u0 + j * (int) gridDim.x), ra_in = 2 * (it & 15);
                 float o[4];
                 if (u < units_r) {
                     const int ei = u / ng, ra = (u - ei * ng) * 32 + ra_in, e = sh.ve[ei];
@@ -298,7 +318,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
                 }
             }
             if (nu & 1) {
-                const int u = u0 + nu4 * (int) gridDim.x;
+                const int u = unit_of(u0 + nu4 * (int) gridDim.x);
                 float o[2];
                 if (u < units_r) {
                     const int ei = u / ng, ra = (u - ei * ng) * 32 + warp, e = sh.ve[ei];
@@ -315,7 +335,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_layer_t1_kernel(FusedArg
             }
             __syncthreads();
             if (warp < nu) {                                     // one warp rounds one unit
-                const int u = u0 + warp * (int) gridDim.x;
+                const int u = unit_of(u0 + warp * (int) gridDim.x);
                 int e, g;
                 if (u < units_r) { const int ei = u / ng; e = sh.ve[ei]; g = u - ei * ng; }
                 else { e = k; g = A.sh_lo / 32 + (u - units_r); }
