@@ -225,7 +225,8 @@ MAYA_API int maya_moe_combine_add(const float* out, int base, int lo, int hi, co
  * types the grouped GEMM takes: Q8_0, Q4_K, IQ2_S, IQ3_S (the i-quants need w_cols % 2048 == 0: 16-byte aligned rows). */
 MAYA_API int maya_mmq_supported(int type);
 /* mmq::q8_bytes (moe_mmq.hpp:20): bytes of `rows` quantized activation rows of `cols` values.  The rows are stored as
- * f16: each value is d * q of the row's q8_1 image (d = f16(amax / 127) per 32 values, q = round(x / d)), the
+ * f16: each value is d * q of the row's q8_1 rounding as llama.cpp's MMQ quantizer does it (per 32 values
+ * d_inv = 127 / amax, q = round(x * d_inv), d = 1 / d_inv, kept as f16), the
  * operand the f16 tensor-core product reads, followed by one f16 per 32 values - f16(sum of the unquantized values)
  * minus the sum of the stored ones, what llama.cpp's MMQ keeps as the "ds4" layout's sum (mmq.cuh:27-46) - padded with
  * zeros to a multiple of 64: (cols + roundup(cols / 32, 64)) * 2 bytes a row.  A Q4_K product multiplies a group's

@@ -132,7 +132,7 @@ class Oracle:
             d_inv = (np.float32(127.0) / am).astype(np.float32)
             d = (np.float32(1.0) / d_inv).astype(np.float32)
             v = (xb * d_inv).astype(np.float32)
-        u = np.where(am > 0, np.sign(v) * np.floor(np.abs(v) + np.float32(0.5)), 0.0).astype(np.float32)
+        u = np.where(am > 0, np.sign(v) * np.floor(np.abs(v).astype(np.float64) + 0.5), 0.0).astype(np.float32)   # roundf
         offset = t == 12                                                   # Q4_K: the ds4 layout
         ds = d.astype(np.float16).astype(np.float32) if offset else d
         xr = np.where(am > 0, u * ds, 0.0).astype(np.float32).reshape(n, K).astype(np.float64)

@@ -105,15 +105,15 @@ __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *(__half2*) &u; 
 __device__ __forceinline__ __half2 bytes01_plus1024(uint32_t x) { return bits_h2(__byte_perm(x, 0x64646464u, 0x4140)); }
 __device__ __forceinline__ __half2 bytes23_plus1024(uint32_t x) { return bits_h2(__byte_perm(x, 0x64646464u, 0x4342)); }
 
-// The one-value-per-lane q8_1 rounding of maya_mmq_quantize: d = min(amax / 127, 65504) kept as f16, q = round(v / d)
-// clamped to +-127, result f16(d) * q.
+// The one-value-per-lane q8_1 rounding of maya_mmq_quantize: d_inv = 127 / amax, q = round(v * d_inv) clamped to +-127,
+// d = min(1 / d_inv, 65504) kept as f16, result f16(d) * q.
 // `xa` (valid in lane 0): the group's sum correction, f16(S) - sum of the stored f16(d * q), with S added in quantize_mmq_q8_1's order - four
 // consecutive values left to right, then a tree over the eight partial sums at distances 4, 2, 1.
 __device__ __forceinline__ __half q8_1_round_warp(float v, float& xa) {
     const float amax = __uint_as_float(__reduce_max_sync(0xFFFFFFFFu, __float_as_uint(fabsf(v))));
-    const float d = fminf(__fdiv_rn(amax, 127.0f), 65504.0f);
-    const float q = amax == 0.0f ? 0.0f : fmaxf(-127.0f, fminf(127.0f, roundf(__fdiv_rn(v, d))));
-    const float dh = __half2float(__float2half_rn(d));
+    const float d_inv = __fdiv_rn(127.0f, amax);
+    const float q = amax == 0.0f ? 0.0f : fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(v, d_inv))));
+    const float dh = amax == 0.0f ? 0.0f : __half2float(__float2half_rn(fminf(__fdiv_rn(1.0f, d_inv), 65504.0f)));
     float s = __fadd_rn(v, __shfl_down_sync(0xFFFFFFFFu, v, 1));
     s = __fadd_rn(s, __shfl_down_sync(0xFFFFFFFFu, v, 2));
     s = __fadd_rn(s, __shfl_down_sync(0xFFFFFFFFu, v, 3));               // lanes 0, 4, ..., 28: their four values
@@ -726,15 +726,18 @@ __global__ void __launch_bounds__(256) mmq_quantize_kernel(const X* __restrict__
     for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-    const float d = fminf(__fdiv_rn(amax, 127.0f), 65504.0f), dh = __half2float(__float2half_rn(d));
+    // the rounding of llama.cpp's quantize_mmq_q8_1 as the reference's host model states it: d_inv = 127 / amax,
+    // q = round(x * d_inv), d = 1 / d_inv (kept as f16 here)
+    const float d_inv = __fdiv_rn(127.0f, amax);
+    const float dh = amax == 0.0f ? 0.0f : __half2float(__float2half_rn(fminf(__fdiv_rn(1.0f, d_inv), 65504.0f)));
     uint32_t o[4];
     float bsum = 0.0f;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         float q0 = 0.0f, q1 = 0.0f;
         if (amax != 0.0f) {
-            q0 = fmaxf(-127.0f, fminf(127.0f, roundf(__fdiv_rn(v[2 * k], d))));
-            q1 = fmaxf(-127.0f, fminf(127.0f, roundf(__fdiv_rn(v[2 * k + 1], d))));
+            q0 = fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(v[2 * k], d_inv))));
+            q1 = fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(v[2 * k + 1], d_inv))));
         }
         const __half2 r = __floats2half2_rn(dh * q0, dh * q1);
         o[k] = h2_bits(r);
