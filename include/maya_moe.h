@@ -241,6 +241,13 @@ MAYA_API int maya_mmq_quantize(const float* x, const int32_t* ids, void* xq, int
 /* The same from bf16 activations (raw bf16 bits, widened to f32 exactly); ld in bf16 elements. */
 MAYA_API int maya_mmq_quantize_bf16(const uint16_t* x, const int32_t* ids, void* xq, int type, int64_t cols, int64_t ld,
                                     int64_t rows, void* stream);
+/* No counterpart in the reference (which gathers: mmq::quantize with ids = row_tok rounds a token's row once per route):
+ * row t of x (tokens rows) is rounded once and its image stored to the k rows pos[t * k + j] of xq (pos as
+ * maya_expert_scatter writes it).  xq ends up byte for byte what maya_mmq_quantize(x, row_tok, ...) writes. */
+MAYA_API int maya_mmq_quantize_routed(const float* x, const int32_t* pos, int k, void* xq, int type, int64_t cols, int64_t ld,
+                                      int64_t tokens, void* stream);
+MAYA_API int maya_mmq_quantize_routed_bf16(const uint16_t* x, const int32_t* pos, int k, void* xq, int type, int64_t cols,
+                                           int64_t ld, int64_t tokens, void* stream);
 /* mmq::Product (moe_mmq.hpp:41-53), field for field, plus three optional fields the reference has no need of. */
 typedef struct maya_mmq_product {
     const void* w;               /* n matrices, expert_bytes apart; 16-byte aligned */

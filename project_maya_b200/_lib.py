@@ -107,6 +107,8 @@ _SIGNATURES = {
     "maya_mmq_q8_bytes": (c_size_t, [c_int64, c_int64]),
     "maya_mmq_quantize": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p]),
     "maya_mmq_quantize_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p]),
+    "maya_mmq_quantize_routed": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p]),
+    "maya_mmq_quantize_routed_bf16": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p]),
     "maya_mmq_run": (c_int, [C.POINTER(MmqProduct), c_void_p]),
     "maya_mmq_run_glu": (c_int, [C.POINTER(MmqProduct), c_float, c_void_p]),
     "maya_moe_combine_rows_local": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,

@@ -264,8 +264,20 @@ def mmq_quantize(x, ids, ggml_type: int, rows: int | None = None, xq=None, strea
     cols, ld = x.shape[1], x.stride(0)
     rows = rows if rows is not None else (ids.numel() if ids is not None else x.shape[0])
     xq = xq if xq is not None else torch.empty(max(mmq_q8_bytes(rows, cols), 16), dtype=torch.uint8, device=x.device)
-    _check("mmq_quantize", _lib.load().maya_mmq_quantize(_ptr(x), _ptr(ids), _ptr(xq), ggml_type, cols, ld, rows,
-                                                        _stream(stream)))
+    assert x.dtype in (torch.float32, torch.bfloat16)
+    fn = _lib.load().maya_mmq_quantize_bf16 if x.dtype == torch.bfloat16 else _lib.load().maya_mmq_quantize
+    _check("mmq_quantize", fn(_ptr(x), _ptr(ids), _ptr(xq), ggml_type, cols, ld, rows, _stream(stream)))
+    return xq
+
+
+def mmq_quantize_routed(x, pos, k: int, ggml_type: int, xq=None, stream=None):
+    """No counterpart in the reference: every row of x rounded once, its q8_1 image stored to the k rows pos[t * k + j]
+    (pos from expert_groups) - the bytes mmq_quantize(x, row_tok, ...) writes."""
+    assert x.dtype in (torch.float32, torch.bfloat16)
+    T, cols, ld = x.shape[0], x.shape[1], x.stride(0)
+    xq = xq if xq is not None else torch.empty(max(mmq_q8_bytes(T * k, cols), 16), dtype=torch.uint8, device=x.device)
+    fn = _lib.load().maya_mmq_quantize_routed_bf16 if x.dtype == torch.bfloat16 else _lib.load().maya_mmq_quantize_routed
+    _check("mmq_quantize_routed", fn(_ptr(x), _ptr(pos), k, _ptr(xq), ggml_type, cols, ld, T, _stream(stream)))
     return xq
 
 
@@ -501,6 +513,7 @@ class MoePrefill:
         assert T <= self.max_tokens and x.shape == (T, H) and x.dtype in (torch.float32, torch.bfloat16)
         n = T * k
         quant = lib.maya_mmq_quantize_bf16 if x.dtype == torch.bfloat16 else lib.maya_mmq_quantize
+        quant_routed = lib.maya_mmq_quantize_routed_bf16 if x.dtype == torch.bfloat16 else lib.maya_mmq_quantize_routed
         ids, w = self.ids[:T], self.weights[:T]
         _check("router_top10", lib.maya_router_top10(_ptr(logits), T, E, k, _ptr(ids), _ptr(w), s))
         _check("expert_count", lib.maya_expert_count(_ptr(ids), n, E, _ptr(self.counts), _ptr(self.rank), s))
@@ -508,7 +521,8 @@ class MoePrefill:
         _check("expert_scatter", lib.maya_expert_scatter(_ptr(ids), _ptr(self.rank), _ptr(self.bounds), n, k,
                                                          _ptr(self.row_tok), _ptr(self.pos), s))
         qtype = self.pools[0][0] if self.pools else cfg.gu_type
-        _check("mmq_quantize", quant(_ptr(x), _ptr(self.row_tok), _ptr(self.xq), qtype, H, x.stride(0), n, s))
+        # each token rounded once, its image stored to its k sorted rows (the bytes quant(x, row_tok, ...) would write)
+        _check("mmq_quantize_routed", quant_routed(_ptr(x), _ptr(self.pos), k, _ptr(self.xq), qtype, H, x.stride(0), T, s))
         for gt, dt, blobs, stride, down_off, n_p, emap in self.pools:
             gu = mmq_product(blobs, gt, 2 * FF, H, stride, n_p, self.xq, self.bounds, None, n, None, FF, expert_map=emap,
                              error=self.err, xq_out=self.hq)        # h leaves the product already quantized

@@ -696,34 +696,36 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
     if (tid == 0 && failed(P) && A.error != nullptr) atomicExch(A.error, 1u);
 }
 
-// x rows (gathered through ids) -> f16 rows of their q8_1 image.  A thread owns 8 consecutive values (one 16-byte
-// store), the 4 threads of a 32-value block find its amax with two shuffles.
-template<typename X>
+// x rows -> f16 rows of their q8_1 image.  A thread owns 8 consecutive values (one 16-byte store), the 4 threads of a
+// 32-value block find its amax with two shuffles.  blockIdx.x is the row, blockIdx.y * 256 + threadIdx.x the 8-value chunk.
+// ROUTED = false: image row r is x row ids[r] (ids == nullptr: r).  ROUTED = true: x row t is rounded once and its image
+// stored to the k rows pos[t * k + j] (the sorted rows of the token's k routes) - the same bytes as the gathered form
+// writes through row_tok, at one eighth of the arithmetic for k = 8.
+template<typename X, bool ROUTED>
 __global__ void __launch_bounds__(256) mmq_quantize_kernel(const X* __restrict__ x, const int* __restrict__ ids,
-                                                           __half* __restrict__ xq, int64_t cols, int64_t ld,
-                                                           int64_t n_chunks) {
-    const int64_t i = (int64_t) blockIdx.x * 256 + threadIdx.x;
-    const bool live = i < n_chunks;                  // n_chunks is a multiple of 4: a block's 4 threads live together
-    const int64_t cpr = cols / 8, row = live ? i / cpr : 0, c = live ? i - row * cpr : 0;
-    const int64_t src = ids ? ids[row] : row;
+                                                           __half* __restrict__ xq, int cols, int64_t ld, int k) {
+    const int64_t row = blockIdx.x;
+    const int cpr = cols >> 3, c = (int) blockIdx.y * 256 + (int) threadIdx.x;
+    const bool live = c < cpr;                       // cpr is a multiple of 4: a block's 4 threads live together
+    const int64_t src = (!ROUTED && ids) ? ids[row] : row;
     float v[8];
     if (live) {
         if constexpr (sizeof(X) == 2) {              // bf16 bits, widened exactly
             const uint4 u = *(const uint4*) (x + src * ld + c * 8);
             const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-            for (int k = 0; k < 4; ++k) { v[2 * k] = __uint_as_float(w[k] << 16); v[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u); }
+            for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
         } else {
             const float4 a = *(const float4*) (x + src * ld + c * 8), b = *(const float4*) (x + src * ld + c * 8 + 4);
             v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
         }
     } else {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) v[k] = 0.0f;
+        for (int i = 0; i < 8; ++i) v[i] = 0.0f;
     }
     float amax = 0.0f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
     // the rounding of llama.cpp's quantize_mmq_q8_1 as the reference's host model states it: d_inv = 127 / amax,
@@ -733,14 +735,14 @@ __global__ void __launch_bounds__(256) mmq_quantize_kernel(const X* __restrict__
     uint32_t o[4];
     float bsum = 0.0f;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int i = 0; i < 4; ++i) {
         float q0 = 0.0f, q1 = 0.0f;
         if (amax != 0.0f) {
-            q0 = fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(v[2 * k], d_inv))));
-            q1 = fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(v[2 * k + 1], d_inv))));
+            q0 = fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(v[2 * i], d_inv))));
+            q1 = fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(v[2 * i + 1], d_inv))));
         }
         const __half2 r = __floats2half2_rn(dh * q0, dh * q1);
-        o[k] = h2_bits(r);
+        o[i] = h2_bits(r);
         bsum += __low2float(r) + __high2float(r);     // the stored values: multiples of one power of two, 24 bits in all - exact
     }
     // The group's sum correction (see xq_tail): S in quantize_mmq_q8_1's order - each 4 consecutive values left to right
@@ -752,34 +754,43 @@ __global__ void __launch_bounds__(256) mmq_quantize_kernel(const X* __restrict__
     s1 = __fadd_rn(s1, __shfl_xor_sync(0xFFFFFFFFu, s1, 1));
     bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 1);
     bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 2);
-    const float xa = __half2float(__float2half_rn(__fadd_rn(s0, s1))) - bsum;
+    const __half xa = __float2half_rn(__half2float(__float2half_rn(__fadd_rn(s0, s1))) - bsum);
     // a warp's eight groups: their corrections leave as one 16-byte store when a row is a whole number of warps
     const bool packed = (cols & 255) == 0;
+    uint4 cw = make_uint4(0u, 0u, 0u, 0u);
     if (packed) {
-        const uint32_t mine = (uint32_t) __half_as_ushort(__float2half_rn(xa));
+        const uint32_t mine = (uint32_t) __half_as_ushort(xa);
         const uint32_t pair = mine | (__shfl_down_sync(0xFFFFFFFFu, mine, 4) << 16);        // lanes 0, 8, 16, 24: groups (2i, 2i + 1)
         const uint32_t p1 = __shfl_sync(0xFFFFFFFFu, pair, 8), p2 = __shfl_sync(0xFFFFFFFFu, pair, 16), p3 = __shfl_sync(0xFFFFFFFFu, pair, 24);
-        if (live && (threadIdx.x & 31) == 0) *(uint4*) (xq + row * xq_ld(cols) + cols + (c >> 2)) = make_uint4(pair, p1, p2, p3);
+        cw = make_uint4(pair, p1, p2, p3);
     }
-    if (live) {
-        const int64_t ldq = xq_ld(cols);
-        *(uint4*) (xq + row * ldq + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
-        if (!packed && (c & 3) == 0) xq[row * ldq + cols + (c >> 2)] = __float2half_rn(xa);
+    if (!live) return;
+    const int64_t ldq = xq_ld(cols);
+    const int nd = ROUTED ? k : 1;
+    for (int j = 0; j < nd; ++j) {
+        const int64_t dr = ROUTED ? (int64_t) ids[row * k + j] : row;
+        __half* d = xq + dr * ldq;
+        *(uint4*) (d + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+        if (packed) { if ((threadIdx.x & 31) == 0) *(uint4*) (d + cols + (c >> 2)) = cw; }
+        else if ((c & 3) == 0) d[cols + (c >> 2)] = xa;
         if (c == 0)                                   // the zero padding behind the row's corrections
-            for (int64_t t = cols + cols / 32; t < ldq; ++t) xq[row * ldq + t] = __float2half_rn(0.0f);
+            for (int64_t t = cols + cols / 32; t < ldq; ++t) d[t] = __float2half_rn(0.0f);
     }
 }
 
 template<typename X>
-int launch_quantize(const X* x, const int32_t* ids, void* xq, int type, int64_t cols, int64_t ld, int64_t rows, void* stream) {
+int launch_quantize(const X* x, const int32_t* ids, void* xq, int type, int64_t cols, int64_t ld, int64_t rows, int k, void* stream) {
     if (!maya_mmq_supported(type)) return refuse(MAYA_ERR_TYPE);
     if (rows <= 0) return MAYA_OK;
-    if (!x || !xq || cols <= 0 || cols % 32 || ld < cols) return refuse(MAYA_ERR_ARG);
+    if (!x || !xq || cols <= 0 || cols % 32 || ld < cols || cols > 0x7FFFFFF0ll) return refuse(MAYA_ERR_ARG);
+    if (k < 0 || (k > 0 && !ids)) return refuse(MAYA_ERR_ARG);
     if (!aligned16(x) || !aligned16(xq) || (ld * sizeof(X)) % 16) return refuse(MAYA_ERR_ARG);   // 16-byte loads and stores
-    const int64_t nc = rows * (cols / 8);
-    if ((nc + 255) / 256 > 0x7FFFFFFF) return refuse(MAYA_ERR_LIMIT);
-    mmq_quantize_kernel<X><<<(unsigned) ((nc + 255) / 256), 256, 0, as_stream(stream)>>>(x, ids, (__half*) xq, cols, ld, nc);
-    return note_launch("mmq_quantize");
+    const int64_t by = (cols / 8 + 255) / 256;
+    if (rows > 0x7FFFFFFFll || by > 65535) return refuse(MAYA_ERR_LIMIT);
+    const dim3 grid((unsigned) rows, (unsigned) by);
+    if (k > 0) mmq_quantize_kernel<X, true><<<grid, 256, 0, as_stream(stream)>>>(x, ids, (__half*) xq, (int) cols, ld, k);
+    else mmq_quantize_kernel<X, false><<<grid, 256, 0, as_stream(stream)>>>(x, ids, (__half*) xq, (int) cols, ld, 0);
+    return note_launch(k > 0 ? "mmq_quantize_routed" : "mmq_quantize");
 }
 
 // ---- tensor maps (driver entry point looked up once; the library does not link libcuda)
@@ -883,11 +894,21 @@ extern "C" size_t maya_mmq_q8_bytes(int64_t rows, int64_t cols) {
 }
 extern "C" int maya_mmq_quantize(const float* x, const int32_t* ids, void* xq, int type, int64_t cols, int64_t ld,
                                  int64_t rows, void* stream) {
-    return launch_quantize<float>(x, ids, xq, type, cols, ld, rows, stream);
+    return launch_quantize<float>(x, ids, xq, type, cols, ld, rows, 0, stream);
 }
 extern "C" int maya_mmq_quantize_bf16(const uint16_t* x, const int32_t* ids, void* xq, int type, int64_t cols, int64_t ld,
                                       int64_t rows, void* stream) {
-    return launch_quantize<uint16_t>(x, ids, xq, type, cols, ld, rows, stream);
+    return launch_quantize<uint16_t>(x, ids, xq, type, cols, ld, rows, 0, stream);
+}
+extern "C" int maya_mmq_quantize_routed(const float* x, const int32_t* pos, int k, void* xq, int type, int64_t cols, int64_t ld,
+                                        int64_t tokens, void* stream) {
+    if (k <= 0) return refuse(MAYA_ERR_ARG);
+    return launch_quantize<float>(x, pos, xq, type, cols, ld, tokens, k, stream);
+}
+extern "C" int maya_mmq_quantize_routed_bf16(const uint16_t* x, const int32_t* pos, int k, void* xq, int type, int64_t cols,
+                                             int64_t ld, int64_t tokens, void* stream) {
+    if (k <= 0) return refuse(MAYA_ERR_ARG);
+    return launch_quantize<uint16_t>(x, pos, xq, type, cols, ld, tokens, k, stream);
 }
 extern "C" int maya_mmq_run(const maya_mmq_product* p, void* stream) { return run_product(p, false, 0.0f, as_stream(stream)); }
 extern "C" int maya_mmq_run_glu(const maya_mmq_product* p, float limit, void* stream) {

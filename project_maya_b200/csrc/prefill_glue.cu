@@ -13,30 +13,37 @@
 namespace maya {
 namespace {
 
-// One block per expert: walks all pairs in order, 1024 at a time; a pair's rank is the number of earlier pairs routed to
-// the same expert (ballot + popcount inside a warp, warp totals through shared memory).
+// One block per expert.  Warp w owns the pairs [w * per, (w + 1) * per) (per a multiple of 32): a first walk counts its
+// pairs routed to this expert, the warps' totals meet in shared memory once, a second walk writes the ranks - a pair's
+// rank is the number of earlier pairs routed to the same expert (ballot + popcount inside a warp).
 __global__ void __launch_bounds__(1024) expert_count_kernel(const int* __restrict__ ids, int n, int* __restrict__ counts,
                                                             int* __restrict__ rank) {
     const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     __shared__ int s_wc[32];
-    int base = 0;
-    for (int c0 = 0; c0 < n; c0 += 1024) {
-        const int i = c0 + tid;
-        const bool m = i < n && ids[i] == e;
-        const unsigned ballot = __ballot_sync(0xffffffffu, m);
-        if (lane == 0) s_wc[warp] = __popc(ballot);
-        __syncthreads();
-        int off = base, tot = 0;
-        for (int w = 0; w < 32; ++w) {
-            const int c = s_wc[w];
-            if (w < warp) off += c;
-            tot += c;
-        }
-        if (m) rank[i] = off + __popc(ballot & ((1u << lane) - 1u));
-        base += tot;
-        __syncthreads();
+    const int per = ((n + 1023) / 1024) * 32;
+    const int i0 = warp * per, i1 = min(n, i0 + per);
+    int cnt = 0;
+#pragma unroll 4
+    for (int i = i0 + lane; i < i1; i += 32) cnt += ids[i] == e;
+    for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+    if (lane == 0) s_wc[warp] = cnt;
+    __syncthreads();
+    int base = 0, tot = 0;
+    for (int w = 0; w < 32; ++w) {
+        const int c = s_wc[w];
+        if (w < warp) base += c;
+        tot += c;
     }
-    if (tid == 0) counts[e] = base;
+    if (cnt != 0) {                                   // warp-uniform: nothing to rank otherwise
+        for (int c0 = i0; c0 < i1; c0 += 32) {        // whole warps walk (i0 and per are multiples of 32)
+            const int i = c0 + lane;
+            const bool m = i < i1 && ids[i] == e;
+            const unsigned ballot = __ballot_sync(0xffffffffu, m);
+            if (m) rank[i] = base + __popc(ballot & ((1u << lane) - 1u));
+            base += __popc(ballot);
+        }
+    }
+    if (tid == 0) counts[e] = tot;
 }
 
 // bounds[0] = 0, bounds[e + 1] = bounds[e] + counts[e]; one block.
@@ -95,6 +102,40 @@ __global__ void __launch_bounds__(256) combine_rows_kernel(const float* __restri
     float m = 0.0f;
     for (int j = 0; j < k; ++j) m = __fmaf_rn(w[t * k + j], out[(size_t) pos[t * k + j] * n_embd + e], m);
     ffn[(size_t) t * n_embd + e] = __fadd_rn(m, sh ? sh[(size_t) t * n_embd + e] : 0.0f);
+}
+// the same, four columns a thread (n_embd % 4 == 0, 16-byte aligned rows): the k rows' loads are issued together
+template<int K>
+__global__ void __launch_bounds__(256) combine_rows4_kernel(const float* __restrict__ out, const int* __restrict__ pos,
+                                                            const float* __restrict__ w, const float* __restrict__ sh,
+                                                            int k, int n_embd, float* __restrict__ ffn) {
+    const int t = blockIdx.y, e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (e >= n_embd) return;
+    const int kk = K > 0 ? K : k;
+    float4 m = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if constexpr (K > 0) {
+        float4 o[K];
+        float wj[K];
+#pragma unroll
+        for (int j = 0; j < K; ++j) {
+            wj[j] = w[t * K + j];
+            o[j] = __ldcs((const float4*) (out + (size_t) pos[t * K + j] * n_embd + e));
+        }
+#pragma unroll
+        for (int j = 0; j < K; ++j) {
+            m.x = __fmaf_rn(wj[j], o[j].x, m.x); m.y = __fmaf_rn(wj[j], o[j].y, m.y);
+            m.z = __fmaf_rn(wj[j], o[j].z, m.z); m.w = __fmaf_rn(wj[j], o[j].w, m.w);
+        }
+    } else {
+        for (int j = 0; j < kk; ++j) {
+            const float wj = w[t * kk + j];
+            const float4 o = __ldcs((const float4*) (out + (size_t) pos[t * kk + j] * n_embd + e));
+            m.x = __fmaf_rn(wj, o.x, m.x); m.y = __fmaf_rn(wj, o.y, m.y); m.z = __fmaf_rn(wj, o.z, m.z); m.w = __fmaf_rn(wj, o.w, m.w);
+        }
+    }
+    float4 s4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (sh) s4 = *(const float4*) (sh + (size_t) t * n_embd + e);
+    m.x = __fadd_rn(m.x, s4.x); m.y = __fadd_rn(m.y, s4.y); m.z = __fadd_rn(m.z, s4.z); m.w = __fadd_rn(m.w, s4.w);
+    *(float4*) (ffn + (size_t) t * n_embd + e) = m;
 }
 
 // the same over this rank's experts only: a route whose expert id is outside [e_lo, e_hi) contributes an exact zero
@@ -196,6 +237,12 @@ extern "C" int maya_moe_combine_rows(const float* out, const int* pos, const flo
                                      int n_embd, float* ffn, void* stream) {
     if (T <= 0) return MAYA_OK;
     if (!out || !pos || !w || !ffn || k <= 0 || n_embd <= 0) return refuse(MAYA_ERR_ARG);
+    if (n_embd % 4 == 0 && aligned16(out) && aligned16(ffn) && (!sh || aligned16(sh))) {
+        const dim3 grid4((unsigned) ((n_embd / 4 + 255) / 256), (unsigned) T);
+        if (k == 8) combine_rows4_kernel<8><<<grid4, 256, 0, as_stream(stream)>>>(out, pos, w, sh, k, n_embd, ffn);
+        else combine_rows4_kernel<0><<<grid4, 256, 0, as_stream(stream)>>>(out, pos, w, sh, k, n_embd, ffn);
+        return note_launch("moe_combine_rows");
+    }
     const dim3 grid((unsigned) ((n_embd + 255) / 256), (unsigned) T);
     combine_rows_kernel<<<grid, 256, 0, as_stream(stream)>>>(out, pos, w, sh, k, n_embd, ffn);
     return note_launch("moe_combine_rows");

@@ -421,3 +421,71 @@ def test_c5_batch64_through_prompt_path_and_expert_parallel_partition(T, api, or
         T.cuda.synchronize()
         assert not ranks[r].poisoned()
         assert fused.cpu().numpy().tobytes() == summed.tobytes(), f"rank {r}: not the rank-ordered sum"
+
+
+@pytest.mark.parametrize("n_tok,k,E", [(1, 8, 256), (37, 8, 16), (300, 4, 8), (4096, 8, 256), (129, 1, 3)])
+def test_expert_group_is_the_stable_sort_by_expert(T, api, n_tok, k, E):
+    """glmb::expert_count / expert_scatter (glm_batch.hpp:131-139): a pair's rank is the number of earlier pairs routed to
+    the same expert, its sorted row = the expert's base + rank - numpy's stable argsort by expert id."""
+    rng = H.rng_for(f"group-{n_tok}-{k}-{E}")
+    ids = np.stack([rng.choice(E, size=min(k, E), replace=False) for _ in range(n_tok)]).astype(np.int32)
+    k = ids.shape[1]
+    counts, bounds, pos, row_tok = api.expert_group(dev(T, ids), E)
+    T.cuda.synchronize()
+    flat = ids.reshape(-1)
+    want_counts = np.bincount(flat, minlength=E)
+    order = np.argsort(flat, kind="stable")
+    assert np.array_equal(counts.cpu().numpy(), want_counts)
+    assert np.array_equal(bounds.cpu().numpy(), np.concatenate([[0], np.cumsum(want_counts)]))
+    assert np.array_equal(row_tok.cpu().numpy(), order // k)
+    want_pos = np.empty_like(order)
+    want_pos[order] = np.arange(order.size)
+    assert np.array_equal(pos.cpu().numpy(), want_pos)
+
+
+@pytest.mark.parametrize("cols", [256, 1536, 96])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_routed_quantizer_writes_the_gathered_image(T, api, cols, dtype):
+    """maya_mmq_quantize_routed (each token rounded once, stored to its k sorted rows) against maya_mmq_quantize through
+    row_tok (mmq::quantize with ids, moe_mmq.hpp:34): the same bytes."""
+    n_tok, k, E = 53, 4, 7
+    rng = H.rng_for(f"routedq-{cols}-{dtype}")
+    ids = np.stack([rng.choice(E, size=k, replace=False) for _ in range(n_tok)]).astype(np.int32)
+    x = dev(T, rng.standard_normal((n_tok, cols)).astype(np.float32))
+    x[5] = 0.0                                              # an all-zero row: d = 0, every correction 0
+    if dtype == "bf16":
+        x = x.to(T.bfloat16)
+    _, _, pos, row_tok = api.expert_group(dev(T, ids), E)
+    want = api.mmq_quantize(x, row_tok, H.Q4_K)
+    got = T.full_like(want, 0xA5)
+    api.mmq_quantize_routed(x, pos, k, H.Q4_K, xq=got)
+    T.cuda.synchronize()
+    assert T.equal(got, want)
+
+
+@pytest.mark.parametrize("k", [8, 3])
+def test_combine_rows_four_columns_a_thread_equals_one_column_a_thread(T, api, k):
+    """maya_moe_combine_rows takes four columns a thread when its rows are 16-byte aligned, one otherwise: the same
+    chain m = 0, m = fma(w_j, out[pos_j], m) in plan order, + sh - bitwise."""
+    n_tok, n_embd = 41, 520
+    rng = H.rng_for(f"combine4-{k}")
+    n = n_tok * k
+    pos = dev(T, rng.permutation(n).astype(np.int32))
+    w = dev(T, rng.random((n_tok, k)).astype(np.float32))
+    sh = dev(T, rng.standard_normal((n_tok, n_embd)).astype(np.float32))
+    buf = dev(T, rng.standard_normal(n * n_embd + 4).astype(np.float32))
+    out_al = buf[:n * n_embd].view(n, n_embd)
+    out_off = buf[1:1 + n * n_embd]                          # 4 bytes off a 16-byte boundary: the one-column kernel
+    out_off.copy_(out_al.reshape(-1).clone())
+    out_off = out_off.view(n, n_embd)
+    out_al2 = out_off.clone()                                # aligned again, same values
+    a = api.moe_combine_rows(out_al2, pos, w, sh, n_tok, k, n_embd)
+    b = api.moe_combine_rows(out_off, pos, w, sh, n_tok, k, n_embd)
+    c = api.moe_combine_rows(out_al2, pos, w, None, n_tok, k, n_embd)
+    T.cuda.synchronize()
+    assert T.equal(a, b)
+    ref = T.zeros((n_tok, n_embd), dtype=T.float64, device="cuda")
+    for j in range(k):
+        ref += w[:, j:j + 1].double() * out_al2[pos.view(n_tok, k)[:, j].long()].double()
+    assert float((c.double() - ref).abs().max()) <= 1e-5
+    assert float((a.double() - ref - sh.double()).abs().max()) <= 1e-5
