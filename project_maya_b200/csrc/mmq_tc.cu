@@ -167,12 +167,23 @@ __device__ __forceinline__ void q80_stage(const uint8_t* rrow, uint32_t* r) {
     const uint32_t dw = w[kOff / 4];
     const __half dh = __ushort_as_half((unsigned short) ((kOff % 4) ? (dw >> 16) : (dw & 0xFFFF)));
     const __half2 d2 = __half2half2(dh), k1152 = __float2half2_rn(1152.0f);
+    constexpr int kQ = kOff + 2;
+    if constexpr (kQ % 4 != 0) {
+        // the quants start two bytes into a word: values (4i, 4i + 1) are bytes 2, 3 of word i and values (4i + 2, 4i + 3)
+        // bytes 0, 1 of word i + 1 - picked by the same byte permutes that widen them, no aligning permute
+        uint32_t u[9];
+#pragma unroll
+        for (int i = 0; i < 9; ++i) u[i] = w[kQ / 4 + i] ^ 0x80808080u;     // q + 128 as unsigned bytes
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            r[2 * i] = h2_bits(__hmul2(__hsub2(bytes23_plus1024(u[i]), k1152), d2));
+            r[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes01_plus1024(u[i + 1]), k1152), d2));
+        }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        constexpr int kQ = kOff + 2;
-        uint32_t x;
-        if constexpr (kQ % 4 == 0) x = w[kQ / 4 + i];
-        else x = __byte_perm(w[kQ / 4 + i], w[kQ / 4 + i + 1], 0x5432);
+        uint32_t x = w[kQ / 4 + i];
         x ^= 0x80808080u;                                                  // q + 128 as unsigned bytes
         r[2 * i] = h2_bits(__hmul2(__hsub2(bytes01_plus1024(x), k1152), d2));
         r[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes23_plus1024(x), k1152), d2));
@@ -261,6 +272,8 @@ struct Pipe {                       // static shared memory of a block
 
 __device__ __forceinline__ bool failed(const Pipe& P) { return *(volatile const int*) &P.fail != 0; }
 // Bounded wait; false when this wait ran out (the block's failure flag is then set) or another role has failed.
+// (try_wait with a suspend-time hint, so that the waiting single-lane roles poll less, changed nothing when only the
+// loaders used it and cost 0.7 % when the issuers and the expanding warps did.)
 __device__ __forceinline__ bool wait_or_fail(Pipe& P, uint64_t* bar, uint32_t parity) {
     for (unsigned i = 0; i < (1u << 21); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
