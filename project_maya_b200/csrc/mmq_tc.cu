@@ -105,27 +105,40 @@ __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *(__half2*) &u; 
 __device__ __forceinline__ __half2 bytes01_plus1024(uint32_t x) { return bits_h2(__byte_perm(x, 0x64646464u, 0x4140)); }
 __device__ __forceinline__ __half2 bytes23_plus1024(uint32_t x) { return bits_h2(__byte_perm(x, 0x64646464u, 0x4342)); }
 
-// The one-value-per-lane q8_1 rounding of maya_mmq_quantize: d_inv = 127 / amax, q = round(v * d_inv) clamped to +-127,
-// d = min(1 / d_inv, 65504) kept as f16, result f16(d) * q.
-// `xa` (valid in lane 0): the group's sum correction, f16(S) - sum of the stored f16(d * q), with S added in quantize_mmq_q8_1's order - four
-// consecutive values left to right, then a tree over the eight partial sums at distances 4, 2, 1.
-__device__ __forceinline__ __half q8_1_round_warp(float v, float& xa) {
-    const float amax = __uint_as_float(__reduce_max_sync(0xFFFFFFFFu, __float_as_uint(fabsf(v))));
-    const float d_inv = __fdiv_rn(127.0f, amax);
-    const float q = amax == 0.0f ? 0.0f : fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(v, d_inv))));
-    const float dh = amax == 0.0f ? 0.0f : __half2float(__float2half_rn(fminf(__fdiv_rn(1.0f, d_inv), 65504.0f)));
-    float s = __fadd_rn(v, __shfl_down_sync(0xFFFFFFFFu, v, 1));
-    s = __fadd_rn(s, __shfl_down_sync(0xFFFFFFFFu, v, 2));
-    s = __fadd_rn(s, __shfl_down_sync(0xFFFFFFFFu, v, 3));               // lanes 0, 4, ..., 28: their four values
-    s = __fadd_rn(s, __shfl_xor_sync(0xFFFFFFFFu, s, 16));
-    s = __fadd_rn(s, __shfl_xor_sync(0xFFFFFFFFu, s, 8));
-    s = __fadd_rn(s, __shfl_xor_sync(0xFFFFFFFFu, s, 4));
-    const __half r = __float2half_rn(dh * q);
-    float b = __half2float(r);               // the sum of the 32 STORED values: multiples of one power of two, 24 bits in all -
+// The q8_1 rounding of maya_mmq_quantize for a thread that holds 8 consecutive values of a 32-value group (the group's
+// four threads are four consecutive lanes; every lane of the warp must call): llama.cpp's quantize_mmq_q8_1 as the
+// reference's host model states it - d_inv = 127 / amax, q = round(v * d_inv) clamped to +-127, d = min(1 / d_inv, 65504)
+// kept as f16, stored f16(d) * q.  o = the 8 stored values; the return value is the group's sum correction
+// f16(S) - sum of the stored values, with S added in quantize_mmq_q8_1's order: four consecutive values left to right
+// (this thread holds partial sums 2j and 2j + 1 of the group's eight), then the tree at distances 4, 2, 1.
+__device__ __forceinline__ __half q8_1_round8(const float (&v)[8], uint32_t (&o)[4]) {
+    float amax = 0.0f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) b += __shfl_xor_sync(0xFFFFFFFFu, b, o);   // exact in f32 in any order
-    xa = __half2float(__float2half_rn(s)) - b;
-    return r;
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    const float d_inv = __fdiv_rn(127.0f, amax);
+    const float dh = amax == 0.0f ? 0.0f : __half2float(__float2half_rn(fminf(__fdiv_rn(1.0f, d_inv), 65504.0f)));
+    float bsum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float q0 = 0.0f, q1 = 0.0f;
+        if (amax != 0.0f) {
+            q0 = fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(v[2 * i], d_inv))));
+            q1 = fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(v[2 * i + 1], d_inv))));
+        }
+        const __half2 r = __floats2half2_rn(dh * q0, dh * q1);
+        o[i] = h2_bits(r);
+        bsum += __low2float(r) + __high2float(r);     // the stored values: multiples of one power of two, 24 bits in all - exact
+    }
+    float s0 = __fadd_rn(__fadd_rn(__fadd_rn(v[0], v[1]), v[2]), v[3]), s1 = __fadd_rn(__fadd_rn(__fadd_rn(v[4], v[5]), v[6]), v[7]);
+    s0 = __fadd_rn(s0, __shfl_xor_sync(0xFFFFFFFFu, s0, 2));
+    s1 = __fadd_rn(s1, __shfl_xor_sync(0xFFFFFFFFu, s1, 2));
+    s0 = __fadd_rn(s0, __shfl_xor_sync(0xFFFFFFFFu, s0, 1));
+    s1 = __fadd_rn(s1, __shfl_xor_sync(0xFFFFFFFFu, s1, 1));
+    bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 1);
+    bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 2);
+    return __float2half_rn(__half2float(__float2half_rn(__fadd_rn(s0, s1))) - bsum);
 }
 
 // ---- Q4_K: the 16-byte header of a 144-byte block -> d * sc and -(dmin * m) of its 8 sub-blocks, as half2 pairs
@@ -179,14 +192,13 @@ __device__ __forceinline__ void q80_stage(const uint8_t* rrow, uint32_t* r) {
             r[2 * i] = h2_bits(__hmul2(__hsub2(bytes23_plus1024(u[i]), k1152), d2));
             r[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes01_plus1024(u[i + 1]), k1152), d2));
         }
-        return;
-    }
+    } else {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        uint32_t x = w[kQ / 4 + i];
-        x ^= 0x80808080u;                                                  // q + 128 as unsigned bytes
-        r[2 * i] = h2_bits(__hmul2(__hsub2(bytes01_plus1024(x), k1152), d2));
-        r[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes23_plus1024(x), k1152), d2));
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t x = w[kQ / 4 + i] ^ 0x80808080u;
+            r[2 * i] = h2_bits(__hmul2(__hsub2(bytes01_plus1024(x), k1152), d2));
+            r[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes23_plus1024(x), k1152), d2));
+        }
     }
 }
 
@@ -542,8 +554,11 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
             uint8_t* const stg = smem;
             constexpr int kThreadsEpi = kDqWarps * 32;
             if constexpr (GLU) {
-                // 16 warps = 4 lane quadrants x 4 groups; a group takes every 4th chunk of 8 activation rows, so the
-                // groups stay balanced whatever the row count.  One pass: the whole tile fits in shared memory.
+                // Two passes.  First the tile goes from tensor memory to shared memory as h = SwiGLU(gate, up) in f32,
+                // [activation row][128]: 16 warps = 4 lane quadrants x 4 groups, a group takes every 4th chunk of 8
+                // activation rows.  Then, for the f16 image, every thread rounds 8 consecutive values of a row at a time
+                // (4 threads a 32-value group, as maya_mmq_quantize does: the same function, the same bytes) - the
+                // groups' amax and sums cost two shuffles each instead of a warp-wide reduction per value.
                 __half* b16 = (__half*) stg;                             // [rows][128] f16 image of h
                 float* b32 = (float*) (stg + TN * 128 * 2);              // [rows][128] h
                 __half* bxa = (__half*) (stg + TN * 128 * 6);            // [rows][4] sum corrections of the row's four 32-value groups
@@ -555,20 +570,24 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                     tmem_ld8(lane_base + col0, v);
                     tmem_ld8(lane_base + kAccCols + col0, up);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) v[j] = swiglu(v[j], up[j], A.limit);
-                    if (A.xq_out) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            if (col0 + j < nrows) {                                                          // uniform in the warp
-                                float xa;
-                                b16[(col0 + j) * 128 + mcol] = q8_1_round_warp(v[j], xa);
-                                if (lane == 0) bxa[(col0 + j) * 4 + q] = __float2half_rn(xa);
-                            }
-                    }
-                    if (A.dst) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            if (col0 + j < nrows) b32[(col0 + j) * 128 + mcol] = v[j];
+                    for (int j = 0; j < 8; ++j)
+                        if (col0 + j < nrows) b32[(col0 + j) * 128 + mcol] = swiglu(v[j], up[j], A.limit);   // uniform in the warp
+                }
+                if (A.xq_out) {
+                    named_bar_sync(2, kThreadsEpi);
+                    const int ch = tid & 15;                             // the row's 8-value chunk; a warp covers two rows
+                    for (int r0 = 0; r0 < nrows; r0 += kThreadsEpi / 16) {
+                        const int r = r0 + (tid >> 4);
+                        const bool live = r < nrows;                     // the same for a group's four threads
+                        const float* src = b32 + (live ? r : 0) * 128 + 8 * ch;
+                        const float4 lo = *(const float4*) src, hi = *(const float4*) (src + 4);
+                        const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                        uint32_t o[4];
+                        const __half xa = q8_1_round8(v, o);
+                        if (live) {
+                            *(uint4*) (b16 + r * 128 + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
+                            if ((ch & 3) == 0) bxa[r * 4 + (ch >> 2)] = xa;
+                        }
                     }
                 }
                 fence_proxy_async();
@@ -736,38 +755,8 @@ __global__ void __launch_bounds__(256) mmq_quantize_kernel(const X* __restrict__
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.0f;
     }
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-    // the rounding of llama.cpp's quantize_mmq_q8_1 as the reference's host model states it: d_inv = 127 / amax,
-    // q = round(x * d_inv), d = 1 / d_inv (kept as f16 here)
-    const float d_inv = __fdiv_rn(127.0f, amax);
-    const float dh = amax == 0.0f ? 0.0f : __half2float(__float2half_rn(fminf(__fdiv_rn(1.0f, d_inv), 65504.0f)));
     uint32_t o[4];
-    float bsum = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float q0 = 0.0f, q1 = 0.0f;
-        if (amax != 0.0f) {
-            q0 = fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(v[2 * i], d_inv))));
-            q1 = fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(v[2 * i + 1], d_inv))));
-        }
-        const __half2 r = __floats2half2_rn(dh * q0, dh * q1);
-        o[i] = h2_bits(r);
-        bsum += __low2float(r) + __high2float(r);     // the stored values: multiples of one power of two, 24 bits in all - exact
-    }
-    // The group's sum correction (see xq_tail): S in quantize_mmq_q8_1's order - each 4 consecutive values left to right
-    // (this thread holds partial sums 2j and 2j + 1 of the group's eight), then the tree at distances 4, 2, 1.
-    float s0 = __fadd_rn(__fadd_rn(__fadd_rn(v[0], v[1]), v[2]), v[3]), s1 = __fadd_rn(__fadd_rn(__fadd_rn(v[4], v[5]), v[6]), v[7]);
-    s0 = __fadd_rn(s0, __shfl_xor_sync(0xFFFFFFFFu, s0, 2));
-    s1 = __fadd_rn(s1, __shfl_xor_sync(0xFFFFFFFFu, s1, 2));
-    s0 = __fadd_rn(s0, __shfl_xor_sync(0xFFFFFFFFu, s0, 1));
-    s1 = __fadd_rn(s1, __shfl_xor_sync(0xFFFFFFFFu, s1, 1));
-    bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 1);
-    bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 2);
-    const __half xa = __float2half_rn(__half2float(__float2half_rn(__fadd_rn(s0, s1))) - bsum);
+    const __half xa = q8_1_round8(v, o);
     // a warp's eight groups: their corrections leave as one 16-byte store when a row is a whole number of warps
     const bool packed = (cols & 255) == 0;
     uint4 cw = make_uint4(0u, 0u, 0u, 0u);
