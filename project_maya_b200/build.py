@@ -54,8 +54,16 @@ def generate_grids() -> Path:
     return dst
 
 
-def build(force: bool = False, verbose: bool = False, extra_flags: list[str] | None = None) -> Path:
+def build(force: bool = False, verbose: bool = False, extra_flags: list[str] | None = None, stamps: bool = False) -> Path:
+    """stamps: a second library, libmaya_moe_stamps.so, whose grouped GEMM records clock stamps of its tiles' phases
+    (-DMAYA_MMQ_STAMPS; read by mmq_tile_phases.py).  The product library is built without them."""
     generate_grids()
+    global OBJ, LIB
+    if stamps:
+        OBJ, LIB = PKG / "build_stamps", PKG / "libmaya_moe_stamps.so"
+        extra_flags = (extra_flags or []) + ["-DMAYA_MMQ_STAMPS"]
+    else:
+        OBJ, LIB = PKG / "build", PKG / "libmaya_moe.so"
     OBJ.mkdir(exist_ok=True)
     sources = sorted(CSRC.glob("*.cu"))
     headers = list(CSRC.glob("*.cuh")) + list((CSRC / "generated").glob("*.inc")) + list((ROOT / "include").glob("*.h"))
@@ -95,9 +103,10 @@ def main() -> None:
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--ptxas-v", action="store_true", help="print registers / spills / shared memory per kernel")
+    ap.add_argument("--stamps", action="store_true", help="build libmaya_moe_stamps.so (tile-phase clock stamps in the grouped GEMM)")
     a = ap.parse_args()
     extra = ["-Xptxas", "-v"] if a.ptxas_v else None
-    lib = build(force=a.force or a.ptxas_v, verbose=a.verbose or a.ptxas_v, extra_flags=extra)
+    lib = build(force=a.force or a.ptxas_v, verbose=a.verbose or a.ptxas_v, extra_flags=extra, stamps=a.stamps)
     print(lib)
 
 

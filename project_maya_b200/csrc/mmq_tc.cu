@@ -80,6 +80,14 @@ static_assert(kUnits<MAYA_Q4_K> <= kMaxUnits && kUnits<MAYA_Q8_0> <= kMaxUnits &
 // MMQ keeps that unquantized sum beside the block (the "ds4" q8_1 layout) and a type with a constant term per group
 // (Q4_K: -dmin * m) multiplies the term by it, not by the sum of the rounded values; here the same result comes from
 // extra K steps inside a Q4_K product: A = -dmin * m of a row's groups, B = xa.  Other types do not read the tail.
+// Optional clock stamps of a tile's phases (built only with -DMAYA_MMQ_STAMPS, see build.py --stamps and
+// mmq_tile_phases.py): 16 slots per tile for the first 4096 tiles of each of the four (type class, fused) kernels.
+#ifdef MAYA_MMQ_STAMPS
+__device__ long long g_stamps[4 * 4096 * 16];
+#define MAYA_STAMP(i) do { if (stamp_id >= 0) stamps[(i)] = clock64(); } while (0)
+#else
+#define MAYA_STAMP(i) do { } while (0)
+#endif
 __host__ __device__ constexpr int64_t xq_tail(int64_t cols) { return ((cols / 32) + 63) & ~(int64_t) 63; }
 __host__ __device__ constexpr int64_t xq_ld(int64_t cols) { return cols + xq_tail(cols); }
 
@@ -360,6 +368,12 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
     // groups - A = the groups' constant terms -dmin * m, B = the tail of the activation image (see xq_tail); the last pair
     // of a K that is not a multiple of 2048 is padded with zeros.  ntp = how many such pairs.
     const int ntp = T == MAYA_Q4_K ? (nkb + 7) / 8 : 0;
+#ifdef MAYA_MMQ_STAMPS
+    const int stamp_lin = (int) (blockIdx.y * gridDim.x + blockIdx.x);
+    const int stamp_id = stamp_lin < 4096 ? stamp_lin : -1;
+    long long* const stamps = g_stamps + ((size_t) ((T == MAYA_Q4_K || T == MAYA_IQ3_S ? 2 : 0) + (GLU ? 1 : 0)) * 4096 + max(stamp_id, 0)) * 16;
+    if (tid == 0 && stamp_id >= 0) { stamps[0] = clock64(); stamps[14] = nrows; stamps[15] = nkt / 2 + ntp; }
+#endif
 
     uint8_t* const raw = smem + kBRing<T>;
     if (tid == 0) {
@@ -407,6 +421,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = P.tmem;
+    if (tid == 0) MAYA_STAMP(1);                    // set-up done
 
     if (warp < kDqWarps) {
         // ------------------------------------------------------------ weight expansion
@@ -545,6 +560,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
         tc_fence_after();
         named_bar_sync(3, kDqWarps * 32);            // every expansion warp gets here (all waits are bounded) ...
         ok = !failed(P);                             // ... and they agree: the epilogue's barriers need all of them
+        if (tid == 0) MAYA_STAMP(4);                 // accumulators complete, expanding warps met
         if (ok) {
             // The tile leaves through shared memory (both rings are free now: every load was consumed): the warps drop
             // their lanes' values into [activation row][weight row] order, then one bulk copy per activation row
@@ -573,6 +589,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                     for (int j = 0; j < 8; ++j)
                         if (col0 + j < nrows) b32[(col0 + j) * 128 + mcol] = swiglu(v[j], up[j], A.limit);   // uniform in the warp
                 }
+                if (tid == 0) MAYA_STAMP(5);             // SwiGLU tile in shared memory
                 if (A.xq_out) {
                     named_bar_sync(2, kThreadsEpi);
                     const int ch = tid & 15;                             // the row's 8-value chunk; a warp covers two rows
@@ -590,6 +607,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                         }
                     }
                 }
+                if (tid == 0) MAYA_STAMP(6);             // tile rounded
                 fence_proxy_async();
                 named_bar_sync(1, kThreadsEpi);
                 if (tid < nrows) {                                       // one activation row each
@@ -681,6 +699,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                 if (!rb && !wait_or_fail(P, &P.b_full[(bfull - bfull0) >> 3], ph_b)) { ok = false; break; }   // not there yet: the bounded wait
                 if (!ra && !wait_or_fail(P, &P.a_full[(afull - afull0) >> 3], ph_a)) { ok = false; break; }
                 tc_fence_after();
+                if (my == 0 && kp == 0) MAYA_STAMP(2);       // the first product
                 mma_f16_ts_x4_commit(d0, at, d0b, d1b, d2b, d3b, idesc, first, done_bar);
                 first = 1;
                 at += 64; afull += 8;
@@ -688,6 +707,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                 b_lo += kBStage >> 4; bfull += 8;
                 if (b_lo == b_lo_end) { b_lo = b_lo0; bfull = bfull0; ph_b ^= 1; }
             }
+            if (my == 0) MAYA_STAMP(3);                      // the last product issued
             if (ok) mma_commit(&P.final);
         }
     } else if (warp == kDqWarps + 2) {
@@ -722,6 +742,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUt
                 for (int kb2 = max(0, issued - NB); kb2 < issued; ++kb2) wait_or_fail(P, &P.b_full[kb2 % NB], (kb2 / NB) & 1);
         }
     }
+    if (tid == 0) MAYA_STAMP(7);                    // written back
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 512);
@@ -887,6 +908,12 @@ int run_product(const maya_mmq_product* p, bool glu, float limit, cudaStream_t s
 
 using namespace maya;
 
+#ifdef MAYA_MMQ_STAMPS
+// 4 x 4096 x 16 int64: [Q8_0/IQ2_S down, gate/up, Q4_K/IQ3_S down, gate/up][tile][stamp]; slots 14, 15 = rows, K-step pairs
+extern "C" __attribute__((visibility("default"))) int maya_mmq_stamps_read(long long* host) {
+    return (int) cudaMemcpyFromSymbol(host, g_stamps, sizeof(g_stamps));
+}
+#endif
 extern "C" int maya_mmq_supported(int type) {
     return type == MAYA_Q4_K || type == MAYA_Q8_0 || type == MAYA_IQ2_S || type == MAYA_IQ3_S;
 }
