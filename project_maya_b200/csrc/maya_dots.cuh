@@ -83,6 +83,52 @@ __device__ __forceinline__ XQ xq_load(const XCols& x, int col, int kb) {
     return v;
 }
 
+// ---------------------------------------------------------------- the planar form of the staged columns
+// rows_dot's lanes read consecutive calls, i.e. q8_1 blocks XB apart (XB = the blocks a call of the weight type spans:
+// 2 for Q4_K and Q5_K, 1 otherwise).  In the form above a lane's 16-byte reads then start 32 * XB bytes apart and the
+// eight lanes of a quarter warp fall on 4 / XB bank groups: 2- and 4-way conflicts on every activation load, which made
+// the multi-column kernels wait on the shared-memory pipe.  Here a column is stored as 2 * XB planes of 16-byte pieces -
+// plane 2 * (block % XB) + half, piece block / XB - and its scales and sums as XB planes of words, so that consecutive
+// lanes read consecutive pieces.  Same sizes and the same per-column offsets as the form above.
+template<int XB, bool SUM_F16 = false>
+__device__ __forceinline__ void xcols_stage_p(const uint8_t* xq, size_t col_stride, int nblk, int ncols, int4* q, float* d,
+                                              int* isum) {
+    const int total = nblk * ncols, ni = nblk / XB;
+    for (int i = threadIdx.x; i < total * 8; i += blockDim.x) {
+        const int b = i >> 3, w = i & 7, c = b / nblk, kb = b - c * nblk;
+        const int plane = 2 * (kb % XB) + (w >> 2);
+        ((int*) q)[(((size_t) c * 2 * XB + plane) * ni + kb / XB) * 4 + (w & 3)] =
+            *(const int*) (xq + (size_t) c * col_stride + (size_t) kb * kQ81Bytes + 4 + 4 * w);
+    }
+    for (int b = threadIdx.x; b < total; b += blockDim.x) {
+        const int c = b / nblk, kb = b - c * nblk;
+        const uint8_t* src = xq + (size_t) c * col_stride + (size_t) kb * kQ81Bytes;
+        const int at = c * nblk + (kb % XB) * ni + kb / XB;
+        d[at] = ld_f16(src);
+        if constexpr (SUM_F16) {
+            isum[at] = __float_as_int(ld_f16(src + 2));
+        } else {
+            int s = 0;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) s = __dp4a(*(const int*) (src + 4 + 4 * w), 0x01010101, s);
+            isum[at] = s;
+        }
+    }
+}
+template<int XB>
+__device__ __forceinline__ XQ xq_load_p(const XCols& x, int col, int kb) {
+    XQ v;
+    const int ni = x.nblk / XB, j = kb % XB, i = kb / XB;
+    const int4* p = x.q + ((size_t) col * 2 * XB + 2 * j) * ni + i;
+    const int4 a = p[0], c = p[ni];
+    v.u[0] = a.x; v.u[1] = a.y; v.u[2] = a.z; v.u[3] = a.w;
+    v.u[4] = c.x; v.u[5] = c.y; v.u[6] = c.z; v.u[7] = c.w;
+    const int at = col * x.nblk + j * ni + i;
+    v.d = x.d[at];
+    v.isum = x.isum[at];
+    return v;
+}
+
 // ---------------------------------------------------------------- sign masks
 // Four sign bits (bit i = weight i negative) -> a word whose byte i is 0xFF when bit i is set.  n * 0x10204080 puts
 // bit i at bit 8i+7 (the 16 partial products land on distinct bits, so nothing carries); prmt's sign-replicate mode
@@ -434,7 +480,8 @@ template<int T> __device__ __forceinline__ void load_tab(uint32_t* s_tab) {
 // rows[r]: the row's first block; calls are lane-strided over the row (call c = lane, lane + 32, ...); each lane adds
 // its calls in ascending order (explicitly rounded multiplies and adds, never contracted, so a column's bits do not
 // depend on how many columns the instantiation carries), then the butterfly sum.  out[r][c].
-template<int T, int NR, int NC>
+// x: columns staged by xcols_stage_p<XL> (XL = the call's span in q8_1 blocks unless two types share the columns).
+template<int T, int NR, int NC, int XL = Dec<T>::xblk>
 __device__ __forceinline__ void rows_dot(const uint8_t* const* rows, const XCols& x, int ncols, int n_in, int lane,
                                          const uint32_t* tab, float (&out)[NR][NC]) {
     using D = Dec<T>;
@@ -460,9 +507,9 @@ __device__ __forceinline__ void rows_dot(const uint8_t* const* rows, const XCols
 #pragma unroll
             for (int c = 0; c < NC; ++c)
                 if (c < ncols) {
-                    const XQ a = xq_load(x, c, xb);
+                    const XQ a = xq_load_p<XL>(x, c, xb);
                     XQ b = a;
-                    if constexpr (D::xblk == 2) b = xq_load(x, c, xb + 1);
+                    if constexpr (D::xblk == 2) b = xq_load_p<XL>(x, c, xb + 1);
 #pragma unroll
                     for (int j = 0; j < RP; ++j)
                         if (r0 + j < NR) acc[r0 + j][c] = __fadd_rn(acc[r0 + j][c], dec[j].dot(a, b));

@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(kMvWarps * 32) mmvq_kernel(const uint8_t* __re
     const int nblk = n_in / 32;
     const XCols x = xcols_carve(s_raw + Fmt<T>::tab_words * 4, nblk, ncols, &xq_q, &xq_d, &xq_s);
     load_tab<T>(s_tab);
-    xcols_stage<T == MAYA_IQ1_S>(xq, (size_t) nblk * kQ81Bytes, nblk, ncols, xq_q, xq_d, xq_s);
+    xcols_stage_p<Dec<T>::xblk, T == MAYA_IQ1_S>(xq, (size_t) nblk * kQ81Bytes, nblk, ncols, xq_q, xq_d, xq_s);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t rb = row_bytes(T, n_in);

@@ -65,7 +65,7 @@ __device__ __forceinline__ void shared_down_rows(const uint8_t* sh_down, const u
     const int nblk = n_ff_sh / 32;
     const XCols x = xcols_carve(smem + Fmt<TS>::tab_words * 4, nblk, 1, &q, &d, &is);
     load_tab<TS>(s_tab);
-    xcols_stage(sh_hq, 0, nblk, 1, q, d, is);
+    xcols_stage_p<Dec<TS>::xblk>(sh_hq, 0, nblk, 1, q, d, is);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int per = (n_embd + n_chunks - 1) / n_chunks;
@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(kGuWarps * 32, 2) gate_up_kernel(Groups G, int
         __syncthreads();   // the previous pass is done with the staged columns and s_g / s_u
         for (int c = 0; c < nc; ++c) {
             const int tok = G.tok(eb + c);
-            xcols_stage<T == MAYA_IQ1_S>(xq + (size_t) tok * xq_stride, 0, nblk, 1, q + (size_t) 2 * c * nblk, d + (size_t) c * nblk,
+            xcols_stage_p<Dec<T>::xblk, T == MAYA_IQ1_S>(xq + (size_t) tok * xq_stride, 0, nblk, 1, q + (size_t) 2 * c * nblk, d + (size_t) c * nblk,
                         is + (size_t) c * nblk);
         }
         __syncthreads();
@@ -202,20 +202,22 @@ __global__ void __launch_bounds__(kGuWarps * 32) gate_up_mixed_kernel(Groups G, 
     for (int eb = e0; eb < e1; eb += kNC) {
         const int nc = min(kNC, e1 - eb);
         __syncthreads();
+        // the two types read the same staged columns: the planar form of the wider call span serves both
+        constexpr int XL = Dec<TG>::xblk > Dec<TU>::xblk ? Dec<TG>::xblk : Dec<TU>::xblk;
         for (int c = 0; c < nc; ++c)
-            xcols_stage(xq + (size_t) G.tok(eb + c) * xq_stride, 0, nblk, 1, q + (size_t) 2 * c * nblk, d + (size_t) c * nblk,
-                        is + (size_t) c * nblk);
+            xcols_stage_p<XL>(xq + (size_t) G.tok(eb + c) * xq_stride, 0, nblk, 1, q + (size_t) 2 * c * nblk, d + (size_t) c * nblk,
+                              is + (size_t) c * nblk);
         __syncthreads();
         float og[RPW][kNC], ou[RPW][kNC];
         if (nc == 1) {
             float a[RPW][1], b[RPW][1];
-            rows_dot<TG, RPW, 1>(grow, x, 1, n_embd, lane, s_tab_g, a);
-            rows_dot<TU, RPW, 1>(urow, x, 1, n_embd, lane, s_tab_u, b);
+            rows_dot<TG, RPW, 1, XL>(grow, x, 1, n_embd, lane, s_tab_g, a);
+            rows_dot<TU, RPW, 1, XL>(urow, x, 1, n_embd, lane, s_tab_u, b);
 #pragma unroll
             for (int j = 0; j < RPW; ++j) { og[j][0] = a[j][0]; ou[j][0] = b[j][0]; }
         } else {
-            rows_dot<TG, RPW, kNC>(grow, x, nc, n_embd, lane, s_tab_g, og);
-            rows_dot<TU, RPW, kNC>(urow, x, nc, n_embd, lane, s_tab_u, ou);
+            rows_dot<TG, RPW, kNC, XL>(grow, x, nc, n_embd, lane, s_tab_g, og);
+            rows_dot<TU, RPW, kNC, XL>(urow, x, nc, n_embd, lane, s_tab_u, ou);
         }
         if (lane == 0) {
 #pragma unroll
@@ -248,7 +250,7 @@ __global__ void __launch_bounds__(kDownWarps * 32) down_plan_kernel(maya_moe_pla
     const int nblk = n_ff / 32;
     const XCols x = xcols_carve(s_raw + Fmt<T>::tab_words * 4, nblk, k, &q, &d, &is);
     load_tab<T>(s_tab);
-    xcols_stage<T == MAYA_IQ1_S>(hq, (size_t) nblk * kQ81Bytes, nblk, k, q, d, is);
+    xcols_stage_p<Dec<T>::xblk, T == MAYA_IQ1_S>(hq, (size_t) nblk * kQ81Bytes, nblk, k, q, d, is);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int r0 = (int) blockIdx.x * kDownRows + warp * kDownRowsPerWarp;
@@ -319,7 +321,7 @@ __global__ void __launch_bounds__(kDownWarps * 32, 4) down_groups_kernel(Groups 
         __syncthreads();
         for (int c = 0; c < nc; ++c) {
             const int dst = G.slot(eb + c);
-            xcols_stage<T == MAYA_IQ1_S>(hq + (size_t) dst * nblk * kQ81Bytes, 0, nblk, 1, q + (size_t) 2 * c * nblk, d + (size_t) c * nblk,
+            xcols_stage_p<Dec<T>::xblk, T == MAYA_IQ1_S>(hq + (size_t) dst * nblk * kQ81Bytes, 0, nblk, 1, q + (size_t) 2 * c * nblk, d + (size_t) c * nblk,
                         is + (size_t) c * nblk);
         }
         __syncthreads();
