@@ -25,6 +25,12 @@ __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, 
                  "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+// `bytes` contiguous bytes of this GPU's global memory asked into L2 (nothing to wait for).  Skipped unless the address
+// and the size are multiples of 16, which the instruction needs.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gmem, uint32_t bytes) {
+    if (((((uintptr_t) gmem) | bytes) & 15u) != 0 || bytes == 0) return;
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(

@@ -18,6 +18,7 @@
 #include "maya_dots.cuh"
 #include "maya_internal.cuh"
 #include "maya_peer_ar.cuh"
+#include "maya_stream.cuh"
 
 namespace maya {
 namespace {
@@ -126,6 +127,12 @@ __global__ void __launch_bounds__(kGuWarps * 32, 2) gate_up_kernel(Groups G, int
         const int r = chunk * kGuRows + warp * RPW + j;
         rows[j] = blob + (size_t) r * rb;
         rows[RPW + j] = blob + up_off + (size_t) r * rb;
+    }
+    // The warp's rows are asked into L2 now, while the block stages its columns: the dots' own loads (one dependent
+    // round per 32 calls of a row) then wait for L2 instead of device memory from the second round on.
+    if (lane == 0) {
+        bulk_prefetch_l2(rows[0], (uint32_t) (RPW * rb));
+        bulk_prefetch_l2(rows[RPW], (uint32_t) (RPW * rb));
     }
     for (int eb = e0; eb < e1; eb += kNC) {
         const int nc = min(kNC, e1 - eb);
@@ -316,6 +323,8 @@ __global__ void __launch_bounds__(kDownWarps * 32, 4) down_groups_kernel(Groups 
 #pragma unroll
     for (int j = 0; j < kDownRowsPerWarp; ++j)
         rows[j] = (const uint8_t*) ptr + down_off + (size_t) min(r0 + j, n_embd - 1) * rb;
+    if (lane == 0 && r0 + kDownRowsPerWarp <= n_embd)             // the warp's rows into L2 while the columns are staged
+        bulk_prefetch_l2(rows[0], (uint32_t) (kDownRowsPerWarp * rb));
     for (int eb = e0; eb < e1; eb += kNC) {
         const int nc = min(kNC, e1 - eb);
         __syncthreads();
