@@ -634,6 +634,8 @@ int win_combine_ar(const unsigned long long* plan_ptr, const float* plan_w, int 
 }
 
 // moe_win_experts; with `ar` the cross-rank sum of out[T][n_embd] (contiguous) runs inside the combine launch.
+bool window_down_stream_supported(int d_type, int T, int n_ff);
+int window_down_stream(int d_type, const maya_moe_win* w, cudaStream_t s);
 int win_experts(int gu_type, int d_type, const maya_moe_win* w, const maya_peer_ar* ar, int mi, unsigned seq, cudaStream_t s) {
     if (!w || !w->plan_w || !w->xq || !w->hq || !w->part || !w->out) return refuse(MAYA_ERR_ARG);
     if (w->cpu_flag != nullptr && w->cpu_part == nullptr) return refuse(MAYA_ERR_ARG);
@@ -656,7 +658,9 @@ int win_experts(int gu_type, int d_type, const maya_moe_win* w, const maya_peer_
     st = gate_up_groups(gu_type, A, cap, w->n_embd, w->n_ff, up_off, w->limit, w->xq, w->xq_stride, w->hq, nullptr, 0,
                         nullptr, 0, nullptr, s);
     if (st != MAYA_OK) return st;
-    st = down_groups(d_type, A, cap, w->n_embd, w->n_ff, w->down_off, w->hq, w->part, s);
+    // the down rows streamed through shared memory where the shape allows (moe_window.cu), else read in place
+    st = window_down_stream_supported(d_type, w->T, w->n_ff) ? window_down_stream(d_type, w, s)
+                                                              : down_groups(d_type, A, cap, w->n_embd, w->n_ff, w->down_off, w->hq, w->part, s);
     if (st != MAYA_OK) return st;
     if (ar != nullptr)
         return win_combine_ar(w->plan_ptr, w->plan_w, w->T, w->k, w->n_embd, w->part, w->cpu_part, w->cpu_flag, w->sh_out, w->out,
