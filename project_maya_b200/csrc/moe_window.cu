@@ -11,7 +11,7 @@
 // The arithmetic is rows_dot<T, 4, NC>'s, value for value (the same decode, the same column loop, the same lane order),
 // so every token's result stays bit-identical to the single-token kernels'.
 //
-// Plain (non-multicast) bulk copies of this GPU's own memory; every wait is bounded, and a wait that runs out makes the
+// Plain bulk copies (one destination: this block) of this GPU's own memory; every wait is bounded, and a wait that runs out makes the
 // block stop (its outputs are then missing) after the copies in flight were given the same bounded time to land.  A
 // blob that is not 16-byte aligned (bulk copies need it) is copied with ordinary loads instead.
 #include "maya_dots.cuh"
