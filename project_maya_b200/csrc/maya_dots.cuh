@@ -173,31 +173,35 @@ template<> struct Dec<MAYA_Q8_0> {
     }
 };
 
+// The 16-byte header of a Q4_K / Q5_K block (d, dmin as f16, then 12 bytes of packed 6-bit scales and mins), read with
+// ONE load - a block starts on a 16-byte boundary, as its quants' loads assume too - and the fields of sub-blocks 2j and
+// 2j + 1 taken from registers (j < 2: plain 6-bit fields; j >= 2: 4 low bits + 2 high bits).  Read byte by byte it was
+// five to nine loads a call, each touching as many cache lines as the warp has blocks.
+__device__ __forceinline__ void kquant_header(const uint8_t* blk, int j, float& d, float& dmin, int& sc0, int& sc1, int& m0,
+                                              int& m1) {
+    const int4 h = *(const int4*) blk;
+    const uint32_t dm = (uint32_t) h.x;
+    d = __half2float(__ushort_as_half((uint16_t) (dm & 0xFFFF)));
+    dmin = __half2float(__ushort_as_half((uint16_t) (dm >> 16)));
+    // with s12 = the 12 scale bytes and jj = j % 2: p1 = s12[2 jj], s12[2 jj + 1]; p2 = s12[2 jj + 4 ..]; p3 = s12[2 jj + 8 ..]
+    const int sh = 16 * (j & 1);
+    const uint32_t p1 = ((uint32_t) h.y >> sh) & 0xFFFFu, p2 = ((uint32_t) h.z >> sh) & 0xFFFFu, p3 = ((uint32_t) h.w >> sh) & 0xFFFFu;
+    if (j < 2) {
+        sc0 = (int) (p1 & 63u); m0 = (int) (p2 & 63u);
+        sc1 = (int) ((p1 >> 8) & 63u); m1 = (int) ((p2 >> 8) & 63u);
+    } else {
+        sc0 = (int) ((p3 & 0x0Fu) | (((p1 & 0xFFu) >> 6) << 4)); m0 = (int) (((p3 & 0xFFu) >> 4) | (((p2 & 0xFFu) >> 6) << 4));
+        sc1 = (int) (((p3 >> 8) & 0x0Fu) | ((p1 >> 14) << 4)); m1 = (int) ((p3 >> 12) | ((p2 >> 14) << 4));
+    }
+}
+
 template<> struct Dec<MAYA_Q4_K> {
     static constexpr int cpb = 4, xblk = 2;
     int lo[8], hi[8];
     int sc0, sc1, m0, m1;
     float d, dmin;
     __device__ __forceinline__ void load(const uint8_t* blk, int j, const uint32_t*) {
-        // The block's 16-byte header in ONE load (a block is 144 bytes and starts on a 16-byte boundary, as its quants'
-        // loads below assume too); the fields come out of registers.  Read byte by byte it was five to nine loads a call,
-        // each touching as many cache lines as the warp has blocks.
-        const int4 h = *(const int4*) blk;
-        const uint32_t dm = (uint32_t) h.x;
-        d = __half2float(__ushort_as_half((uint16_t) (dm & 0xFFFF)));
-        dmin = __half2float(__ushort_as_half((uint16_t) (dm >> 16)));
-        // 6-bit scales / mins of sub-blocks 2j and 2j+1 (j < 2: plain 6-bit fields; j >= 2: 4 low bits + 2 high bits).
-        // With s12 = the header's 12 scale bytes: p1 = s12[2 jj], s12[2 jj + 1], p2 = s12[2 jj + 4 ..], p3 = s12[2 jj + 8 ..]
-        // for jj = j % 2.
-        const int sh = 16 * (j & 1);
-        const uint32_t p1 = ((uint32_t) h.y >> sh) & 0xFFFFu, p2 = ((uint32_t) h.z >> sh) & 0xFFFFu, p3 = ((uint32_t) h.w >> sh) & 0xFFFFu;
-        if (j < 2) {
-            sc0 = (int) (p1 & 63u); m0 = (int) (p2 & 63u);
-            sc1 = (int) ((p1 >> 8) & 63u); m1 = (int) ((p2 >> 8) & 63u);
-        } else {
-            sc0 = (int) ((p3 & 0x0Fu) | (((p1 & 0xFFu) >> 6) << 4)); m0 = (int) (((p3 & 0xFFu) >> 4) | (((p2 & 0xFFu) >> 6) << 4));
-            sc1 = (int) (((p3 >> 8) & 0x0Fu) | ((p1 >> 14) << 4)); m1 = (int) ((p3 >> 12) | ((p2 >> 14) << 4));
-        }
+        kquant_header(blk, j, d, dmin, sc0, sc1, m0, m1);
         const int4* q = (const int4*) (blk + 16 + 32 * j);
         const int4 q0 = q[0], q1 = q[1];
         const int qq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
@@ -276,18 +280,7 @@ template<> struct Dec<MAYA_Q5_K> {
     int sc0, sc1, m0, m1;
     float d, dmin;
     __device__ __forceinline__ void load(const uint8_t* blk, int j, const uint32_t*) {
-        const uint32_t dm = ld_u32(blk);
-        d = __half2float(__ushort_as_half((uint16_t) (dm & 0xFFFF)));
-        dmin = __half2float(__ushort_as_half((uint16_t) (dm >> 16)));
-        const uint8_t* s12 = blk + 4;
-        const int a = 2 * j;
-        if (j < 2) {
-            sc0 = s12[a] & 63; m0 = s12[a + 4] & 63;
-            sc1 = s12[a + 1] & 63; m1 = s12[a + 5] & 63;
-        } else {
-            sc0 = (s12[a + 4] & 0x0F) | ((s12[a - 4] >> 6) << 4); m0 = (s12[a + 4] >> 4) | ((s12[a] >> 6) << 4);
-            sc1 = (s12[a + 5] & 0x0F) | ((s12[a - 3] >> 6) << 4); m1 = (s12[a + 5] >> 4) | ((s12[a + 1] >> 6) << 4);
-        }
+        kquant_header(blk, j, d, dmin, sc0, sc1, m0, m1);
         const int4* h = (const int4*) (blk + 16);
         const int4* q = (const int4*) (blk + 48 + 32 * j);
         const int4 h0 = h[0], h1 = h[1], q0 = q[0], q1 = q[1];
