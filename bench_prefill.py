@@ -26,9 +26,15 @@ def tensor_peak(sustained: bool = False) -> tuple[float, str]:
     """The pool's measured cuBLAS bf16 rate: the burst figure (a kernel timed alone for a few ms) or the sustained one
     (seconds at the board's power limit)."""
     p = ROOT / "MEASURED_PEAKS.json"
+    fallback = 1400.0 if sustained else 1590.0
     if p.exists():
-        return float(json.loads(p.read_text())["bf16_tflops_sustained" if sustained else "bf16_tflops"]), "measured"
-    return (1400.0 if sustained else 1590.0), "fallback"
+        try:
+            v = json.loads(p.read_text()).get("bf16_tflops_sustained" if sustained else "bf16_tflops")
+            if v:
+                return float(v), "measured"
+        except (ValueError, OSError):
+            pass
+    return fallback, "fallback"
 
 
 def build_pools(torch, api, seed: int, E: int):
